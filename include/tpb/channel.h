@@ -1,0 +1,147 @@
+// Abstract channel interfaces: a channel moves tensor bytes between two endpoints and may use
+// transport connections (handed over by the pipe) for its control traffic. Counterpart of
+// tensorpipe/channel/{context,channel}.h. The k-th send on one endpoint is matched with the k-th
+// recv on the other; callbacks may complete out of order (the pipe re-orders them).
+//
+// Beyond the reference: sendBatch/recvBatch hand a channel all tensors of one message that it
+// carries, so that a device channel can move them with ONE fused kernel launch and one control
+// frame; the default implementation just loops over send/recv.
+#pragma once
+
+#include <cstddef>
+#include <functional>
+#include <memory>
+#include <optional>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include <tpb/buffer.h>
+#include <tpb/device.h>
+#include <tpb/error.h>
+#include <tpb/message.h>
+#include <tpb/transport.h>
+
+namespace tpb {
+namespace channel {
+
+enum class Endpoint : bool { kConnect, kListen };
+
+using TSendCallback = std::function<void(const Error&)>;
+using TRecvCallback = std::function<void(const Error&)>;
+
+struct SendItem {
+  Buffer buffer;
+  size_t length = 0;                 // packed bytes in the source dtype
+  DType dtype = DType::kBytes;
+  std::optional<StridedView> view;   // non-contiguous source
+  Device targetDevice;               // where the peer will put it (known to the pipe)
+  TSendCallback callback;
+};
+
+struct RecvItem {
+  Buffer buffer;
+  size_t length = 0;                 // packed bytes in the SOURCE dtype (what the descriptor says)
+  std::optional<DType> castTo;       // convert while moving; buffer holds the converted size
+  Device sourceDevice;
+  TRecvCallback callback;
+};
+
+class Channel {
+ public:
+  virtual void send(Buffer buffer, size_t length, TSendCallback callback) = 0;
+  virtual void recv(Buffer buffer, size_t length, TRecvCallback callback) = 0;
+
+  virtual void sendBatch(std::vector<SendItem> items) {
+    for (auto& it : items) {
+      if (it.view.has_value()) {
+        it.callback(TPB_CREATE_ERROR(LogicError, "this channel cannot send strided views"));
+        continue;
+      }
+      send(it.buffer, it.length, std::move(it.callback));
+    }
+  }
+  virtual void recvBatch(std::vector<RecvItem> items) {
+    for (auto& it : items) {
+      if (it.castTo.has_value()) {
+        it.callback(TPB_CREATE_ERROR(LogicError, "this channel cannot cast while receiving"));
+        continue;
+      }
+      recv(it.buffer, it.length, std::move(it.callback));
+    }
+  }
+  // True if sendBatch/recvBatch understand StridedView and castTo.
+  virtual bool supportsLayouts() const { return false; }
+
+  virtual void setId(std::string id) = 0;
+  virtual void close() = 0;
+  virtual ~Channel() = default;
+};
+
+class Context {
+ public:
+  virtual bool isViable() const = 0;
+  virtual size_t numConnectionsNeeded() const { return 1; }
+  // One opaque descriptor per local device this channel can serve.
+  virtual const std::unordered_map<Device, std::string>& deviceDescriptors() const = 0;
+  virtual bool canCommunicateWithRemote(
+      const std::string& localDeviceDescriptor,
+      const std::string& remoteDeviceDescriptor) const {
+    return localDeviceDescriptor == remoteDeviceDescriptor;
+  }
+  virtual std::shared_ptr<Channel> createChannel(
+      std::vector<std::shared_ptr<transport::Connection>> connections, Endpoint endpoint) = 0;
+  virtual void setId(std::string id) = 0;
+  virtual void close() = 0;
+  virtual void join() = 0;
+  virtual ~Context() = default;
+};
+
+// ---- factories ------------------------------------------------------------------------------
+namespace basic {
+std::shared_ptr<Context> create();
+}
+namespace xth {
+std::shared_ptr<Context> create();
+}
+namespace cma {
+std::shared_ptr<Context> create();
+}
+namespace mpt {
+std::shared_ptr<Context> create(
+    std::vector<std::shared_ptr<transport::Context>> contexts,
+    std::vector<std::shared_ptr<transport::Listener>> listeners);
+}
+namespace cuda_basic {
+// Universal fallback for CUDA tensors: stages through pinned host memory with pack/unpack
+// kernels and moves the staged bytes with any CPU channel.
+std::shared_ptr<Context> create(std::shared_ptr<Context> cpuContext);
+}
+namespace cuda_p2p {
+struct Options {
+  size_t eagerThreshold = 64 * 1024;     // batches up to this many bytes go through the inbox
+  size_t inboxBytes = 8u << 20;          // per-peer inbox ring in device memory
+  int maxCtas = 0;                        // 0 = one persistent CTA per SM
+  bool waitWithKernel = false;            // true: bounded wait kernel; false: stream memory op
+  uint64_t waitTimeoutNs = 2'000'000'000ull;  // bound of the wait kernel
+  bool useBulkCopy = true;                // TMA bulk pipeline for aligned contiguous data
+};
+// The device-to-device channel: a persistent sm_100a kernel on the sender pushes straight into
+// the receiver's memory (same process: raw pointers; other process: IPC-mapped) and publishes a
+// release-ordered flag. Replaces both cuda_xth and cuda_ipc of the reference.
+std::shared_ptr<Context> create(Options options = Options());
+}  // namespace cuda_p2p
+namespace cuda_xth {
+inline std::shared_ptr<Context> create() { return cuda_p2p::create(); }
+}
+namespace cuda_ipc {
+inline std::shared_ptr<Context> create() { return cuda_p2p::create(); }
+}
+namespace cuda_gdr {
+// GPUDirect RDMA across hosts needs InfiniBand NICs, which a single NVSwitch box does not have:
+// the factory probes and reports a non-viable context.
+std::shared_ptr<Context> create();
+}
+
+}  // namespace channel
+}  // namespace tpb

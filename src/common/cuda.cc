@@ -1,0 +1,178 @@
+#include "common/cuda.h"
+
+#include <map>
+#include <set>
+
+#include <tpb/buffer.h>
+
+namespace tpb {
+
+namespace {
+template <typename F>
+bool loadSym(void* h, F& fn, std::initializer_list<const char*> names) {
+  for (const char* n : names) {
+    void* p = ::dlsym(h, n);
+    if (p) {
+      fn = reinterpret_cast<F>(p);
+      return true;
+    }
+  }
+  return false;
+}
+}  // namespace
+
+const CudaLib& CudaLib::get() {
+  static CudaLib lib = [] {
+    CudaLib l;
+    l.handle = ::dlopen("libcuda.so.1", RTLD_LOCAL | RTLD_LAZY);
+    if (!l.handle) {
+      const char* e = ::dlerror();
+      l.why = e ? e : "dlopen(libcuda.so.1) failed";
+      TPB_VLOG(9) << "CUDA driver not loaded: " << l.why;
+      return l;
+    }
+    bool all = loadSym(l.handle, l.cuInit, {"cuInit"}) &&
+        loadSym(l.handle, l.cuDeviceGetCount, {"cuDeviceGetCount"}) &&
+        loadSym(l.handle, l.cuPointerGetAttribute, {"cuPointerGetAttribute"}) &&
+        loadSym(l.handle, l.cuMemGetAddressRange, {"cuMemGetAddressRange_v2"}) &&
+        loadSym(l.handle, l.cuGetErrorString, {"cuGetErrorString"}) &&
+        loadSym(l.handle, l.cuCtxGetCurrent, {"cuCtxGetCurrent"});
+    // Stream memory operations are optional (the wait kernel is the fallback).
+    loadSym(l.handle, l.cuStreamWaitValue32, {"cuStreamWaitValue32_v2", "cuStreamWaitValue32"});
+    loadSym(l.handle, l.cuStreamWriteValue32, {"cuStreamWriteValue32_v2", "cuStreamWriteValue32"});
+    if (!all) {
+      l.why = "libcuda.so.1 lacks required symbols";
+      return l;
+    }
+    int rc = l.cuInit(0);
+    if (rc != 0) {
+      l.why = "cuInit: " + l.errorString(rc);
+      return l;
+    }
+    int n = 0;
+    if (l.cuDeviceGetCount(&n) != 0 || n == 0) {
+      l.why = "no CUDA devices";
+      return l;
+    }
+    l.ok = true;
+    return l;
+  }();
+  return lib;
+}
+
+const NvmlLib& NvmlLib::get() {
+  static NvmlLib lib = [] {
+    NvmlLib l;
+    l.handle = ::dlopen("libnvidia-ml.so.1", RTLD_LOCAL | RTLD_LAZY);
+    if (!l.handle) return l;
+    int (*init)() = nullptr;
+    if (!loadSym(l.handle, init, {"nvmlInit_v2"}) ||
+        !loadSym(l.handle, l.deviceGetHandleByUUID, {"nvmlDeviceGetHandleByUUID"}) ||
+        !loadSym(l.handle, l.deviceGetP2PStatus, {"nvmlDeviceGetP2PStatus"}))
+      return l;
+    if (init() != 0) return l;
+    l.ok = true;
+    return l;
+  }();
+  return lib;
+}
+
+bool NvmlLib::p2pOk(const std::string& uuidA, const std::string& uuidB) const {
+  if (!ok) return false;
+  void *a = nullptr, *b = nullptr;
+  if (deviceGetHandleByUUID(uuidA.c_str(), &a) != 0) return false;
+  if (deviceGetHandleByUUID(uuidB.c_str(), &b) != 0) return false;
+  int rd = -1, wr = -1;
+  if (deviceGetP2PStatus(a, b, 0, &rd) != 0 || deviceGetP2PStatus(a, b, 1, &wr) != 0) return false;
+  return rd == 0 && wr == 0;
+}
+
+int cudaDeviceCountNoThrow() {
+  if (!CudaLib::get().ok) return 0;
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+std::string cudaDeviceUuid(int device) {
+  cudaDeviceProp prop;
+  TPB_CUDA_CHECK(cudaGetDeviceProperties(&prop, device));
+  const unsigned char* b = reinterpret_cast<const unsigned char*>(prop.uuid.bytes);
+  char buf[64];
+  std::snprintf(buf, sizeof(buf),
+                "GPU-%02x%02x%02x%02x-%02x%02x-%02x%02x-%02x%02x-%02x%02x%02x%02x%02x%02x", b[0],
+                b[1], b[2], b[3], b[4], b[5], b[6], b[7], b[8], b[9], b[10], b[11], b[12], b[13],
+                b[14], b[15]);
+  return buf;
+}
+
+int cudaDeviceForPointer(const void* ptr) {
+  const CudaLib& lib = CudaLib::get();
+  if (!lib.ok || ptr == nullptr) return -1;
+  int ordinal = -1;
+  int rc = lib.cuPointerGetAttribute(&ordinal, CudaLib::kAttrDeviceOrdinal,
+                                     reinterpret_cast<CUdeviceptr_t>(ptr));
+  if (rc != 0) return -1;
+  return ordinal;
+}
+
+bool cudaAllocationInfo(const void* ptr, void** base, size_t* size, unsigned long long* bufferId) {
+  const CudaLib& lib = CudaLib::get();
+  if (!lib.ok) return false;
+  CUdeviceptr_t b = 0;
+  size_t s = 0;
+  if (lib.cuMemGetAddressRange(&b, &s, reinterpret_cast<CUdeviceptr_t>(ptr)) != 0) return false;
+  unsigned long long id = 0;
+  if (lib.cuPointerGetAttribute(&id, CudaLib::kAttrBufferId, reinterpret_cast<CUdeviceptr_t>(ptr)) != 0)
+    return false;
+  *base = reinterpret_cast<void*>(b);
+  *size = s;
+  *bufferId = id;
+  return true;
+}
+
+bool cudaEnablePeerAccessOnce(int device, int peer) {
+  if (device == peer) return true;
+  static std::mutex m;
+  static std::map<std::pair<int, int>, bool> done;
+  std::unique_lock<std::mutex> lock(m);
+  auto it = done.find({device, peer});
+  if (it != done.end()) return it->second;
+  bool ok = false;
+  int can = 0;
+  if (cudaDeviceCanAccessPeer(&can, device, peer) == cudaSuccess && can) {
+    CudaDeviceGuard g(device);
+    cudaError_t e = cudaDeviceEnablePeerAccess(peer, 0);
+    if (e == cudaSuccess || e == cudaErrorPeerAccessAlreadyEnabled) ok = true;
+    cudaGetLastError();
+  }
+  done[{device, peer}] = ok;
+  return ok;
+}
+
+int cudaSmCount(int device) {
+  static std::mutex m;
+  static std::map<int, int> cache;
+  std::unique_lock<std::mutex> lock(m);
+  auto it = cache.find(device);
+  if (it != cache.end()) return it->second;
+  int n = 0;
+  TPB_CUDA_CHECK(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device));
+  cache[device] = n;
+  return n;
+}
+
+int cudaDeviceForPointerOrHint(const CudaBuffer& b) {
+  if (b.deviceIndex >= 0) return b.deviceIndex;
+  int d = cudaDeviceForPointer(b.ptr);
+  if (d < 0) {
+    // A null pointer (legal for an empty tensor) belongs to the current device.
+    if (cudaGetDevice(&d) != cudaSuccess) d = 0;
+  }
+  return d;
+}
+
+}  // namespace tpb

@@ -3,7 +3,9 @@
 # __graft_entry__.build() runs; nvcc cross-compiles for sm_100a without a GPU present.
 CUDA_HOME ?= /usr/local/cuda
 PYTHON ?= python
-CXX ?= g++
+# The system compiler links libstdc++ dynamically, like PyTorch; a toolchain that links it
+# statically would put a second copy of the C++ runtime into the Python process.
+CXX := $(shell command -v /usr/bin/g++ || echo g++)
 NVCC ?= $(CUDA_HOME)/bin/nvcc
 
 BUILD := build

@@ -1,0 +1,311 @@
+#!/usr/bin/env python
+"""Headline benchmark: pipe GPU->GPU throughput and small-message latency.
+
+One step = every rank sends one bf16 tensor of `--bytes` (default 256 MiB, larger than L2, so no
+L2 flush is needed) through a Pipe to the next rank of a ring and receives one from the previous
+rank; with one GPU the two pipe ends live in one process on the same device. The value is the
+whole-job aggregate GB/s (N x bytes / step time), timed on the device with CUDA events, max over
+ranks. Also reported: a size sweep from 4 KiB to 1 GiB, p50/p99 small-message latency, the
+64-tensor mixed-dtype message, and an end-to-end number through the Python API that includes a
+host->device copy of every step's input from pinned memory and a device->host read of a checksum.
+
+    python bench.py                          # 1 GPU
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
+        --master-port 29511 bench.py --gpus 2
+    python bench.py --impl reference         # the reference's own build, same metric
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, REPO)
+
+METRIC = "pipe_gpu_to_gpu_GBps"
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=50)
+    p.add_argument("--warmup", type=int, default=5)
+    p.add_argument("--impl", default="native", choices=["native", "reference"])
+    p.add_argument("--bytes", type=int, default=256 << 20)
+    p.add_argument("--depth", type=int, default=2, help="writes kept in flight")
+    p.add_argument("--no-sweep", action="store_true")
+    p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--no-bulk", action="store_true", help="plain ld/st path instead of TMA bulk copies")
+    p.add_argument("--max-sweep-bytes", type=int, default=1 << 30)
+    return p.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index):
+        self.device_index = device_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(prefix="tpb_clocks_", suffix=".csv")
+            os.close(fd)
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.device_index), f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=self.out, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.out.close()
+        sm, sm_max, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                parts = [x.strip() for x in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    sm_max.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        os.unlink(self.path)
+        return {
+            "sm_mhz": statistics.median(sm) if sm else None,
+            "sm_max_mhz": max(sm_max) if sm_max else None,
+            "samples": len(sm),
+            "reasons": sorted(reasons),
+        }
+
+
+def percentile(samples, q):
+    if not samples:
+        return None
+    s = sorted(samples)
+    return s[min(len(s) - 1, int(q * len(s)))]
+
+
+def maybe_relaunch_under_torchrun(args):
+    """`python bench.py --gpus N` without a launcher: start the ranks ourselves."""
+    if args.gpus > 1 and "RANK" not in os.environ:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29533"),
+               os.path.abspath(__file__)] + sys.argv[1:]
+        sys.exit(subprocess.call(cmd))
+
+
+def run_reference(args):
+    from baseline import reference_arm
+    reference_arm.main(args, METRIC)
+
+
+def run_native(args):
+    import torch
+    import torch.distributed as dist
+    import tensorpipe_b200 as tpb
+    from tensorpipe_b200 import _C
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def gather(obj):
+        if world == 1:
+            return [obj]
+        out = [None] * world
+        dist.all_gather_object(out, obj)
+        return out
+
+    max_bytes = max(args.bytes, 0 if args.no_sweep else args.max_sweep_bytes)
+    rb = _C.RingBench(device=local_rank, use_bulk_copy=not args.no_bulk, max_bytes=max_bytes)
+    urls = gather(f"{rb.listen_url()}|{local_rank}")
+    rb.connect(urls[(rank + 1) % world])
+
+    # Correctness first: byte-exact on-device verification at a few sizes.
+    for size in (4096, 1 << 20, (8 << 20) + 16):
+        res = rb.run_stream(size, 2, 1, True)
+        if res.mismatches:
+            raise SystemExit(f"verification failed at {size} bytes: {res.mismatches} bytes differ")
+    barrier()
+
+    # Headline: W warm-up steps, then exactly K timed steps.
+    rb.run_stream(args.bytes, max(args.warmup, 3), args.depth, False)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches_before = _C.kernel_launch_count()
+    res = rb.run_stream(args.bytes, args.steps, args.depth, False)
+    launches = _C.kernel_launch_count() - launches_before
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = max_over_ranks(res.device_ms)
+    ms_per_step = ms / args.steps
+    value = world * args.bytes / (ms_per_step * 1e-3) / 1e9
+
+    sweep = []
+    if not args.no_sweep:
+        size = 4096
+        while size <= args.max_sweep_bytes:
+            iters = 100 if size <= (64 << 20) else 20
+            rb.run_stream(size, 10, args.depth, False)
+            barrier()
+            r = rb.run_stream(size, iters, args.depth, False)
+            barrier()
+            t = max_over_ranks(r.device_ms) / iters
+            sweep.append({"bytes": size, "us_per_msg": round(t * 1e3, 2),
+                          "GBps": round(world * size / (t * 1e-3) / 1e9, 2)})
+            size *= 2
+
+    # Small-message latency: one token around the ring, host clock, data visible on the device.
+    barrier()
+    rb.run_latency(4096, 50, rank, world)
+    barrier()
+    lat = rb.run_latency(4096, 1000, rank, world)
+    barrier()
+    latency = None
+    if rank == 0 and lat:
+        latency = {"bytes": 4096, "p50_us": round(percentile(lat, 0.5), 2), "p99_us": round(percentile(lat, 0.99), 2),
+                   "mean_us": round(sum(lat) / len(lat), 2), "hops": world}
+
+    # 64-tensor mixed-dtype message (strided views + receiver-requested casts), one fused launch.
+    barrier()
+    rb.run_mixed(3, 1)
+    barrier()
+    mres, mixed_bytes = rb.run_mixed(10, 1)
+    barrier()
+    mixed_ms = max_over_ranks(mres.device_ms) / 10
+    mixed = {"tensors": 64, "bytes_per_msg": mixed_bytes, "ms_per_msg": round(mixed_ms, 4),
+             "GBps": round(world * mixed_bytes / (mixed_ms * 1e-3) / 1e9, 2),
+             "kernel_launches_per_msg": mres.kernel_launches / 10}
+
+    e2e = None
+    if not args.no_e2e:
+        e2e = run_e2e(args, tpb, torch, dist, rank, world, local_rank, barrier, max_over_ranks, gather)
+
+    del rb
+    if world > 1:
+        dist.barrier()
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": round(value, 3), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 5), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "native",
+            "config": {"model": "pipe ring: 1 bf16 tensor per message", "global_batch": world,
+                       "seq_len": args.bytes // 2, "bytes_per_message": args.bytes,
+                       "parallelism": f"ring{world}" if world > 1 else "loopback (two pipes, one process, one GPU)",
+                       "l2": "inputs larger than L2 (no flush)", "writes_in_flight": args.depth,
+                       "path": "plain ld/st" if args.no_bulk else "TMA bulk"},
+            "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e, "sweep": sweep, "latency": latency,
+            "mixed_64_tensor_message": mixed,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_e2e(args, tpb, torch, dist, rank, world, local_rank, barrier, max_over_ranks, gather):
+    """The same ring through the public Python API. Every step copies its input from pinned host
+    memory to the device, sends it, receives the neighbour's tensor and reads a checksum back."""
+    dev = torch.device("cuda", local_rank)
+    nbytes = args.bytes
+    steps = max(5, min(args.steps, 20))
+    send_ctx = tpb.default_context(f"e2e-send{rank}")
+    recv_ctx = tpb.default_context(f"e2e-recv{rank}")
+    listener = recv_ctx.listen(["uv://127.0.0.1", "shm://"])
+    accepted = listener.accept_future()
+    urls = gather(listener.url("uv"))
+    devices = gather(local_rank)
+    out_pipe = send_ctx.connect(urls[(rank + 1) % world])
+    in_pipe = accepted.result(60)
+    target = f"cuda:{devices[(rank + 1) % world]}"
+
+    host_in = torch.empty(nbytes // 2, dtype=torch.bfloat16).pin_memory()
+    host_in.normal_()
+    x = torch.empty(nbytes // 2, dtype=torch.bfloat16, device=dev)
+    bufs = [torch.empty(nbytes // 2, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    result = torch.empty(1, dtype=torch.float32).pin_memory()
+
+    def step(i):
+        x.copy_(host_in, non_blocking=True)                       # H2D, nbytes
+        sent = out_pipe.send([x], target_devices=[target])
+        msg = in_pipe.recv(out=[bufs[i & 1]]).result(120)
+        sent.result(120)
+        checksum = msg.tensors[0][:4096].float().sum()
+        result.copy_(checksum.reshape(1), non_blocking=True)      # D2H, 4 bytes
+        torch.cuda.current_stream().synchronize()
+        return float(result[0])
+
+    for i in range(3):
+        step(i)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(steps):
+        step(i)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    barrier()
+    dt = max_over_ranks(dt)
+    out_pipe.close()
+    in_pipe.close()
+    send_ctx.join()
+    recv_ctx.join()
+    return {"value": round(world * nbytes * steps / dt / 1e9, 3), "unit": "GB/s", "steps": steps,
+            "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": 4,
+            "api": "tensorpipe_b200.Pipe.send / Pipe.recv (torch tensors)"}
+
+
+def main():
+    args = parse_args()
+    maybe_relaunch_under_torchrun(args)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_native(args)
+
+
+if __name__ == "__main__":
+    main()

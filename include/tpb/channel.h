@@ -43,6 +43,7 @@ struct RecvItem {
   Buffer buffer;
   size_t length = 0;                 // packed bytes in the SOURCE dtype (what the descriptor says)
   std::optional<DType> castTo;       // convert while moving; buffer holds the converted size
+  DType srcDtype = DType::kBytes;    // element type of the incoming data (needed with castTo)
   Device sourceDevice;
   TRecvCallback callback;
 };

@@ -109,7 +109,11 @@ class Allocation final {
 
   struct Tensor {
     Buffer buffer;
-    std::optional<DType> castTo;  // extension: receiver-requested dtype conversion
+    // Extension: receiver-requested dtype conversion. `sourceDtype` is the element type the
+    // sender's data has (the receiver learns it from the tensor's metadata); the buffer holds
+    // length / dtypeSize(sourceDtype) * dtypeSize(castTo) bytes.
+    std::optional<DType> castTo;
+    DType sourceDtype = DType::kBytes;
   };
   std::vector<Tensor> tensors;
 };

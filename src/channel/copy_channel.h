@@ -1,0 +1,257 @@
+// Shared machinery of the two "receiver pulls" CPU channels:
+//   xth — both endpoints are in one process; the receiver memcpy's from the sender's pointer
+//         (tensorpipe/channel/xth/channel_impl.cc:30-33,101-126,260-272, context_impl.cc:84-123);
+//   cma — endpoints are different processes on one host; the receiver reads the sender's memory
+//         with process_vm_readv (tensorpipe/channel/cma/channel_impl.cc:30-34,
+//         context_impl.cc:39-68,109-127).
+// Protocol on the channel's connection (both directions share it): the sender writes
+// Descriptor{pid, ptr}; the receiver, once its matching recv() exists, queues the copy on the
+// context's copy thread, fires its callback and writes Done{}; the sender's callback fires when
+// Done arrives. Sends and receives are matched in order, so no sequence numbers travel.
+#pragma once
+
+#include <condition_variable>
+#include <deque>
+#include <mutex>
+#include <set>
+#include <thread>
+#include <variant>
+
+#include <tpb/channel.h>
+
+#include "common/defs.h"
+#include "common/loop.h"
+#include "common/nop.h"
+#include "transport/nop_io.h"
+
+namespace tpb {
+namespace channel {
+namespace copy {
+
+struct DescriptorMsg {
+  uint64_t pid = 0;
+  uint64_t ptr = 0;
+  TPB_NOP_STRUCTURE(DescriptorMsg, pid, ptr)
+};
+struct DoneMsg {
+  uint8_t ok = 1;
+  TPB_NOP_STRUCTURE(DoneMsg, ok)
+};
+using Packet = std::variant<DescriptorMsg, DoneMsg>;
+
+// Does the copy; returns an error or success. Runs on the copy thread.
+using CopyFn = Error (*)(uint64_t remotePid, const void* remotePtr, void* localPtr, size_t length);
+
+class ContextImpl;
+
+class ChannelImpl final : public Channel, public std::enable_shared_from_this<ChannelImpl> {
+ public:
+  ChannelImpl(std::shared_ptr<ContextImpl> ctx, std::shared_ptr<transport::Connection> conn)
+      : ctx_(std::move(ctx)), conn_(std::move(conn)) {}
+  ~ChannelImpl() override { conn_->close(); }
+  void init();
+  void send(Buffer buffer, size_t length, TSendCallback cb) override;
+  void recv(Buffer buffer, size_t length, TRecvCallback cb) override;
+  void setId(std::string id) override { (void)id; }
+  void close() override;
+  void closeFromLoop(const Error& e);
+
+ private:
+  void armRead();
+  void matchRecvs();
+  struct PendingRecv {
+    void* ptr;
+    size_t length;
+    TRecvCallback cb;
+  };
+  std::shared_ptr<ContextImpl> ctx_;
+  std::shared_ptr<transport::Connection> conn_;
+  Error error_;
+  std::deque<TSendCallback> sendsAwaitingDone_;
+  std::deque<PendingRecv> recvs_;
+  std::deque<DescriptorMsg> descriptors_;
+  size_t copiesInFlight_ = 0;
+};
+
+class ContextImpl final : public Context, public std::enable_shared_from_this<ContextImpl> {
+ public:
+  ContextImpl(std::string descriptor, CopyFn fn, const char* threadName)
+      : copyFn_(fn) {
+    descriptors_[Device(kCpuDeviceType, 0)] = std::move(descriptor);
+    thread_ = std::thread([this, threadName]() {
+      setThreadName(threadName);
+      for (;;) {
+        std::function<void()> job;
+        {
+          std::unique_lock<std::mutex> l(mu_);
+          cv_.wait(l, [&] { return stop_ || !jobs_.empty(); });
+          if (jobs_.empty()) return;
+          job = std::move(jobs_.front());
+          jobs_.pop_front();
+        }
+        job();
+      }
+    });
+  }
+  ~ContextImpl() override { stopThread(); }
+  bool isViable() const override { return true; }
+  const std::unordered_map<Device, std::string>& deviceDescriptors() const override { return descriptors_; }
+  std::shared_ptr<Channel> createChannel(std::vector<std::shared_ptr<transport::Connection>> conns, Endpoint) override {
+    TPB_THROW_ASSERT_IF(conns.size() != 1, "this channel needs exactly one connection");
+    auto ch = std::make_shared<ChannelImpl>(shared_from_this(), std::move(conns[0]));
+    ch->init();
+    return ch;
+  }
+  void setId(std::string id) override { (void)id; }
+  void close() override {
+    loop_.deferToLoop([this, self = shared_from_this()]() {
+      if (closed_) return;
+      closed_ = true;
+      auto chans = channels_;
+      for (auto& w : chans)
+        if (auto c = w.lock()) c->closeFromLoop(TPB_CREATE_ERROR(ContextClosedError));
+      channels_.clear();
+    });
+  }
+  void join() override {
+    if (joined_.exchange(true)) return;
+    close();
+    loop_.runInLoop([]() {});
+    stopThread();
+    loop_.runInLoop([]() {});
+  }
+  void stopThread() {
+    {
+      std::unique_lock<std::mutex> l(mu_);
+      stop_ = true;
+    }
+    cv_.notify_all();
+    if (thread_.joinable()) thread_.join();
+  }
+  // The copy runs on the copy thread; `done` is then deferred to the loop.
+  void requestCopy(uint64_t pid, const void* remote, void* local, size_t len, std::function<void(const Error&)> done) {
+    auto self = shared_from_this();
+    {
+      std::unique_lock<std::mutex> l(mu_);
+      jobs_.push_back([self, pid, remote, local, len, done = std::move(done)]() {
+        Error e = self->copyFn_(pid, remote, local, len);
+        self->loop_.deferToLoop([done, e]() { done(e); });
+      });
+    }
+    cv_.notify_one();
+  }
+  OnDemandLoop loop_;
+  bool closed_ = false;
+  std::set<std::weak_ptr<ChannelImpl>, std::owner_less<std::weak_ptr<ChannelImpl>>> channels_;
+
+ private:
+  CopyFn copyFn_;
+  std::unordered_map<Device, std::string> descriptors_;
+  std::thread thread_;
+  std::mutex mu_;
+  std::condition_variable cv_;
+  std::deque<std::function<void()>> jobs_;
+  bool stop_ = false;
+  std::atomic<bool> joined_{false};
+};
+
+inline void ChannelImpl::init() {
+  auto self = shared_from_this();
+  ctx_->loop_.deferToLoop([self]() {
+    if (self->ctx_->closed_) return self->closeFromLoop(TPB_CREATE_ERROR(ContextClosedError));
+    self->ctx_->channels_.insert(self);
+    self->armRead();
+  });
+}
+
+inline void ChannelImpl::armRead() {
+  auto self = shared_from_this();
+  transport::readNop<Packet>(*conn_, [self](const Error& e, Packet p) {
+    self->ctx_->loop_.deferToLoop([self, e, p]() {
+      if (self->error_) return;
+      if (e) return self->closeFromLoop(e);
+      if (std::holds_alternative<DescriptorMsg>(p)) {
+        self->descriptors_.push_back(std::get<DescriptorMsg>(p));
+        self->matchRecvs();
+      } else {
+        if (self->sendsAwaitingDone_.empty())
+          return self->closeFromLoop(TPB_CREATE_ERROR(LogicError, "unexpected completion from the peer"));
+        auto cb = std::move(self->sendsAwaitingDone_.front());
+        self->sendsAwaitingDone_.pop_front();
+        cb(Error::kSuccess);
+      }
+      if (!self->error_) self->armRead();
+    });
+  });
+}
+
+inline void ChannelImpl::matchRecvs() {
+  auto self = shared_from_this();
+  while (!recvs_.empty() && !descriptors_.empty()) {
+    PendingRecv r = std::move(recvs_.front());
+    recvs_.pop_front();
+    DescriptorMsg d = descriptors_.front();
+    descriptors_.pop_front();
+    ++copiesInFlight_;
+    ctx_->requestCopy(d.pid, reinterpret_cast<const void*>(d.ptr), r.ptr, r.length,
+                      [self, cb = std::move(r.cb)](const Error& e) {
+                        --self->copiesInFlight_;
+                        if (e) {
+                          cb(e);
+                          return self->closeFromLoop(e);
+                        }
+                        if (self->error_) return cb(self->error_);
+                        cb(Error::kSuccess);
+                        Packet done = DoneMsg{};
+                        transport::writeNop(*self->conn_, done, [self](const Error& we) {
+                          if (we) self->ctx_->loop_.deferToLoop([self, we]() { self->closeFromLoop(we); });
+                        });
+                      });
+  }
+}
+
+inline void ChannelImpl::send(Buffer buffer, size_t length, TSendCallback cb) {
+  auto self = shared_from_this();
+  ctx_->loop_.deferToLoop([self, buffer, length, cb = std::move(cb)]() mutable {
+    if (self->error_) return cb(self->error_);
+    if (length == 0) return cb(Error::kSuccess);
+    Packet p = DescriptorMsg{static_cast<uint64_t>(::getpid()),
+                             reinterpret_cast<uint64_t>(buffer.unwrap<CpuBuffer>().ptr)};
+    self->sendsAwaitingDone_.push_back(std::move(cb));
+    transport::writeNop(*self->conn_, p, [self](const Error& we) {
+      if (we) self->ctx_->loop_.deferToLoop([self, we]() { self->closeFromLoop(we); });
+    });
+  });
+}
+
+inline void ChannelImpl::recv(Buffer buffer, size_t length, TRecvCallback cb) {
+  auto self = shared_from_this();
+  ctx_->loop_.deferToLoop([self, buffer, length, cb = std::move(cb)]() mutable {
+    if (self->error_) return cb(self->error_);
+    if (length == 0) return cb(Error::kSuccess);
+    self->recvs_.push_back({buffer.unwrap<CpuBuffer>().ptr, length, std::move(cb)});
+    self->matchRecvs();
+  });
+}
+
+inline void ChannelImpl::close() {
+  auto self = shared_from_this();
+  ctx_->loop_.deferToLoop([self]() { self->closeFromLoop(TPB_CREATE_ERROR(ChannelClosedError)); });
+}
+
+inline void ChannelImpl::closeFromLoop(const Error& e) {
+  if (error_) return;
+  error_ = e;
+  conn_->close();
+  ctx_->channels_.erase(weak_from_this());
+  auto sends = std::move(sendsAwaitingDone_);
+  auto recvs = std::move(recvs_);
+  sendsAwaitingDone_.clear();
+  recvs_.clear();
+  for (auto& cb : sends) cb(error_);
+  for (auto& r : recvs) r.cb(error_);
+}
+
+}  // namespace copy
+}  // namespace channel
+}  // namespace tpb

@@ -1,0 +1,955 @@
+// The CUDA device-to-device channel.
+//
+// One channel covers what the reference needs two for: cuda_xth (same process,
+// tensorpipe/channel/cuda_xth/channel_impl.cc:40-77,147-168) and cuda_ipc (other process on the
+// same host, tensorpipe/channel/cuda_ipc/channel_impl.cc:107-317,319-492). Instead of copy-engine
+// memcpys through staging slots with a control round trip per 8 MiB chunk, the SENDER runs one
+// persistent kernel (kernels/push.cu) that reads its own tensors and stores straight into the
+// receiver's memory, for all tensors of the message at once, then publishes a flag in the
+// receiver's memory.
+//
+// Control protocol on the channel's single connection (one nop-encoded Packet per frame); both
+// endpoints number their non-empty batches independently per direction, and the k-th batch sent
+// matches the k-th batch received:
+//
+//   rendezvous   R -> S  RecvReady{seq, where each tensor goes (raw pointer if same process, else
+//                        IPC handle of the allocation + offset), requested dtypes}
+//                S       launches the push on the sender's stream, fires send callbacks
+//                S -> R  Launched{seq}
+//                R       makes its stream wait for the flag (stream memory op, or the bounded
+//                        wait kernel), fires recv callbacks
+//   eager        S       (small batch, peer inbox already mapped, credits left) pushes into the
+//                        peer's inbox ring at send time without waiting for the receiver
+//                S -> R  Launched{seq, eager, inbox offset}
+//                R       waits for the flag, unpacks inbox -> tensors (applying casts), later
+//                        returns the ring space with Credit{}
+//
+// Why the receiver only enqueues a wait after Launched arrived: a wait placed on a stream before
+// the matching push exists could end up ahead of a push that the peer is itself waiting for (both
+// sides using one stream for sends and receives) and dead-lock the two GPUs. With this rule every
+// wait refers to a push that is already enqueued, so stream dependencies cannot form a cycle.
+//
+// Same process: completion is a CUDA event instead of a flag; nothing is mapped.
+#include <unistd.h>
+
+#include <array>
+#include <deque>
+#include <map>
+#include <set>
+
+#include <tpb/channel.h>
+
+#include "common/cuda.h"
+#include "common/defs.h"
+#include "common/loop.h"
+#include "common/nop.h"
+#include "common/system.h"
+#include "kernels/push.h"
+#include "transport/nop_io.h"
+
+namespace tpb {
+namespace channel {
+namespace cuda_p2p {
+
+namespace {
+
+using Handle = std::array<uint8_t, 64>;
+static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+
+constexpr uint32_t kFlagSlots = 256;
+constexpr size_t kFlagsBytes = 4096;      // flags, then counter/status words, then the inbox
+constexpr size_t kCounterOffset = 2048;   // within the first 4 KiB
+constexpr size_t kStatusOffset = 2304;
+constexpr size_t kInboxAlign = 256;
+
+struct DeviceDescriptor {
+  std::string bootId;
+  int64_t pid = 0;
+  std::string uuid;
+  TPB_NOP_STRUCTURE(DeviceDescriptor, bootId, pid, uuid)
+};
+
+struct TargetWire {
+  uint64_t ptr = 0;       // same process: the address; else: offset inside the allocation
+  uint64_t bytes = 0;     // bytes the destination holds
+  uint8_t dtype = 0;      // requested destination dtype (DType), 0 = as sent
+  uint8_t srcDtype = 0;   // what the receiver believes the source dtype is (with a cast)
+  uint8_t hasHandle = 0;
+  Handle handle{};
+  uint64_t bufferId = 0;
+  TPB_NOP_STRUCTURE(TargetWire, ptr, bytes, dtype, srcDtype, hasHandle, handle, bufferId)
+};
+
+struct ArenaWire {
+  Handle handle{};
+  uint64_t inboxBytes = 0;
+  TPB_NOP_STRUCTURE(ArenaWire, handle, inboxBytes)
+};
+
+struct RecvReady {
+  uint64_t seq = 0;
+  int32_t deviceIdx = 0;  // receiver-side device of this batch
+  std::optional<ArenaWire> arena;
+  std::vector<TargetWire> targets;
+  TPB_NOP_STRUCTURE(RecvReady, seq, deviceIdx, arena, targets)
+};
+
+struct Launched {
+  uint64_t seq = 0;
+  uint8_t eager = 0;
+  uint64_t inboxOffset = 0;
+  uint64_t creditValue = 0;
+  uint64_t event = 0;  // same process: cudaEvent_t recorded after the push
+  std::string error;
+  TPB_NOP_STRUCTURE(Launched, seq, eager, inboxOffset, creditValue, event, error)
+};
+
+struct Credit {
+  int32_t deviceIdx = 0;
+  uint64_t value = 0;
+  TPB_NOP_STRUCTURE(Credit, deviceIdx, value)
+};
+
+using Packet = std::variant<RecvReady, Launched, Credit>;
+
+std::string processIdentity() {
+  auto boot = getBootID();
+  return (boot ? *boot : std::string("?")) + "_" + std::to_string(::getpid());
+}
+
+// ---- process-wide cache of opened IPC mappings ----------------------------------------------
+class MappingCache {
+ public:
+  static MappingCache& get() {
+    static MappingCache c;
+    return c;
+  }
+  // Returns the local address of the peer allocation's base, opening it on first use. The
+  // current device must be the one that will access it.
+  void* open(const Handle& h, std::string* err) {
+    std::unique_lock<std::mutex> lock(m_);
+    auto it = map_.find(h);
+    if (it != map_.end()) return it->second;
+    cudaIpcMemHandle_t ch;
+    std::memcpy(&ch, h.data(), sizeof(ch));
+    void* p = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&p, ch, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      if (err) *err = std::string("cudaIpcOpenMemHandle: ") + cudaGetErrorString(e);
+      return nullptr;
+    }
+    map_.emplace(h, p);
+    return p;
+  }
+
+ private:
+  std::mutex m_;
+  std::map<Handle, void*> map_;
+};
+
+class ContextImpl;
+
+struct Arena {
+  int device = -1;
+  uint8_t* base = nullptr;  // cudaMalloc'ed: [4 KiB flags/counter/status][inbox]
+  size_t inboxBytes = 0;
+  Handle handle{};
+  bool announced = false;  // told the peer about it
+  uint32_t* flag(uint64_t seq) const { return reinterpret_cast<uint32_t*>(base) + (seq % kFlagSlots); }
+  // One arrive counter per launching stream: launches on different streams may overlap.
+  uint32_t* counter(cudaStream_t s) {
+    auto it = counterOf.find(s);
+    if (it == counterOf.end()) {
+      if (counterOf.size() >= (kStatusOffset - kCounterOffset) / 4)
+        throw std::runtime_error("cuda_p2p: too many distinct streams used with one channel");
+      it = counterOf.emplace(s, static_cast<uint32_t>(counterOf.size())).first;
+    }
+    return reinterpret_cast<uint32_t*>(base + kCounterOffset) + it->second;
+  }
+  std::map<cudaStream_t, uint32_t> counterOf;
+  uint32_t* status() const { return reinterpret_cast<uint32_t*>(base + kStatusOffset); }
+  uint8_t* inbox() const { return base + kFlagsBytes; }
+};
+
+struct PeerArena {  // the peer's arena for one of ITS devices, mapped here
+  uint8_t* base = nullptr;
+  size_t inboxBytes = 0;
+  uint64_t head = 0, tail = 0;  // inbox ring cursors (bytes, free-running)
+  uint32_t* flag(uint64_t seq) const { return reinterpret_cast<uint32_t*>(base) + (seq % kFlagSlots); }
+  uint8_t* inbox() const { return base + kFlagsBytes; }
+};
+
+inline uint32_t flagValueFor(uint64_t seq) { return static_cast<uint32_t>(seq / kFlagSlots + 1); }
+
+struct SendOp {
+  uint64_t seq = 0;
+  int srcDevice = -1;
+  Device targetDevice;
+  std::vector<SendItem> items;
+  bool launched = false;
+  std::optional<RecvReady> ready;
+};
+
+struct RecvOp {
+  uint64_t seq = 0;
+  int device = -1;
+  std::vector<RecvItem> items;
+  bool readySent = false;
+  std::optional<Launched> notice;
+};
+
+class ChannelImpl final : public Channel, public std::enable_shared_from_this<ChannelImpl> {
+ public:
+  ChannelImpl(std::shared_ptr<ContextImpl> ctx, std::shared_ptr<transport::Connection> conn, Options opts)
+      : ctx_(std::move(ctx)), conn_(std::move(conn)), opts_(opts) {}
+  ~ChannelImpl() override;
+
+  void init();
+  void send(Buffer buffer, size_t length, TSendCallback cb) override {
+    SendItem it;
+    it.buffer = buffer;
+    it.length = length;
+    it.targetDevice = Device(kCudaDeviceType, -1);
+    it.callback = std::move(cb);
+    std::vector<SendItem> v;
+    v.push_back(std::move(it));
+    sendBatch(std::move(v));
+  }
+  void recv(Buffer buffer, size_t length, TRecvCallback cb) override {
+    RecvItem it;
+    it.buffer = buffer;
+    it.length = length;
+    it.sourceDevice = Device(kCudaDeviceType, -1);
+    it.callback = std::move(cb);
+    std::vector<RecvItem> v;
+    v.push_back(std::move(it));
+    recvBatch(std::move(v));
+  }
+  void sendBatch(std::vector<SendItem> items) override;
+  void recvBatch(std::vector<RecvItem> items) override;
+  bool supportsLayouts() const override { return true; }
+  void setId(std::string id) override { id_ = std::move(id); }
+  void close() override;
+  void closeFromLoop(const Error& e);
+
+ private:
+  void initFromLoop();
+  void armRead();
+  void onPacket(Packet p);
+  void onHello(const std::string& peerIdentity);
+  void sendBatchFromLoop(std::vector<SendItem> items);
+  void recvBatchFromLoop(std::vector<RecvItem> items);
+  void tryLaunch(SendOp& op);
+  bool tryEager(SendOp& op);
+  void launchRendezvous(SendOp& op);
+  void finishSend(SendOp& op, const Error& e);
+  void sendReady(RecvOp& op);
+  void completeRecv(RecvOp& op);
+  void finishRecv(RecvOp& op, const Error& e);
+  void returnCredits();
+  void writePacket(const Packet& p);
+  Arena* arenaFor(int device, Error& err);
+  template <typename It>
+  static std::vector<std::vector<It>> splitByDevicePair(std::vector<It>& items, bool send);
+
+  std::shared_ptr<ContextImpl> ctx_;
+  std::shared_ptr<transport::Connection> conn_;
+  Options opts_;
+  std::string id_ = "N/A";
+  Error error_;
+  bool helloDone_ = false;
+  bool sameProcess_ = false;
+  std::string peerIdentity_;
+  uint64_t nextSendSeq_ = 0, nextRecvSeq_ = 0;
+  std::deque<SendOp> sendOps_;
+  std::deque<RecvOp> recvOps_;
+  std::map<uint64_t, RecvReady> earlyReady_;     // RecvReady that arrived before its sendBatch
+  std::map<uint64_t, Launched> earlyLaunched_;   // Launched that arrived before its recvBatch
+  std::map<int, Arena> arenas_;                  // my devices
+  std::map<int, PeerArena> peerArenas_;          // peer's devices
+  struct PendingCredit {
+    std::unique_ptr<CudaEvent> done;
+    int device;
+    uint64_t value;
+  };
+  std::deque<PendingCredit> pendingCredits_;
+  // Events handed to the peer (same process) must outlive their use.
+  std::deque<std::unique_ptr<CudaEvent>> eventPool_;
+  std::vector<std::pair<uint32_t*, uint32_t>> enqueuedWaits_;  // for cancellation on error
+};
+
+class ContextImpl final : public Context, public std::enable_shared_from_this<ContextImpl> {
+ public:
+  explicit ContextImpl(Options opts) : opts_(opts) {
+    const int n = cudaDeviceCountNoThrow();
+    if (n == 0) return;
+    auto boot = getBootID();
+    if (!boot) return;
+    for (int i = 0; i < n; ++i) {
+      cudaDeviceProp prop;
+      if (cudaGetDeviceProperties(&prop, i) != cudaSuccess) {
+        cudaGetLastError();
+        return;
+      }
+      if (!prop.unifiedAddressing) return;
+      DeviceDescriptor d;
+      d.bootId = *boot;
+      d.pid = ::getpid();
+      d.uuid = cudaDeviceUuid(i);
+      uuids_.push_back(d.uuid);
+      auto bytes = nop::encode(d);
+      descriptors_[Device(kCudaDeviceType, i)] = std::string(bytes.begin(), bytes.end());
+    }
+    viable_ = true;
+  }
+  bool isViable() const override { return viable_; }
+  const std::unordered_map<Device, std::string>& deviceDescriptors() const override { return descriptors_; }
+  bool canCommunicateWithRemote(const std::string& local, const std::string& remote) const override {
+    DeviceDescriptor l, r;
+    if (!nop::decode(local.data(), local.size(), l) || !nop::decode(remote.data(), remote.size(), r)) return false;
+    if (l.bootId != r.bootId) return false;
+    int li = indexOf(l.uuid), ri = indexOf(r.uuid);
+    if (li < 0) return false;
+    if (l.uuid == r.uuid) return true;  // same GPU (two pipes, or two processes sharing it)
+    if (ri >= 0) {
+      int ab = 0, ba = 0;
+      if (cudaDeviceCanAccessPeer(&ab, li, ri) != cudaSuccess || cudaDeviceCanAccessPeer(&ba, ri, li) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+      }
+      return ab && ba;
+    }
+    // The peer's GPU is hidden from this process (CUDA_VISIBLE_DEVICES): ask NVML.
+    const NvmlLib& nvml = NvmlLib::get();
+    return nvml.p2pOk(l.uuid, r.uuid) && nvml.p2pOk(r.uuid, l.uuid);
+  }
+  std::shared_ptr<Channel> createChannel(std::vector<std::shared_ptr<transport::Connection>> conns,
+                                         Endpoint) override {
+    TPB_THROW_ASSERT_IF(conns.size() != 1, "cuda_p2p needs exactly one connection");
+    auto ch = std::make_shared<ChannelImpl>(shared_from_this(), std::move(conns[0]), opts_);
+    ch->init();
+    return ch;
+  }
+  void setId(std::string id) override { (void)id; }
+  void close() override {
+    loop_.deferToLoop([this, self = shared_from_this()]() {
+      if (closed_) return;
+      closed_ = true;
+      auto chans = channels_;
+      for (auto& w : chans)
+        if (auto c = w.lock()) c->closeFromLoop(TPB_CREATE_ERROR(ContextClosedError));
+      channels_.clear();
+    });
+  }
+  void join() override {
+    close();
+    loop_.runInLoop([]() {});
+  }
+  void enroll(std::weak_ptr<ChannelImpl> c) { channels_.insert(std::move(c)); }
+  void unenroll(const std::weak_ptr<ChannelImpl>& c) { channels_.erase(c); }
+  bool closed() const { return closed_; }
+  OnDemandLoop loop_;
+
+ private:
+  int indexOf(const std::string& uuid) const {
+    for (size_t i = 0; i < uuids_.size(); ++i)
+      if (uuids_[i] == uuid) return static_cast<int>(i);
+    return -1;
+  }
+  Options opts_;
+  bool viable_ = false;
+  bool closed_ = false;
+  std::vector<std::string> uuids_;
+  std::unordered_map<Device, std::string> descriptors_;
+  std::set<std::weak_ptr<ChannelImpl>, std::owner_less<std::weak_ptr<ChannelImpl>>> channels_;
+};
+
+// ---- channel --------------------------------------------------------------------------------
+ChannelImpl::~ChannelImpl() {
+  conn_->close();
+  for (auto& a : arenas_) {
+    if (a.second.base) {
+      // Freeing synchronises the device; this only happens when a pipe goes away.
+      int prev = -1;
+      cudaGetDevice(&prev);
+      cudaSetDevice(a.second.device);
+      cudaFree(a.second.base);
+      if (prev >= 0) cudaSetDevice(prev);
+    }
+  }
+}
+
+void ChannelImpl::init() {
+  auto self = shared_from_this();
+  ctx_->loop_.deferToLoop([self]() { self->initFromLoop(); });
+}
+
+void ChannelImpl::initFromLoop() {
+  if (ctx_->closed()) return closeFromLoop(TPB_CREATE_ERROR(ContextClosedError));
+  ctx_->enroll(weak_from_this());
+  // Hello: who am I (decides between raw pointers and IPC mappings).
+  auto self = shared_from_this();
+  transport::writeNop(*conn_, processIdentity(), [self](const Error& e) {
+    if (e) self->ctx_->loop_.deferToLoop([self, e]() { self->closeFromLoop(e); });
+  });
+  transport::readNop<std::string>(*conn_, [self](const Error& e, std::string peer) {
+    self->ctx_->loop_.deferToLoop([self, e, peer]() {
+      if (e) return self->closeFromLoop(e);
+      self->onHello(peer);
+    });
+  });
+}
+
+void ChannelImpl::onHello(const std::string& peer) {
+  if (error_) return;
+  peerIdentity_ = peer;
+  sameProcess_ = peer == processIdentity();
+  helloDone_ = true;
+  TPB_VLOG(4) << "Channel " << id_ << " peer " << peer << (sameProcess_ ? " (same process)" : " (other process)");
+  armRead();
+  for (size_t i = 0; i < recvOps_.size() && !error_; ++i)
+    if (!recvOps_[i].readySent && !recvOps_[i].notice) sendReady(recvOps_[i]);
+  for (size_t i = 0; i < sendOps_.size() && !error_; ++i) tryLaunch(sendOps_[i]);
+  while (!sendOps_.empty() && sendOps_.front().launched) sendOps_.pop_front();
+}
+
+void ChannelImpl::armRead() {
+  auto self = shared_from_this();
+  transport::readNop<Packet>(*conn_, [self](const Error& e, Packet p) {
+    self->ctx_->loop_.deferToLoop([self, e, p = std::move(p)]() mutable {
+      if (self->error_) return;
+      if (e) return self->closeFromLoop(e);
+      self->onPacket(std::move(p));
+      if (!self->error_) self->armRead();
+    });
+  });
+}
+
+void ChannelImpl::writePacket(const Packet& p) {
+  auto self = shared_from_this();
+  transport::writeNop(*conn_, p, [self](const Error& e) {
+    if (e) self->ctx_->loop_.deferToLoop([self, e]() { self->closeFromLoop(e); });
+  });
+}
+
+Arena* ChannelImpl::arenaFor(int device, Error& err) {
+  auto it = arenas_.find(device);
+  if (it != arenas_.end()) return &it->second;
+  Arena a;
+  a.device = device;
+  a.inboxBytes = opts_.inboxBytes;
+  CudaDeviceGuard g(device);
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, kFlagsBytes + a.inboxBytes);
+  if (e == cudaSuccess) e = cudaMemset(p, 0, kFlagsBytes);
+  if (e == cudaSuccess && !sameProcess_) {
+    cudaIpcMemHandle_t h;
+    e = cudaIpcGetMemHandle(&h, p);
+    if (e == cudaSuccess) std::memcpy(a.handle.data(), &h, sizeof(h));
+  }
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    if (p) cudaFree(p);
+    err = cudaErrorToError(e, "allocating the channel arena");
+    return nullptr;
+  }
+  a.base = static_cast<uint8_t*>(p);
+  return &arenas_.emplace(device, a).first->second;
+}
+
+template <typename It>
+std::vector<std::vector<It>> ChannelImpl::splitByDevicePair(std::vector<It>& items, bool send) {
+  // Both ends split a batch by (source device, target device) in order of first appearance, so
+  // that every sub-batch has one launching GPU and one flag.
+  std::vector<std::pair<std::pair<int, int>, std::vector<It>>> groups;
+  for (auto& it : items) {
+    int mine = it.buffer.device().index;
+    int theirs;
+    if constexpr (std::is_same_v<It, SendItem>) theirs = it.targetDevice.index;
+    else theirs = it.sourceDevice.index;
+    std::pair<int, int> key = send ? std::make_pair(mine, theirs) : std::make_pair(theirs, mine);
+    auto g = std::find_if(groups.begin(), groups.end(), [&](const auto& p) { return p.first == key; });
+    if (g == groups.end()) {
+      groups.emplace_back(key, std::vector<It>());
+      g = groups.end() - 1;
+    }
+    g->second.push_back(std::move(it));
+  }
+  std::vector<std::vector<It>> out;
+  for (auto& g : groups) out.push_back(std::move(g.second));
+  return out;
+}
+
+void ChannelImpl::sendBatch(std::vector<SendItem> items) {
+  auto self = shared_from_this();
+  auto shared = std::make_shared<std::vector<SendItem>>(std::move(items));
+  ctx_->loop_.deferToLoop([self, shared]() { self->sendBatchFromLoop(std::move(*shared)); });
+}
+
+void ChannelImpl::recvBatch(std::vector<RecvItem> items) {
+  auto self = shared_from_this();
+  auto shared = std::make_shared<std::vector<RecvItem>>(std::move(items));
+  ctx_->loop_.deferToLoop([self, shared]() { self->recvBatchFromLoop(std::move(*shared)); });
+}
+
+void ChannelImpl::sendBatchFromLoop(std::vector<SendItem> items) {
+  std::vector<SendItem> live;
+  for (auto& it : items) {
+    if (error_) it.callback(error_);
+    else if (it.length == 0) it.callback(Error::kSuccess);  // nothing travels for an empty tensor
+    else live.push_back(std::move(it));
+  }
+  if (live.empty()) return;
+  returnCredits();
+  for (auto& group : splitByDevicePair(live, true)) {
+    if (error_) {
+      for (auto& it : group) it.callback(error_);
+      continue;
+    }
+    SendOp op;
+    op.seq = nextSendSeq_++;
+    op.srcDevice = group[0].buffer.device().index;
+    op.targetDevice = group[0].targetDevice;
+    op.items = std::move(group);
+    auto early = earlyReady_.find(op.seq);
+    if (early != earlyReady_.end()) {
+      op.ready = std::move(early->second);
+      earlyReady_.erase(early);
+    }
+    sendOps_.push_back(std::move(op));
+    tryLaunch(sendOps_.back());
+  }
+  while (!sendOps_.empty() && sendOps_.front().launched) sendOps_.pop_front();
+}
+
+void ChannelImpl::tryLaunch(SendOp& op) {
+  if (op.launched || error_ || !helloDone_) return;
+  try {
+    if (op.ready) return launchRendezvous(op);
+    if (!sameProcess_ && tryEager(op)) return;
+  } catch (const std::exception& ex) {
+    closeFromLoop(TPB_CREATE_ERROR(CudaError, ex.what()));
+  }
+}
+
+bool ChannelImpl::tryEager(SendOp& op) {
+  if (opts_.eagerThreshold == 0) return false;
+  auto pa = peerArenas_.find(op.targetDevice.index);
+  if (pa == peerArenas_.end()) return false;
+  PeerArena& peer = pa->second;
+  uint64_t total = 0;
+  for (auto& it : op.items) total += (it.length + kInboxAlign - 1) / kInboxAlign * kInboxAlign;
+  if (total > opts_.eagerThreshold || total > peer.inboxBytes / 2) return false;
+  const uint64_t cap = peer.inboxBytes;
+  const uint64_t pos = peer.head % cap;
+  const uint64_t skip = pos + total > cap ? cap - pos : 0;
+  if (peer.head + skip + total - peer.tail > cap) return false;  // no credits: use rendezvous
+  const uint64_t offset = (peer.head + skip) % cap;
+  peer.head += skip + total;
+
+  Error err;
+  Arena* mine = arenaFor(op.srcDevice, err);
+  if (!mine) {
+    closeFromLoop(err);
+    return true;
+  }
+  CudaDeviceGuard g(op.srcDevice);
+  kernels::PushPlan plan;
+  uint64_t cursor = offset;
+  for (auto& it : op.items) {
+    kernels::CopyItem c;
+    c.src = it.buffer.unwrap<CudaBuffer>().ptr;
+    c.dst = peer.inbox() + cursor;
+    c.srcBytes = it.length;
+    c.srcDtype = it.dtype;
+    c.dstDtype = it.dtype;  // a requested cast is applied by the receiver's unpack
+    if (it.view) {
+      c.strided = true;
+      c.view = *it.view;
+      c.srcDtype = c.dstDtype = it.view->dtype;
+    }
+    kernels::appendToPlan(plan, c, opts_.useBulkCopy);
+    cursor += (it.length + kInboxAlign - 1) / kInboxAlign * kInboxAlign;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(op.items[0].buffer.unwrap<CudaBuffer>().stream);
+  const int ctas = opts_.maxCtas > 0 ? opts_.maxCtas : cudaSmCount(op.srcDevice);
+  kernels::launchPush(plan, stream, ctas, peer.flag(op.seq), flagValueFor(op.seq), mine->counter(stream), mine->status());
+  Launched l;
+  l.seq = op.seq;
+  l.eager = 1;
+  l.inboxOffset = offset;
+  l.creditValue = peer.head;
+  writePacket(l);
+  finishSend(op, Error::kSuccess);
+  return true;
+}
+
+void ChannelImpl::launchRendezvous(SendOp& op) {
+  const RecvReady& ready = *op.ready;
+  if (ready.targets.size() != op.items.size()) {
+    return closeFromLoop(TPB_CREATE_ERROR(LogicError, "peer announced a different number of tensors"));
+  }
+  CudaDeviceGuard g(op.srcDevice);
+  uint8_t* peerArenaBase = nullptr;
+  if (!sameProcess_) {
+    if (ready.arena) {
+      std::string why;
+      void* base = MappingCache::get().open(ready.arena->handle, &why);
+      if (!base) return closeFromLoop(TPB_CREATE_ERROR(CudaError, why));
+      PeerArena pa;
+      pa.base = static_cast<uint8_t*>(base);
+      pa.inboxBytes = ready.arena->inboxBytes;
+      peerArenas_[ready.deviceIdx] = pa;
+    }
+    auto it = peerArenas_.find(ready.deviceIdx);
+    if (it == peerArenas_.end())
+      return closeFromLoop(TPB_CREATE_ERROR(LogicError, "peer never announced its arena for that device"));
+    peerArenaBase = it->second.base;
+  } else if (ready.deviceIdx != op.srcDevice) {
+    if (!cudaEnablePeerAccessOnce(op.srcDevice, ready.deviceIdx))
+      return closeFromLoop(TPB_CREATE_ERROR(CudaError, "peer access between the two GPUs cannot be enabled"));
+  }
+
+  kernels::PushPlan plan;
+  for (size_t i = 0; i < op.items.size(); ++i) {
+    SendItem& it = op.items[i];
+    const TargetWire& t = ready.targets[i];
+    kernels::CopyItem c;
+    c.src = it.buffer.unwrap<CudaBuffer>().ptr;
+    if (sameProcess_) {
+      c.dst = reinterpret_cast<void*>(t.ptr);
+    } else {
+      if (!t.hasHandle)
+        return closeFromLoop(TPB_CREATE_ERROR(CudaError, "the receiver could not export its buffer over CUDA IPC"));
+      std::string why;
+      void* base = MappingCache::get().open(t.handle, &why);
+      if (!base) return closeFromLoop(TPB_CREATE_ERROR(CudaError, why));
+      c.dst = static_cast<uint8_t*>(base) + t.ptr;
+    }
+    c.srcBytes = it.length;
+    c.srcDtype = it.view ? it.view->dtype : it.dtype;
+    if (c.srcDtype == DType::kBytes && t.dtype) c.srcDtype = static_cast<DType>(t.srcDtype);
+    c.dstDtype = t.dtype ? static_cast<DType>(t.dtype) : c.srcDtype;
+    if (it.view) {
+      c.strided = true;
+      c.view = *it.view;
+    }
+    if (c.dstDtype != c.srcDtype && !kernels::castSupported(c.srcDtype, c.dstDtype))
+      return closeFromLoop(TPB_CREATE_ERROR(LogicError, "unsupported dtype conversion requested by the receiver"));
+    if (kernels::convertedBytes(it.length, c.srcDtype, c.dstDtype) != t.bytes)
+      return closeFromLoop(TPB_CREATE_ERROR(LogicError, "receiver's buffer size does not match the tensor"));
+    kernels::appendToPlan(plan, c, opts_.useBulkCopy);
+  }
+
+  // Launch on the first tensor's stream; tensors on other streams are fenced in and out with events.
+  cudaStream_t stream = static_cast<cudaStream_t>(op.items[0].buffer.unwrap<CudaBuffer>().stream);
+  std::vector<cudaStream_t> others;
+  for (auto& it : op.items) {
+    cudaStream_t s = static_cast<cudaStream_t>(it.buffer.unwrap<CudaBuffer>().stream);
+    if (s != stream && std::find(others.begin(), others.end(), s) == others.end()) others.push_back(s);
+  }
+  for (cudaStream_t s : others) {
+    CudaEvent ev(op.srcDevice);
+    ev.record(s);
+    ev.wait(stream, op.srcDevice);
+  }
+  const int ctas = opts_.maxCtas > 0 ? opts_.maxCtas : cudaSmCount(op.srcDevice);
+  Launched l;
+  l.seq = op.seq;
+  if (sameProcess_) {
+    kernels::launchPush(plan, stream, ctas, nullptr, 0, nullptr, nullptr);
+    auto ev = std::make_unique<CudaEvent>(op.srcDevice);
+    ev->record(stream);
+    l.event = reinterpret_cast<uint64_t>(ev->raw());
+    for (cudaStream_t s : others) ev->wait(s, op.srcDevice);
+    eventPool_.push_back(std::move(ev));
+    if (eventPool_.size() > 1024) eventPool_.pop_front();  // long since consumed by the receiver
+  } else {
+    Error err;
+    Arena* mine = arenaFor(op.srcDevice, err);
+    if (!mine) return closeFromLoop(err);
+    uint32_t* flag = reinterpret_cast<uint32_t*>(peerArenaBase) + (op.seq % kFlagSlots);
+    kernels::launchPush(plan, stream, ctas, flag, flagValueFor(op.seq), mine->counter(stream), mine->status());
+    if (!others.empty()) {
+      CudaEvent ev(op.srcDevice);
+      ev.record(stream);
+      for (cudaStream_t s : others) ev.wait(s, op.srcDevice);
+    }
+  }
+  writePacket(l);
+  finishSend(op, Error::kSuccess);
+}
+
+void ChannelImpl::finishSend(SendOp& op, const Error& e) {
+  op.launched = true;
+  auto items = std::move(op.items);
+  for (auto& it : items) it.callback(e);
+}
+
+void ChannelImpl::recvBatchFromLoop(std::vector<RecvItem> items) {
+  std::vector<RecvItem> live;
+  for (auto& it : items) {
+    if (error_) it.callback(error_);
+    else if (it.length == 0) it.callback(Error::kSuccess);
+    else live.push_back(std::move(it));
+  }
+  if (live.empty()) return;
+  returnCredits();
+  for (auto& group : splitByDevicePair(live, false)) {
+    if (error_) {
+      for (auto& it : group) it.callback(error_);
+      continue;
+    }
+    RecvOp op;
+    op.seq = nextRecvSeq_++;
+    op.device = group[0].buffer.device().index;
+    op.items = std::move(group);
+    auto early = earlyLaunched_.find(op.seq);
+    if (early != earlyLaunched_.end()) {
+      op.notice = std::move(early->second);
+      earlyLaunched_.erase(early);
+    }
+    recvOps_.push_back(std::move(op));
+    RecvOp& ref = recvOps_.back();
+    if (ref.notice) completeRecv(ref);
+    else if (helloDone_) sendReady(ref);
+  }
+  while (!recvOps_.empty() && recvOps_.front().items.empty()) recvOps_.pop_front();
+}
+
+void ChannelImpl::sendReady(RecvOp& op) {
+  if (error_) return;
+  RecvReady r;
+  r.seq = op.seq;
+  r.deviceIdx = op.device;
+  try {
+    if (!sameProcess_) {
+      Error err;
+      Arena* a = arenaFor(op.device, err);
+      if (!a) return closeFromLoop(err);
+      if (!a->announced) {
+        ArenaWire w;
+        w.handle = a->handle;
+        w.inboxBytes = a->inboxBytes;
+        r.arena = w;
+        a->announced = true;
+      }
+    }
+    for (auto& it : op.items) {
+      TargetWire t;
+      void* ptr = it.buffer.unwrap<CudaBuffer>().ptr;
+      t.dtype = it.castTo ? static_cast<uint8_t>(*it.castTo) : 0;
+      t.srcDtype = static_cast<uint8_t>(it.srcDtype);
+      // Bytes the destination holds; the sender checks them against what it is about to write.
+      t.bytes = it.castTo ? kernels::convertedBytes(it.length, it.srcDtype, *it.castTo) : it.length;
+      if (sameProcess_) {
+        t.ptr = reinterpret_cast<uint64_t>(ptr);
+      } else {
+        void* base = nullptr;
+        size_t size = 0;
+        unsigned long long id = 0;
+        if (cudaAllocationInfo(ptr, &base, &size, &id)) {
+          CudaDeviceGuard g(op.device);
+          cudaIpcMemHandle_t h;
+          cudaError_t e = cudaIpcGetMemHandle(&h, base);
+          if (e == cudaSuccess) {
+            std::memcpy(t.handle.data(), &h, sizeof(h));
+            t.hasHandle = 1;
+            t.bufferId = id;
+            t.ptr = static_cast<uint64_t>(static_cast<uint8_t*>(ptr) - static_cast<uint8_t*>(base));
+          } else {
+            cudaGetLastError();
+          }
+        }
+      }
+      r.targets.push_back(t);
+    }
+  } catch (const std::exception& ex) {
+    return closeFromLoop(TPB_CREATE_ERROR(CudaError, ex.what()));
+  }
+  op.readySent = true;
+  writePacket(r);
+}
+
+void ChannelImpl::completeRecv(RecvOp& op) {
+  const Launched& n = *op.notice;
+  if (!n.error.empty()) return closeFromLoop(TPB_CREATE_ERROR(CudaError, n.error));
+  try {
+    CudaDeviceGuard g(op.device);
+    cudaStream_t stream = static_cast<cudaStream_t>(op.items[0].buffer.unwrap<CudaBuffer>().stream);
+    std::vector<cudaStream_t> others;
+    for (auto& it : op.items) {
+      cudaStream_t s = static_cast<cudaStream_t>(it.buffer.unwrap<CudaBuffer>().stream);
+      if (s != stream && std::find(others.begin(), others.end(), s) == others.end()) others.push_back(s);
+    }
+    if (sameProcess_) {
+      cudaEvent_t ev = reinterpret_cast<cudaEvent_t>(n.event);
+      TPB_CUDA_CHECK(cudaStreamWaitEvent(stream, ev, 0));
+      for (cudaStream_t s : others) TPB_CUDA_CHECK(cudaStreamWaitEvent(s, ev, 0));
+    } else {
+      Error err;
+      Arena* a = arenaFor(op.device, err);
+      if (!a) return closeFromLoop(err);
+      uint32_t* flag = a->flag(op.seq);
+      const uint32_t value = flagValueFor(op.seq);
+      const CudaLib& lib = CudaLib::get();
+      if (!opts_.waitWithKernel && lib.cuStreamWaitValue32) {
+        int rc = lib.cuStreamWaitValue32(stream, reinterpret_cast<CUdeviceptr_t>(flag), value, CudaLib::kWaitGeq);
+        if (rc != 0) return closeFromLoop(TPB_CREATE_ERROR(CudaError, "cuStreamWaitValue32: " + lib.errorString(rc)));
+      } else {
+        kernels::launchWaitFlag(stream, flag, value, opts_.waitTimeoutNs, a->status());
+      }
+      enqueuedWaits_.emplace_back(flag, value);
+      if (enqueuedWaits_.size() > 64) enqueuedWaits_.erase(enqueuedWaits_.begin());
+      if (n.eager) {
+        // Unpack inbox -> tensors on the receiver's stream, applying the requested casts.
+        kernels::PushPlan plan;
+        uint64_t cursor = n.inboxOffset;
+        for (auto& it : op.items) {
+          kernels::CopyItem c;
+          c.src = a->inbox() + cursor;
+          c.dst = it.buffer.unwrap<CudaBuffer>().ptr;
+          c.srcBytes = it.length;
+          if (it.castTo) {
+            c.srcDtype = it.srcDtype;
+            c.dstDtype = *it.castTo;
+          }
+          kernels::appendToPlan(plan, c, opts_.useBulkCopy);
+          cursor += (it.length + kInboxAlign - 1) / kInboxAlign * kInboxAlign;
+        }
+        const int ctas = opts_.maxCtas > 0 ? opts_.maxCtas : cudaSmCount(op.device);
+        kernels::launchPush(plan, stream, ctas, nullptr, 0, nullptr, nullptr);
+        PendingCredit pc;
+        pc.done = std::make_unique<CudaEvent>(op.device);
+        pc.done->record(stream);
+        pc.device = op.device;
+        pc.value = n.creditValue;
+        pendingCredits_.push_back(std::move(pc));
+      }
+      if (!others.empty()) {
+        CudaEvent ev(op.device);
+        ev.record(stream);
+        for (cudaStream_t s : others) ev.wait(s, op.device);
+      }
+    }
+  } catch (const std::exception& ex) {
+    return closeFromLoop(TPB_CREATE_ERROR(CudaError, ex.what()));
+  }
+  finishRecv(op, Error::kSuccess);
+}
+
+void ChannelImpl::finishRecv(RecvOp& op, const Error& e) {
+  auto items = std::move(op.items);
+  op.items.clear();
+  for (auto& it : items) it.callback(e);
+}
+
+void ChannelImpl::returnCredits() {
+  // Inbox space is handed back once the unpack kernel that read it has finished; this is
+  // checked opportunistically whenever the channel does anything (a sender that runs out of
+  // credits falls back to rendezvous, whose traffic makes us come through here again).
+  uint64_t value = 0;
+  int device = -1;
+  while (!pendingCredits_.empty() && pendingCredits_.front().done->query()) {
+    value = pendingCredits_.front().value;
+    device = pendingCredits_.front().device;
+    pendingCredits_.pop_front();
+  }
+  if (device >= 0 && !error_) {
+    Credit c;
+    c.deviceIdx = device;
+    c.value = value;
+    writePacket(c);
+  }
+}
+
+void ChannelImpl::onPacket(Packet p) {
+  if (std::holds_alternative<RecvReady>(p)) {
+    RecvReady& r = std::get<RecvReady>(p);
+    for (auto& op : sendOps_) {
+      if (op.seq == r.seq) {
+        if (op.launched) {
+          // Already sent eagerly. Still learn the peer's arena if this message carried it.
+          if (r.arena && !sameProcess_) {
+            CudaDeviceGuard g(op.srcDevice);
+            std::string why;
+            if (void* base = MappingCache::get().open(r.arena->handle, &why)) {
+              PeerArena pa;
+              pa.base = static_cast<uint8_t*>(base);
+              pa.inboxBytes = r.arena->inboxBytes;
+              peerArenas_[r.deviceIdx] = pa;
+            }
+          }
+          return;
+        }
+        op.ready = std::move(r);
+        tryLaunch(op);
+        while (!sendOps_.empty() && sendOps_.front().launched) sendOps_.pop_front();
+        return;
+      }
+    }
+    if (r.seq >= nextSendSeq_) earlyReady_.emplace(r.seq, std::move(r));
+    // else: for a batch that was sent eagerly and already retired — nothing to do
+  } else if (std::holds_alternative<Launched>(p)) {
+    Launched& l = std::get<Launched>(p);
+    for (auto& op : recvOps_) {
+      if (op.seq == l.seq && !op.items.empty()) {
+        op.notice = std::move(l);
+        completeRecv(op);
+        while (!recvOps_.empty() && recvOps_.front().items.empty()) recvOps_.pop_front();
+        returnCredits();
+        return;
+      }
+    }
+    earlyLaunched_.emplace(l.seq, std::move(l));
+  } else {
+    const Credit& c = std::get<Credit>(p);
+    auto it = peerArenas_.find(c.deviceIdx);
+    if (it != peerArenas_.end() && c.value > it->second.tail) it->second.tail = c.value;
+  }
+}
+
+void ChannelImpl::close() {
+  auto self = shared_from_this();
+  ctx_->loop_.deferToLoop([self]() { self->closeFromLoop(TPB_CREATE_ERROR(ChannelClosedError)); });
+}
+
+void ChannelImpl::closeFromLoop(const Error& e) {
+  if (error_) return;
+  error_ = e;
+  TPB_VLOG(4) << "Channel " << id_ << " is closing: " << e.what();
+  conn_->close();
+  ctx_->unenroll(weak_from_this());
+  // Release any stream still parked on a flag that will now never be written: write the awaited
+  // value from the host so the stream drains (the error reaches the user through callbacks).
+  if (!enqueuedWaits_.empty()) {
+    // On a private non-blocking stream: the user's stream (possibly the legacy default stream,
+    // which blocking calls would queue behind) is exactly what is stuck.
+    cudaStream_t s = nullptr;
+    if (cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) == cudaSuccess) {
+      for (auto& w : enqueuedWaits_)
+        cudaMemcpyAsync(w.first, &w.second, sizeof(uint32_t), cudaMemcpyHostToDevice, s);
+      cudaStreamSynchronize(s);
+      cudaStreamDestroy(s);
+    }
+    cudaGetLastError();
+    enqueuedWaits_.clear();
+  }
+  auto sends = std::move(sendOps_);
+  auto recvs = std::move(recvOps_);
+  sendOps_.clear();
+  recvOps_.clear();
+  for (auto& op : sends)
+    for (auto& it : op.items) it.callback(error_);
+  for (auto& op : recvs)
+    for (auto& it : op.items) it.callback(error_);
+}
+
+}  // namespace
+
+std::shared_ptr<Context> create(Options options) { return std::make_shared<ContextImpl>(options); }
+
+}  // namespace cuda_p2p
+}  // namespace channel
+}  // namespace tpb

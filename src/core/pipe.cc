@@ -524,6 +524,7 @@ void PipeImpl::receiveTensorsOfMessage(ReadOperation& op) {
     item.buffer = ta.buffer;
     item.length = td.length;
     item.castTo = ta.castTo;
+    item.srcDtype = ta.sourceDtype;
     item.sourceDevice = td.sourceDevice;
     ++op.numTensorsBeingReceived;
     item.callback = callbackWrapper_([seq](PipeImpl& impl) {

@@ -1,0 +1,113 @@
+// Host-visible interface of the device kernels.
+//
+//   K1/K6  tpb_push_pack   one persistent launch walks a table of copy entries (many tensors,
+//                          contiguous or 2-D strided, optional dtype cast), moves them to their
+//                          destinations — local memory or a peer GPU's memory mapped into this
+//                          process — and finally publishes a release-ordered flag.
+//   K2     tpb_wait_flag   bounded wait for such a flag on the receiver's stream.
+//   K3     unpack          the same kernel as K1 with a local inbox as the source.
+//   K7     tpb_delay       bounded busy kernel that scribbles over a buffer (stream-order tests).
+//   K8     tpb_fill / tpb_verify   seeded pattern generator and on-device comparison.
+//
+// The reference has no device code of its own (its data path is cudaMemcpyAsync, see
+// tensorpipe/channel/cuda_ipc/channel_impl.cc:238-252,453-463 and cuda_xth/channel_impl.cc:66-77);
+// these kernels replace those call sites.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <vector>
+
+#include <tpb/message.h>
+
+namespace tpb {
+namespace kernels {
+
+enum EntryKind : uint32_t {
+  kCopyBulk = 0,     // contiguous, src/dst/bytes all multiples of 16: TMA bulk pipeline
+  kCopyPlain = 1,    // contiguous, any alignment: vectorised ld/st
+  kCastPlain = 2,    // contiguous with dtype conversion
+  kStrided = 3,      // 2-D strided source -> packed destination (optional conversion)
+};
+
+struct alignas(16) PushEntry {
+  const void* src;
+  void* dst;
+  uint64_t count;        // bytes for kCopy*, elements for kCast*/kStrided (= rows*cols)
+  uint32_t kind;
+  uint8_t srcDtype, dstDtype, srcElemSize, dstElemSize;
+  int64_t rows, cols, rowStride, colStride;  // kStrided only, in elements
+  uint32_t tileStart;    // first tile of this entry within its class (bulk / plain)
+  uint32_t numTiles;
+};
+static_assert(sizeof(PushEntry) == 80, "entry layout");
+
+constexpr int kMaxEntriesSmall = 8;
+constexpr int kMaxEntriesLarge = 96;
+constexpr uint32_t kBulkTileBytes = 32 * 1024;
+constexpr int kBulkStages = 4;
+constexpr uint32_t kPlainTileBytes = 64 * 1024;
+constexpr int kStridedTile = 64;  // elements per side
+constexpr int kThreads = 512;
+
+// Status word values written by kernels (0 = fine).
+enum KernelStatus : uint32_t {
+  kStatusOk = 0,
+  kStatusWaitTimeout = 1,     // tpb_wait_flag gave up
+  kStatusBarrierTimeout = 2,  // a bulk load never completed
+};
+
+struct PushPlan {
+  std::vector<PushEntry> entries;
+  uint32_t bulkTiles = 0;
+  uint32_t plainTiles = 0;
+  uint64_t totalBytesOut = 0;
+};
+
+struct CopyItem {
+  const void* src = nullptr;
+  void* dst = nullptr;
+  uint64_t srcBytes = 0;            // packed bytes in the source dtype
+  DType srcDtype = DType::kBytes;
+  DType dstDtype = DType::kBytes;   // == srcDtype (or kBytes) when no conversion
+  bool strided = false;
+  StridedView view;
+};
+
+// True if (src -> dst) is a conversion the kernels implement.
+bool castSupported(DType src, DType dst);
+uint64_t convertedBytes(uint64_t srcBytes, DType src, DType dst);
+
+// Splits items into kernel entries (aligned body for the bulk path, ragged head/tail for the
+// plain path) and numbers their tiles. `useBulk=false` routes everything through the plain path.
+void appendToPlan(PushPlan& plan, const CopyItem& item, bool useBulk);
+
+// Launches the plan on `stream` of the current device. `flag` may be null; when set, `counter`
+// must point to a zeroed 32-bit word in this device's memory that is private to launches
+// serialised on one stream (the kernel leaves it zeroed again). `status` may be null.
+// Returns the number of kernel launches made (plans with many entries take several).
+int launchPush(const PushPlan& plan, cudaStream_t stream, int maxCtas, uint32_t* flag,
+               uint32_t flagValue, uint32_t* counter, uint32_t* status);
+
+// Waits until *flag - value >= 0 (cyclic) or until timeoutNs elapsed; writes kStatusOk or
+// kStatusWaitTimeout to *status (device or mapped host memory).
+void launchWaitFlag(cudaStream_t stream, const uint32_t* flag, uint32_t value, uint64_t timeoutNs,
+                    uint32_t* status);
+
+// Keeps the stream busy for roughly `microseconds` (capped at 2 s) while scribbling into buf.
+void launchDelay(cudaStream_t stream, void* buf, size_t bytes, uint32_t microseconds);
+
+// buf[i] = pattern(seed, i) over 32-bit words (and trailing bytes).
+void launchFill(cudaStream_t stream, void* buf, size_t bytes, uint64_t seed);
+// Adds the number of mismatching bytes versus pattern(seed) to *mismatches (device memory).
+void launchVerify(cudaStream_t stream, const void* buf, size_t bytes, uint64_t seed,
+                  unsigned long long* mismatches);
+// Host restatement of the pattern, for CPU-side checks.
+uint8_t patternByte(uint64_t seed, uint64_t index);
+
+// Total kernel launches made by this process (for benchmarks' accounting).
+uint64_t launchCount();
+
+}  // namespace kernels
+}  // namespace tpb

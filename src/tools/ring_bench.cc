@@ -1,0 +1,500 @@
+#include "tools/ring_bench.h"
+
+#include <atomic>
+#include <chrono>
+#include <cmath>
+#include <future>
+#include <mutex>
+#include <random>
+#include <thread>
+
+#include <tpb/tpb.h>
+
+#include "common/cuda.h"
+#include "kernels/push.h"
+
+namespace tpb {
+namespace tools {
+
+namespace {
+using Clock = std::chrono::steady_clock;
+double msSince(Clock::time_point t0) {
+  return std::chrono::duration<double, std::milli>(Clock::now() - t0).count();
+}
+void failOn(const Error& e, const char* what) {
+  if (e) throw std::runtime_error(std::string(what) + ": " + e.what());
+}
+template <typename T>
+T waitOrThrow(std::future<T>& f, int seconds, const char* what) {
+  if (f.wait_for(std::chrono::seconds(seconds)) != std::future_status::ready)
+    throw std::runtime_error(std::string("timed out: ") + what);
+  return f.get();
+}
+}  // namespace
+
+struct RingBench::Impl {
+  RingBenchOptions opts;
+  std::shared_ptr<Context> sendCtx, recvCtx;
+  std::shared_ptr<Listener> listener;
+  std::shared_ptr<Pipe> sendPipe, recvPipe;
+  int nextDevice = 0;
+  cudaStream_t sendStream = nullptr, recvStream = nullptr;
+  uint8_t* src = nullptr;
+  uint8_t* dst[2] = {nullptr, nullptr};
+  unsigned long long* mismatches = nullptr;
+  cudaEvent_t evStart = nullptr, evEnd = nullptr;
+  uint64_t srcSeed = 0;
+
+  std::shared_ptr<Context> makeContext(const std::string& name) {
+    auto ctx = std::make_shared<Context>(ContextOptions().name(name));
+    ctx->registerTransport(0, "uv", transport::uv::create());
+    if (opts.useShm) ctx->registerTransport(10, "shm", transport::shm::create());
+    auto basic = channel::basic::create();
+    ctx->registerChannel(0, "basic", basic);
+    if (opts.channel == "cuda_basic") {
+      ctx->registerChannel(5, "cuda_basic", channel::cuda_basic::create(channel::basic::create()));
+    } else {
+      channel::cuda_p2p::Options o;
+      o.useBulkCopy = opts.useBulkCopy;
+      o.waitWithKernel = opts.waitWithKernel;
+      o.eagerThreshold = opts.eagerThreshold;
+      o.maxCtas = opts.maxCtas;
+      ctx->registerChannel(10, "cuda_p2p", channel::cuda_p2p::create(o));
+    }
+    return ctx;
+  }
+
+  void fillSource(size_t bytes, uint64_t seed) {
+    kernels::launchFill(sendStream, src, bytes, seed);
+    TPB_CUDA_CHECK(cudaStreamSynchronize(sendStream));
+    srcSeed = seed;
+  }
+};
+
+RingBench::RingBench(RingBenchOptions opts) : impl_(new Impl) {
+  Impl& m = *impl_;
+  m.opts = opts;
+  TPB_CUDA_CHECK(cudaSetDevice(opts.device));
+  TPB_CUDA_CHECK(cudaStreamCreateWithFlags(&m.sendStream, cudaStreamNonBlocking));
+  TPB_CUDA_CHECK(cudaStreamCreateWithFlags(&m.recvStream, cudaStreamNonBlocking));
+  TPB_CUDA_CHECK(cudaMalloc(&m.src, opts.maxBytes));
+  TPB_CUDA_CHECK(cudaMalloc(&m.dst[0], opts.maxBytes));
+  TPB_CUDA_CHECK(cudaMalloc(&m.dst[1], opts.maxBytes));
+  TPB_CUDA_CHECK(cudaMalloc(&m.mismatches, sizeof(unsigned long long)));
+  TPB_CUDA_CHECK(cudaMemset(m.mismatches, 0, sizeof(unsigned long long)));
+  TPB_CUDA_CHECK(cudaEventCreate(&m.evStart));
+  TPB_CUDA_CHECK(cudaEventCreate(&m.evEnd));
+  m.sendCtx = m.makeContext("send" + std::to_string(opts.device));
+  m.recvCtx = m.makeContext("recv" + std::to_string(opts.device));
+  std::vector<std::string> urls = {"uv://127.0.0.1"};
+  if (opts.useShm) urls.push_back("shm://");
+  m.listener = m.recvCtx->listen(urls);
+}
+
+RingBench::~RingBench() {
+  Impl& m = *impl_;
+  m.sendPipe.reset();
+  m.recvPipe.reset();
+  m.listener.reset();
+  if (m.sendCtx) m.sendCtx->join();
+  if (m.recvCtx) m.recvCtx->join();
+  cudaSetDevice(m.opts.device);
+  cudaDeviceSynchronize();
+  cudaFree(m.src);
+  cudaFree(m.dst[0]);
+  cudaFree(m.dst[1]);
+  cudaFree(m.mismatches);
+  cudaEventDestroy(m.evStart);
+  cudaEventDestroy(m.evEnd);
+  cudaStreamDestroy(m.sendStream);
+  cudaStreamDestroy(m.recvStream);
+}
+
+std::string RingBench::listenUrl() const { return impl_->listener->url("uv"); }
+
+void RingBench::connect(const std::string& nextUrl) {
+  Impl& m = *impl_;
+  std::promise<std::pair<Error, std::shared_ptr<Pipe>>> accepted;
+  m.listener->accept([&](const Error& e, std::shared_ptr<Pipe> p) { accepted.set_value({e, std::move(p)}); });
+  // "url|device": the device index the next rank receives on.
+  std::string url = nextUrl;
+  m.nextDevice = m.opts.device;
+  auto bar = nextUrl.rfind('|');
+  if (bar != std::string::npos) {
+    url = nextUrl.substr(0, bar);
+    m.nextDevice = std::stoi(nextUrl.substr(bar + 1));
+  }
+  m.sendPipe = m.sendCtx->connect(url);
+  auto f = accepted.get_future();
+  auto [e, p] = waitOrThrow(f, 60, "accepting the previous rank's pipe");
+  failOn(e, "accept");
+  m.recvPipe = std::move(p);
+}
+
+PhaseResult RingBench::runStream(size_t bytes, int steps, int depth, bool verify) {
+  Impl& m = *impl_;
+  if (bytes > m.opts.maxBytes) throw std::runtime_error("tensor larger than the benchmark's buffers");
+  TPB_CUDA_CHECK(cudaSetDevice(m.opts.device));
+  if (verify) {
+    m.fillSource(bytes, 0x5eed0000 + bytes);
+    TPB_CUDA_CHECK(cudaMemsetAsync(m.mismatches, 0, sizeof(unsigned long long), m.recvStream));
+    TPB_CUDA_CHECK(cudaMemsetAsync(m.dst[0], 0, bytes, m.recvStream));
+    TPB_CUDA_CHECK(cudaMemsetAsync(m.dst[1], 0, bytes, m.recvStream));
+    TPB_CUDA_CHECK(cudaStreamSynchronize(m.recvStream));
+    depth = 1;
+  }
+  const uint64_t launches0 = kernels::launchCount();
+
+  struct State {
+    std::mutex mu;
+    int sent = 0, inflight = 0, received = 0, armed = 0, descs = 0;
+    Error error;
+    std::promise<void> recvDone, sendDone;
+    bool recvSet = false, sendSet = false;
+  };
+  auto st = std::make_shared<State>();
+  Impl* mp = &m;
+
+  // ---- receiver: descriptor -> allocation -> read, re-armed as soon as the read is issued ----
+  auto armRead = std::make_shared<std::function<void()>>();
+  *armRead = [=]() {
+    {
+      std::unique_lock<std::mutex> l(st->mu);
+      if (st->armed >= steps || st->error) return;
+      ++st->armed;
+    }
+    mp->recvPipe->readDescriptor([=](const Error& e, Descriptor d) {
+      if (e) {
+        std::unique_lock<std::mutex> l(st->mu);
+        st->error = e;
+        if (!st->recvSet) { st->recvSet = true; st->recvDone.set_value(); }
+        return;
+      }
+      int k;
+      {
+        std::unique_lock<std::mutex> l(st->mu);
+        k = st->descs++;
+      }
+      Allocation a;
+      Allocation::Tensor t;
+      t.buffer = CudaBuffer{mp->dst[k & 1], mp->recvStream, mp->opts.device};
+      a.tensors.push_back(t);
+      mp->recvPipe->read(std::move(a), [=](const Error& e2) {
+        bool last = false;
+        {
+          std::unique_lock<std::mutex> l(st->mu);
+          if (e2) st->error = e2;
+          ++st->received;
+          last = st->received == steps || bool(st->error);
+        }
+        if (!e2 && verify) {
+          cudaSetDevice(mp->opts.device);
+          kernels::launchVerify(mp->recvStream, mp->dst[k & 1], bytes, mp->srcSeed, mp->mismatches);
+          cudaStreamSynchronize(mp->recvStream);
+        }
+        if (last) {
+          cudaSetDevice(mp->opts.device);
+          cudaEventRecord(mp->evEnd, mp->recvStream);
+          std::unique_lock<std::mutex> l(st->mu);
+          if (!st->recvSet) { st->recvSet = true; st->recvDone.set_value(); }
+        } else if (verify) {
+          (*armRead)();
+        }
+      });
+      if (!verify) (*armRead)();
+    });
+  };
+
+  // ---- sender: keep `depth` writes in flight ----
+  auto pump = std::make_shared<std::function<void()>>();
+  *pump = [=]() {
+    for (;;) {
+      {
+        std::unique_lock<std::mutex> l(st->mu);
+        if (st->error || st->inflight >= depth || st->sent >= steps) {
+          if ((st->sent >= steps && st->inflight == 0) || st->error) {
+            if (!st->sendSet) { st->sendSet = true; st->sendDone.set_value(); }
+          }
+          return;
+        }
+        ++st->sent;
+        ++st->inflight;
+      }
+      Message msg;
+      Message::Tensor t;
+      t.buffer = CudaBuffer{mp->src, mp->sendStream, mp->opts.device};
+      t.length = bytes;
+      t.targetDevice = Device(kCudaDeviceType, mp->nextDevice);
+      t.dtype = DType::kBF16;
+      msg.tensors.push_back(t);
+      mp->sendPipe->write(std::move(msg), [=](const Error& e) {
+        {
+          std::unique_lock<std::mutex> l(st->mu);
+          if (e) st->error = e;
+          --st->inflight;
+        }
+        (*pump)();
+      });
+    }
+  };
+
+  auto t0 = Clock::now();
+  TPB_CUDA_CHECK(cudaEventRecord(m.evStart, m.recvStream));
+  (*armRead)();
+  (*pump)();
+  auto fr = st->recvDone.get_future();
+  auto fs = st->sendDone.get_future();
+  waitOrThrow(fr, 300, "receiving");
+  waitOrThrow(fs, 300, "sending");
+  // Break the self-references of the recursive closures.
+  *armRead = nullptr;
+  *pump = nullptr;
+  failOn(st->error, "ring stream");
+  TPB_CUDA_CHECK(cudaEventSynchronize(m.evEnd));
+  PhaseResult r;
+  r.hostMs = msSince(t0);
+  float ms = 0;
+  TPB_CUDA_CHECK(cudaEventElapsedTime(&ms, m.evStart, m.evEnd));
+  r.deviceMs = ms;
+  TPB_CUDA_CHECK(cudaStreamSynchronize(m.sendStream));
+  if (verify) {
+    unsigned long long bad = 0;
+    TPB_CUDA_CHECK(cudaMemcpy(&bad, m.mismatches, sizeof(bad), cudaMemcpyDeviceToHost));
+    r.mismatches = bad;
+  }
+  r.kernelLaunches = kernels::launchCount() - launches0;
+  return r;
+}
+
+std::vector<double> RingBench::runLatency(size_t bytes, int laps, int rank, int world) {
+  Impl& m = *impl_;
+  TPB_CUDA_CHECK(cudaSetDevice(m.opts.device));
+  struct State {
+    std::mutex mu;
+    int lapsDone = 0;
+    Error error;
+    std::vector<double> samples;
+    Clock::time_point t0;
+    std::promise<void> done;
+    bool set = false;
+  };
+  auto st = std::make_shared<State>();
+  Impl* mp = &m;
+  const bool starter = rank == 0;
+
+  auto finish = [=]() {
+    std::unique_lock<std::mutex> l(st->mu);
+    if (!st->set) { st->set = true; st->done.set_value(); }
+  };
+  auto sendToken = std::make_shared<std::function<void()>>();
+  *sendToken = [=]() {
+    Message msg;
+    Message::Tensor t;
+    t.buffer = CudaBuffer{mp->src, mp->sendStream, mp->opts.device};
+    t.length = bytes;
+    t.targetDevice = Device(kCudaDeviceType, mp->nextDevice);
+    msg.tensors.push_back(t);
+    if (starter) st->t0 = Clock::now();
+    mp->sendPipe->write(std::move(msg), [=](const Error& e) {
+      if (e) {
+        { std::unique_lock<std::mutex> l(st->mu); st->error = e; }
+        finish();
+      }
+    });
+  };
+  auto armRead = std::make_shared<std::function<void()>>();
+  *armRead = [=]() {
+    mp->recvPipe->readDescriptor([=](const Error& e, Descriptor) {
+      if (e) {
+        { std::unique_lock<std::mutex> l(st->mu); st->error = e; }
+        return finish();
+      }
+      Allocation a;
+      Allocation::Tensor t;
+      t.buffer = CudaBuffer{mp->dst[0], mp->recvStream, mp->opts.device};
+      a.tensors.push_back(t);
+      mp->recvPipe->read(std::move(a), [=](const Error& e2) {
+        if (e2) {
+          { std::unique_lock<std::mutex> l(st->mu); st->error = e2; }
+          return finish();
+        }
+        cudaSetDevice(mp->opts.device);
+        cudaStreamSynchronize(mp->recvStream);  // the data is on the device now
+        int done;
+        {
+          std::unique_lock<std::mutex> l(st->mu);
+          if (starter)
+            st->samples.push_back(std::chrono::duration<double, std::micro>(Clock::now() - st->t0).count() / world);
+          done = ++st->lapsDone;
+        }
+        if (done < laps) {
+          (*armRead)();
+          (*sendToken)();
+        } else {
+          if (!starter) (*sendToken)();  // pass the last token on so the starter finishes its lap
+          finish();
+        }
+      });
+    });
+  };
+  (*armRead)();
+  if (starter) (*sendToken)();
+  auto f = st->done.get_future();
+  waitOrThrow(f, 300, "latency laps");
+  // Let the final write of a non-starter complete before tearing the closures down.
+  TPB_CUDA_CHECK(cudaStreamSynchronize(m.sendStream));
+  std::this_thread::sleep_for(std::chrono::milliseconds(20));
+  *armRead = nullptr;
+  *sendToken = nullptr;
+  failOn(st->error, "ring latency");
+  return st->samples;
+}
+
+PhaseResult RingBench::runMixed(int steps, uint64_t seed, uint64_t* bytesPerStep, bool verify) {
+  Impl& m = *impl_;
+  TPB_CUDA_CHECK(cudaSetDevice(m.opts.device));
+  // 64 tensors: dtype cycles fp32, bf16, int64; sizes log-uniform in [1 KiB, 16 MiB]; every 4th
+  // is a transposed 2-D view; every other fp32 tensor is cast to bf16 by the receiver.
+  struct Spec {
+    DType dtype;
+    uint64_t elems;
+    bool transposed;
+    bool cast;
+    int64_t rows, cols;
+    uint64_t srcOff, dstOff, srcBytes, dstBytes;
+  };
+  std::mt19937_64 rng(seed);
+  std::vector<Spec> specs;
+  uint64_t srcCursor = 0, dstCursor = 0, wire = 0;
+  int fp32Count = 0;
+  for (int i = 0; i < 64; ++i) {
+    Spec s{};
+    s.dtype = i % 3 == 0 ? DType::kF32 : (i % 3 == 1 ? DType::kBF16 : DType::kI64);
+    const double lg = std::log(1024.0) + (std::log(16.0 * 1024 * 1024) - std::log(1024.0)) *
+                                              (static_cast<double>(rng() % 100000) / 100000.0);
+    uint64_t bytes = static_cast<uint64_t>(std::exp(lg));
+    const uint64_t es = dtypeSize(s.dtype);
+    s.transposed = i % 4 == 3;
+    s.cols = 64;
+    s.rows = static_cast<int64_t>(std::max<uint64_t>(1, bytes / es / s.cols));
+    s.elems = static_cast<uint64_t>(s.rows) * s.cols;
+    s.srcBytes = s.elems * es;
+    if (s.dtype == DType::kF32) s.cast = (fp32Count++ % 2) == 0;
+    s.dstBytes = s.cast ? s.elems * 2 : s.srcBytes;
+    s.srcOff = srcCursor;
+    s.dstOff = dstCursor;
+    srcCursor += (s.srcBytes + 255) / 256 * 256;
+    dstCursor += (s.dstBytes + 255) / 256 * 256;
+    wire += s.dstBytes;
+    specs.push_back(s);
+  }
+  if (srcCursor > m.opts.maxBytes) throw std::runtime_error("mixed message larger than the benchmark's buffers");
+  if (bytesPerStep) *bytesPerStep = wire;
+  (void)verify;
+  const uint64_t launches0 = kernels::launchCount();
+
+  struct State {
+    std::mutex mu;
+    int received = 0, sent = 0;
+    Error error;
+    std::promise<void> recvDone, sendDone;
+    bool recvSet = false, sendSet = false;
+  };
+  auto st = std::make_shared<State>();
+  Impl* mp = &m;
+  auto specsPtr = std::make_shared<std::vector<Spec>>(specs);
+
+  auto armRead = std::make_shared<std::function<void()>>();
+  *armRead = [=]() {
+    mp->recvPipe->readDescriptor([=](const Error& e, Descriptor d) {
+      auto fail = [&](const Error& err) {
+        std::unique_lock<std::mutex> l(st->mu);
+        st->error = err;
+        if (!st->recvSet) { st->recvSet = true; st->recvDone.set_value(); }
+      };
+      if (e) return fail(e);
+      Allocation a;
+      for (const Spec& s : *specsPtr) {
+        Allocation::Tensor t;
+        t.buffer = CudaBuffer{mp->dst[0] + s.dstOff, mp->recvStream, mp->opts.device};
+        if (s.cast) {
+          t.castTo = DType::kBF16;
+          t.sourceDtype = DType::kF32;
+        }
+        a.tensors.push_back(t);
+      }
+      mp->recvPipe->read(std::move(a), [=](const Error& e2) {
+        bool last;
+        {
+          std::unique_lock<std::mutex> l(st->mu);
+          if (e2) st->error = e2;
+          last = ++st->received == steps || bool(st->error);
+        }
+        if (last) {
+          cudaSetDevice(mp->opts.device);
+          cudaEventRecord(mp->evEnd, mp->recvStream);
+          std::unique_lock<std::mutex> l(st->mu);
+          if (!st->recvSet) { st->recvSet = true; st->recvDone.set_value(); }
+        } else {
+          (*armRead)();
+        }
+      });
+    });
+  };
+  auto sendOne = std::make_shared<std::function<void()>>();
+  *sendOne = [=]() {
+    Message msg;
+    for (const Spec& s : *specsPtr) {
+      Message::Tensor t;
+      t.buffer = CudaBuffer{mp->src + s.srcOff, mp->sendStream, mp->opts.device};
+      t.length = s.srcBytes;
+      t.dtype = s.dtype;
+      t.targetDevice = Device(kCudaDeviceType, mp->nextDevice);
+      if (s.transposed) {
+        // The buffer holds a [cols, rows] row-major matrix; we send its transpose [rows, cols].
+        StridedView v;
+        v.dtype = s.dtype;
+        v.rows = s.rows;
+        v.cols = s.cols;
+        v.rowStride = 1;
+        v.colStride = s.rows;
+        t.view = v;
+      }
+      msg.tensors.push_back(t);
+    }
+    mp->sendPipe->write(std::move(msg), [=](const Error& e) {
+      bool more;
+      {
+        std::unique_lock<std::mutex> l(st->mu);
+        if (e) st->error = e;
+        more = ++st->sent < steps && !st->error;
+        if (!more && !st->sendSet) { st->sendSet = true; st->sendDone.set_value(); }
+      }
+      if (more) (*sendOne)();
+    });
+  };
+
+  auto t0 = Clock::now();
+  TPB_CUDA_CHECK(cudaEventRecord(m.evStart, m.recvStream));
+  (*armRead)();
+  (*sendOne)();
+  auto fr = st->recvDone.get_future();
+  auto fs = st->sendDone.get_future();
+  waitOrThrow(fr, 300, "receiving");
+  waitOrThrow(fs, 300, "sending");
+  *armRead = nullptr;
+  *sendOne = nullptr;
+  failOn(st->error, "mixed messages");
+  TPB_CUDA_CHECK(cudaEventSynchronize(m.evEnd));
+  PhaseResult r;
+  r.hostMs = msSince(t0);
+  float ms = 0;
+  TPB_CUDA_CHECK(cudaEventElapsedTime(&ms, m.evStart, m.evEnd));
+  r.deviceMs = ms;
+  TPB_CUDA_CHECK(cudaStreamSynchronize(m.sendStream));
+  r.kernelLaunches = kernels::launchCount() - launches0;
+  return r;
+}
+
+}  // namespace tools
+}  // namespace tpb

@@ -408,6 +408,7 @@ class ConnectionImpl final : public FdHandler, public std::enable_shared_from_th
     ctx_->reactor().deferToLoop([self, op = std::move(op)]() mutable {
       if (self->error_) return op.fn(self->error_);
       self->writes_.push_back(std::move(op));
+      if (self->peerGone_) return self->closeFromLoop(TPB_CREATE_ERROR(EOFError));
       if (self->state_ == kEstablished) self->processWrites();
     });
   }
@@ -445,6 +446,7 @@ class ConnectionImpl final : public FdHandler, public std::enable_shared_from_th
   uint32_t peerInboxToken_ = 0, peerOutboxToken_ = 0;
   bool tokensRegistered_ = false;
   bool watching_ = false;
+  bool peerGone_ = false;
   std::deque<ReadOp> reads_;
   std::deque<WriteOp> writes_;
 };
@@ -507,9 +509,14 @@ void ConnectionImpl::handleFdEvents(int events) {
   }
   if (events & (EPOLLIN | EPOLLRDHUP | EPOLLHUP | EPOLLERR)) {
     // Nothing legitimate arrives on the socket after bootstrap: this is the peer going away.
-    // Drain what is already in the inbox first so completed frames are not lost.
-    if (state_ == kEstablished) processReads();
-    if (state_ != kClosed) closeFromLoop(TPB_CREATE_ERROR(EOFError));
+    // Frames it completed before leaving are still in the inbox and stay readable (as bytes in
+    // a TCP socket buffer would); the connection fails once a read cannot be satisfied.
+    if (state_ != kEstablished) return closeFromLoop(TPB_CREATE_ERROR(EOFError));
+    peerGone_ = true;
+    if (watching_) ctx_->reactor().unwatchFd(sock_);
+    watching_ = false;
+    if (!writes_.empty()) return closeFromLoop(TPB_CREATE_ERROR(EOFError));
+    processReads();
   }
 }
 
@@ -544,7 +551,7 @@ void ConnectionImpl::processReads() {
       op.haveHeader = true;
       if (op.userBuffer) {
         if (op.frameLen != op.expected) {
-          pokePeer(peerOutboxToken_);
+          if (!peerGone_) pokePeer(peerOutboxToken_);
           closeFromLoop(TPB_CREATE_ERROR(ShortReadError, static_cast<ssize_t>(op.expected),
                                          static_cast<ssize_t>(op.frameLen)));
           return;
@@ -560,13 +567,17 @@ void ConnectionImpl::processReads() {
       op.bodyRead += n;
       if (op.bodyRead < op.frameLen) {
         // Let the writer refill while we wait for the rest.
-        if (n > 0) { pokePeer(peerOutboxToken_); consumed = false; }
+        if (n > 0 && !peerGone_) { pokePeer(peerOutboxToken_); consumed = false; }
         break;
       }
     }
     ReadOp done = std::move(reads_.front());
     reads_.pop_front();
     done.fn(Error::kSuccess, done.ptr, done.frameLen);
+  }
+  if (peerGone_) {
+    if (state_ == kEstablished && !reads_.empty()) closeFromLoop(TPB_CREATE_ERROR(EOFError));
+    return;
   }
   if (consumed && state_ == kEstablished) pokePeer(peerOutboxToken_);
 }

@@ -1,0 +1,287 @@
+"""Torch-facing layer over the native module.
+
+The reference's Python bindings only move CPU buffers (tensorpipe/python/tensorpipe.cc:103-130);
+here a message carries torch tensors on CPU or CUDA, a receiver may ask for a dtype conversion
+while the data moves, and 2-D strided views (e.g. a transposed matrix) are sent without first
+being made contiguous when the selected channel can pack them on the fly.
+"""
+from __future__ import annotations
+
+import json
+import threading
+from concurrent.futures import Future
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence
+
+import torch
+
+from . import _C
+
+DTYPE_CODES = {
+    torch.float32: 1,
+    torch.bfloat16: 2,
+    torch.float16: 3,
+    torch.int64: 4,
+    torch.int32: 5,
+    torch.uint8: 6,
+    torch.float64: 7,
+    torch.int16: 8,
+    torch.int8: 6,
+    torch.bool: 6,
+}
+_CASTABLE = (torch.float32, torch.bfloat16, torch.float16)
+_DTYPE_BY_NAME = {str(d).replace("torch.", ""): d for d in DTYPE_CODES}
+
+
+def kernel_launch_count() -> int:
+    """Kernels launched by this library in this process so far."""
+    return _C.kernel_launch_count()
+
+
+def _stream_handle(device: torch.device) -> int:
+    if device.type != "cuda":
+        return 0
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _device_str(device: torch.device) -> str:
+    if device.type == "cuda":
+        index = device.index if device.index is not None else torch.cuda.current_device()
+        return f"cuda:{index}"
+    return "cpu:0"
+
+
+@dataclass
+class Message:
+    """An outgoing message: metadata bytes, payloads (bytes-like) and torch tensors."""
+
+    tensors: Sequence[torch.Tensor] = ()
+    payloads: Sequence[bytes] = ()
+    metadata: bytes = b""
+    target_devices: Optional[Sequence[Optional[str]]] = None  # e.g. ["cuda:1", None]
+
+
+@dataclass
+class ReceivedMessage:
+    metadata: bytes = b""
+    payloads: List[bytearray] = field(default_factory=list)
+    tensors: List[torch.Tensor] = field(default_factory=list)
+
+
+class Pipe:
+    """One end of a pipe. `write`/`read_descriptor`/`read` mirror the native one-shot callback
+    API; `send`/`recv` are future-returning conveniences built on them."""
+
+    def __init__(self, native: "_C.Pipe"):
+        self._p = native
+        self._lock = threading.Lock()
+
+    @property
+    def remote_name(self) -> str:
+        return self._p.remote_name()
+
+    def close(self) -> None:
+        self._p.close()
+
+    # ---- native-shaped API ----
+    def write(self, message: Message, callback: Callable[[str], None]) -> None:
+        out = _C.OutgoingMessage(bytes(message.metadata))
+        for p in message.payloads:
+            out.add_payload(p if isinstance(p, (bytes, bytearray, memoryview)) else bytes(p))
+        targets = message.target_devices or [None] * len(message.tensors)
+        for t, target in zip(message.tensors, targets):
+            self._add_tensor(out, t, target)
+        self._p.write(out, callback)
+
+    def _add_tensor(self, out, t: torch.Tensor, target: Optional[str]) -> None:
+        local = _device_str(t.device)
+        view = None
+        code = DTYPE_CODES.get(t.dtype, 0)
+        if not t.is_contiguous():
+            packable = (
+                t.dim() == 2
+                and t.numel() > 0
+                and t.device.type == "cuda"
+                and target is not None
+                and self._p.channel_supports_layouts(local, target)
+            )
+            if packable:
+                view = (t.shape[0], t.shape[1], t.stride(0), t.stride(1))
+            else:
+                t = t.contiguous()
+        meta = json.dumps({"dtype": str(t.dtype).replace("torch.", ""), "shape": list(t.shape)}).encode()
+        dev_type, dev_index = local.split(":")
+        out.add_tensor(
+            t.data_ptr(),
+            t.numel() * t.element_size(),
+            dev_type,
+            int(dev_index),
+            _stream_handle(t.device),
+            meta,
+            code,
+            view,
+            target,
+            t,
+        )
+
+    def read_descriptor(self, callback: Callable[[str, dict], None]) -> None:
+        self._p.read_descriptor(callback)
+
+    def read(self, allocation: "_C.Allocation", callback: Callable[[str], None]) -> None:
+        self._p.read(allocation, callback)
+
+    # ---- conveniences ----
+    def send(self, tensors: Sequence[torch.Tensor] = (), payloads: Sequence[bytes] = (), metadata: bytes = b"",
+             target_devices: Optional[Sequence[Optional[str]]] = None) -> Future:
+        fut: Future = Future()
+
+        def done(err: str) -> None:
+            if err:
+                fut.set_exception(RuntimeError(err))
+            else:
+                fut.set_result(None)
+
+        self.write(Message(tensors, payloads, metadata, target_devices), done)
+        return fut
+
+    def recv(self, device: Optional[str] = None, cast: Optional[Dict[int, torch.dtype]] = None,
+             out: Optional[Sequence[torch.Tensor]] = None) -> Future:
+        """Receive the next message. Tensors are allocated with torch on `device` (default: the
+        device the sender asked for, else the sender's own device type), or written into `out`.
+        `cast` maps a tensor index to the dtype this side wants it converted to on the way."""
+        fut: Future = Future()
+        cast = cast or {}
+
+        def on_descriptor(err: str, desc: dict) -> None:
+            if err:
+                fut.set_exception(RuntimeError(err))
+                return
+            try:
+                msg = ReceivedMessage(metadata=desc["metadata"])
+                alloc = _C.Allocation()
+                for p in desc["payloads"]:
+                    buf = bytearray(p["length"])
+                    msg.payloads.append(buf)
+                    alloc.add_payload(buf)
+                for i, td in enumerate(desc["tensors"]):
+                    meta = json.loads(td["metadata"].decode()) if td["metadata"] else None
+                    src_dtype = _DTYPE_BY_NAME[meta["dtype"]] if meta else torch.uint8
+                    shape = meta["shape"] if meta else [td["length"]]
+                    want = cast.get(i)
+                    dst_dtype = want if want is not None else src_dtype
+                    where = td["target_device"] or device or (
+                        f"cuda:{torch.cuda.current_device()}" if td["source_device"].startswith("cuda") else "cpu")
+                    if out is not None:
+                        t = out[i]
+                    else:
+                        t = torch.empty(shape, dtype=dst_dtype, device=where.replace("cpu:0", "cpu"))
+                    msg.tensors.append(t)
+                    dev_type, _, dev_index = _device_str(t.device).partition(":")
+                    cast_code = None
+                    if want is not None and want != src_dtype:
+                        if want not in _CASTABLE or src_dtype not in _CASTABLE:
+                            raise ValueError(f"cannot convert {src_dtype} to {want} in flight")
+                        cast_code = DTYPE_CODES[want]
+                    alloc.add_tensor(t.data_ptr(), dev_type, int(dev_index), _stream_handle(t.device), cast_code,
+                                     DTYPE_CODES.get(src_dtype, 0), t)
+
+                def on_read(err2: str) -> None:
+                    if err2:
+                        fut.set_exception(RuntimeError(err2))
+                    else:
+                        fut.set_result(msg)
+
+                self._p.read(alloc, on_read)
+            except Exception as exc:  # surface allocation problems to the waiter
+                fut.set_exception(exc)
+
+        self._p.read_descriptor(on_descriptor)
+        return fut
+
+
+class Listener:
+    def __init__(self, native: "_C.Listener"):
+        self._l = native
+
+    def accept(self, callback: Callable[[str, Optional[Pipe]], None]) -> None:
+        self._l.accept(lambda err, p: callback(err, Pipe(p) if p is not None else None))
+
+    def accept_future(self) -> Future:
+        fut: Future = Future()
+
+        def done(err: str, pipe: Optional[Pipe]) -> None:
+            if err:
+                fut.set_exception(RuntimeError(err))
+            else:
+                fut.set_result(pipe)
+
+        self.accept(done)
+        return fut
+
+    def url(self, transport: str = "uv") -> str:
+        return self._l.url(transport)
+
+    def addresses(self) -> Dict[str, str]:
+        return self._l.addresses()
+
+    def close(self) -> None:
+        self._l.close()
+
+
+class Context:
+    def __init__(self, name: str = ""):
+        self._c = _C.Context(name)
+        self._joined = False
+
+    def register_transport(self, priority: int, name: str, transport) -> None:
+        self._c.register_transport(priority, name, transport)
+
+    def register_channel(self, priority: int, name: str, channel) -> None:
+        self._c.register_channel(priority, name, channel)
+
+    def listen(self, urls: Sequence[str]) -> Listener:
+        return Listener(self._c.listen(list(urls)))
+
+    def connect(self, url: str, remote_name: str = "") -> Pipe:
+        return Pipe(self._c.connect(url, remote_name))
+
+    def stats(self) -> dict:
+        return self._c.stats()
+
+    def close(self) -> None:
+        self._c.close()
+
+    def join(self) -> None:
+        if not self._joined:
+            self._joined = True
+            self._c.join()
+
+    def __enter__(self) -> "Context":
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self.join()
+
+
+def default_context(name: str = "", shm: bool = True, cuda: Optional[bool] = None, mpt_lanes: int = 0,
+                    **cuda_p2p_options) -> Context:
+    """A context with every sensible backend registered, best first:
+    transports shm (same host) > uv (TCP); channels cuda_p2p (GPU<->GPU over NVLink / same GPU) >
+    cuda_basic (anything involving a GPU, staged through pinned memory) > xth (CPU, same process)
+    > cma (CPU, same host) > mpt (CPU, striped over TCP lanes, optional) > basic (CPU, anywhere).
+    Backends that cannot work on this machine drop out silently."""
+    ctx = Context(name)
+    ctx.register_transport(0, "uv", _C.create_uv_transport())
+    if shm:
+        ctx.register_transport(10, "shm", _C.create_shm_transport())
+    ctx.register_channel(0, "basic", _C.create_basic_channel())
+    if mpt_lanes > 0:
+        ctx.register_channel(5, "mpt_uv", _C.create_mpt_channel(mpt_lanes))
+    ctx.register_channel(10, "cma", _C.create_cma_channel())
+    ctx.register_channel(20, "xth", _C.create_xth_channel())
+    if cuda is None:
+        cuda = torch.cuda.is_available()
+    if cuda:
+        ctx.register_channel(50, "cuda_basic", _C.create_cuda_basic_channel(_C.create_basic_channel()))
+        ctx.register_channel(100, "cuda_p2p", _C.create_cuda_p2p_channel(**cuda_p2p_options))
+    return ctx

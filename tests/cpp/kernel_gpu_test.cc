@@ -1,0 +1,350 @@
+// GPU tests of the device kernels against plain CPU restatements of the same operations:
+// memcpy, a strided 2-D gather and IEEE float -> bfloat16 round-to-nearest-even. Shapes include
+// the adversarial ones (0, 1, 15, 16, 17 bytes, odd offsets, sizes that straddle tile edges,
+// many tensors in one launch), and every destination is fenced by canary bytes.
+#include <cuda_runtime.h>
+
+#include <cstring>
+#include <random>
+
+#include "common/cuda.h"
+#include "kernels/push.h"
+#include "test_util.h"
+
+using namespace tpb;
+using namespace tpb::kernels;
+
+namespace {
+
+#define CK(x) TPB_CUDA_CHECK(x)
+
+constexpr size_t kGuard = 256;
+
+struct DeviceBuf {
+  uint8_t* p = nullptr;
+  size_t n = 0;
+  explicit DeviceBuf(size_t bytes) : n(bytes) { CK(cudaMalloc(&p, bytes ? bytes : 1)); }
+  ~DeviceBuf() { cudaFree(p); }
+};
+
+std::vector<uint8_t> download(const uint8_t* p, size_t n) {
+  std::vector<uint8_t> v(n);
+  if (n) CK(cudaMemcpy(v.data(), p, n, cudaMemcpyDeviceToHost));
+  return v;
+}
+
+uint16_t f32ToBf16(float f) {
+  uint32_t x;
+  std::memcpy(&x, &f, 4);
+  if ((x & 0x7fffffffu) > 0x7f800000u) return static_cast<uint16_t>((x >> 16) | 0x40);  // quiet NaN
+  uint32_t lsb = (x >> 16) & 1;
+  x += 0x7fffu + lsb;
+  return static_cast<uint16_t>(x >> 16);
+}
+float bf16ToF32(uint16_t h) {
+  uint32_t x = static_cast<uint32_t>(h) << 16;
+  float f;
+  std::memcpy(&f, &x, 4);
+  return f;
+}
+
+// Runs one plan with a single contiguous copy and checks bytes + canaries.
+void checkCopy(size_t bytes, size_t srcOff, size_t dstOff, bool bulk, int ctas) {
+  DeviceBuf src(bytes + srcOff + 64), dst(bytes + dstOff + 2 * kGuard);
+  std::vector<uint8_t> host(bytes + srcOff + 64);
+  std::mt19937 rng(static_cast<uint32_t>(bytes * 31 + srcOff * 7 + dstOff));
+  for (auto& b : host) b = static_cast<uint8_t>(rng());
+  CK(cudaMemcpy(src.p, host.data(), host.size(), cudaMemcpyHostToDevice));
+  CK(cudaMemset(dst.p, 0xCD, dst.n));
+  PushPlan plan;
+  CopyItem it;
+  it.src = src.p + srcOff;
+  it.dst = dst.p + kGuard + dstOff;
+  it.srcBytes = bytes;
+  appendToPlan(plan, it, bulk);
+  if (!plan.entries.empty()) launchPush(plan, nullptr, ctas, nullptr, 0, nullptr, nullptr);
+  CK(cudaDeviceSynchronize());
+  auto out = download(dst.p, dst.n);
+  for (size_t i = 0; i < kGuard + dstOff; ++i)
+    if (out[i] != 0xCD) throw tpbtest::TestFailure("front canary overwritten, bytes=" + std::to_string(bytes));
+  for (size_t i = 0; i < bytes; ++i)
+    if (out[kGuard + dstOff + i] != host[srcOff + i])
+      throw tpbtest::TestFailure("mismatch at byte " + std::to_string(i) + " of " + std::to_string(bytes) +
+                                 " (srcOff " + std::to_string(srcOff) + ", dstOff " + std::to_string(dstOff) +
+                                 ", bulk " + std::to_string(bulk) + ")");
+  for (size_t i = kGuard + dstOff + bytes; i < out.size(); ++i)
+    if (out[i] != 0xCD) throw tpbtest::TestFailure("back canary overwritten, bytes=" + std::to_string(bytes));
+}
+
+}  // namespace
+
+TPB_GPU_TEST(Kernel, ContiguousCopySmallAndRagged, 1) {
+  for (bool bulk : {false, true})
+    for (size_t bytes : {size_t(0), size_t(1), size_t(15), size_t(16), size_t(17), size_t(255), size_t(2047),
+                         size_t(2048), size_t(4096), size_t(4099), size_t(65536), size_t(65537), size_t(100000)})
+      for (size_t so : {size_t(0), size_t(1), size_t(8)})
+        for (size_t d : {size_t(0), size_t(1), size_t(8), size_t(13)}) checkCopy(bytes, so, d, bulk, 148);
+}
+
+TPB_GPU_TEST(Kernel, ContiguousCopyLarge, 1) {
+  // Tile-edge sizes and more tiles than CTAs (and fewer CTAs than tiles, on purpose).
+  for (bool bulk : {false, true}) {
+    checkCopy((32u << 10) * 4 * 3 + 48, 0, 0, bulk, 2);
+    checkCopy((1u << 20) + 16, 16, 16, bulk, 148);
+    checkCopy((64u << 20) + 5, 3, 3, bulk, 148);
+    checkCopy((8u << 20), 0, 16, bulk, 7);
+  }
+}
+
+TPB_GPU_TEST(Kernel, CastFloat32ToBfloat16MatchesRoundToNearestEven, 1) {
+  for (size_t n : {size_t(1), size_t(7), size_t(8), size_t(1000), size_t(65536 / 2 + 3), size_t(1 << 20)}) {
+    std::vector<float> host(n);
+    std::mt19937 rng(static_cast<uint32_t>(n));
+    std::normal_distribution<float> dist(0.f, 1.f);
+    for (auto& f : host) f = dist(rng);
+    if (n > 6) {
+      host[0] = 1.00390625f;  // exactly halfway between two bf16 values (ties to even)
+      host[1] = 1.01171875f;
+      host[2] = -0.f;
+      host[3] = 3.4e38f;
+      host[4] = 1e-40f;  // denormal
+      host[5] = std::numeric_limits<float>::infinity();
+    }
+    DeviceBuf src(n * 4), dst(n * 2 + 2 * kGuard);
+    CK(cudaMemcpy(src.p, host.data(), n * 4, cudaMemcpyHostToDevice));
+    CK(cudaMemset(dst.p, 0xCD, dst.n));
+    PushPlan plan;
+    CopyItem it;
+    it.src = src.p;
+    it.dst = dst.p + kGuard;
+    it.srcBytes = n * 4;
+    it.srcDtype = DType::kF32;
+    it.dstDtype = DType::kBF16;
+    appendToPlan(plan, it, true);
+    launchPush(plan, nullptr, 148, nullptr, 0, nullptr, nullptr);
+    CK(cudaDeviceSynchronize());
+    auto out = download(dst.p, dst.n);
+    for (size_t i = 0; i < n; ++i) {
+      uint16_t got;
+      std::memcpy(&got, &out[kGuard + 2 * i], 2);
+      EXPECT_EQ(got, f32ToBf16(host[i]));
+    }
+    EXPECT_EQ(int(out[kGuard - 1]), 0xCD);
+    EXPECT_EQ(int(out[kGuard + 2 * n]), 0xCD);
+
+    // and back: bf16 -> fp32 is exact
+    DeviceBuf back(n * 4);
+    PushPlan plan2;
+    CopyItem it2;
+    it2.src = dst.p + kGuard;
+    it2.dst = back.p;
+    it2.srcBytes = n * 2;
+    it2.srcDtype = DType::kBF16;
+    it2.dstDtype = DType::kF32;
+    appendToPlan(plan2, it2, true);
+    launchPush(plan2, nullptr, 148, nullptr, 0, nullptr, nullptr);
+    CK(cudaDeviceSynchronize());
+    auto outBack = download(back.p, n * 4);
+    for (size_t i = 0; i < n; ++i) {
+      float got;
+      std::memcpy(&got, &outBack[4 * i], 4);
+      float want = bf16ToF32(f32ToBf16(host[i]));
+      EXPECT_TRUE(std::memcmp(&got, &want, 4) == 0);
+    }
+  }
+}
+
+TPB_GPU_TEST(Kernel, StridedViewsPackLikeACpuGather, 1) {
+  struct Case {
+    int64_t rows, cols;
+    bool transposed;
+    size_t es;
+  };
+  for (Case c : {Case{1, 1, true, 4}, Case{3, 5, true, 2}, Case{100, 37, true, 4}, Case{64, 64, true, 8},
+                 Case{257, 129, true, 2}, Case{1000, 64, true, 4}, Case{33, 70, false, 4}, Case{128, 200, false, 1}}) {
+    // Source storage: transposed => a [cols, rows] row-major matrix viewed as [rows, cols];
+    // otherwise a [rows, 2*cols] matrix of which we take every other column (colStride 2).
+    const int64_t storageElems = c.transposed ? c.rows * c.cols : c.rows * c.cols * 2;
+    std::vector<uint8_t> host(storageElems * c.es);
+    std::mt19937 rng(static_cast<uint32_t>(c.rows * 131 + c.cols));
+    for (auto& b : host) b = static_cast<uint8_t>(rng());
+    StridedView v;
+    v.dtype = c.es == 1 ? DType::kU8 : c.es == 2 ? DType::kBF16 : c.es == 4 ? DType::kF32 : DType::kI64;
+    v.rows = c.rows;
+    v.cols = c.cols;
+    v.rowStride = c.transposed ? 1 : c.cols * 2;
+    v.colStride = c.transposed ? c.rows : 2;
+    const size_t packed = c.rows * c.cols * c.es;
+    DeviceBuf src(host.size()), dst(packed + 2 * kGuard);
+    CK(cudaMemcpy(src.p, host.data(), host.size(), cudaMemcpyHostToDevice));
+    CK(cudaMemset(dst.p, 0xCD, dst.n));
+    PushPlan plan;
+    CopyItem it;
+    it.src = src.p;
+    it.dst = dst.p + kGuard;
+    it.srcBytes = packed;
+    it.srcDtype = v.dtype;
+    it.dstDtype = v.dtype;
+    it.strided = true;
+    it.view = v;
+    appendToPlan(plan, it, true);
+    launchPush(plan, nullptr, 148, nullptr, 0, nullptr, nullptr);
+    CK(cudaDeviceSynchronize());
+    auto out = download(dst.p, dst.n);
+    for (int64_t r = 0; r < c.rows; ++r)
+      for (int64_t col = 0; col < c.cols; ++col) {
+        const uint8_t* want = &host[(r * v.rowStride + col * v.colStride) * c.es];
+        const uint8_t* got = &out[kGuard + (r * c.cols + col) * c.es];
+        if (std::memcmp(want, got, c.es) != 0)
+          throw tpbtest::TestFailure("strided mismatch at (" + std::to_string(r) + "," + std::to_string(col) +
+                                     ") of " + std::to_string(c.rows) + "x" + std::to_string(c.cols));
+      }
+    EXPECT_EQ(int(out[kGuard - 1]), 0xCD);
+    EXPECT_EQ(int(out[kGuard + packed]), 0xCD);
+  }
+}
+
+TPB_GPU_TEST(Kernel, StridedWithCast, 1) {
+  const int64_t rows = 130, cols = 70;
+  std::vector<float> host(rows * cols);
+  std::mt19937 rng(5);
+  std::normal_distribution<float> dist(0.f, 3.f);
+  for (auto& f : host) f = dist(rng);
+  DeviceBuf src(host.size() * 4), dst(rows * cols * 2);
+  CK(cudaMemcpy(src.p, host.data(), host.size() * 4, cudaMemcpyHostToDevice));
+  PushPlan plan;
+  CopyItem it;
+  it.src = src.p;
+  it.dst = dst.p;
+  it.srcBytes = rows * cols * 4;
+  it.srcDtype = DType::kF32;
+  it.dstDtype = DType::kBF16;
+  it.strided = true;
+  it.view = StridedView{DType::kF32, rows, cols, 1, rows};
+  appendToPlan(plan, it, true);
+  launchPush(plan, nullptr, 148, nullptr, 0, nullptr, nullptr);
+  CK(cudaDeviceSynchronize());
+  auto out = download(dst.p, rows * cols * 2);
+  for (int64_t r = 0; r < rows; ++r)
+    for (int64_t c = 0; c < cols; ++c) {
+      uint16_t got;
+      std::memcpy(&got, &out[(r * cols + c) * 2], 2);
+      EXPECT_EQ(got, f32ToBf16(host[c * rows + r]));
+    }
+}
+
+TPB_GPU_TEST(Kernel, ManyTensorsInOneLaunchAndAcrossLaunchLimit, 1) {
+  for (int count : {3, 8, 9, 64, 150}) {
+    std::mt19937 rng(count);
+    struct T {
+      size_t bytes, srcOff, dstOff;
+    };
+    std::vector<T> ts;
+    size_t srcTotal = 0, dstTotal = 0;
+    for (int i = 0; i < count; ++i) {
+      size_t bytes = 1 + rng() % (i % 5 == 0 ? 300000 : 5000);
+      size_t skew = i % 3 == 0 ? 0 : (rng() % 16);
+      ts.push_back({bytes, srcTotal + skew, dstTotal + (i % 2 ? skew : 0)});
+      srcTotal += bytes + 64;
+      dstTotal += bytes + 64;
+    }
+    std::vector<uint8_t> host(srcTotal);
+    for (auto& b : host) b = static_cast<uint8_t>(rng());
+    DeviceBuf src(srcTotal), dst(dstTotal);
+    CK(cudaMemcpy(src.p, host.data(), srcTotal, cudaMemcpyHostToDevice));
+    CK(cudaMemset(dst.p, 0xCD, dstTotal));
+    PushPlan plan;
+    for (auto& t : ts) {
+      CopyItem it;
+      it.src = src.p + t.srcOff;
+      it.dst = dst.p + t.dstOff;
+      it.srcBytes = t.bytes;
+      appendToPlan(plan, it, true);
+    }
+    int launches = launchPush(plan, nullptr, 148, nullptr, 0, nullptr, nullptr);
+    EXPECT_TRUE(launches >= 1);
+    CK(cudaDeviceSynchronize());
+    auto out = download(dst.p, dstTotal);
+    std::vector<uint8_t> want(dstTotal, 0xCD);
+    for (auto& t : ts) std::memcpy(&want[t.dstOff], &host[t.srcOff], t.bytes);
+    EXPECT_TRUE(out == want);
+  }
+}
+
+TPB_GPU_TEST(Kernel, FlagIsPublishedAndCounterResets, 1) {
+  DeviceBuf src(1 << 20), dst(1 << 20), words(256);
+  CK(cudaMemset(words.p, 0, 256));
+  uint32_t* flag = reinterpret_cast<uint32_t*>(words.p);
+  uint32_t* counter = flag + 16;
+  uint32_t* status = flag + 32;
+  launchFill(nullptr, src.p, 1 << 20, 77);
+  for (uint32_t round = 1; round <= 3; ++round) {
+    PushPlan plan;
+    CopyItem it;
+    it.src = src.p;
+    it.dst = dst.p;
+    it.srcBytes = 1 << 20;
+    appendToPlan(plan, it, round != 2);
+    launchPush(plan, nullptr, 148, flag, round, counter, status);
+    // The flag is already set when the wait kernel starts (same stream): it must return OK.
+    launchWaitFlag(nullptr, flag, round, 1'000'000'000ull, status + 1);
+    CK(cudaDeviceSynchronize());
+    auto w = download(words.p, 256);
+    uint32_t f, c, s0, s1;
+    std::memcpy(&f, &w[0], 4);
+    std::memcpy(&c, &w[64], 4);
+    std::memcpy(&s0, &w[128], 4);
+    std::memcpy(&s1, &w[132], 4);
+    EXPECT_EQ(f, round);
+    EXPECT_EQ(c, 0u);
+    EXPECT_EQ(s0, 0u);
+    EXPECT_EQ(s1, uint32_t(kStatusOk));
+  }
+  unsigned long long* bad;
+  CK(cudaMalloc(&bad, 8));
+  CK(cudaMemset(bad, 0, 8));
+  launchVerify(nullptr, dst.p, 1 << 20, 77, bad);
+  unsigned long long h = 1;
+  CK(cudaMemcpy(&h, bad, 8, cudaMemcpyDeviceToHost));
+  EXPECT_EQ(h, 0ull);
+  cudaFree(bad);
+}
+
+TPB_GPU_TEST(Kernel, WaitGivesUpWithATimeoutStatus, 1) {
+  // A flag that nothing sets: the wait must end by itself and say so, leaving the context usable.
+  DeviceBuf words(64);
+  CK(cudaMemset(words.p, 0, 64));
+  uint32_t* flag = reinterpret_cast<uint32_t*>(words.p);
+  auto t0 = std::chrono::steady_clock::now();
+  launchWaitFlag(nullptr, flag, 5, 50'000'000ull /* 50 ms */, flag + 1);
+  CK(cudaDeviceSynchronize());
+  double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+  auto w = download(words.p, 64);
+  uint32_t status;
+  std::memcpy(&status, &w[4], 4);
+  EXPECT_EQ(status, uint32_t(kStatusWaitTimeout));
+  EXPECT_TRUE(ms >= 40 && ms < 5000);
+  // The context still works.
+  launchFill(nullptr, words.p, 64, 1);
+  CK(cudaDeviceSynchronize());
+}
+
+TPB_GPU_TEST(Kernel, FillAndVerifyAgreeWithTheHostPattern, 1) {
+  for (size_t bytes : {size_t(1), size_t(7), size_t(4096), size_t(100003)}) {
+    DeviceBuf buf(bytes);
+    launchFill(nullptr, buf.p, bytes, 99);
+    CK(cudaDeviceSynchronize());
+    auto out = download(buf.p, bytes);
+    for (size_t i = 0; i < bytes; ++i) EXPECT_EQ(int(out[i]), int(patternByte(99, i)));
+    unsigned long long* bad;
+    CK(cudaMalloc(&bad, 8));
+    CK(cudaMemset(bad, 0, 8));
+    launchVerify(nullptr, buf.p, bytes, 99, bad);
+    CK(cudaMemset(buf.p + bytes / 2, out[bytes / 2] ^ 0xff, 1));
+    launchVerify(nullptr, buf.p, bytes, 99, bad);
+    unsigned long long h = 0;
+    CK(cudaMemcpy(&h, bad, 8, cudaMemcpyDeviceToHost));
+    EXPECT_EQ(h, 1ull);
+    cudaFree(bad);
+  }
+}

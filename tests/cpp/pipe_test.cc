@@ -375,3 +375,26 @@ TPB_TEST(Context, ServerPingPongTwice) {
         ctx->join();
       });
 }
+
+// The client dials the TCP address; the handshake then notices that both ends also have the
+// higher-priority shm transport and moves every connection of the pipe over to it.
+TPB_TEST(Pipe, UpgradesToShmTransport) {
+  auto msg = makeMessage(21, {64, 70000}, {1024, 5u << 20});
+  runPair([&](Pipe& p) {
+            expectSame(msg, readSync(p));
+            writeSync(p, msg.view(false));
+          },
+          [&](Pipe& p) {
+            writeSync(p, msg.view(false));
+            expectSame(msg, readSync(p));
+          },
+          {"uv://127.0.0.1", "shm://"}, true);
+}
+
+TPB_TEST(Pipe, ManyMessagesOverShm) {
+  constexpr int kN = 200;
+  auto msg = makeMessage(22, {256}, {4096});
+  runPair([&](Pipe& p) { for (int i = 0; i < kN; ++i) { expectSame(msg, readSync(p)); writeSync(p, msg.view(true)); } },
+          [&](Pipe& p) { for (int i = 0; i < kN; ++i) { writeSync(p, msg.view(true)); expectSame(msg, readSync(p)); } },
+          {"uv://127.0.0.1", "shm://"}, true);
+}

@@ -69,7 +69,34 @@ int main(int argc, char** argv) {
     std::cout << "[ RUN  ] " << t.name << std::endl;
     auto t0 = std::chrono::steady_clock::now();
     try {
-      t.fn();
+      if (gpu) {
+        // Each GPU test runs in a child so that this process never initialises CUDA (tests that
+        // fork peer processes need a CUDA-free parent) and one test's device state cannot leak
+        // into the next.
+        std::cout.flush();
+        pid_t pid = ::fork();
+        if (pid == 0) {
+          int rc = 0;
+          try {
+            t.fn();
+          } catch (const tpbtest::TestSkipped& e) {
+            std::cout << "  skipped: " << e.what() << std::endl;
+            rc = 77;
+          } catch (const std::exception& e) {
+            std::cout << "  " << e.what() << std::endl;
+            rc = 1;
+          }
+          std::cout.flush();
+          ::_exit(rc);
+        }
+        int st = 0;
+        ::waitpid(pid, &st, 0);
+        if (WIFEXITED(st) && WEXITSTATUS(st) == 77) throw tpbtest::TestSkipped("see above");
+        if (!WIFEXITED(st) || WEXITSTATUS(st) != 0)
+          throw tpbtest::TestFailure("child exited with status " + std::to_string(st));
+      } else {
+        t.fn();
+      }
       auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
       std::cout << "[  OK  ] " << t.name << " (" << ms << " ms)" << std::endl;
       ++passed;

@@ -1,0 +1,366 @@
+// Generic transport suite, instantiated for every transport (the approach of
+// tensorpipe/test/transport/*_test.cc: one body, every backend), plus backend-specific cases:
+// 16 MiB single frame on TCP, frames several times larger than the ring on shm, wrap-around.
+#include <tpb/transport.h>
+
+#include <random>
+
+#include "transport/nop_io.h"
+#include "core/nop_types.h"
+#include "test_util.h"
+
+using namespace tpb;
+using namespace tpbtest;
+
+namespace {
+
+struct Backend {
+  const char* name;
+  std::function<std::shared_ptr<transport::Context>()> make;
+  const char* listenAddr;
+};
+const Backend kBackends[] = {
+    {"uv", [] { return transport::uv::create(); }, "127.0.0.1"},
+    {"shm", [] { return transport::shm::create(); }, ""},
+};
+
+std::shared_ptr<transport::Connection> acceptSync(transport::Listener& l) {
+  std::promise<std::pair<Error, std::shared_ptr<transport::Connection>>> p;
+  l.accept([&](const Error& e, std::shared_ptr<transport::Connection> c) { p.set_value({e, std::move(c)}); });
+  auto f = p.get_future();
+  auto [e, c] = waitFor(f);
+  if (e) throw TestFailure("accept: " + e.what());
+  return c;
+}
+void writeSync(transport::Connection& c, const void* p, size_t n) {
+  std::promise<Error> pr;
+  c.write(p, n, [&](const Error& e) { pr.set_value(e); });
+  auto f = pr.get_future();
+  Error e = waitFor(f);
+  if (e) throw TestFailure("write: " + e.what());
+}
+std::vector<uint8_t> readSync(transport::Connection& c) {
+  std::promise<std::pair<Error, std::vector<uint8_t>>> pr;
+  c.read([&](const Error& e, const void* p, size_t n) {
+    std::vector<uint8_t> v;
+    if (!e) v.assign(static_cast<const uint8_t*>(p), static_cast<const uint8_t*>(p) + n);
+    pr.set_value({e, std::move(v)});
+  });
+  auto f = pr.get_future();
+  auto [e, v] = waitFor(f);
+  if (e) throw TestFailure("read: " + e.what());
+  return v;
+}
+std::vector<uint8_t> randomBytes(size_t n, uint32_t seed) {
+  std::vector<uint8_t> v(n);
+  std::mt19937 rng(seed);
+  for (auto& b : v) b = static_cast<uint8_t>(rng());
+  return v;
+}
+
+void forEachBackend(std::function<void(const Backend&)> body) {
+  for (const auto& b : kBackends) {
+    try {
+      body(b);
+    } catch (const TestFailure& e) {
+      throw TestFailure(std::string("[") + b.name + "] " + e.what());
+    }
+  }
+}
+
+void runPair(const Backend& b, std::function<void(transport::Connection&)> server,
+             std::function<void(transport::Connection&)> client) {
+  ThreadPeers peers;
+  peers.run(
+      [&](ThreadPeers& pg) {
+        auto ctx = b.make();
+        auto l = ctx->listen(b.listenAddr);
+        pg.sendToClient(l->addr());
+        auto c = acceptSync(*l);
+        server(*c);
+        pg.recvFromClient();
+        ctx->join();
+      },
+      [&](ThreadPeers& pg) {
+        auto ctx = b.make();
+        auto c = ctx->connect(pg.recvFromServer());
+        client(*c);
+        pg.sendToServer("done");
+        ctx->join();
+      });
+}
+
+}  // namespace
+
+TPB_TEST(Transport, ContextBasicsAndDomainDescriptor) {
+  forEachBackend([](const Backend& b) {
+    auto c1 = b.make();
+    auto c2 = b.make();
+    EXPECT_TRUE(c1->isViable());
+    EXPECT_FALSE(c1->domainDescriptor().empty());
+    EXPECT_TRUE(c1->canCommunicateWithRemote(c2->domainDescriptor()));
+    EXPECT_FALSE(c1->canCommunicateWithRemote("something else"));
+    c1->join();
+    c2->join();
+  });
+}
+
+TPB_TEST(Transport, ConnectionPingPong) {
+  forEachBackend([](const Backend& b) {
+    auto ping = randomBytes(1000, 1), pong = randomBytes(77, 2);
+    runPair(
+        b,
+        [&](transport::Connection& c) {
+          EXPECT_TRUE(readSync(c) == ping);
+          writeSync(c, pong.data(), pong.size());
+        },
+        [&](transport::Connection& c) {
+          writeSync(c, ping.data(), ping.size());
+          EXPECT_TRUE(readSync(c) == pong);
+        });
+  });
+}
+
+TPB_TEST(Transport, ZeroLengthFrameIsANotification) {
+  forEachBackend([](const Backend& b) {
+    runPair(
+        b, [&](transport::Connection& c) { EXPECT_EQ(readSync(c).size(), size_t(0)); },
+        [&](transport::Connection& c) { writeSync(c, nullptr, 0); });
+  });
+}
+
+TPB_TEST(Transport, NopObjectRoundTrip) {
+  forEachBackend([](const Backend& b) {
+    runPair(
+        b,
+        [&](transport::Connection& c) {
+          std::promise<std::pair<Error, Packet>> pr;
+          transport::readNop<Packet>(c, [&](const Error& e, Packet p) { pr.set_value({e, p}); });
+          auto f = pr.get_future();
+          auto [e, p] = waitFor(f);
+          EXPECT_FALSE(bool(e));
+          EXPECT_EQ(std::get<RequestedConnection>(p).registrationId, uint64_t(424242));
+        },
+        [&](transport::Connection& c) {
+          std::promise<Error> pr;
+          Packet p = RequestedConnection{424242};
+          transport::writeNop(c, p, [&](const Error& e) { pr.set_value(e); });
+          auto f = pr.get_future();
+          EXPECT_FALSE(bool(waitFor(f)));
+        });
+  });
+}
+
+TPB_TEST(Transport, QueueWritesBeforeReadsKeepsOrder) {
+  forEachBackend([](const Backend& b) {
+    constexpr int kN = 200;
+    runPair(
+        b,
+        [&](transport::Connection& c) {
+          for (int i = 0; i < kN; ++i) {
+            auto v = readSync(c);
+            EXPECT_EQ(v.size(), size_t(100 + i));
+            EXPECT_EQ(int(v[0]), i & 0xff);
+          }
+        },
+        [&](transport::Connection& c) {
+          std::vector<std::vector<uint8_t>> bufs;
+          std::atomic<int> done{0};
+          std::promise<void> all;
+          for (int i = 0; i < kN; ++i) bufs.emplace_back(100 + i, static_cast<uint8_t>(i));
+          for (int i = 0; i < kN; ++i)
+            c.write(bufs[i].data(), bufs[i].size(), [&](const Error& e) {
+              if (e) return;
+              if (++done == kN) all.set_value();
+            });
+          auto f = all.get_future();
+          waitFor(f);
+        });
+  });
+}
+
+TPB_TEST(Transport, LargeFrameAndChunking) {
+  // 16 MiB: one frame on TCP; eight times the ring on shm, so it travels in pieces while the
+  // reader drains (with and without a caller-provided buffer).
+  forEachBackend([](const Backend& b) {
+    auto big = randomBytes(16u << 20, 7);
+    runPair(
+        b,
+        [&](transport::Connection& c) {
+          EXPECT_TRUE(readSync(c) == big);
+          std::vector<uint8_t> into(big.size());
+          std::promise<Error> pr;
+          c.read(into.data(), into.size(), [&](const Error& e, const void*, size_t) { pr.set_value(e); });
+          auto f = pr.get_future();
+          EXPECT_FALSE(bool(waitFor(f)));
+          EXPECT_TRUE(into == big);
+        },
+        [&](transport::Connection& c) {
+          writeSync(c, big.data(), big.size());
+          writeSync(c, big.data(), big.size());
+        });
+  });
+}
+
+TPB_TEST(Transport, ManySmallFramesWrapTheRing) {
+  // 3 MiB of 1000-byte frames wraps a 2 MiB ring more than once, headers straddling the edge.
+  forEachBackend([](const Backend& b) {
+    constexpr int kN = 3000;
+    auto payload = randomBytes(1000, 3);
+    runPair(
+        b,
+        [&](transport::Connection& c) {
+          for (int i = 0; i < kN; ++i) EXPECT_TRUE(readSync(c) == payload);
+        },
+        [&](transport::Connection& c) {
+          for (int i = 0; i < kN; ++i) writeSync(c, payload.data(), payload.size());
+        });
+  });
+}
+
+TPB_TEST(Transport, ListenerQueuesAcceptCallbacksAndConnections) {
+  forEachBackend([](const Backend& b) {
+    auto ctx = b.make();
+    auto l = ctx->listen(b.listenAddr);
+    // Two accepts armed before anyone connects...
+    std::promise<Error> a1, a2;
+    std::shared_ptr<transport::Connection> s1, s2;
+    l->accept([&](const Error& e, std::shared_ptr<transport::Connection> c) { s1 = c; a1.set_value(e); });
+    l->accept([&](const Error& e, std::shared_ptr<transport::Connection> c) { s2 = c; a2.set_value(e); });
+    auto c1 = ctx->connect(l->addr());
+    auto c2 = ctx->connect(l->addr());
+    auto f1 = a1.get_future(), f2 = a2.get_future();
+    EXPECT_FALSE(bool(waitFor(f1)));
+    EXPECT_FALSE(bool(waitFor(f2)));
+    // ...and a connection made before its accept is armed waits in the backlog.
+    auto c3 = ctx->connect(l->addr());
+    std::this_thread::sleep_for(std::chrono::milliseconds(20));
+    auto s3 = acceptSync(*l);
+    EXPECT_TRUE(s3 != nullptr);
+    ctx->join();
+  });
+}
+
+TPB_TEST(Transport, CloseFailsPendingOperationsAndPeerSeesEof) {
+  forEachBackend([](const Backend& b) {
+    runPair(
+        b,
+        [&](transport::Connection& c) {
+          std::promise<Error> pr;
+          c.read([&](const Error& e, const void*, size_t) { pr.set_value(e); });
+          c.close();
+          auto f = pr.get_future();
+          EXPECT_TRUE(waitFor(f).isOfType<transport::ConnectionClosedError>());
+        },
+        [&](transport::Connection& c) {
+          std::promise<Error> pr;
+          c.read([&](const Error& e, const void*, size_t) { pr.set_value(e); });
+          auto f = pr.get_future();
+          Error e = waitFor(f);
+          EXPECT_TRUE(bool(e));  // EOF (or a reset on TCP)
+        });
+  });
+}
+
+TPB_TEST(Transport, ConnectToNobodyFails) {
+  auto ctx = transport::uv::create();
+  auto c = ctx->connect("127.0.0.1:1");
+  std::promise<Error> pr;
+  c->read([&](const Error& e, const void*, size_t) { pr.set_value(e); });
+  auto f = pr.get_future();
+  EXPECT_TRUE(bool(waitFor(f)));
+  ctx->join();
+
+  auto sctx = transport::shm::create();
+  auto sc = sctx->connect("tpb-nobody-listens-here");
+  std::promise<Error> pr2;
+  sc->read([&](const Error& e, const void*, size_t) { pr2.set_value(e); });
+  auto f2 = pr2.get_future();
+  EXPECT_TRUE(bool(waitFor(f2)));
+  sctx->join();
+}
+
+TPB_TEST(Transport, CallbacksAreNeverInline) {
+  // A mutex held across the call and taken in the callback deadlocks if the callback is inline.
+  forEachBackend([](const Backend& b) {
+    auto ctx = b.make();
+    auto l = ctx->listen(b.listenAddr);
+    auto c = ctx->connect(l->addr());
+    auto s = acceptSync(*l);
+    std::mutex m;
+    std::promise<void> done;
+    {
+      std::unique_lock<std::mutex> lock(m);
+      s->close();
+      s->read([&](const Error&, const void*, size_t) {
+        std::unique_lock<std::mutex> inner(m);
+        done.set_value();
+      });
+      std::this_thread::sleep_for(std::chrono::milliseconds(5));
+    }
+    auto f = done.get_future();
+    waitFor(f);
+    ctx->join();
+  });
+}
+
+TPB_TEST(Transport, ListenerAfterContextCloseFailsAccept) {
+  forEachBackend([](const Backend& b) {
+    auto ctx = b.make();
+    ctx->close();
+    auto l = ctx->listen(b.listenAddr);
+    EXPECT_FALSE(l->addr().empty() && std::string(b.name) == "uv");
+    std::promise<Error> pr;
+    l->accept([&](const Error& e, std::shared_ptr<transport::Connection>) { pr.set_value(e); });
+    auto f = pr.get_future();
+    EXPECT_TRUE(bool(waitFor(f)));
+    ctx->join();
+  });
+}
+
+TPB_TEST(TransportShm, PeerProcessDeathIsDetected) {
+  // A peer that is killed (no goodbye) must surface as an error on the survivor's pending read.
+  ProcessPeers::run(
+      [](const ProcessPeers::Side& me) {
+        auto ctx = transport::shm::create();
+        auto l = ctx->listen("");
+        me.send(l->addr());
+        auto c = acceptSync(*l);
+        EXPECT_EQ(readSync(*c).size(), size_t(3));
+        std::promise<Error> pr;
+        c->read([&](const Error& e, const void*, size_t) { pr.set_value(e); });
+        me.send("kill yourself");
+        auto f = pr.get_future();
+        Error e = waitFor(f);
+        EXPECT_TRUE(e.isOfType<EOFError>());
+        ctx->join();
+      },
+      [](const ProcessPeers::Side& me) {
+        auto ctx = transport::shm::create();
+        auto c = ctx->connect(me.recv());
+        writeSync(*c, "abc", 3);
+        me.recv();
+        ::_exit(0);  // die without closing anything
+      });
+}
+
+TPB_TEST(TransportUv, AddressHelpers) {
+  auto [e, addr] = transport::tcp::lookupAddrForIface("lo");
+  EXPECT_FALSE(bool(e));
+  EXPECT_EQ(addr, std::string("127.0.0.1"));
+  auto [e2, addr2] = transport::tcp::lookupAddrForIface("no-such-iface0");
+  EXPECT_TRUE(e2.isOfType<transport::NoAddrFoundError>());
+  // IPv6 loopback listen + connect.
+  auto ctx = transport::uv::create();
+  try {
+    auto l = ctx->listen("[::1]");
+    EXPECT_TRUE(l->addr().rfind("[::1]:", 0) == 0);
+    auto c = ctx->connect(l->addr());
+    auto s = acceptSync(*l);
+    writeSync(*c, "x", 1);
+    EXPECT_EQ(readSync(*s).size(), size_t(1));
+  } catch (const std::system_error&) {
+    // no IPv6 on this machine: nothing to check
+  }
+  ctx->join();
+}

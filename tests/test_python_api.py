@@ -1,0 +1,105 @@
+"""Python API tests: torch-tensor messages over CPU channels here, CUDA channels under -m gpu.
+(The reference's only Python test is a CPU read/write, tensorpipe/test/python/tensorpipe.py:14-83.)"""
+import threading
+
+import pytest
+import torch
+
+import tensorpipe_b200 as tpb
+
+
+def connected_pair(**kw):
+    a = tpb.default_context("a", **kw)
+    b = tpb.default_context("b", **kw)
+    listener = a.listen(["uv://127.0.0.1", "shm://"])
+    fut = listener.accept_future()
+    out_pipe = b.connect(listener.url("uv"), remote_name="a")
+    in_pipe = fut.result(30)
+    return a, b, listener, out_pipe, in_pipe
+
+
+def test_cpu_message_round_trip(built):
+    a, b, listener, out_pipe, in_pipe = connected_pair(cuda=False)
+    x = torch.randn(1000, 10)
+    y = torch.arange(12).reshape(3, 4).t()  # non-contiguous: made contiguous on the way
+    sent = out_pipe.send([x, y], payloads=[b"hello", bytearray(b"xyz")], metadata=b"meta")
+    msg = in_pipe.recv().result(30)
+    sent.result(30)
+    assert msg.metadata == b"meta"
+    assert [bytes(p) for p in msg.payloads] == [b"hello", b"xyz"]
+    assert torch.equal(msg.tensors[0], x) and torch.equal(msg.tensors[1], y)
+    assert in_pipe.remote_name == "b" and out_pipe.remote_name == "a"
+    stats = a.stats()
+    assert stats["messages_read"] == 1 and stats["tensor_bytes_received"] == x.numel() * 4 + 12 * 8
+    a.join()
+    b.join()
+
+
+def test_callbacks_are_ordered_and_errors_reach_python(built):
+    a, b, listener, out_pipe, in_pipe = connected_pair(cuda=False)
+    order = []
+    done = threading.Event()
+    n = 20
+    for i in range(n):
+        def cb(err, i=i):
+            order.append((i, err))
+            if len(order) == n:
+                done.set()
+        out_pipe.write(tpb.Message([torch.full((100,), float(i))]), cb)
+    for i in range(n):
+        msg = in_pipe.recv().result(30)
+        assert float(msg.tensors[0][0]) == float(i)
+    assert done.wait(30)
+    assert order == [(i, "") for i in range(n)]
+    # After close every pending callback fires with an error string.
+    fut = in_pipe.recv()
+    in_pipe.close()
+    with pytest.raises(RuntimeError):
+        fut.result(30)
+    a.join()
+    b.join()
+
+
+def test_mpt_lanes_carry_tensors(built):
+    a = tpb.Context("a")
+    b = tpb.Context("b")
+    for ctx in (a, b):
+        ctx.register_transport(0, "uv", tpb._C.create_uv_transport())
+        ctx.register_channel(0, "mpt_uv", tpb._C.create_mpt_channel(3))
+    listener = a.listen(["uv://127.0.0.1"])
+    fut = listener.accept_future()
+    out_pipe = b.connect(listener.url("uv"))
+    in_pipe = fut.result(30)
+    x = torch.randn(1_000_003)
+    sent = out_pipe.send([x])
+    msg = in_pipe.recv().result(30)
+    sent.result(30)
+    assert torch.equal(msg.tensors[0], x)
+    assert a.stats()["bytes_per_channel"] == {"mpt_uv": x.numel() * 4}
+    a.join()
+    b.join()
+
+
+@pytest.mark.gpu
+def test_cuda_tensors_views_and_casts(built):
+    a, b, listener, out_pipe, in_pipe = connected_pair()
+    x = torch.randn(513, 257, device="cuda")
+    y = torch.randn(100, 64, device="cuda", dtype=torch.bfloat16).t()
+    z = torch.arange(1000, device="cuda")
+    sent = out_pipe.send([x, y, z], payloads=[b"p"], target_devices=["cuda:0"] * 3)
+    msg = in_pipe.recv(cast={0: torch.bfloat16}).result(30)
+    sent.result(30)
+    torch.cuda.synchronize()
+    assert torch.equal(msg.tensors[0], x.to(torch.bfloat16))
+    assert torch.equal(msg.tensors[1], y)
+    assert torch.equal(msg.tensors[2], z)
+    assert a.stats()["bytes_per_channel"].get("cuda_p2p", 0) > 0
+    assert tpb.kernel_launch_count() > 0
+    a.join()
+    b.join()
+
+
+@pytest.mark.gpu
+def test_smoke_entry_point(built):
+    import __graft_entry__
+    __graft_entry__.smoke()

@@ -749,8 +749,10 @@ void ChannelImpl::sendReady(RecvOp& op) {
         void* base = nullptr;
         size_t size = 0;
         unsigned long long id = 0;
+        // The driver queries below need this device's context current on the calling thread,
+        // which may be a transport thread that never touched CUDA.
+        CudaDeviceGuard g(op.device);
         if (cudaAllocationInfo(ptr, &base, &size, &id)) {
-          CudaDeviceGuard g(op.device);
           cudaIpcMemHandle_t h;
           cudaError_t e = cudaIpcGetMemHandle(&h, base);
           if (e == cudaSuccess) {

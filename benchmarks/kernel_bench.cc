@@ -1,0 +1,166 @@
+// Micro-benchmark of the push/pack kernel on one GPU, without any pipe around it: HBM -> HBM copy
+// bandwidth for several shapes of the TMA bulk pipeline, the register (plain) path, conversion and
+// strided packing, against cudaMemcpyAsync device-to-device as the yardstick the reference's
+// channels use (tensorpipe/channel/cuda_xth/channel_impl.cc:66-77). Timed with CUDA events after
+// warm-up; buffers larger than L2; prints one line per case.
+//
+//   kernel_bench [--bytes N] [--iters K] [--case substring]
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "common/cuda.h"
+#include "kernels/push.h"
+
+using namespace tpb;
+using namespace tpb::kernels;
+
+#define CK(x) TPB_CUDA_CHECK(x)
+
+struct Timer {
+  cudaEvent_t a, b;
+  Timer() {
+    CK(cudaEventCreate(&a));
+    CK(cudaEventCreate(&b));
+  }
+  template <typename F>
+  double run(int warm, int iters, F&& f) {
+    for (int i = 0; i < warm; ++i) f();
+    CK(cudaDeviceSynchronize());
+    CK(cudaEventRecord(a));
+    for (int i = 0; i < iters; ++i) f();
+    CK(cudaEventRecord(b));
+    CK(cudaEventSynchronize(b));
+    float ms = 0;
+    CK(cudaEventElapsedTime(&ms, a, b));
+    return ms / iters;
+  }
+};
+
+int main(int argc, char** argv) {
+  size_t bytes = 1ull << 30;
+  int iters = 20;
+  std::string only;
+  for (int i = 1; i + 1 < argc; i += 2) {
+    std::string k = argv[i];
+    if (k == "--bytes") bytes = std::strtoull(argv[i + 1], nullptr, 10);
+    else if (k == "--iters") iters = std::atoi(argv[i + 1]);
+    else if (k == "--case") only = argv[i + 1];
+  }
+  CK(cudaSetDevice(0));
+  int sms = cudaSmCount(0);
+  uint8_t *src, *dst;
+  CK(cudaMalloc(&src, bytes + 256));
+  CK(cudaMalloc(&dst, bytes + 256));
+  CK(cudaMemset(src, 1, bytes + 256));
+  CK(cudaMemset(dst, 2, bytes + 256));
+  uint32_t* words;
+  CK(cudaMalloc(&words, 256));
+  CK(cudaMemset(words, 0, 256));
+  Timer timer;
+  auto report = [&](const std::string& name, size_t movedBytes, double ms) {
+    std::printf("%-44s %10.1f us  %8.1f GB/s payload  %8.1f GB/s read+write\n", name.c_str(), ms * 1e3,
+                movedBytes / (ms * 1e-3) / 1e9, 2.0 * movedBytes / (ms * 1e-3) / 1e9);
+    std::fflush(stdout);
+  };
+  auto want = [&](const std::string& name) { return only.empty() || name.find(only) != std::string::npos; };
+
+  if (want("memcpy")) {
+    double ms = timer.run(3, iters, [&] { CK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, nullptr)); });
+    report("cudaMemcpyAsync D2D", bytes, ms);
+  }
+  struct Shape {
+    uint32_t tile, stages;
+  };
+  for (Shape sh : {Shape{16384, 4}, Shape{16384, 8}, Shape{32768, 2}, Shape{32768, 3}, Shape{32768, 4},
+                   Shape{49152, 3}, Shape{65536, 2}, Shape{24576, 6}}) {
+    char name[96];
+    std::snprintf(name, sizeof(name), "bulk tile=%uK stages=%u", sh.tile / 1024, sh.stages);
+    if (!want(name) && !want("bulk")) continue;
+    PushTuning t;
+    t.bulkTileBytes = sh.tile;
+    t.bulkStages = sh.stages;
+    setPushTuning(t);
+    for (int ctas : {sms, sms / 2}) {
+      PushPlan plan;
+      CopyItem it;
+      it.src = src;
+      it.dst = dst;
+      it.srcBytes = bytes;
+      appendToPlan(plan, it, true);
+      double ms = timer.run(3, iters, [&] { launchPush(plan, nullptr, ctas, words, 1, words + 16, nullptr); });
+      report(std::string(name) + " ctas=" + std::to_string(ctas), bytes, ms);
+    }
+  }
+  setPushTuning(PushTuning());
+  if (want("plain")) {
+    PushPlan plan;
+    CopyItem it;
+    it.src = src;
+    it.dst = dst;
+    it.srcBytes = bytes;
+    appendToPlan(plan, it, false);
+    double ms = timer.run(3, iters, [&] { launchPush(plan, nullptr, sms, words, 1, words + 16, nullptr); });
+    report("plain ld/st (light kernel)", bytes, ms);
+    PushPlan skew;
+    it.src = src + 4;
+    it.dst = dst + 8;
+    appendToPlan(skew, it, true);
+    ms = timer.run(3, iters, [&] { launchPush(skew, nullptr, sms, nullptr, 0, nullptr, nullptr); });
+    report("plain, relatively misaligned by 4 bytes", bytes, ms);
+  }
+  if (want("cast")) {
+    PushPlan plan;
+    CopyItem it;
+    it.src = src;
+    it.dst = dst;
+    it.srcBytes = bytes;
+    it.srcDtype = DType::kF32;
+    it.dstDtype = DType::kBF16;
+    appendToPlan(plan, it, true);
+    double ms = timer.run(3, iters, [&] { launchPush(plan, nullptr, sms, nullptr, 0, nullptr, nullptr); });
+    std::printf("%-44s %10.1f us  %8.1f GB/s read, %8.1f GB/s read+write\n", "cast fp32 -> bf16", ms * 1e3,
+                bytes / (ms * 1e-3) / 1e9, 1.5 * bytes / (ms * 1e-3) / 1e9);
+  }
+  if (want("strided")) {
+    for (size_t es : {size_t(2), size_t(4), size_t(8)}) {
+      const int64_t cols = 4096;
+      const int64_t rows = static_cast<int64_t>(bytes / es / cols);
+      PushPlan plan;
+      CopyItem it;
+      it.src = src;
+      it.dst = dst;
+      it.srcBytes = static_cast<uint64_t>(rows) * cols * es;
+      it.strided = true;
+      it.view = StridedView{es == 2 ? DType::kBF16 : es == 4 ? DType::kF32 : DType::kI64, rows, cols, 1, rows};
+      it.srcDtype = it.dstDtype = it.view.dtype;
+      appendToPlan(plan, it, true);
+      double ms = timer.run(2, iters / 2 + 1, [&] { launchPush(plan, nullptr, sms, nullptr, 0, nullptr, nullptr); });
+      report("transposed view, " + std::to_string(es) + "-byte elements", it.srcBytes, ms);
+    }
+  }
+  if (want("small")) {
+    // Launch-bound regime: back-to-back launches of a 4 KiB copy.
+    for (bool bulk : {false, true}) {
+      PushTuning t;
+      t.bulkMinBytes = bulk ? 1024 : 512 * 1024;
+      setPushTuning(t);
+      PushPlan plan;
+      CopyItem it;
+      it.src = src;
+      it.dst = dst;
+      it.srcBytes = 4096;
+      appendToPlan(plan, it, true);
+      double ms = timer.run(20, 200, [&] { launchPush(plan, nullptr, sms, words, 1, words + 16, nullptr); });
+      report(bulk ? "4 KiB, full kernel (bulk path)" : "4 KiB, light kernel", 4096, ms);
+    }
+    setPushTuning(PushTuning());
+    double ms = timer.run(20, 200, [&] { CK(cudaMemcpyAsync(dst, src, 4096, cudaMemcpyDeviceToDevice, nullptr)); });
+    report("4 KiB, cudaMemcpyAsync D2D", 4096, ms);
+  }
+  return 0;
+}

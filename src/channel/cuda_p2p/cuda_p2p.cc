@@ -24,6 +24,13 @@
 //                R       waits for the flag, unpacks inbox -> tensors (applying casts), later
 //                        returns the ring space with Credit{}
 //
+// Which batches go eager is a rule both ends evaluate identically, so the receiver never sends a
+// RecvReady for them: a batch is eager iff it is no larger than the receiver's eager threshold
+// and comes after the batch whose RecvReady announced the receiver's arena for that device.
+// Sends launch strictly in order, which is what makes "after" well defined on the sender. A sender
+// without inbox credits waits for a Credit, which the receiver returns as soon as its unpack
+// kernel has finished (a poller thread watches the event).
+//
 // Why the receiver only enqueues a wait after Launched arrived: a wait placed on a stream before
 // the matching push exists could end up ahead of a push that the peer is itself waiting for (both
 // sides using one stream for sends and receives) and dead-lock the two GPUs. With this rule every
@@ -43,6 +50,7 @@
 #include "common/defs.h"
 #include "common/loop.h"
 #include "common/nop.h"
+#include "common/poller.h"
 #include "common/system.h"
 #include "kernels/push.h"
 #include "transport/nop_io.h"
@@ -83,7 +91,8 @@ struct TargetWire {
 struct ArenaWire {
   Handle handle{};
   uint64_t inboxBytes = 0;
-  TPB_NOP_STRUCTURE(ArenaWire, handle, inboxBytes)
+  uint64_t eagerThreshold = 0;  // the receiver owns the inbox, so it sets the limit
+  TPB_NOP_STRUCTURE(ArenaWire, handle, inboxBytes, eagerThreshold)
 };
 
 struct RecvReady {
@@ -110,7 +119,14 @@ struct Credit {
   TPB_NOP_STRUCTURE(Credit, deviceIdx, value)
 };
 
-using Packet = std::variant<RecvReady, Launched, Credit>;
+// A sender that ran out of inbox space asks for credits; until then the receiver returns them
+// opportunistically (whenever it handles something else) and keeps its poller thread idle.
+struct CreditRequest {
+  int32_t deviceIdx = 0;
+  TPB_NOP_STRUCTURE(CreditRequest, deviceIdx)
+};
+
+using Packet = std::variant<RecvReady, Launched, Credit, CreditRequest>;
 
 std::string processIdentity() {
   auto boot = getBootID();
@@ -155,7 +171,7 @@ struct Arena {
   uint8_t* base = nullptr;  // cudaMalloc'ed: [4 KiB flags/counter/status][inbox]
   size_t inboxBytes = 0;
   Handle handle{};
-  bool announced = false;  // told the peer about it
+  int64_t announcedSeq = -1;  // receive batch whose RecvReady told the peer about this arena
   uint32_t* flag(uint64_t seq) const { return reinterpret_cast<uint32_t*>(base) + (seq % kFlagSlots); }
   // One arrive counter per launching stream: launches on different streams may overlap.
   uint32_t* counter(cudaStream_t s) {
@@ -176,6 +192,9 @@ struct PeerArena {  // the peer's arena for one of ITS devices, mapped here
   uint8_t* base = nullptr;
   size_t inboxBytes = 0;
   uint64_t head = 0, tail = 0;  // inbox ring cursors (bytes, free-running)
+  int64_t announcedSeq = -1;
+  uint64_t eagerThreshold = 0;
+  bool creditRequested = false;
   uint32_t* flag(uint64_t seq) const { return reinterpret_cast<uint32_t*>(base) + (seq % kFlagSlots); }
   uint8_t* inbox() const { return base + kFlagsBytes; }
 };
@@ -196,6 +215,7 @@ struct RecvOp {
   int device = -1;
   std::vector<RecvItem> items;
   bool readySent = false;
+  bool expectEager = false;
   std::optional<Launched> notice;
 };
 
@@ -240,8 +260,14 @@ class ChannelImpl final : public Channel, public std::enable_shared_from_this<Ch
   void onHello(const std::string& peerIdentity);
   void sendBatchFromLoop(std::vector<SendItem> items);
   void recvBatchFromLoop(std::vector<RecvItem> items);
-  void tryLaunch(SendOp& op);
-  bool tryEager(SendOp& op);
+  void pumpSends();
+  bool tryLaunch(SendOp& op);
+  enum class Eager { kNotEligible, kLaunched, kNoCredits };
+  Eager tryEager(SendOp& op);
+  uint64_t alignedTotal(const std::vector<SendItem>& items) const;
+  std::unique_ptr<CudaEvent> takeEvent(int device);
+  void watchLastCredit();
+  bool creditWanted_ = false;
   void launchRendezvous(SendOp& op);
   void finishSend(SendOp& op, const Error& e);
   void sendReady(RecvOp& op);
@@ -276,6 +302,7 @@ class ChannelImpl final : public Channel, public std::enable_shared_from_this<Ch
   std::deque<PendingCredit> pendingCredits_;
   // Events handed to the peer (same process) must outlive their use.
   std::deque<std::unique_ptr<CudaEvent>> eventPool_;
+  std::map<int, std::vector<std::unique_ptr<CudaEvent>>> freeEvents_;  // recycled credit events
   std::vector<std::pair<uint32_t*, uint32_t>> enqueuedWaits_;  // for cancellation on error
 };
 
@@ -345,7 +372,10 @@ class ContextImpl final : public Context, public std::enable_shared_from_this<Co
   void join() override {
     close();
     loop_.runInLoop([]() {});
+    poller_.stop();
+    loop_.runInLoop([]() {});
   }
+  Poller poller_;
   void enroll(std::weak_ptr<ChannelImpl> c) { channels_.insert(std::move(c)); }
   void unenroll(const std::weak_ptr<ChannelImpl>& c) { channels_.erase(c); }
   bool closed() const { return closed_; }
@@ -409,9 +439,8 @@ void ChannelImpl::onHello(const std::string& peer) {
   TPB_VLOG(4) << "Channel " << id_ << " peer " << peer << (sameProcess_ ? " (same process)" : " (other process)");
   armRead();
   for (size_t i = 0; i < recvOps_.size() && !error_; ++i)
-    if (!recvOps_[i].readySent && !recvOps_[i].notice) sendReady(recvOps_[i]);
-  for (size_t i = 0; i < sendOps_.size() && !error_; ++i) tryLaunch(sendOps_[i]);
-  while (!sendOps_.empty() && sendOps_.front().launched) sendOps_.pop_front();
+    if (!recvOps_[i].readySent && !recvOps_[i].notice && !recvOps_[i].expectEager) sendReady(recvOps_[i]);
+  pumpSends();
 }
 
 void ChannelImpl::armRead() {
@@ -518,33 +547,62 @@ void ChannelImpl::sendBatchFromLoop(std::vector<SendItem> items) {
       earlyReady_.erase(early);
     }
     sendOps_.push_back(std::move(op));
-    tryLaunch(sendOps_.back());
   }
-  while (!sendOps_.empty() && sendOps_.front().launched) sendOps_.pop_front();
+  pumpSends();
 }
 
-void ChannelImpl::tryLaunch(SendOp& op) {
-  if (op.launched || error_ || !helloDone_) return;
+// Sends launch strictly in order: the first batch that cannot go yet (no RecvReady, or no inbox
+// credits) holds back the ones behind it.
+void ChannelImpl::pumpSends() {
+  while (!error_ && helloDone_ && !sendOps_.empty()) {
+    SendOp& op = sendOps_.front();
+    if (!op.launched && !tryLaunch(op)) break;
+    if (error_ || sendOps_.empty()) break;
+    sendOps_.pop_front();
+  }
+}
+
+bool ChannelImpl::tryLaunch(SendOp& op) {
   try {
-    if (op.ready) return launchRendezvous(op);
-    if (!sameProcess_ && tryEager(op)) return;
+    if (!sameProcess_) {
+      Eager e = tryEager(op);
+      if (e == Eager::kLaunched) return true;
+      if (e == Eager::kNoCredits) return false;
+    }
+    if (!op.ready) return false;
+    launchRendezvous(op);
+    return !error_;
   } catch (const std::exception& ex) {
     closeFromLoop(TPB_CREATE_ERROR(CudaError, ex.what()));
+    return false;
   }
 }
 
-bool ChannelImpl::tryEager(SendOp& op) {
-  if (opts_.eagerThreshold == 0) return false;
-  auto pa = peerArenas_.find(op.targetDevice.index);
-  if (pa == peerArenas_.end()) return false;
-  PeerArena& peer = pa->second;
+uint64_t ChannelImpl::alignedTotal(const std::vector<SendItem>& items) const {
   uint64_t total = 0;
-  for (auto& it : op.items) total += (it.length + kInboxAlign - 1) / kInboxAlign * kInboxAlign;
-  if (total > opts_.eagerThreshold || total > peer.inboxBytes / 2) return false;
+  for (auto& it : items) total += (it.length + kInboxAlign - 1) / kInboxAlign * kInboxAlign;
+  return total;
+}
+
+ChannelImpl::Eager ChannelImpl::tryEager(SendOp& op) {
+  auto pa = peerArenas_.find(op.targetDevice.index);
+  if (pa == peerArenas_.end()) return Eager::kNotEligible;
+  PeerArena& peer = pa->second;
+  const uint64_t total = alignedTotal(op.items);
+  // The rule the receiver evaluates too (see the top of this file).
+  if (static_cast<int64_t>(op.seq) <= peer.announcedSeq || total > peer.eagerThreshold) return Eager::kNotEligible;
   const uint64_t cap = peer.inboxBytes;
   const uint64_t pos = peer.head % cap;
   const uint64_t skip = pos + total > cap ? cap - pos : 0;
-  if (peer.head + skip + total - peer.tail > cap) return false;  // no credits: use rendezvous
+  if (peer.head + skip + total - peer.tail > cap) {
+    if (!peer.creditRequested) {
+      peer.creditRequested = true;
+      CreditRequest req;
+      req.deviceIdx = op.targetDevice.index;
+      writePacket(req);
+    }
+    return Eager::kNoCredits;  // wait for a Credit
+  }
   const uint64_t offset = (peer.head + skip) % cap;
   peer.head += skip + total;
 
@@ -552,7 +610,7 @@ bool ChannelImpl::tryEager(SendOp& op) {
   Arena* mine = arenaFor(op.srcDevice, err);
   if (!mine) {
     closeFromLoop(err);
-    return true;
+    return Eager::kLaunched;
   }
   CudaDeviceGuard g(op.srcDevice);
   kernels::PushPlan plan;
@@ -582,7 +640,7 @@ bool ChannelImpl::tryEager(SendOp& op) {
   l.creditValue = peer.head;
   writePacket(l);
   finishSend(op, Error::kSuccess);
-  return true;
+  return Eager::kLaunched;
 }
 
 void ChannelImpl::launchRendezvous(SendOp& op) {
@@ -600,6 +658,8 @@ void ChannelImpl::launchRendezvous(SendOp& op) {
       PeerArena pa;
       pa.base = static_cast<uint8_t*>(base);
       pa.inboxBytes = ready.arena->inboxBytes;
+      pa.eagerThreshold = std::min<uint64_t>(ready.arena->eagerThreshold, ready.arena->inboxBytes / 2);
+      pa.announcedSeq = static_cast<int64_t>(ready.seq);
       peerArenas_[ready.deviceIdx] = pa;
     }
     auto it = peerArenas_.find(ready.deviceIdx);
@@ -710,10 +770,19 @@ void ChannelImpl::recvBatchFromLoop(std::vector<RecvItem> items) {
       op.notice = std::move(early->second);
       earlyLaunched_.erase(early);
     }
+    // Same rule as the sender's: small batches after the arena announcement arrive eagerly.
+    if (!sameProcess_) {
+      auto a = arenas_.find(op.device);
+      uint64_t total = 0;
+      for (auto& it : op.items) total += (it.length + kInboxAlign - 1) / kInboxAlign * kInboxAlign;
+      const uint64_t threshold = std::min<uint64_t>(opts_.eagerThreshold, opts_.inboxBytes / 2);
+      op.expectEager = a != arenas_.end() && a->second.announcedSeq >= 0 &&
+          static_cast<int64_t>(op.seq) > a->second.announcedSeq && total <= threshold;
+    }
     recvOps_.push_back(std::move(op));
     RecvOp& ref = recvOps_.back();
     if (ref.notice) completeRecv(ref);
-    else if (helloDone_) sendReady(ref);
+    else if (helloDone_ && !ref.expectEager) sendReady(ref);
   }
   while (!recvOps_.empty() && recvOps_.front().items.empty()) recvOps_.pop_front();
 }
@@ -728,12 +797,13 @@ void ChannelImpl::sendReady(RecvOp& op) {
       Error err;
       Arena* a = arenaFor(op.device, err);
       if (!a) return closeFromLoop(err);
-      if (!a->announced) {
+      if (a->announcedSeq < 0) {
         ArenaWire w;
         w.handle = a->handle;
         w.inboxBytes = a->inboxBytes;
+        w.eagerThreshold = opts_.eagerThreshold;
         r.arena = w;
-        a->announced = true;
+        a->announcedSeq = static_cast<int64_t>(op.seq);
       }
     }
     for (auto& it : op.items) {
@@ -823,11 +893,12 @@ void ChannelImpl::completeRecv(RecvOp& op) {
         const int ctas = opts_.maxCtas > 0 ? opts_.maxCtas : cudaSmCount(op.device);
         kernels::launchPush(plan, stream, ctas, nullptr, 0, nullptr, nullptr);
         PendingCredit pc;
-        pc.done = std::make_unique<CudaEvent>(op.device);
+        pc.done = takeEvent(op.device);
         pc.done->record(stream);
         pc.device = op.device;
         pc.value = n.creditValue;
         pendingCredits_.push_back(std::move(pc));
+        if (creditWanted_) watchLastCredit();
       }
       if (!others.empty()) {
         CudaEvent ev(op.device);
@@ -847,6 +918,23 @@ void ChannelImpl::finishRecv(RecvOp& op, const Error& e) {
   for (auto& it : items) it.callback(e);
 }
 
+// The sender is starved: have the poller tell us the moment the newest unpack has finished.
+void ChannelImpl::watchLastCredit() {
+  if (pendingCredits_.empty()) return;
+  cudaEvent_t raw = pendingCredits_.back().done->raw();
+  auto self = shared_from_this();
+  ctx_->poller_.watch([raw]() { return cudaEventQuery(raw) != cudaErrorNotReady; },
+                      [self]() { self->ctx_->loop_.deferToLoop([self]() { self->returnCredits(); }); });
+}
+
+std::unique_ptr<CudaEvent> ChannelImpl::takeEvent(int device) {
+  auto& pool = freeEvents_[device];
+  if (pool.empty()) return std::make_unique<CudaEvent>(device);
+  auto ev = std::move(pool.back());
+  pool.pop_back();
+  return ev;
+}
+
 void ChannelImpl::returnCredits() {
   // Inbox space is handed back once the unpack kernel that read it has finished; this is
   // checked opportunistically whenever the channel does anything (a sender that runs out of
@@ -856,6 +944,7 @@ void ChannelImpl::returnCredits() {
   while (!pendingCredits_.empty() && pendingCredits_.front().done->query()) {
     value = pendingCredits_.front().value;
     device = pendingCredits_.front().device;
+    freeEvents_[device].push_back(std::move(pendingCredits_.front().done));
     pendingCredits_.pop_front();
   }
   if (device >= 0 && !error_) {
@@ -863,36 +952,23 @@ void ChannelImpl::returnCredits() {
     c.deviceIdx = device;
     c.value = value;
     writePacket(c);
+    if (pendingCredits_.empty()) creditWanted_ = false;
   }
 }
 
 void ChannelImpl::onPacket(Packet p) {
   if (std::holds_alternative<RecvReady>(p)) {
     RecvReady& r = std::get<RecvReady>(p);
+    bool matched = false;
     for (auto& op : sendOps_) {
       if (op.seq == r.seq) {
-        if (op.launched) {
-          // Already sent eagerly. Still learn the peer's arena if this message carried it.
-          if (r.arena && !sameProcess_) {
-            CudaDeviceGuard g(op.srcDevice);
-            std::string why;
-            if (void* base = MappingCache::get().open(r.arena->handle, &why)) {
-              PeerArena pa;
-              pa.base = static_cast<uint8_t*>(base);
-              pa.inboxBytes = r.arena->inboxBytes;
-              peerArenas_[r.deviceIdx] = pa;
-            }
-          }
-          return;
-        }
         op.ready = std::move(r);
-        tryLaunch(op);
-        while (!sendOps_.empty() && sendOps_.front().launched) sendOps_.pop_front();
-        return;
+        matched = true;
+        break;
       }
     }
-    if (r.seq >= nextSendSeq_) earlyReady_.emplace(r.seq, std::move(r));
-    // else: for a batch that was sent eagerly and already retired — nothing to do
+    if (!matched && r.seq >= nextSendSeq_) earlyReady_.emplace(r.seq, std::move(r));
+    pumpSends();
   } else if (std::holds_alternative<Launched>(p)) {
     Launched& l = std::get<Launched>(p);
     for (auto& op : recvOps_) {
@@ -905,10 +981,18 @@ void ChannelImpl::onPacket(Packet p) {
       }
     }
     earlyLaunched_.emplace(l.seq, std::move(l));
-  } else {
+  } else if (std::holds_alternative<Credit>(p)) {
     const Credit& c = std::get<Credit>(p);
     auto it = peerArenas_.find(c.deviceIdx);
-    if (it != peerArenas_.end() && c.value > it->second.tail) it->second.tail = c.value;
+    if (it != peerArenas_.end()) {
+      if (c.value > it->second.tail) it->second.tail = c.value;
+      it->second.creditRequested = false;
+    }
+    pumpSends();
+  } else if (std::holds_alternative<CreditRequest>(p)) {
+    creditWanted_ = true;
+    returnCredits();
+    watchLastCredit();
   }
 }
 

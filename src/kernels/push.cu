@@ -2,20 +2,24 @@
 //
 // tpb_push_pack is ONE persistent launch (at most one CTA per SM) that serves a whole message:
 //
-//   * Warp 0 is a copy engine. Its elected lane drives a 4-stage pipeline of TMA bulk copies:
-//     global -> shared (completion on an mbarrier) and shared -> global (bulk groups), 32 KiB
-//     per stage, for every entry whose source, destination and size are 16-byte multiples.
-//     The loads only ever read THIS GPU's memory; the stores may target a peer GPU's memory
-//     mapped over NVLink. No thread touches the bytes.
-//   * Warps 1..15 handle what the bulk path cannot: ragged heads and tails, relatively
-//     misaligned buffers, dtype conversion (fp32 <-> bf16/fp16) and 2-D strided sources, which
-//     go through a padded shared-memory tile so that both the strided reads and the packed
-//     writes are coalesced.
-//   * Tiles are dealt round-robin to CTAs (tile t belongs to CTA t mod gridDim.x), so no
-//     scheduling state lives in global memory.
+//   * Warp 0 is a copy engine. Its elected lane drives a multi-stage pipeline of TMA bulk copies:
+//     global -> shared (completion on an mbarrier) and shared -> global (bulk groups), for every
+//     entry whose source, destination and size are 16-byte multiples. The loads only ever read
+//     THIS GPU's memory; the stores may target a peer GPU's memory mapped over NVLink. No thread
+//     touches the bytes. Tile size and depth are run-time parameters (PushTuning).
+//   * The other warps handle what the bulk path cannot, one 8 KiB "warp tile" at a time and
+//     without CTA-wide barriers: ragged heads and tails, relatively misaligned buffers, dtype
+//     conversion (fp32 <-> bf16/fp16), and 2-D strided sources, which a warp transposes through
+//     its private padded shared-memory tile so that both the strided reads and the packed writes
+//     are coalesced.
+//   * Tiles are dealt round-robin (bulk tile t to CTA t mod gridDim.x, warp tile t to warp
+//     t mod #warps), so no scheduling state lives in global memory.
 //   * Completion: every CTA makes its writes visible system-wide, then arrives on a counter;
 //     the last CTA resets the counter and publishes the flag with a release store at system
 //     scope. The flag lives in the receiver's memory; its stream waits on it.
+//
+// A "light" instantiation (256 threads, static shared memory only, no bulk pipeline) serves small
+// messages, where launch latency matters more than bandwidth.
 //
 // Every wait in here is bounded: a bulk load that does not complete within the limit makes the
 // CTA record kStatusBarrierTimeout, drain its own outstanding stores and fall through to the
@@ -26,6 +30,7 @@
 #include <cuda_fp16.h>
 
 #include <atomic>
+#include <mutex>
 #include <stdexcept>
 #include <string>
 
@@ -35,6 +40,10 @@ namespace kernels {
 namespace {
 
 std::atomic<uint64_t> gLaunches{0};
+std::mutex gTuningMutex;
+PushTuning gTuning;
+
+constexpr uint32_t kWarpTileBytes = kStridedTile * (kStridedTile / 2 + 1) * 8;  // 4352 B per warp: 32 x 17 x 8-byte, or 32 x 33 x 4-byte
 
 // ---- PTX wrappers -----------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smemAddr(const void* p) {
@@ -102,9 +111,6 @@ __device__ __forceinline__ uint64_t globalTimerNs() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-__device__ __forceinline__ void plainBarrier(int nthreads) {
-  asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
-}
 
 // ---- parameters ---------------------------------------------------------------------------------
 template <int N>
@@ -117,29 +123,20 @@ struct PushParams {
   uint32_t* flag;
   uint32_t* counter;
   uint32_t* status;
-};
-
-struct SharedStorage {
-  alignas(128) uint8_t stages[kBulkStages][kBulkTileBytes];
-  alignas(16) uint8_t tile[kStridedTile * (kStridedTile + 1) * 8];
-  alignas(8) uint64_t full[kBulkStages];
+  uint32_t bulkTileBytes;
+  uint32_t bulkStages;
 };
 
 template <int N>
 __device__ __forceinline__ const PushEntry* findEntry(const PushParams<N>& p, uint32_t tile, bool bulk) {
   // Entries of one class have increasing tileStart; a linear scan over <=96 entries in the
-  // constant bank costs less than the tile it locates.
-  const PushEntry* found = nullptr;
+  // constant bank (uniform across the warp) costs less than the tile it locates.
   for (uint32_t i = 0; i < p.numEntries; ++i) {
     const PushEntry& e = p.entries[i];
-    bool isBulk = e.kind == kCopyBulk;
-    if (isBulk != bulk) continue;
-    if (tile >= e.tileStart && tile < e.tileStart + e.numTiles) {
-      found = &e;
-      break;
-    }
+    if ((e.kind == kCopyBulk) != bulk) continue;
+    if (tile - e.tileStart < e.numTiles) return &e;
   }
-  return found;
+  return nullptr;
 }
 
 // ---- conversions --------------------------------------------------------------------------------
@@ -160,139 +157,165 @@ __device__ __forceinline__ __nv_bfloat16 fromFloat<__nv_bfloat16>(float v) { ret
 template <>
 __device__ __forceinline__ __half fromFloat<__half>(float v) { return __float2half_rn(v); }
 
-// ---- plain contiguous copy ----------------------------------------------------------------------
+// ---- plain contiguous copy: one warp, one 8 KiB tile ----------------------------------------------
 template <typename V>
-__device__ __forceinline__ void copyVec(const uint8_t* src, uint8_t* dst, uint64_t bytes, int tid, int nthr) {
+__device__ __forceinline__ void copyVec(const uint8_t* src, uint8_t* dst, uint32_t bytes, int lane) {
   const V* s = reinterpret_cast<const V*>(src);
   V* d = reinterpret_cast<V*>(dst);
-  const uint64_t n = bytes / sizeof(V);
+  const uint32_t n = bytes / sizeof(V);
   constexpr int kUnroll = 8;
-  uint64_t i = tid;
+  uint32_t i = lane;
   // Issue kUnroll independent loads before the first store: bytes in flight, not instructions,
   // are what fills an NVLink or HBM pipe.
-  for (; i + static_cast<uint64_t>(kUnroll - 1) * nthr < n; i += static_cast<uint64_t>(kUnroll) * nthr) {
+  for (; i + (kUnroll - 1) * 32 < n; i += kUnroll * 32) {
     V r[kUnroll];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) r[u] = s[i + static_cast<uint64_t>(u) * nthr];
+    for (int u = 0; u < kUnroll; ++u) r[u] = s[i + u * 32];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) d[i + static_cast<uint64_t>(u) * nthr] = r[u];
+    for (int u = 0; u < kUnroll; ++u) d[i + u * 32] = r[u];
   }
-  for (; i < n; i += nthr) d[i] = s[i];
-  // Trailing bytes that do not fill a vector.
-  const uint64_t done = n * sizeof(V);
-  for (uint64_t b = done + tid; b < bytes; b += nthr) dst[b] = src[b];
+  for (; i < n; i += 32) d[i] = s[i];
+  const uint32_t done = n * sizeof(V);
+  for (uint32_t b = done + lane; b < bytes; b += 32) dst[b] = src[b];
 }
 
-__device__ __forceinline__ void copyPlainTile(const PushEntry& e, uint32_t localTile, int tid, int nthr) {
+__device__ __forceinline__ void copyPlainTile(const PushEntry& e, uint32_t localTile, int lane) {
   const uint64_t off = static_cast<uint64_t>(localTile) * kPlainTileBytes;
-  uint64_t bytes = e.count - off;
-  if (bytes > kPlainTileBytes) bytes = kPlainTileBytes;
+  const uint64_t left = e.count - off;
+  const uint32_t bytes = left > kPlainTileBytes ? kPlainTileBytes : static_cast<uint32_t>(left);
   const uint8_t* src = static_cast<const uint8_t*>(e.src) + off;
   uint8_t* dst = static_cast<uint8_t*>(e.dst) + off;
   const uintptr_t a = reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst);
-  if ((a & 15) == 0) copyVec<uint4>(src, dst, bytes, tid, nthr);
-  else if ((a & 7) == 0) copyVec<uint2>(src, dst, bytes, tid, nthr);
-  else if ((a & 3) == 0) copyVec<uint32_t>(src, dst, bytes, tid, nthr);
-  else if ((a & 1) == 0) copyVec<uint16_t>(src, dst, bytes, tid, nthr);
-  else copyVec<uint8_t>(src, dst, bytes, tid, nthr);
+  if ((a & 15) == 0) copyVec<uint4>(src, dst, bytes, lane);
+  else if ((a & 7) == 0) copyVec<uint2>(src, dst, bytes, lane);
+  else if ((a & 3) == 0) copyVec<uint32_t>(src, dst, bytes, lane);
+  else if ((a & 1) == 0) copyVec<uint16_t>(src, dst, bytes, lane);
+  else copyVec<uint8_t>(src, dst, bytes, lane);
 }
 
 // ---- contiguous conversion ----------------------------------------------------------------------
 template <typename S, typename D>
-__device__ __forceinline__ void castTileTyped(const PushEntry& e, uint32_t localTile, int tid, int nthr) {
+__device__ __forceinline__ void castTileTyped(const PushEntry& e, uint32_t localTile, int lane) {
   // A tile is kPlainTileBytes of DESTINATION bytes.
-  const uint64_t perTile = kPlainTileBytes / sizeof(D);
+  constexpr uint32_t perTile = kPlainTileBytes / sizeof(D);
   const uint64_t first = static_cast<uint64_t>(localTile) * perTile;
-  uint64_t n = e.count - first;
-  if (n > perTile) n = perTile;
+  const uint64_t left = e.count - first;
+  const uint32_t n = left > perTile ? perTile : static_cast<uint32_t>(left);
   const S* s = static_cast<const S*>(e.src) + first;
   D* d = static_cast<D*>(e.dst) + first;
-  constexpr int kVec = 16 / sizeof(D) < 16 / sizeof(S) ? 16 / sizeof(S) : 16 / sizeof(D);  // elems per step
+  constexpr int kVec = 16 / sizeof(D) < 16 / sizeof(S) ? 16 / sizeof(S) : 16 / sizeof(D);  // elements per step
   const bool aligned = ((reinterpret_cast<uintptr_t>(s) & 15) == 0) && ((reinterpret_cast<uintptr_t>(d) & 15) == 0);
-  uint64_t vecElems = aligned ? (n / kVec) * kVec : 0;
-  for (uint64_t i = static_cast<uint64_t>(tid) * kVec; i < vecElems; i += static_cast<uint64_t>(nthr) * kVec) {
+  const uint32_t vecElems = aligned ? (n / kVec) * kVec : 0;
+  for (uint32_t i = lane * kVec; i < vecElems; i += 32 * kVec) {
     alignas(16) S in[kVec];
     alignas(16) D out[kVec];
     constexpr int kInVecs = kVec * sizeof(S) / 16;
-    constexpr int kOutVecs = (kVec * sizeof(D) + 15) / 16;
+    constexpr int kOutVecs = kVec * sizeof(D) / 16;
 #pragma unroll
-    for (int v = 0; v < kInVecs; ++v)
-      reinterpret_cast<uint4*>(in)[v] = reinterpret_cast<const uint4*>(s + i)[v];
+    for (int v = 0; v < kInVecs; ++v) reinterpret_cast<uint4*>(in)[v] = reinterpret_cast<const uint4*>(s + i)[v];
 #pragma unroll
     for (int k = 0; k < kVec; ++k) out[k] = fromFloat<D>(toFloat<S>(in[k]));
-    if (kVec * sizeof(D) >= 16) {
 #pragma unroll
-      for (int v = 0; v < kOutVecs; ++v) reinterpret_cast<uint4*>(d + i)[v] = reinterpret_cast<uint4*>(out)[v];
-    } else {
-      *reinterpret_cast<uint2*>(d + i) = *reinterpret_cast<uint2*>(out);
-    }
+    for (int v = 0; v < kOutVecs; ++v) reinterpret_cast<uint4*>(d + i)[v] = reinterpret_cast<uint4*>(out)[v];
   }
-  for (uint64_t i = vecElems + tid; i < n; i += nthr) d[i] = fromFloat<D>(toFloat<S>(s[i]));
+  for (uint32_t i = vecElems + lane; i < n; i += 32) d[i] = fromFloat<D>(toFloat<S>(s[i]));
 }
 
-__device__ __forceinline__ void castTile(const PushEntry& e, uint32_t localTile, int tid, int nthr) {
+__device__ __noinline__ void castTile(const PushEntry& e, uint32_t localTile, int lane) {
   const uint32_t key = (static_cast<uint32_t>(e.srcDtype) << 8) | e.dstDtype;
   constexpr uint32_t F32 = static_cast<uint32_t>(DType::kF32), BF = static_cast<uint32_t>(DType::kBF16),
                      F16 = static_cast<uint32_t>(DType::kF16);
   switch (key) {
-    case (F32 << 8) | BF: castTileTyped<float, __nv_bfloat16>(e, localTile, tid, nthr); break;
-    case (F32 << 8) | F16: castTileTyped<float, __half>(e, localTile, tid, nthr); break;
-    case (BF << 8) | F32: castTileTyped<__nv_bfloat16, float>(e, localTile, tid, nthr); break;
-    case (F16 << 8) | F32: castTileTyped<__half, float>(e, localTile, tid, nthr); break;
-    case (BF << 8) | F16: castTileTyped<__nv_bfloat16, __half>(e, localTile, tid, nthr); break;
-    case (F16 << 8) | BF: castTileTyped<__half, __nv_bfloat16>(e, localTile, tid, nthr); break;
+    case (F32 << 8) | BF: castTileTyped<float, __nv_bfloat16>(e, localTile, lane); break;
+    case (F32 << 8) | F16: castTileTyped<float, __half>(e, localTile, lane); break;
+    case (BF << 8) | F32: castTileTyped<__nv_bfloat16, float>(e, localTile, lane); break;
+    case (F16 << 8) | F32: castTileTyped<__half, float>(e, localTile, lane); break;
+    case (BF << 8) | F16: castTileTyped<__nv_bfloat16, __half>(e, localTile, lane); break;
+    case (F16 << 8) | BF: castTileTyped<__half, __nv_bfloat16>(e, localTile, lane); break;
     default: break;  // rejected on the host
   }
 }
 
-// ---- 2-D strided source through a shared-memory tile ----------------------------------------------
-// The tile is staged as raw source elements: smem[c][r] when the source is contiguous along rows
-// (a transposed matrix), smem[r][c] otherwise. Writes are always coalesced along dst columns.
+// ---- 2-D strided source through a per-warp shared-memory tile ------------------------------------
+// A warp stages TR x 32 raw source elements as tile[c][r] (row stride TR+1 words keeps both access
+// patterns free of bank conflicts for 4-byte elements), reading along whichever source dimension is
+// contiguous, then writes rows of the packed destination: 32 consecutive elements per store.
 template <typename S, typename D, bool kConvert>
-__device__ __forceinline__ void stridedTileTyped(const PushEntry& e, uint32_t localTile, int tid, int nthr,
-                                                 uint8_t* tileMem) {
-  constexpr int T = kStridedTile;
+__device__ __forceinline__ void stridedTileTyped(const PushEntry& e, uint32_t localTile, int lane, uint8_t* tileMem) {
+  constexpr int TC = kStridedTile;                                 // columns per tile
+  constexpr int TR = sizeof(S) == 8 ? kStridedTile / 2 : kStridedTile;  // rows per tile
   S* tile = reinterpret_cast<S*>(tileMem);
-  const int64_t tilesPerRow = (e.cols + T - 1) / T;
-  const int64_t r0 = (localTile / tilesPerRow) * T;
-  const int64_t c0 = (localTile % tilesPerRow) * T;
-  const int nr = static_cast<int>(e.rows - r0 < T ? e.rows - r0 : T);
-  const int nc = static_cast<int>(e.cols - c0 < T ? e.cols - c0 : T);
+  const int64_t tilesPerRow = (e.cols + TC - 1) / TC;
+  const int64_t r0 = (localTile / tilesPerRow) * TR;
+  const int64_t c0 = (localTile % tilesPerRow) * TC;
+  const int nr = static_cast<int>(e.rows - r0 < TR ? e.rows - r0 : TR);
+  const int nc = static_cast<int>(e.cols - c0 < TC ? e.cols - c0 : TC);
   const S* src = static_cast<const S*>(e.src);
   D* dst = static_cast<D*>(e.dst);
   const bool rowsFast = (e.rowStride == 1 || e.rows == 1) && e.colStride != 1;
+  constexpr int kBatch = 4;  // independent loads issued before their results are parked in the tile
   if (rowsFast) {
-    // consecutive threads walk down a source column: coalesced reads
-    for (int idx = tid; idx < nr * nc; idx += nthr) {
-      const int c = idx / nr, r = idx % nr;
-      tile[c * (T + 1) + r] = src[(r0 + r) * e.rowStride + (c0 + c) * e.colStride];
+    // lanes walk down a source column: coalesced reads when the source is a transposed matrix
+    for (int rb = 0; rb < nr; rb += 32) {
+      const int r = rb + lane;
+      const S* colPtr = src + (r0 + r) * e.rowStride + c0 * e.colStride;
+      for (int c = 0; c < nc; c += kBatch) {
+        S v[kBatch];
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k)
+          if (r < nr && c + k < nc) v[k] = colPtr[static_cast<int64_t>(c + k) * e.colStride];
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k)
+          if (r < nr && c + k < nc) tile[(c + k) * (TR + 1) + r] = v[k];
+      }
     }
   } else {
-    for (int idx = tid; idx < nr * nc; idx += nthr) {
-      const int r = idx / nc, c = idx % nc;
-      tile[c * (T + 1) + r] = src[(r0 + r) * e.rowStride + (c0 + c) * e.colStride];
+    for (int cb = 0; cb < nc; cb += 32) {
+      const int c = cb + lane;
+      const S* rowPtr = src + r0 * e.rowStride + (c0 + c) * e.colStride;
+      for (int r = 0; r < nr; r += kBatch) {
+        S v[kBatch];
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k)
+          if (c < nc && r + k < nr) v[k] = rowPtr[static_cast<int64_t>(r + k) * e.rowStride];
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k)
+          if (c < nc && r + k < nr) tile[c * (TR + 1) + r + k] = v[k];
+      }
     }
   }
-  plainBarrier(nthr);
-  for (int idx = tid; idx < nr * nc; idx += nthr) {
-    const int r = idx / nc, c = idx % nc;
-    const S v = tile[c * (T + 1) + r];
-    D out;
-    if constexpr (kConvert) out = fromFloat<D>(toFloat<S>(v));
-    else out = v;
-    dst[(r0 + r) * e.cols + (c0 + c)] = out;
+  __syncwarp();
+  {
+    const int c = lane;  // TC == 32: one column per lane
+    D* rowPtr = dst + r0 * e.cols + c0 + c;
+    for (int r = 0; r < nr; r += kBatch) {
+      S v[kBatch];
+#pragma unroll
+      for (int k = 0; k < kBatch; ++k)
+        if (c < nc && r + k < nr) v[k] = tile[c * (TR + 1) + r + k];
+#pragma unroll
+      for (int k = 0; k < kBatch; ++k) {
+        if (c < nc && r + k < nr) {
+          D out;
+          if constexpr (kConvert) out = fromFloat<D>(toFloat<S>(v[k]));
+          else out = v[k];
+          rowPtr[static_cast<int64_t>(r + k) * e.cols] = out;
+        }
+      }
+    }
   }
-  plainBarrier(nthr);  // the tile is reused by the next strided tile
+  __syncwarp();  // the tile is reused by this warp's next strided tile
 }
 
-__device__ __forceinline__ void stridedTile(const PushEntry& e, uint32_t localTile, int tid, int nthr,
-                                            uint8_t* tileMem) {
+// Not inlined: ten instantiations of the tile routine would otherwise set the register budget of
+// the whole kernel, including the copy loops that want many loads in flight.
+__device__ __noinline__ void stridedTile(const PushEntry& e, uint32_t localTile, int lane, uint8_t* tileMem) {
   if (e.srcDtype == e.dstDtype || e.dstDtype == static_cast<uint8_t>(DType::kBytes)) {
     switch (e.srcElemSize) {
-      case 1: stridedTileTyped<uint8_t, uint8_t, false>(e, localTile, tid, nthr, tileMem); break;
-      case 2: stridedTileTyped<uint16_t, uint16_t, false>(e, localTile, tid, nthr, tileMem); break;
-      case 4: stridedTileTyped<uint32_t, uint32_t, false>(e, localTile, tid, nthr, tileMem); break;
-      default: stridedTileTyped<uint64_t, uint64_t, false>(e, localTile, tid, nthr, tileMem); break;
+      case 1: stridedTileTyped<uint8_t, uint8_t, false>(e, localTile, lane, tileMem); break;
+      case 2: stridedTileTyped<uint16_t, uint16_t, false>(e, localTile, lane, tileMem); break;
+      case 4: stridedTileTyped<uint32_t, uint32_t, false>(e, localTile, lane, tileMem); break;
+      default: stridedTileTyped<uint64_t, uint64_t, false>(e, localTile, lane, tileMem); break;
     }
     return;
   }
@@ -300,29 +323,67 @@ __device__ __forceinline__ void stridedTile(const PushEntry& e, uint32_t localTi
   constexpr uint32_t F32 = static_cast<uint32_t>(DType::kF32), BF = static_cast<uint32_t>(DType::kBF16),
                      F16 = static_cast<uint32_t>(DType::kF16);
   switch (key) {
-    case (F32 << 8) | BF: stridedTileTyped<float, __nv_bfloat16, true>(e, localTile, tid, nthr, tileMem); break;
-    case (F32 << 8) | F16: stridedTileTyped<float, __half, true>(e, localTile, tid, nthr, tileMem); break;
-    case (BF << 8) | F32: stridedTileTyped<__nv_bfloat16, float, true>(e, localTile, tid, nthr, tileMem); break;
-    case (F16 << 8) | F32: stridedTileTyped<__half, float, true>(e, localTile, tid, nthr, tileMem); break;
-    case (BF << 8) | F16: stridedTileTyped<__nv_bfloat16, __half, true>(e, localTile, tid, nthr, tileMem); break;
-    case (F16 << 8) | BF: stridedTileTyped<__half, __nv_bfloat16, true>(e, localTile, tid, nthr, tileMem); break;
+    case (F32 << 8) | BF: stridedTileTyped<float, __nv_bfloat16, true>(e, localTile, lane, tileMem); break;
+    case (F32 << 8) | F16: stridedTileTyped<float, __half, true>(e, localTile, lane, tileMem); break;
+    case (BF << 8) | F32: stridedTileTyped<__nv_bfloat16, float, true>(e, localTile, lane, tileMem); break;
+    case (F16 << 8) | F32: stridedTileTyped<__half, float, true>(e, localTile, lane, tileMem); break;
+    case (BF << 8) | F16: stridedTileTyped<__nv_bfloat16, __half, true>(e, localTile, lane, tileMem); break;
+    case (F16 << 8) | BF: stridedTileTyped<__half, __nv_bfloat16, true>(e, localTile, lane, tileMem); break;
     default: break;
   }
 }
 
-// ---- the kernel ---------------------------------------------------------------------------------
+// Warp tiles t = firstWarp, firstWarp + totalWarps, ... of the plain class.
+template <int N>
+__device__ __forceinline__ void runPlainWarp(const PushParams<N>& p, uint32_t firstWarp, uint32_t totalWarps, int lane,
+                                             uint8_t* tileMem) {
+  for (uint32_t t = firstWarp; t < p.plainTiles; t += totalWarps) {
+    const PushEntry* e = findEntry(p, t, false);
+    const uint32_t local = t - e->tileStart;
+    if (e->kind == kCopyPlain) copyPlainTile(*e, local, lane);
+    else if (e->kind == kCastPlain) castTile(*e, local, lane);
+    else stridedTile(*e, local, lane, tileMem);
+  }
+}
+
+template <int N>
+__device__ __forceinline__ void publish(const PushParams<N>& p) {
+  if (p.flag == nullptr) return;
+  // Make this thread's writes visible system-wide before the CTA reports in.
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (gridDim.x == 1) {
+      // Only one CTA: the barrier above already ordered every write of the launch before this.
+      storeReleaseSys(p.flag, p.flagValue);
+      return;
+    }
+    const uint32_t arrived = atomicAdd(p.counter, 1u);
+    if (arrived == gridDim.x - 1) {
+      *p.counter = 0;  // ready for the next launch on this stream
+      __threadfence_system();
+      storeReleaseSys(p.flag, p.flagValue);
+    }
+  }
+}
+
+// ---- the kernels --------------------------------------------------------------------------------
 template <int N>
 __global__ void __launch_bounds__(kThreads, 1) tpb_push_pack(const __grid_constant__ PushParams<N> p) {
   extern __shared__ uint8_t smemRaw[];
-  // dynamic shared memory is only guaranteed 16-byte aligned: round up for the bulk stages
-  SharedStorage& sm = *reinterpret_cast<SharedStorage*>(
-      (reinterpret_cast<uintptr_t>(smemRaw) + 127) & ~static_cast<uintptr_t>(127));
+  // Layout: [bulk stages][warp tiles][mbarriers]; dynamic shared memory is only guaranteed to be
+  // 16-byte aligned, the bulk stages want 128.
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 127) & ~static_cast<uintptr_t>(127));
+  uint8_t* stages = base;
+  uint8_t* warpTiles = base + static_cast<size_t>(p.bulkStages) * p.bulkTileBytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(warpTiles + (kThreads / 32 - 1) * kWarpTileBytes);
 
   const int tid = threadIdx.x;
+  const int S = static_cast<int>(p.bulkStages);
   const bool haveBulk = p.bulkTiles > blockIdx.x;
 
   if (tid == 0 && haveBulk) {
-    for (int s = 0; s < kBulkStages; ++s) mbarInit(&sm.full[s], 1);
+    for (int s = 0; s < S; ++s) mbarInit(&full[s], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
@@ -332,14 +393,14 @@ __global__ void __launch_bounds__(kThreads, 1) tpb_push_pack(const __grid_consta
     if (tid == 0 && haveBulk) {
       const uint32_t first = blockIdx.x, step = gridDim.x;
       const uint32_t mine = (p.bulkTiles - first + step - 1) / step;  // tiles this CTA owns
+      const uint32_t tileBytes = p.bulkTileBytes;
       bool failed = false;
-      // Describe my i-th tile.
       auto describe = [&](uint32_t i, const uint8_t*& src, uint8_t*& dst, uint32_t& bytes) {
         const uint32_t t = first + i * step;
         const PushEntry* e = findEntry(p, t, true);
-        const uint64_t off = static_cast<uint64_t>(t - e->tileStart) * kBulkTileBytes;
+        const uint64_t off = static_cast<uint64_t>(t - e->tileStart) * tileBytes;
         const uint64_t left = e->count - off;
-        bytes = left < kBulkTileBytes ? static_cast<uint32_t>(left) : kBulkTileBytes;
+        bytes = left < tileBytes ? static_cast<uint32_t>(left) : tileBytes;
         src = static_cast<const uint8_t*>(e->src) + off;
         dst = static_cast<uint8_t*>(e->dst) + off;
       };
@@ -348,15 +409,15 @@ __global__ void __launch_bounds__(kThreads, 1) tpb_push_pack(const __grid_consta
         uint8_t* dst;
         uint32_t bytes;
         describe(i, src, dst, bytes);
-        const int s = i % kBulkStages;
-        mbarExpectTx(&sm.full[s], bytes);
-        bulkLoad(sm.stages[s], src, bytes, &sm.full[s]);
+        const int s = i % S;
+        mbarExpectTx(&full[s], bytes);
+        bulkLoad(stages + static_cast<size_t>(s) * tileBytes, src, bytes, &full[s]);
       };
-      const uint32_t prologue = mine < static_cast<uint32_t>(kBulkStages) ? mine : kBulkStages;
+      const uint32_t prologue = mine < static_cast<uint32_t>(S) ? mine : S;
       for (uint32_t i = 0; i < prologue; ++i) issueLoad(i);
       for (uint32_t c = 0; c < mine; ++c) {
-        const int s = c % kBulkStages;
-        if (!mbarWaitBounded(&sm.full[s], (c / kBulkStages) & 1)) {
+        const int s = c % S;
+        if (!mbarWaitBounded(&full[s], (c / S) & 1)) {
           failed = true;
           break;
         }
@@ -365,13 +426,13 @@ __global__ void __launch_bounds__(kThreads, 1) tpb_push_pack(const __grid_consta
         uint32_t bytes;
         describe(c, src, dst, bytes);
         fenceProxyAsync();
-        bulkStore(dst, sm.stages[s], bytes);
+        bulkStore(dst, stages + static_cast<size_t>(s) * tileBytes, bytes);
         bulkCommit();
         // Refill the stage whose store was issued one iteration ago: by now it has most likely
         // finished reading shared memory, so this wait rarely stalls the pipeline.
-        if (c >= 1 && (c - 1) + kBulkStages < mine) {
+        if (c >= 1 && (c - 1) + S < mine) {
           bulkWaitRead<1>();
-          issueLoad((c - 1) + kBulkStages);
+          issueLoad((c - 1) + S);
         }
       }
       bulkWaitAll();  // stores are complete (not merely read out of shared memory)
@@ -379,29 +440,21 @@ __global__ void __launch_bounds__(kThreads, 1) tpb_push_pack(const __grid_consta
     }
   } else {
     // ---- warps 1..: everything that needs registers ----
-    const int ptid = tid - 32;
-    const int pn = kThreads - 32;
-    for (uint32_t t = blockIdx.x; t < p.plainTiles; t += gridDim.x) {
-      const PushEntry* e = findEntry(p, t, false);
-      const uint32_t local = t - e->tileStart;
-      if (e->kind == kCopyPlain) copyPlainTile(*e, local, ptid, pn);
-      else if (e->kind == kCastPlain) castTile(*e, local, ptid, pn);
-      else stridedTile(*e, local, ptid, pn, sm.tile);
-    }
+    constexpr uint32_t kPlainWarps = kThreads / 32 - 1;
+    const uint32_t warp = tid / 32 - 1;
+    runPlainWarp(p, blockIdx.x * kPlainWarps + warp, gridDim.x * kPlainWarps, tid & 31,
+                 warpTiles + warp * kWarpTileBytes);
   }
+  publish(p);
+}
 
-  if (p.flag == nullptr) return;
-  // Make this thread's writes visible system-wide before the CTA reports in.
-  __threadfence_system();
-  __syncthreads();
-  if (tid == 0) {
-    const uint32_t arrived = atomicAdd(p.counter, 1u);
-    if (arrived == gridDim.x - 1) {
-      *p.counter = 0;  // ready for the next launch on this stream
-      __threadfence_system();
-      storeReleaseSys(p.flag, p.flagValue);
-    }
-  }
+template <int N>
+__global__ void __launch_bounds__(kLightThreads, 2) tpb_push_pack_light(const __grid_constant__ PushParams<N> p) {
+  __shared__ __align__(16) uint8_t warpTiles[(kLightThreads / 32) * kWarpTileBytes];
+  constexpr uint32_t kWarps = kLightThreads / 32;
+  const uint32_t warp = threadIdx.x / 32;
+  runPlainWarp(p, blockIdx.x * kWarps + warp, gridDim.x * kWarps, threadIdx.x & 31, warpTiles + warp * kWarpTileBytes);
+  publish(p);
 }
 
 __global__ void tpb_wait_flag(const uint32_t* flag, uint32_t value, uint64_t timeoutNs, uint32_t* status) {
@@ -473,17 +526,9 @@ void check(cudaError_t e, const char* what) {
 }
 
 template <int N>
-void launchOne(const PushEntry* entries, uint32_t n, uint32_t bulkTiles, uint32_t plainTiles, cudaStream_t stream,
-               int maxCtas, uint32_t* flag, uint32_t flagValue, uint32_t* counter, uint32_t* status) {
-  static const size_t kSmem = sizeof(SharedStorage) + 128;
-  static bool configured[64] = {};
-  int dev = 0;
-  check(cudaGetDevice(&dev), "cudaGetDevice");
-  if (dev < 64 && !configured[dev]) {
-    check(cudaFuncSetAttribute(tpb_push_pack<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmem)),
-          "cudaFuncSetAttribute");
-    configured[dev] = true;
-  }
+void launchOne(const PushEntry* entries, uint32_t n, uint32_t bulkTiles, uint32_t plainTiles, uint32_t bulkTileBytes,
+               uint32_t bulkStages, cudaStream_t stream, int maxCtas, uint32_t* flag, uint32_t flagValue,
+               uint32_t* counter, uint32_t* status) {
   PushParams<N> p;
   for (uint32_t i = 0; i < n; ++i) p.entries[i] = entries[i];
   p.numEntries = n;
@@ -493,15 +538,53 @@ void launchOne(const PushEntry* entries, uint32_t n, uint32_t bulkTiles, uint32_
   p.flag = flag;
   p.counter = counter;
   p.status = status;
-  uint32_t tiles = bulkTiles > plainTiles ? bulkTiles : plainTiles;
-  uint32_t grid = tiles < static_cast<uint32_t>(maxCtas) ? tiles : static_cast<uint32_t>(maxCtas);
+  p.bulkTileBytes = bulkTileBytes;
+  p.bulkStages = bulkStages;
+  if (bulkTiles == 0) {
+    // Light kernel: 8 warps per CTA, static shared memory only.
+    constexpr uint32_t kWarps = kLightThreads / 32;
+    uint32_t grid = (plainTiles + kWarps - 1) / kWarps;
+    if (grid > static_cast<uint32_t>(maxCtas) * 2) grid = static_cast<uint32_t>(maxCtas) * 2;
+    if (grid == 0) grid = 1;
+    tpb_push_pack_light<N><<<grid, kLightThreads, 0, stream>>>(p);
+    check(cudaGetLastError(), "tpb_push_pack_light launch");
+    ++gLaunches;
+    return;
+  }
+  const size_t smem = static_cast<size_t>(bulkStages) * bulkTileBytes + (kThreads / 32 - 1) * kWarpTileBytes +
+      kMaxBulkStages * sizeof(uint64_t) + 128;
+  static size_t configured[64] = {};
+  int dev = 0;
+  check(cudaGetDevice(&dev), "cudaGetDevice");
+  if (dev < 64 && configured[dev] < smem) {
+    check(cudaFuncSetAttribute(tpb_push_pack<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)),
+          "cudaFuncSetAttribute");
+    configured[dev] = smem;
+  }
+  constexpr uint32_t kPlainWarps = kThreads / 32 - 1;
+  uint32_t want = bulkTiles;
+  const uint32_t plainCtas = (plainTiles + kPlainWarps - 1) / kPlainWarps;
+  if (plainCtas > want) want = plainCtas;
+  uint32_t grid = want < static_cast<uint32_t>(maxCtas) ? want : static_cast<uint32_t>(maxCtas);
   if (grid == 0) grid = 1;
-  tpb_push_pack<N><<<grid, kThreads, kSmem, stream>>>(p);
+  tpb_push_pack<N><<<grid, kThreads, smem, stream>>>(p);
   check(cudaGetLastError(), "tpb_push_pack launch");
   ++gLaunches;
 }
 
 }  // namespace
+
+void setPushTuning(const PushTuning& t) {
+  if (t.bulkStages < 2 || t.bulkStages > static_cast<uint32_t>(kMaxBulkStages) || t.bulkTileBytes % 1024 != 0 ||
+      t.bulkTileBytes == 0 || static_cast<size_t>(t.bulkStages) * t.bulkTileBytes > 160 * 1024)
+    throw std::runtime_error("invalid bulk pipeline tuning");
+  std::unique_lock<std::mutex> l(gTuningMutex);
+  gTuning = t;
+}
+PushTuning getPushTuning() {
+  std::unique_lock<std::mutex> l(gTuningMutex);
+  return gTuning;
+}
 
 // ---- host-side planning -------------------------------------------------------------------------
 bool castSupported(DType s, DType d) {
@@ -518,7 +601,7 @@ namespace {
 void pushEntry(PushPlan& plan, PushEntry e) {
   if (e.count == 0) return;
   if (e.kind == kCopyBulk) {
-    e.numTiles = static_cast<uint32_t>((e.count + kBulkTileBytes - 1) / kBulkTileBytes);
+    e.numTiles = static_cast<uint32_t>((e.count + plan.bulkTileBytes - 1) / plan.bulkTileBytes);
     e.tileStart = plan.bulkTiles;
     plan.bulkTiles += e.numTiles;
   } else if (e.kind == kCopyPlain) {
@@ -531,7 +614,8 @@ void pushEntry(PushPlan& plan, PushEntry e) {
     e.tileStart = plan.plainTiles;
     plan.plainTiles += e.numTiles;
   } else {
-    const uint64_t tr = (e.rows + kStridedTile - 1) / kStridedTile, tc = (e.cols + kStridedTile - 1) / kStridedTile;
+    const int tileRows = e.srcElemSize == 8 ? kStridedTile / 2 : kStridedTile;
+    const uint64_t tr = (e.rows + tileRows - 1) / tileRows, tc = (e.cols + kStridedTile - 1) / kStridedTile;
     e.numTiles = static_cast<uint32_t>(tr * tc);
     e.tileStart = plan.plainTiles;
     plan.plainTiles += e.numTiles;
@@ -541,6 +625,11 @@ void pushEntry(PushPlan& plan, PushEntry e) {
 }  // namespace
 
 void appendToPlan(PushPlan& plan, const CopyItem& item, bool useBulk) {
+  if (plan.bulkTileBytes == 0) {
+    const PushTuning t = getPushTuning();
+    plan.bulkTileBytes = t.bulkTileBytes;
+    plan.bulkStages = t.bulkStages;
+  }
   PushEntry e{};
   e.srcDtype = static_cast<uint8_t>(item.srcDtype);
   const DType dstDtype = item.dstDtype == DType::kBytes ? item.srcDtype : item.dstDtype;
@@ -586,7 +675,7 @@ void appendToPlan(PushPlan& plan, const CopyItem& item, bool useBulk) {
   uint64_t bytes = item.srcBytes;
   const uintptr_t sa = reinterpret_cast<uintptr_t>(src), da = reinterpret_cast<uintptr_t>(dst);
   const bool sameSkew = ((sa ^ da) & 15) == 0;
-  if (!useBulk || !sameSkew || bytes < 2048) {
+  if (!useBulk || !sameSkew || bytes < getPushTuning().bulkMinBytes) {
     e.src = src;
     e.dst = dst;
     e.kind = kCopyPlain;
@@ -627,13 +716,15 @@ int launchPush(const PushPlan& plan, cudaStream_t stream, int maxCtas, uint32_t*
                uint32_t* counter, uint32_t* status) {
   const size_t n = plan.entries.size();
   if (maxCtas <= 0) maxCtas = 1;
+  const uint32_t tileBytes = plan.bulkTileBytes ? plan.bulkTileBytes : 32768;
+  const uint32_t stages = plan.bulkStages ? plan.bulkStages : 4;
   if (n <= static_cast<size_t>(kMaxEntriesLarge)) {
     if (n <= static_cast<size_t>(kMaxEntriesSmall))
       launchOne<kMaxEntriesSmall>(plan.entries.data(), static_cast<uint32_t>(n), plan.bulkTiles, plan.plainTiles,
-                                  stream, maxCtas, flag, flagValue, counter, status);
+                                  tileBytes, stages, stream, maxCtas, flag, flagValue, counter, status);
     else
       launchOne<kMaxEntriesLarge>(plan.entries.data(), static_cast<uint32_t>(n), plan.bulkTiles, plan.plainTiles,
-                                  stream, maxCtas, flag, flagValue, counter, status);
+                                  tileBytes, stages, stream, maxCtas, flag, flagValue, counter, status);
     return 1;
   }
   // More entries than one parameter block holds: several launches on the same stream, each with
@@ -653,8 +744,8 @@ int launchPush(const PushPlan& plan, cudaStream_t stream, int maxCtas, uint32_t*
       }
     }
     const bool last = first + cnt == n;
-    launchOne<kMaxEntriesLarge>(part.data(), static_cast<uint32_t>(cnt), bulk, plain, stream, maxCtas,
-                                last ? flag : nullptr, flagValue, counter, status);
+    launchOne<kMaxEntriesLarge>(part.data(), static_cast<uint32_t>(cnt), bulk, plain, tileBytes, stages, stream,
+                                maxCtas, last ? flag : nullptr, flagValue, counter, status);
     ++launches;
   }
   return launches;

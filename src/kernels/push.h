@@ -45,11 +45,21 @@ static_assert(sizeof(PushEntry) == 80, "entry layout");
 
 constexpr int kMaxEntriesSmall = 8;
 constexpr int kMaxEntriesLarge = 96;
-constexpr uint32_t kBulkTileBytes = 32 * 1024;
-constexpr int kBulkStages = 4;
-constexpr uint32_t kPlainTileBytes = 64 * 1024;
-constexpr int kStridedTile = 64;  // elements per side
-constexpr int kThreads = 512;
+constexpr uint32_t kPlainTileBytes = 8 * 1024;  // one warp's unit of work (destination bytes)
+constexpr int kStridedTile = 32;                // a warp transposes 32x32 elements (16x32 for 8-byte ones)
+constexpr int kThreads = 512;                   // full kernel: warp 0 drives TMA, warps 1..15 use registers
+constexpr int kLightThreads = 256;              // light kernel (no bulk pipeline, static shared memory only)
+constexpr int kMaxBulkStages = 8;
+
+// Shape of the TMA bulk pipeline; process-wide, read when a plan is built. The defaults are the
+// measured optimum on B200 for HBM->HBM and HBM->NVLink streams.
+struct PushTuning {
+  uint32_t bulkTileBytes = 32 * 1024;  // multiple of 1024
+  uint32_t bulkStages = 3;             // 2..kMaxBulkStages; stages * tile must fit in shared memory
+  uint32_t bulkMinBytes = 512 * 1024;  // entries smaller than this take the plain path
+};
+void setPushTuning(const PushTuning& t);
+PushTuning getPushTuning();
 
 // Status word values written by kernels (0 = fine).
 enum KernelStatus : uint32_t {
@@ -63,6 +73,8 @@ struct PushPlan {
   uint32_t bulkTiles = 0;
   uint32_t plainTiles = 0;
   uint64_t totalBytesOut = 0;
+  uint32_t bulkTileBytes = 0;  // fixed by the first bulk entry
+  uint32_t bulkStages = 0;
 };
 
 struct CopyItem {

@@ -64,6 +64,24 @@ struct RingBench::Impl {
     return ctx;
   }
 
+  // A tensor-less message to the next rank and one from the previous rank: lines neighbouring
+  // ranks up to within one message latency before a timed region starts (a collective barrier
+  // leaves them hundreds of microseconds apart).
+  void syncNeighbours() {
+    std::promise<Error> wrote, got;
+    Message m;
+    m.metadata = "sync";
+    sendPipe->write(std::move(m), [&](const Error& e) { wrote.set_value(e); });
+    recvPipe->readDescriptor([&](const Error& e, Descriptor) {
+      if (e) return got.set_value(e);
+      recvPipe->read(Allocation(), [&](const Error& e2) { got.set_value(e2); });
+    });
+    auto fg = got.get_future();
+    auto fw = wrote.get_future();
+    failOn(waitOrThrow(fg, 120, "sync message from the previous rank"), "sync read");
+    failOn(waitOrThrow(fw, 120, "sync message to the next rank"), "sync write");
+  }
+
   void fillSource(size_t bytes, uint64_t seed) {
     kernels::launchFill(sendStream, src, bytes, seed);
     TPB_CUDA_CHECK(cudaStreamSynchronize(sendStream));
@@ -238,6 +256,7 @@ PhaseResult RingBench::runStream(size_t bytes, int steps, int depth, bool verify
     }
   };
 
+  m.syncNeighbours();
   auto t0 = Clock::now();
   TPB_CUDA_CHECK(cudaEventRecord(m.evStart, m.recvStream));
   (*armRead)();
@@ -474,6 +493,7 @@ PhaseResult RingBench::runMixed(int steps, uint64_t seed, uint64_t* bytesPerStep
     });
   };
 
+  m.syncNeighbours();
   auto t0 = Clock::now();
   TPB_CUDA_CHECK(cudaEventRecord(m.evStart, m.recvStream));
   (*armRead)();

@@ -309,6 +309,32 @@ PYBIND11_MODULE(_C, m) {
       });
 
   m.def("kernel_launch_count", &kernels::launchCount);
+  // Direct access to the push/pack kernel for tests and tools: copy byte ranges between device
+  // addresses on the current device with one launch; optionally publish a completion flag
+  // (then `counter_ptr` must point to a zeroed 32-bit word in device memory).
+  m.def(
+      "launch_push",
+      [](const std::vector<std::tuple<uint64_t, uint64_t, uint64_t>>& items, uint64_t stream, bool useBulk,
+         uint64_t flagPtr, uint32_t flagValue, uint64_t counterPtr) {
+        kernels::PushPlan plan;
+        for (const auto& it : items) {
+          kernels::CopyItem c;
+          c.src = reinterpret_cast<const void*>(std::get<0>(it));
+          c.dst = reinterpret_cast<void*>(std::get<1>(it));
+          c.srcBytes = std::get<2>(it);
+          kernels::appendToPlan(plan, c, useBulk);
+        }
+        if (plan.entries.empty() && flagPtr == 0) return 0;
+        int dev = 0;
+        cudaGetDevice(&dev);
+        int sms = 1;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        return kernels::launchPush(plan, reinterpret_cast<cudaStream_t>(stream), sms,
+                                   reinterpret_cast<uint32_t*>(flagPtr), flagValue,
+                                   reinterpret_cast<uint32_t*>(counterPtr), nullptr);
+      },
+      py::arg("items"), py::arg("stream") = 0, py::arg("use_bulk") = true, py::arg("flag_ptr") = 0,
+      py::arg("flag_value") = 0, py::arg("counter_ptr") = 0);
 
   // ---- native benchmark engine ----
   py::class_<tools::PhaseResult>(m, "PhaseResult")

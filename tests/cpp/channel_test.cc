@@ -1,0 +1,445 @@
+// Generic channel suite: one body, every CPU channel, on raw transport connections (no pipe), the
+// way the reference organises its channel tests (tensorpipe/test/channel/channel_test.cc:18-336,
+// channel_test_cpu.cc:19-109): the two peers open N TCP connections tagged with an index, hand
+// them to createChannel on both sides, and exchange tensors.
+#include <tpb/tpb.h>
+
+#include <random>
+
+#include "test_util.h"
+
+using namespace tpb;
+using namespace tpbtest;
+
+namespace {
+
+struct Backend {
+  const char* name;
+  std::function<std::shared_ptr<channel::Context>()> make;
+  bool needsProcesses;  // endpoints must be different processes
+};
+
+std::shared_ptr<channel::Context> makeMpt() {
+  std::vector<std::shared_ptr<transport::Context>> ctxs;
+  std::vector<std::shared_ptr<transport::Listener>> listeners;
+  for (int i = 0; i < 3; ++i) {
+    auto c = transport::uv::create();
+    listeners.push_back(c->listen("127.0.0.1"));
+    ctxs.push_back(std::move(c));
+  }
+  return channel::mpt::create(std::move(ctxs), std::move(listeners));
+}
+
+const Backend kBackends[] = {
+    {"basic", [] { return channel::basic::create(); }, false},
+    {"xth", [] { return channel::xth::create(); }, false},
+    {"mpt", [] { return makeMpt(); }, false},
+    {"cma", [] { return channel::cma::create(); }, true},
+};
+
+// Opens `n` tagged connections between two transport contexts. The server side sorts them by tag.
+struct Wiring {
+  std::shared_ptr<transport::Context> tctx = transport::uv::create();
+  std::shared_ptr<transport::Listener> listener;
+  std::string listen() {
+    listener = tctx->listen("127.0.0.1");
+    return listener->addr();
+  }
+  std::vector<std::shared_ptr<transport::Connection>> acceptAll(size_t n) {
+    std::vector<std::shared_ptr<transport::Connection>> out(n);
+    for (size_t i = 0; i < n; ++i) {
+      std::promise<std::shared_ptr<transport::Connection>> pc;
+      listener->accept([&](const Error& e, std::shared_ptr<transport::Connection> c) { pc.set_value(e ? nullptr : c); });
+      auto fc = pc.get_future();
+      auto c = waitFor(fc);
+      if (!c) throw TestFailure("accept failed");
+      std::promise<uint64_t> tag;
+      c->read([&](const Error& e, const void* p, size_t len) {
+        uint64_t v = UINT64_MAX;
+        if (!e && len == 8) std::memcpy(&v, p, 8);
+        tag.set_value(v);
+      });
+      auto ft = tag.get_future();
+      uint64_t idx = waitFor(ft);
+      if (idx >= n) throw TestFailure("bad connection tag");
+      out[idx] = c;
+    }
+    return out;
+  }
+  std::vector<std::shared_ptr<transport::Connection>> connectAll(const std::string& addr, size_t n) {
+    std::vector<std::shared_ptr<transport::Connection>> out;
+    for (size_t i = 0; i < n; ++i) {
+      auto c = tctx->connect(addr);
+      auto tag = std::make_shared<uint64_t>(i);
+      std::promise<Error> pw;
+      c->write(tag.get(), 8, [&, tag](const Error& e) { pw.set_value(e); });
+      auto fw = pw.get_future();
+      if (waitFor(fw)) throw TestFailure("tag write failed");
+      out.push_back(std::move(c));
+    }
+    return out;
+  }
+};
+
+void sendSync(channel::Channel& ch, void* p, size_t n) {
+  std::promise<Error> pr;
+  ch.send(CpuBuffer{p}, n, [&](const Error& e) { pr.set_value(e); });
+  auto f = pr.get_future();
+  Error e = waitFor(f);
+  if (e) throw TestFailure("send: " + e.what());
+}
+void recvSync(channel::Channel& ch, void* p, size_t n) {
+  std::promise<Error> pr;
+  ch.recv(CpuBuffer{p}, n, [&](const Error& e) { pr.set_value(e); });
+  auto f = pr.get_future();
+  Error e = waitFor(f);
+  if (e) throw TestFailure("recv: " + e.what());
+}
+std::vector<uint8_t> pattern(size_t n, uint32_t seed) {
+  std::vector<uint8_t> v(n);
+  std::mt19937 rng(seed);
+  for (auto& b : v) b = static_cast<uint8_t>(rng());
+  return v;
+}
+
+using Body = std::function<void(channel::Channel&)>;
+
+// Runs server/client bodies over one channel of the backend, as threads or as processes.
+void runChannel(const Backend& b, Body server, Body client) {
+  auto serverSide = [&](std::function<void(std::string)> tell, std::function<std::string()> hear) {
+    auto cctx = b.make();
+    if (!cctx->isViable()) {
+      tell("skip");
+      return;
+    }
+    Wiring w;
+    tell(w.listen());
+    auto conns = w.acceptAll(cctx->numConnectionsNeeded());
+    auto ch = cctx->createChannel(std::move(conns), channel::Endpoint::kListen);
+    server(*ch);
+    hear();
+    ch->close();
+    ch.reset();
+    cctx->join();
+    w.tctx->join();
+  };
+  auto clientSide = [&](std::function<void(std::string)> tell, std::function<std::string()> hear) {
+    std::string addr = hear();
+    if (addr == "skip") return;
+    auto cctx = b.make();
+    Wiring w;
+    auto conns = w.connectAll(addr, cctx->numConnectionsNeeded());
+    auto ch = cctx->createChannel(std::move(conns), channel::Endpoint::kConnect);
+    client(*ch);
+    tell("done");
+    ch->close();
+    ch.reset();
+    cctx->join();
+    w.tctx->join();
+  };
+  if (b.needsProcesses) {
+    ProcessPeers::run(
+        [&](const ProcessPeers::Side& me) { serverSide([&](std::string s) { me.send(s); }, [&] { return me.recv(); }); },
+        [&](const ProcessPeers::Side& me) { clientSide([&](std::string s) { me.send(s); }, [&] { return me.recv(); }); });
+  } else {
+    ThreadPeers peers;
+    peers.run(
+        [&](ThreadPeers& pg) { serverSide([&](std::string s) { pg.sendToClient(s); }, [&] { return pg.recvFromClient(); }); },
+        [&](ThreadPeers& pg) { clientSide([&](std::string s) { pg.sendToServer(s); }, [&] { return pg.recvFromServer(); }); });
+  }
+}
+
+void forEachBackend(std::function<void(const Backend&)> body) {
+  for (const auto& b : kBackends) {
+    try {
+      body(b);
+    } catch (const TestFailure& e) {
+      throw TestFailure(std::string("[") + b.name + "] " + e.what());
+    }
+  }
+}
+
+}  // namespace
+
+TPB_TEST(Channel, DeviceDescriptors) {
+  forEachBackend([](const Backend& b) {
+    auto a = b.make();
+    auto c = b.make();
+    if (!a->isViable()) return;
+    const auto& da = a->deviceDescriptors();
+    const auto& dc = c->deviceDescriptors();
+    EXPECT_TRUE(da.count(Device(kCpuDeviceType, 0)) == 1);
+    for (const auto& d : da) {
+      EXPECT_FALSE(d.second.empty());
+      // Two contexts of one process describe the same endpoint.
+      EXPECT_TRUE(a->canCommunicateWithRemote(d.second, dc.at(d.first)));
+      EXPECT_FALSE(a->canCommunicateWithRemote(d.second, "nonsense"));
+    }
+    a->join();
+    c->join();
+  });
+}
+
+TPB_TEST(Channel, ClientToServerAndBack) {
+  forEachBackend([](const Backend& b) {
+    auto data = pattern(300007, 1);
+    runChannel(
+        b,
+        [&](channel::Channel& ch) {
+          std::vector<uint8_t> got(data.size());
+          recvSync(ch, got.data(), got.size());
+          EXPECT_TRUE(got == data);
+          sendSync(ch, got.data(), got.size());
+        },
+        [&](channel::Channel& ch) {
+          auto copy = data;
+          sendSync(ch, copy.data(), copy.size());
+          std::vector<uint8_t> back(data.size());
+          recvSync(ch, back.data(), back.size());
+          EXPECT_TRUE(back == data);
+        });
+  });
+}
+
+TPB_TEST(Channel, SendMultipleTensorsKeepsOrder) {
+  forEachBackend([](const Backend& b) {
+    constexpr int kN = 20;
+    runChannel(
+        b,
+        [&](channel::Channel& ch) {
+          std::vector<std::vector<uint8_t>> got(kN);
+          std::vector<std::promise<Error>> done(kN);
+          for (int i = 0; i < kN; ++i) {
+            got[i].resize(1000 + i * 997);
+            ch.recv(CpuBuffer{got[i].data()}, got[i].size(), [&, i](const Error& e) { done[i].set_value(e); });
+          }
+          for (int i = 0; i < kN; ++i) {
+            auto f = done[i].get_future();
+            EXPECT_FALSE(bool(waitFor(f)));
+            EXPECT_TRUE(got[i] == pattern(1000 + i * 997, 50 + i));
+          }
+        },
+        [&](channel::Channel& ch) {
+          std::vector<std::vector<uint8_t>> data(kN);
+          std::vector<std::promise<Error>> done(kN);
+          for (int i = 0; i < kN; ++i) {
+            data[i] = pattern(1000 + i * 997, 50 + i);
+            ch.send(CpuBuffer{data[i].data()}, data[i].size(), [&, i](const Error& e) { done[i].set_value(e); });
+          }
+          for (int i = 0; i < kN; ++i) {
+            auto f = done[i].get_future();
+            EXPECT_FALSE(bool(waitFor(f)));
+          }
+        });
+  });
+}
+
+TPB_TEST(Channel, SendTensorsBothWaysAtOnce) {
+  forEachBackend([](const Backend& b) {
+    auto a = pattern(123457, 7), c = pattern(76543, 8);
+    auto side = [&](const std::vector<uint8_t>& mine, const std::vector<uint8_t>& theirs) {
+      return [&](channel::Channel& ch) {
+        auto out = mine;
+        std::vector<uint8_t> in(theirs.size());
+        std::promise<Error> ps, pr;
+        ch.send(CpuBuffer{out.data()}, out.size(), [&](const Error& e) { ps.set_value(e); });
+        ch.recv(CpuBuffer{in.data()}, in.size(), [&](const Error& e) { pr.set_value(e); });
+        auto fs = ps.get_future(), fr = pr.get_future();
+        EXPECT_FALSE(bool(waitFor(fs)));
+        EXPECT_FALSE(bool(waitFor(fr)));
+        EXPECT_TRUE(in == theirs);
+      };
+    };
+    runChannel(b, side(a, c), side(c, a));
+  });
+}
+
+TPB_TEST(Channel, EmptyAndNullTensors) {
+  forEachBackend([](const Backend& b) {
+    auto data = pattern(4096, 9);
+    runChannel(
+        b,
+        [&](channel::Channel& ch) {
+          std::vector<uint8_t> got(data.size());
+          recvSync(ch, nullptr, 0);  // a null pointer with length 0 is legal
+          recvSync(ch, got.data(), got.size());
+          recvSync(ch, got.data(), 0);
+          EXPECT_TRUE(got == data);
+        },
+        [&](channel::Channel& ch) {
+          auto copy = data;
+          sendSync(ch, nullptr, 0);
+          sendSync(ch, copy.data(), copy.size());
+          sendSync(ch, copy.data(), 0);
+        });
+  });
+}
+
+TPB_TEST(Channel, CallbacksAreDeferred) {
+  // The copy must not happen inside recv()/send(): the mutex is held across the call and taken
+  // inside the callback, so a callback that runs inline deadlocks (the reference's check,
+  // tensorpipe/test/channel/channel_test_cpu.cc:45-109).
+  forEachBackend([](const Backend& b) {
+    if (b.needsProcesses) return;
+    auto data = pattern(100000, 3);
+    runChannel(
+        b,
+        [&](channel::Channel& ch) {
+          std::vector<uint8_t> got(data.size());
+          std::mutex m;
+          std::promise<Error> done;
+          {
+            std::unique_lock<std::mutex> lock(m);
+            ch.recv(CpuBuffer{got.data()}, got.size(), [&](const Error& e) {
+              std::unique_lock<std::mutex> inner(m);
+              done.set_value(e);
+            });
+            std::this_thread::sleep_for(std::chrono::milliseconds(2));
+          }
+          auto f = done.get_future();
+          EXPECT_FALSE(bool(waitFor(f)));
+          EXPECT_TRUE(got == data);
+        },
+        [&](channel::Channel& ch) {
+          auto copy = data;
+          std::mutex m;
+          std::promise<Error> done;
+          {
+            std::unique_lock<std::mutex> lock(m);
+            ch.send(CpuBuffer{copy.data()}, copy.size(), [&](const Error& e) {
+              std::unique_lock<std::mutex> inner(m);
+              done.set_value(e);
+            });
+            std::this_thread::sleep_for(std::chrono::milliseconds(2));
+          }
+          auto f = done.get_future();
+          EXPECT_FALSE(bool(waitFor(f)));
+        });
+  });
+}
+
+TPB_TEST(Channel, ClosingFailsPendingOperations) {
+  forEachBackend([](const Backend& b) {
+    runChannel(
+        b,
+        [&](channel::Channel& ch) {
+          std::vector<uint8_t> buf(100);
+          std::promise<Error> pr;
+          ch.recv(CpuBuffer{buf.data()}, buf.size(), [&](const Error& e) { pr.set_value(e); });
+          ch.close();
+          auto f = pr.get_future();
+          EXPECT_TRUE(bool(waitFor(f)));
+        },
+        [&](channel::Channel&) {});
+  });
+}
+
+TPB_TEST(Channel, XthDoesNotMatchAcrossProcessesAndCmaDoes) {
+  ProcessPeers::run(
+      [](const ProcessPeers::Side& me) {
+        auto xth = channel::xth::create();
+        auto cma = channel::cma::create();
+        me.send(xth->deviceDescriptors().at(Device(kCpuDeviceType, 0)));
+        me.send(cma->isViable() ? cma->deviceDescriptors().at(Device(kCpuDeviceType, 0)) : std::string("n/a"));
+        me.recv();
+        xth->join();
+        cma->join();
+      },
+      [](const ProcessPeers::Side& me) {
+        auto xth = channel::xth::create();
+        auto cma = channel::cma::create();
+        std::string remoteXth = me.recv(), remoteCma = me.recv();
+        const std::string& localXth = xth->deviceDescriptors().at(Device(kCpuDeviceType, 0));
+        EXPECT_FALSE(xth->canCommunicateWithRemote(localXth, remoteXth));
+        if (cma->isViable() && remoteCma != "n/a") {
+          const std::string& localCma = cma->deviceDescriptors().at(Device(kCpuDeviceType, 0));
+          EXPECT_TRUE(cma->canCommunicateWithRemote(localCma, remoteCma));
+        }
+        me.send("done");
+        xth->join();
+        cma->join();
+      });
+}
+
+TPB_TEST(Channel, NonViableBackendsDegradeGracefully) {
+  auto gdr = channel::cuda_gdr::create();
+  EXPECT_FALSE(gdr->isViable());
+  EXPECT_TRUE(gdr->deviceDescriptors().empty());
+  auto ibv = transport::ibv::create();
+  EXPECT_FALSE(ibv->isViable());
+  // Registration silently skips them.
+  Context ctx;
+  ctx.registerTransport(0, "ibv", ibv);
+  ctx.registerChannel(0, "cuda_gdr", gdr);
+  ctx.registerTransport(1, "uv", transport::uv::create());
+  EXPECT_THROWS(ctx.listen({"ibv://127.0.0.1"}));
+  ctx.join();
+}
+
+TPB_TEST(Channel, CudaBasicNeverServesCpuToCpu) {
+  auto cb = channel::cuda_basic::create(channel::basic::create());
+  if (!cb->isViable()) return;  // no GPU here: nothing to check
+  const auto& d = cb->deviceDescriptors();
+  const std::string& cpu = d.at(Device(kCpuDeviceType, 0));
+  EXPECT_FALSE(cb->canCommunicateWithRemote(cpu, cpu));
+  cb->join();
+}
+
+// Through a full pipe: the best CPU channel wins per the priorities, and the data arrives.
+TPB_TEST(Channel, PipeSelectsCmaAcrossProcessesAndXthInside) {
+  auto make = [](const std::string& name) {
+    auto ctx = std::make_shared<Context>(ContextOptions().name(name));
+    ctx->registerTransport(0, "uv", transport::uv::create());
+    ctx->registerTransport(1, "shm", transport::shm::create());
+    ctx->registerChannel(0, "basic", channel::basic::create());
+    ctx->registerChannel(10, "cma", channel::cma::create());
+    ctx->registerChannel(20, "xth", channel::xth::create());
+    return ctx;
+  };
+  auto data = pattern(2u << 20, 77);
+  ProcessPeers::run(
+      [&](const ProcessPeers::Side& me) {
+        auto ctx = make("server");
+        auto l = ctx->listen({"uv://127.0.0.1", "shm://"});
+        me.send(l->url("uv"));
+        std::promise<std::shared_ptr<Pipe>> pp;
+        l->accept([&](const Error&, std::shared_ptr<Pipe> p) { pp.set_value(p); });
+        auto fp = pp.get_future();
+        auto pipe = waitFor(fp);
+        std::promise<Descriptor> pd;
+        pipe->readDescriptor([&](const Error&, Descriptor d) { pd.set_value(d); });
+        auto fd = pd.get_future();
+        Descriptor d = waitFor(fd);
+        std::vector<uint8_t> got(d.tensors.at(0).length);
+        Allocation a;
+        Allocation::Tensor t;
+        t.buffer = CpuBuffer{got.data()};
+        a.tensors.push_back(t);
+        std::promise<Error> pr;
+        pipe->read(a, [&](const Error& e) { pr.set_value(e); });
+        auto fr = pr.get_future();
+        EXPECT_FALSE(bool(waitFor(fr)));
+        EXPECT_TRUE(got == data);
+        auto stats = ctx->stats();
+        const bool cmaViable = channel::cma::create()->isViable();
+        EXPECT_EQ(stats.bytesPerChannel[cmaViable ? "cma" : "basic"], uint64_t(data.size()));
+        me.recv();
+        ctx->join();
+      },
+      [&](const ProcessPeers::Side& me) {
+        auto ctx = make("client");
+        auto pipe = ctx->connect(me.recv());
+        auto copy = data;
+        Message m;
+        Message::Tensor t;
+        t.buffer = CpuBuffer{copy.data()};
+        t.length = copy.size();
+        m.tensors.push_back(t);
+        std::promise<Error> pw;
+        pipe->write(m, [&](const Error& e) { pw.set_value(e); });
+        auto fw = pw.get_future();
+        EXPECT_FALSE(bool(waitFor(fw)));
+        me.send("done");
+        ctx->join();
+      });
+}

@@ -1,0 +1,238 @@
+// Unit tests of the common runtime: byte ring (wrap-around, partial reads and writes, a forked
+// producer), ordered operation queue, rearmable callbacks, the on-demand loop, the completion
+// poller, system probes. (Reference counterparts: tensorpipe/test/common/ringbuffer_test.cc,
+// shm_ringbuffer_test.cc, epoll_loop_test.cc.)
+#include <atomic>
+#include <random>
+
+#include "common/callback.h"
+#include "common/epoll_loop.h"
+#include "common/loop.h"
+#include "common/ops.h"
+#include "common/poller.h"
+#include "common/ringbuffer.h"
+#include "common/shm_segment.h"
+#include "common/system.h"
+#include "test_util.h"
+
+using namespace tpb;
+using namespace tpbtest;
+
+TPB_TEST(Common, RingWriteReadAndWrap) {
+  std::vector<uint8_t> mem(Ring::bytesNeeded(64));
+  Ring ring(mem.data(), 64, true);
+  EXPECT_TRUE(ring.valid(mem.size()));
+  EXPECT_EQ(ring.freeBytes(), uint64_t(64));
+  uint8_t in[48], out[48];
+  for (int i = 0; i < 48; ++i) in[i] = static_cast<uint8_t>(i);
+  EXPECT_EQ(ring.write(in, 48), uint64_t(48));
+  EXPECT_EQ(ring.usedBytes(), uint64_t(48));
+  EXPECT_EQ(ring.read(out, 40), uint64_t(40));
+  EXPECT_TRUE(std::memcmp(in, out, 40) == 0);
+  // 8 left; writing 48 more wraps around the end of the data area.
+  EXPECT_EQ(ring.write(in, 48), uint64_t(48));
+  EXPECT_EQ(ring.freeBytes(), uint64_t(8));
+  // A write larger than the free space is partial.
+  EXPECT_EQ(ring.write(in, 20), uint64_t(8));
+  EXPECT_EQ(ring.write(in, 1), uint64_t(0));
+  EXPECT_EQ(ring.read(out, 8), uint64_t(8));
+  EXPECT_TRUE(std::memcmp(in + 40, out, 8) == 0);
+  EXPECT_EQ(ring.read(out, 48), uint64_t(48));
+  EXPECT_TRUE(std::memcmp(in, out, 48) == 0);
+  EXPECT_EQ(ring.read(out, 48), uint64_t(8));
+  EXPECT_EQ(ring.read(out, 1), uint64_t(0));
+}
+
+TPB_TEST(Common, RingBetweenProcessesThroughSharedMemory) {
+  auto [e, seg] = ShmSegment::create(Ring::bytesNeeded(4096));
+  EXPECT_FALSE(bool(e));
+  Ring ring(seg.ptr(), 4096, true);
+  constexpr size_t kTotal = 1 << 20;
+  pid_t pid = ::fork();
+  if (pid == 0) {
+    // producer: a deterministic byte stream, written in odd-sized pieces
+    std::mt19937 rng(1);
+    size_t sent = 0;
+    std::vector<uint8_t> buf(997);
+    while (sent < kTotal) {
+      size_t n = std::min(buf.size(), kTotal - sent);
+      for (size_t i = 0; i < n; ++i) buf[i] = static_cast<uint8_t>((sent + i) * 31);
+      size_t off = 0;
+      while (off < n) off += ring.write(buf.data() + off, n - off);
+      sent += n;
+    }
+    ::_exit(0);
+  }
+  size_t got = 0;
+  std::vector<uint8_t> buf(1500);
+  auto deadline = std::chrono::steady_clock::now() + std::chrono::seconds(30);
+  while (got < kTotal) {
+    uint64_t n = ring.read(buf.data(), buf.size());
+    for (uint64_t i = 0; i < n; ++i) EXPECT_EQ(int(buf[i]), int(static_cast<uint8_t>((got + i) * 31)));
+    got += n;
+    EXPECT_TRUE(std::chrono::steady_clock::now() < deadline);
+  }
+  int st = 0;
+  ::waitpid(pid, &st, 0);
+  EXPECT_TRUE(WIFEXITED(st) && WEXITSTATUS(st) == 0);
+}
+
+TPB_TEST(Common, ShmSegmentIsSharedThroughItsFd) {
+  auto [e, seg] = ShmSegment::create(1 << 16);
+  EXPECT_FALSE(bool(e));
+  std::memset(seg.ptr(), 0x5a, seg.size());
+  auto [e2, again] = ShmSegment::load(::dup(seg.fd()));
+  EXPECT_FALSE(bool(e2));
+  EXPECT_EQ(again.size(), seg.size());
+  EXPECT_EQ(int(static_cast<uint8_t*>(again.ptr())[12345]), 0x5a);
+  static_cast<uint8_t*>(again.ptr())[7] = 9;
+  EXPECT_EQ(int(static_cast<uint8_t*>(seg.ptr())[7]), 9);
+}
+
+namespace {
+struct TestOp {
+  enum State { UNINITIALIZED, STARTED, FINISHED };
+  int64_t sequenceNumber = -1;
+  State state = UNINITIALIZED;
+  bool ready = false;
+};
+}  // namespace
+
+TPB_TEST(Common, OpQueueFinishesInOrderEvenWhenLaterOpsAreReadyFirst) {
+  std::vector<int64_t> finished;
+  OpQueue<TestOp>* qp = nullptr;
+  OpQueue<TestOp> q([&](TestOp& op, TestOp::State prev) {
+    OpQueue<TestOp>::attemptTransition(op, TestOp::UNINITIALIZED, TestOp::STARTED, prev >= TestOp::STARTED);
+    OpQueue<TestOp>::attemptTransition(op, TestOp::STARTED, TestOp::FINISHED, op.ready && prev == TestOp::FINISHED,
+                                       [&]() { finished.push_back(op.sequenceNumber); });
+  });
+  qp = &q;
+  (void)qp;
+  for (int i = 0; i < 4; ++i) q.advanceOperation(q.emplaceBack());
+  EXPECT_EQ(q.size(), size_t(4));
+  // Later operations become ready first: nothing may finish before operation 0.
+  for (int64_t seq : {3, 1, 2}) {
+    q.findOperation(seq)->ready = true;
+    q.advanceOperation(seq);
+  }
+  EXPECT_TRUE(finished.empty());
+  q.findOperation(0)->ready = true;
+  q.advanceOperation(0);
+  EXPECT_EQ(finished.size(), size_t(4));
+  for (int i = 0; i < 4; ++i) EXPECT_EQ(finished[i], int64_t(i));
+  EXPECT_TRUE(q.empty());
+  EXPECT_TRUE(q.findOperation(2) == nullptr);
+}
+
+TPB_TEST(Common, RearmableCallbackPairsEitherOrder) {
+  RearmableCallback<int, std::string> cb;
+  std::vector<std::pair<int, std::string>> seen;
+  cb.trigger(1, "early");  // result first: stored
+  EXPECT_EQ(cb.numStored(), size_t(1));
+  cb.arm([&](int a, std::string s) { seen.emplace_back(a, s); });
+  EXPECT_EQ(seen.size(), size_t(1));
+  cb.arm([&](int a, std::string s) { seen.emplace_back(a, s); });  // callback first: stored
+  EXPECT_EQ(cb.numArmed(), size_t(1));
+  cb.trigger(2, "late");
+  EXPECT_EQ(seen.size(), size_t(2));
+  EXPECT_EQ(seen[1].second, std::string("late"));
+  cb.arm([&](int a, std::string s) { seen.emplace_back(a, s); });
+  cb.triggerAll([] { return std::make_tuple(-1, std::string("closed")); });
+  EXPECT_EQ(seen.back().first, -1);
+}
+
+TPB_TEST(Common, OnDemandLoopRunsOneTaskAtATimeAndNeverNests) {
+  OnDemandLoop loop;
+  std::atomic<int> inside{0}, maxInside{0}, count{0};
+  std::vector<std::thread> threads;
+  for (int t = 0; t < 8; ++t) {
+    threads.emplace_back([&] {
+      for (int i = 0; i < 200; ++i) {
+        loop.deferToLoop([&] {
+          int now = ++inside;
+          int prev = maxInside.load();
+          while (now > prev && !maxInside.compare_exchange_weak(prev, now)) {}
+          // deferring from inside the loop queues instead of nesting
+          if (count.load() % 50 == 0) loop.deferToLoop([&] { ++count; });
+          ++count;
+          --inside;
+        });
+      }
+    });
+  }
+  for (auto& t : threads) t.join();
+  loop.runInLoop([] {});
+  EXPECT_EQ(maxInside.load(), 1);
+  EXPECT_TRUE(count.load() >= 1600);
+  bool in = false;
+  loop.runInLoop([&] { in = loop.inLoop(); });
+  EXPECT_TRUE(in);
+  EXPECT_FALSE(loop.inLoop());
+}
+
+TPB_TEST(Common, EpollLoopDefersAndDeliversFdEvents) {
+  struct Handler : EpollEventHandler {
+    std::promise<int> got;
+    int fd = -1;
+    void handleEventsFromLoop(int events) override {
+      char c;
+      if (::read(fd, &c, 1) == 1) got.set_value(events);  // level-triggered: consume the byte
+    }
+  };
+  EpollLoop loop("TP_test_loop");
+  int fds[2];
+  EXPECT_EQ(::pipe(fds), 0);
+  auto h = std::make_shared<Handler>();
+  h->fd = fds[0];
+  loop.runInLoop([&] { loop.registerDescriptor(fds[0], EPOLLIN, h); });
+  EXPECT_EQ(::write(fds[1], "x", 1), ssize_t(1));
+  auto f = h->got.get_future();
+  EXPECT_TRUE((waitFor(f) & EPOLLIN) != 0);
+  loop.runInLoop([&] { loop.unregisterDescriptor(fds[0]); });
+  std::promise<std::thread::id> where;
+  loop.deferToLoop([&] { where.set_value(std::this_thread::get_id()); });
+  auto fw = where.get_future();
+  EXPECT_TRUE(waitFor(fw) != std::this_thread::get_id());
+  loop.join();
+  // After the thread is gone, deferrals still run (on the caller).
+  bool ran = false;
+  loop.deferToLoop([&] { ran = true; });
+  EXPECT_TRUE(ran);
+  ::close(fds[0]);
+  ::close(fds[1]);
+}
+
+TPB_TEST(Common, PollerFiresOnceWhenTheConditionTurnsTrue) {
+  Poller poller;
+  std::atomic<bool> flag{false};
+  std::atomic<int> fired{0};
+  std::promise<void> done;
+  poller.watch([&] { return flag.load(); }, [&] {
+    ++fired;
+    done.set_value();
+  });
+  std::this_thread::sleep_for(std::chrono::milliseconds(20));
+  EXPECT_EQ(fired.load(), 0);
+  flag = true;
+  auto f = done.get_future();
+  waitFor(f);
+  std::this_thread::sleep_for(std::chrono::milliseconds(5));
+  EXPECT_EQ(fired.load(), 1);
+  // Stopping fires what is still pending, so nobody waits forever.
+  std::atomic<int> late{0};
+  poller.watch([] { return false; }, [&] { ++late; });
+  poller.stop();
+  EXPECT_EQ(late.load(), 1);
+}
+
+TPB_TEST(Common, SystemProbes) {
+  auto boot = getBootID();
+  EXPECT_TRUE(boot.has_value() && boot->size() >= 8);
+  auto net = getLinuxNamespaceId(LinuxNamespace::kNet);
+  auto pid = getLinuxNamespaceId(LinuxNamespace::kPid);
+  EXPECT_TRUE(net.has_value() && pid.has_value());
+  EXPECT_TRUE(net->find('_') != std::string::npos);
+  EXPECT_TRUE(isPow2(64) && !isPow2(65) && !isPow2(0));
+  EXPECT_EQ(nextPow2(65), uint64_t(128));
+  EXPECT_EQ(nextPow2(64), uint64_t(64));
+}

@@ -182,7 +182,8 @@ class ProcessPeers {
   using Fn = std::function<void(const Side&)>;
 
   // Returns the two exit codes; 0/0 means both sides passed.
-  static void run(Fn server, Fn client) {
+  // `clientMayBeKilled`: the client is expected to end by a signal (tests that kill a peer).
+  static void run(Fn server, Fn client, bool clientMayBeKilled = false) {
     int s2c[2], c2s[2];
     if (::pipe(s2c) != 0 || ::pipe(c2s) != 0) throw TestFailure("pipe");
     pid_t ps = spawn([&] { ::close(s2c[0]); ::close(c2s[1]); Side me{c2s[0], s2c[1]}; server(me); });
@@ -192,7 +193,7 @@ class ProcessPeers {
     ::waitpid(ps, &ss, 0);
     ::waitpid(pc, &sc, 0);
     bool okS = WIFEXITED(ss) && WEXITSTATUS(ss) == 0;
-    bool okC = WIFEXITED(sc) && WEXITSTATUS(sc) == 0;
+    bool okC = (WIFEXITED(sc) && WEXITSTATUS(sc) == 0) || (clientMayBeKilled && WIFSIGNALED(sc));
     if (!okS || !okC) {
       std::ostringstream m;
       m << "peer processes failed: server status " << ss << ", client status " << sc;

@@ -59,6 +59,11 @@ class Message:
     payloads: Sequence[bytes] = ()
     metadata: bytes = b""
     target_devices: Optional[Sequence[Optional[str]]] = None  # e.g. ["cuda:1", None]
+    # Per-payload / per-tensor metadata strings. Tensor metadata defaults to a small JSON record
+    # of dtype and shape, which is what lets the receiving side rebuild torch tensors; override it
+    # only when talking to a peer that expects its own format (then tensors arrive as uint8).
+    payload_metadata: Optional[Sequence[bytes]] = None
+    tensor_metadata: Optional[Sequence[bytes]] = None
 
 
 @dataclass
@@ -66,6 +71,8 @@ class ReceivedMessage:
     metadata: bytes = b""
     payloads: List[bytearray] = field(default_factory=list)
     tensors: List[torch.Tensor] = field(default_factory=list)
+    payload_metadata: List[bytes] = field(default_factory=list)
+    tensor_metadata: List[bytes] = field(default_factory=list)
 
 
 class Pipe:
@@ -86,14 +93,16 @@ class Pipe:
     # ---- native-shaped API ----
     def write(self, message: Message, callback: Callable[[str], None]) -> None:
         out = _C.OutgoingMessage(bytes(message.metadata))
-        for p in message.payloads:
-            out.add_payload(p if isinstance(p, (bytes, bytearray, memoryview)) else bytes(p))
+        pmeta = message.payload_metadata or [b""] * len(message.payloads)
+        for p, pm in zip(message.payloads, pmeta):
+            out.add_payload(p if isinstance(p, (bytes, bytearray, memoryview)) else bytes(p), bytes(pm))
         targets = message.target_devices or [None] * len(message.tensors)
-        for t, target in zip(message.tensors, targets):
-            self._add_tensor(out, t, target)
+        tmeta = message.tensor_metadata or [None] * len(message.tensors)
+        for t, target, tm in zip(message.tensors, targets, tmeta):
+            self._add_tensor(out, t, target, tm)
         self._p.write(out, callback)
 
-    def _add_tensor(self, out, t: torch.Tensor, target: Optional[str]) -> None:
+    def _add_tensor(self, out, t: torch.Tensor, target: Optional[str], metadata: Optional[bytes] = None) -> None:
         local = _device_str(t.device)
         view = None
         code = DTYPE_CODES.get(t.dtype, 0)
@@ -109,7 +118,8 @@ class Pipe:
                 view = (t.shape[0], t.shape[1], t.stride(0), t.stride(1))
             else:
                 t = t.contiguous()
-        meta = json.dumps({"dtype": str(t.dtype).replace("torch.", ""), "shape": list(t.shape)}).encode()
+        meta = metadata if metadata is not None else json.dumps(
+            {"dtype": str(t.dtype).replace("torch.", ""), "shape": list(t.shape)}).encode()
         dev_type, dev_index = local.split(":")
         out.add_tensor(
             t.data_ptr(),
@@ -132,7 +142,9 @@ class Pipe:
 
     # ---- conveniences ----
     def send(self, tensors: Sequence[torch.Tensor] = (), payloads: Sequence[bytes] = (), metadata: bytes = b"",
-             target_devices: Optional[Sequence[Optional[str]]] = None) -> Future:
+             target_devices: Optional[Sequence[Optional[str]]] = None,
+             payload_metadata: Optional[Sequence[bytes]] = None,
+             tensor_metadata: Optional[Sequence[bytes]] = None) -> Future:
         fut: Future = Future()
 
         def done(err: str) -> None:
@@ -141,7 +153,7 @@ class Pipe:
             else:
                 fut.set_result(None)
 
-        self.write(Message(tensors, payloads, metadata, target_devices), done)
+        self.write(Message(tensors, payloads, metadata, target_devices, payload_metadata, tensor_metadata), done)
         return fut
 
     def recv(self, device: Optional[str] = None, cast: Optional[Dict[int, torch.dtype]] = None,
@@ -162,9 +174,16 @@ class Pipe:
                 for p in desc["payloads"]:
                     buf = bytearray(p["length"])
                     msg.payloads.append(buf)
+                    msg.payload_metadata.append(p["metadata"])
                     alloc.add_payload(buf)
                 for i, td in enumerate(desc["tensors"]):
-                    meta = json.loads(td["metadata"].decode()) if td["metadata"] else None
+                    msg.tensor_metadata.append(td["metadata"])
+                    try:
+                        meta = json.loads(td["metadata"].decode())
+                        if not (isinstance(meta, dict) and meta.get("dtype") in _DTYPE_BY_NAME and "shape" in meta):
+                            meta = None
+                    except (ValueError, UnicodeDecodeError):
+                        meta = None  # a foreign peer's metadata: deliver the bytes as they are
                     src_dtype = _DTYPE_BY_NAME[meta["dtype"]] if meta else torch.uint8
                     shape = meta["shape"] if meta else [td["length"]]
                     want = cast.get(i)

@@ -366,6 +366,19 @@ PYBIND11_MODULE(_C, m) {
            py::arg("verify") = false, py::call_guard<py::gil_scoped_release>())
       .def("run_latency", &tools::RingBench::runLatency, py::arg("bytes"), py::arg("laps"), py::arg("rank") = 0,
            py::arg("world") = 1, py::call_guard<py::gil_scoped_release>())
+      .def("connect_mesh", &tools::RingBench::connectMesh, py::call_guard<py::gil_scoped_release>())
+      .def(
+          "run_mixed_mesh",
+          [](tools::RingBench& self, int steps, uint64_t seed) {
+            uint64_t bytes = 0;
+            tools::PhaseResult r;
+            {
+              py::gil_scoped_release nogil;
+              r = self.runMixedMesh(steps, seed, &bytes);
+            }
+            return py::make_tuple(r, bytes);
+          },
+          py::arg("steps"), py::arg("seed") = 1)
       .def(
           "run_mixed",
           [](tools::RingBench& self, int steps, uint64_t seed) {

@@ -44,6 +44,12 @@ struct RingBench::Impl {
   unsigned long long* mismatches = nullptr;
   cudaEvent_t evStart = nullptr, evEnd = nullptr;
   uint64_t srcSeed = 0;
+  std::vector<std::shared_ptr<Pipe>> meshSend, meshRecv;  // all-pairs mode
+  std::vector<int> meshSendDevice;
+
+  PhaseResult runMixedOn(const std::vector<std::shared_ptr<Pipe>>& sendPipes, const std::vector<int>& sendDevices,
+                         const std::vector<std::shared_ptr<Pipe>>& recvPipes, int steps, uint64_t seed,
+                         uint64_t* bytesPerMessage);
 
   std::shared_ptr<Context> makeContext(const std::string& name) {
     auto ctx = std::make_shared<Context>(ContextOptions().name(name));
@@ -113,6 +119,8 @@ RingBench::~RingBench() {
   Impl& m = *impl_;
   m.sendPipe.reset();
   m.recvPipe.reset();
+  m.meshSend.clear();
+  m.meshRecv.clear();
   m.listener.reset();
   if (m.sendCtx) m.sendCtx->join();
   if (m.recvCtx) m.recvCtx->join();
@@ -369,48 +377,112 @@ std::vector<double> RingBench::runLatency(size_t bytes, int laps, int rank, int 
   return st->samples;
 }
 
-PhaseResult RingBench::runMixed(int steps, uint64_t seed, uint64_t* bytesPerStep, bool verify) {
-  Impl& m = *impl_;
-  TPB_CUDA_CHECK(cudaSetDevice(m.opts.device));
-  // 64 tensors: dtype cycles fp32, bf16, int64; sizes log-uniform in [1 KiB, 16 MiB]; every 4th
-  // is a transposed 2-D view; every other fp32 tensor is cast to bf16 by the receiver.
-  struct Spec {
-    DType dtype;
-    uint64_t elems;
-    bool transposed;
-    bool cast;
-    int64_t rows, cols;
-    uint64_t srcOff, dstOff, srcBytes, dstBytes;
-  };
+namespace {
+// 64 tensors: dtype cycles fp32, bf16, int64; sizes log-uniform in [1 KiB, 16 MiB]; every 4th is a
+// transposed 2-D view; every other fp32 tensor is cast to bf16 by the receiver.
+struct MixedSpec {
+  DType dtype;
+  bool transposed;
+  bool cast;
+  int64_t rows, cols;
+  uint64_t srcOff, dstOff, srcBytes, dstBytes;
+};
+struct MixedLayout {
+  std::vector<MixedSpec> specs;
+  uint64_t srcTotal = 0, dstTotal = 0, delivered = 0;
+};
+MixedLayout makeMixedLayout(uint64_t seed) {
+  MixedLayout L;
   std::mt19937_64 rng(seed);
-  std::vector<Spec> specs;
-  uint64_t srcCursor = 0, dstCursor = 0, wire = 0;
   int fp32Count = 0;
   for (int i = 0; i < 64; ++i) {
-    Spec s{};
+    MixedSpec s{};
     s.dtype = i % 3 == 0 ? DType::kF32 : (i % 3 == 1 ? DType::kBF16 : DType::kI64);
     const double lg = std::log(1024.0) + (std::log(16.0 * 1024 * 1024) - std::log(1024.0)) *
                                               (static_cast<double>(rng() % 100000) / 100000.0);
-    uint64_t bytes = static_cast<uint64_t>(std::exp(lg));
+    const uint64_t bytes = static_cast<uint64_t>(std::exp(lg));
     const uint64_t es = dtypeSize(s.dtype);
     s.transposed = i % 4 == 3;
     s.cols = 64;
     s.rows = static_cast<int64_t>(std::max<uint64_t>(1, bytes / es / s.cols));
-    s.elems = static_cast<uint64_t>(s.rows) * s.cols;
-    s.srcBytes = s.elems * es;
+    const uint64_t elems = static_cast<uint64_t>(s.rows) * s.cols;
+    s.srcBytes = elems * es;
     if (s.dtype == DType::kF32) s.cast = (fp32Count++ % 2) == 0;
-    s.dstBytes = s.cast ? s.elems * 2 : s.srcBytes;
-    s.srcOff = srcCursor;
-    s.dstOff = dstCursor;
-    srcCursor += (s.srcBytes + 255) / 256 * 256;
-    dstCursor += (s.dstBytes + 255) / 256 * 256;
-    wire += s.dstBytes;
-    specs.push_back(s);
+    s.dstBytes = s.cast ? elems * 2 : s.srcBytes;
+    s.srcOff = L.srcTotal;
+    s.dstOff = L.dstTotal;
+    L.srcTotal += (s.srcBytes + 255) / 256 * 256;
+    L.dstTotal += (s.dstBytes + 255) / 256 * 256;
+    L.delivered += s.dstBytes;
+    L.specs.push_back(s);
   }
-  if (srcCursor > m.opts.maxBytes) throw std::runtime_error("mixed message larger than the benchmark's buffers");
-  if (bytesPerStep) *bytesPerStep = wire;
+  return L;
+}
+}  // namespace
+
+void RingBench::connectMesh(const std::vector<std::string>& urls, int rank) {
+  Impl& m = *impl_;
+  const int world = static_cast<int>(urls.size());
+  std::mutex mu;
+  std::vector<std::shared_ptr<Pipe>> accepted;
+  std::promise<void> all;
+  std::function<void()> arm = [&]() {
+    m.listener->accept([&](const Error& e, std::shared_ptr<Pipe> p) {
+      if (e) return;
+      bool done;
+      {
+        std::unique_lock<std::mutex> l(mu);
+        accepted.push_back(std::move(p));
+        done = static_cast<int>(accepted.size()) == world - 1;
+      }
+      if (done) all.set_value();
+      else arm();
+    });
+  };
+  if (world > 1) arm();
+  for (int j = 0; j < world; ++j) {
+    if (j == rank) continue;
+    std::string url = urls[j];
+    int dev = m.opts.device;
+    auto bar = url.rfind('|');
+    if (bar != std::string::npos) {
+      dev = std::stoi(url.substr(bar + 1));
+      url = url.substr(0, bar);
+    }
+    m.meshSend.push_back(m.sendCtx->connect(url));
+    m.meshSendDevice.push_back(dev);
+  }
+  if (world > 1) {
+    auto f = all.get_future();
+    waitOrThrow(f, 120, "accepting the mesh's pipes");
+  }
+  m.meshRecv = accepted;
+}
+
+PhaseResult RingBench::runMixedMesh(int steps, uint64_t seed, uint64_t* bytesPerMessage) {
+  Impl& m = *impl_;
+  return m.runMixedOn(m.meshSend, m.meshSendDevice, m.meshRecv, steps, seed, bytesPerMessage);
+}
+
+PhaseResult RingBench::runMixed(int steps, uint64_t seed, uint64_t* bytesPerStep, bool verify) {
   (void)verify;
+  Impl& m = *impl_;
+  return m.runMixedOn({m.sendPipe}, {m.nextDevice}, {m.recvPipe}, steps, seed, bytesPerStep);
+}
+
+PhaseResult RingBench::Impl::runMixedOn(const std::vector<std::shared_ptr<Pipe>>& sendPipes,
+                                        const std::vector<int>& sendDevices,
+                                        const std::vector<std::shared_ptr<Pipe>>& recvPipes, int steps,
+                                        uint64_t seed, uint64_t* bytesPerMessage) {
+  Impl& m = *this;
+  TPB_CUDA_CHECK(cudaSetDevice(m.opts.device));
+  auto layout = std::make_shared<MixedLayout>(makeMixedLayout(seed));
+  if (layout->srcTotal > m.opts.maxBytes || layout->dstTotal * recvPipes.size() > m.opts.maxBytes)
+    throw std::runtime_error("mixed messages larger than the benchmark's buffers");
+  if (bytesPerMessage) *bytesPerMessage = layout->delivered;
   const uint64_t launches0 = kernels::launchCount();
+  const int totalRecv = steps * static_cast<int>(recvPipes.size());
+  const int totalSend = steps * static_cast<int>(sendPipes.size());
 
   struct State {
     std::mutex mu;
@@ -421,11 +493,13 @@ PhaseResult RingBench::runMixed(int steps, uint64_t seed, uint64_t* bytesPerStep
   };
   auto st = std::make_shared<State>();
   Impl* mp = &m;
-  auto specsPtr = std::make_shared<std::vector<Spec>>(specs);
 
-  auto armRead = std::make_shared<std::function<void()>>();
-  *armRead = [=]() {
-    mp->recvPipe->readDescriptor([=](const Error& e, Descriptor d) {
+  // One receive chain per incoming pipe, each into its own region of the destination buffer.
+  auto armRead = std::make_shared<std::function<void(size_t, int)>>();
+  *armRead = [=](size_t k, int remaining) {
+    if (remaining == 0) return;
+    auto pipe = recvPipes[k];
+    pipe->readDescriptor([=](const Error& e, Descriptor d) {
       auto fail = [&](const Error& err) {
         std::unique_lock<std::mutex> l(st->mu);
         st->error = err;
@@ -433,21 +507,21 @@ PhaseResult RingBench::runMixed(int steps, uint64_t seed, uint64_t* bytesPerStep
       };
       if (e) return fail(e);
       Allocation a;
-      for (const Spec& s : *specsPtr) {
+      for (const MixedSpec& s : layout->specs) {
         Allocation::Tensor t;
-        t.buffer = CudaBuffer{mp->dst[0] + s.dstOff, mp->recvStream, mp->opts.device};
+        t.buffer = CudaBuffer{mp->dst[0] + k * layout->dstTotal + s.dstOff, mp->recvStream, mp->opts.device};
         if (s.cast) {
           t.castTo = DType::kBF16;
           t.sourceDtype = DType::kF32;
         }
         a.tensors.push_back(t);
       }
-      mp->recvPipe->read(std::move(a), [=](const Error& e2) {
+      pipe->read(std::move(a), [=](const Error& e2) {
         bool last;
         {
           std::unique_lock<std::mutex> l(st->mu);
           if (e2) st->error = e2;
-          last = ++st->received == steps || bool(st->error);
+          last = ++st->received == totalRecv || bool(st->error);
         }
         if (last) {
           cudaSetDevice(mp->opts.device);
@@ -455,20 +529,22 @@ PhaseResult RingBench::runMixed(int steps, uint64_t seed, uint64_t* bytesPerStep
           std::unique_lock<std::mutex> l(st->mu);
           if (!st->recvSet) { st->recvSet = true; st->recvDone.set_value(); }
         } else {
-          (*armRead)();
+          (*armRead)(k, remaining - 1);
         }
       });
     });
   };
-  auto sendOne = std::make_shared<std::function<void()>>();
-  *sendOne = [=]() {
+  // One send chain per outgoing pipe; all of them read the same source tensors.
+  auto sendOne = std::make_shared<std::function<void(size_t, int)>>();
+  *sendOne = [=](size_t k, int remaining) {
+    if (remaining == 0) return;
     Message msg;
-    for (const Spec& s : *specsPtr) {
+    for (const MixedSpec& s : layout->specs) {
       Message::Tensor t;
       t.buffer = CudaBuffer{mp->src + s.srcOff, mp->sendStream, mp->opts.device};
       t.length = s.srcBytes;
       t.dtype = s.dtype;
-      t.targetDevice = Device(kCudaDeviceType, mp->nextDevice);
+      t.targetDevice = Device(kCudaDeviceType, sendDevices[k]);
       if (s.transposed) {
         // The buffer holds a [cols, rows] row-major matrix; we send its transpose [rows, cols].
         StridedView v;
@@ -481,36 +557,38 @@ PhaseResult RingBench::runMixed(int steps, uint64_t seed, uint64_t* bytesPerStep
       }
       msg.tensors.push_back(t);
     }
-    mp->sendPipe->write(std::move(msg), [=](const Error& e) {
-      bool more;
+    sendPipes[k]->write(std::move(msg), [=](const Error& e) {
+      bool done;
       {
         std::unique_lock<std::mutex> l(st->mu);
         if (e) st->error = e;
-        more = ++st->sent < steps && !st->error;
-        if (!more && !st->sendSet) { st->sendSet = true; st->sendDone.set_value(); }
+        done = ++st->sent == totalSend || bool(st->error);
+        if (done && !st->sendSet) { st->sendSet = true; st->sendDone.set_value(); }
       }
-      if (more) (*sendOne)();
+      if (!e) (*sendOne)(k, remaining - 1);
     });
   };
 
-  m.syncNeighbours();
+  if (recvPipes.size() == 1 && sendPipes.size() == 1) m.syncNeighbours();
   auto t0 = Clock::now();
   TPB_CUDA_CHECK(cudaEventRecord(m.evStart, m.recvStream));
-  (*armRead)();
-  (*sendOne)();
+  for (size_t k = 0; k < recvPipes.size(); ++k) (*armRead)(k, steps);
+  for (size_t k = 0; k < sendPipes.size(); ++k) (*sendOne)(k, steps);
   auto fr = st->recvDone.get_future();
   auto fs = st->sendDone.get_future();
-  waitOrThrow(fr, 300, "receiving");
-  waitOrThrow(fs, 300, "sending");
+  if (totalRecv > 0) waitOrThrow(fr, 300, "receiving");
+  if (totalSend > 0) waitOrThrow(fs, 300, "sending");
   *armRead = nullptr;
   *sendOne = nullptr;
   failOn(st->error, "mixed messages");
-  TPB_CUDA_CHECK(cudaEventSynchronize(m.evEnd));
   PhaseResult r;
+  if (totalRecv > 0) {
+    TPB_CUDA_CHECK(cudaEventSynchronize(m.evEnd));
+    float ms = 0;
+    TPB_CUDA_CHECK(cudaEventElapsedTime(&ms, m.evStart, m.evEnd));
+    r.deviceMs = ms;
+  }
   r.hostMs = msSince(t0);
-  float ms = 0;
-  TPB_CUDA_CHECK(cudaEventElapsedTime(&ms, m.evStart, m.evEnd));
-  r.deviceMs = ms;
   TPB_CUDA_CHECK(cudaStreamSynchronize(m.sendStream));
   r.kernelLaunches = kernels::launchCount() - launches0;
   return r;

@@ -56,6 +56,11 @@ class RingBench {
   // tensors cast to bf16 by the receiver), `steps` times. Returns the bytes delivered per step.
   PhaseResult runMixed(int steps, uint64_t seed, uint64_t* bytesPerStep, bool verify);
 
+  // All-pairs mode: dial every other rank's listener ("url|device" per rank, own entry ignored) and
+  // accept everybody's pipe; then every rank sends the mixed message to every other rank at once.
+  void connectMesh(const std::vector<std::string>& urls, int rank);
+  PhaseResult runMixedMesh(int steps, uint64_t seed, uint64_t* bytesPerMessage);
+
  private:
   struct Impl;
   std::unique_ptr<Impl> impl_;

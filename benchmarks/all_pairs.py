@@ -64,7 +64,7 @@ def native(args, r):
             "aggregate_GBps": round(per_gpu_out * r.world / (ms * 1e-3) / 1e9, 2),
             "per_gpu_egress_GBps": round(per_gpu_out / (ms * 1e-3) / 1e9, 2),
             "nvlink_roofline_fraction_of_770GBps": round(per_gpu_out / (ms * 1e-3) / 1e9 / 770.0, 3),
-            "kernel_launches_per_message": res.kernel_launches / (args.iters * 2 * (r.world - 1)),
+            "kernel_launches_per_message": res.kernel_launches / (args.iters * (r.world - 1)),
         }), flush=True)
     del rb
     r.finish()
@@ -83,7 +83,8 @@ def main():
     if not args.python_api:
         return native(args, r)
     ctx, listener, pipes = mesh_pipes(r, "ap")
-    tensors, casts, delivered = make_message(1234, r.device)  # the same shapes on every rank
+    torch.manual_seed(1234)  # every rank builds the same message, values included
+    tensors, casts, delivered = make_message(1234, r.device)
     peers = sorted(pipes)
     devices = r.gather(r.local_rank)
     recv_bufs = {p: [torch.empty(t.shape, dtype=casts.get(i, t.dtype), device=r.device) for i, t in enumerate(tensors)]
@@ -100,7 +101,12 @@ def main():
             for m in msgs:
                 for i, (got, sent) in enumerate(zip(m.tensors, tensors)):
                     want = sent.to(casts[i]) if i in casts else sent
-                    assert torch.equal(got, want.contiguous()), f"tensor {i} differs"
+                    if not torch.equal(got, want.contiguous()):
+                        diff = (got.float() - want.contiguous().float()).abs()
+                        raise AssertionError(
+                            f"tensor {i} differs: shape {tuple(got.shape)} dtype {got.dtype} cast {i in casts} "
+                            f"bad {int((diff > 0).sum())}/{diff.numel()} max {float(diff.max())} "
+                            f"got[:4] {got.flatten()[:4].tolist()} want[:4] {want.flatten()[:4].tolist()}")
 
     one_round(check=True)  # every rank builds the same message, so each can check what it received
     for _ in range(args.warmup):

@@ -46,8 +46,10 @@ struct RingBench::Impl {
   uint64_t srcSeed = 0;
   std::vector<std::shared_ptr<Pipe>> meshSend, meshRecv;  // all-pairs mode
   std::vector<int> meshSendDevice;
+  std::vector<cudaStream_t> meshSendStream;  // one stream per destination so pushes overlap
 
   PhaseResult runMixedOn(const std::vector<std::shared_ptr<Pipe>>& sendPipes, const std::vector<int>& sendDevices,
+                         const std::vector<cudaStream_t>& sendStreams,
                          const std::vector<std::shared_ptr<Pipe>>& recvPipes, int steps, uint64_t seed,
                          uint64_t* bytesPerMessage);
 
@@ -73,7 +75,8 @@ struct RingBench::Impl {
   // A tensor-less message to the next rank and one from the previous rank: lines neighbouring
   // ranks up to within one message latency before a timed region starts (a collective barrier
   // leaves them hundreds of microseconds apart).
-  void syncNeighbours() {
+  void syncNeighbours() { syncOn(sendPipe, recvPipe); }
+  void syncOn(const std::shared_ptr<Pipe>& sendPipe, const std::shared_ptr<Pipe>& recvPipe) {
     std::promise<Error> wrote, got;
     Message m;
     m.metadata = "sync";
@@ -451,6 +454,10 @@ void RingBench::connectMesh(const std::vector<std::string>& urls, int rank) {
     }
     m.meshSend.push_back(m.sendCtx->connect(url));
     m.meshSendDevice.push_back(dev);
+    cudaStream_t st = nullptr;
+    TPB_CUDA_CHECK(cudaSetDevice(m.opts.device));
+    TPB_CUDA_CHECK(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+    m.meshSendStream.push_back(st);
   }
   if (world > 1) {
     auto f = all.get_future();
@@ -461,17 +468,18 @@ void RingBench::connectMesh(const std::vector<std::string>& urls, int rank) {
 
 PhaseResult RingBench::runMixedMesh(int steps, uint64_t seed, uint64_t* bytesPerMessage) {
   Impl& m = *impl_;
-  return m.runMixedOn(m.meshSend, m.meshSendDevice, m.meshRecv, steps, seed, bytesPerMessage);
+  return m.runMixedOn(m.meshSend, m.meshSendDevice, m.meshSendStream, m.meshRecv, steps, seed, bytesPerMessage);
 }
 
 PhaseResult RingBench::runMixed(int steps, uint64_t seed, uint64_t* bytesPerStep, bool verify) {
   (void)verify;
   Impl& m = *impl_;
-  return m.runMixedOn({m.sendPipe}, {m.nextDevice}, {m.recvPipe}, steps, seed, bytesPerStep);
+  return m.runMixedOn({m.sendPipe}, {m.nextDevice}, {m.sendStream}, {m.recvPipe}, steps, seed, bytesPerStep);
 }
 
 PhaseResult RingBench::Impl::runMixedOn(const std::vector<std::shared_ptr<Pipe>>& sendPipes,
                                         const std::vector<int>& sendDevices,
+                                        const std::vector<cudaStream_t>& sendStreams,
                                         const std::vector<std::shared_ptr<Pipe>>& recvPipes, int steps,
                                         uint64_t seed, uint64_t* bytesPerMessage) {
   Impl& m = *this;
@@ -541,7 +549,7 @@ PhaseResult RingBench::Impl::runMixedOn(const std::vector<std::shared_ptr<Pipe>>
     Message msg;
     for (const MixedSpec& s : layout->specs) {
       Message::Tensor t;
-      t.buffer = CudaBuffer{mp->src + s.srcOff, mp->sendStream, mp->opts.device};
+      t.buffer = CudaBuffer{mp->src + s.srcOff, sendStreams[k], mp->opts.device};
       t.length = s.srcBytes;
       t.dtype = s.dtype;
       t.targetDevice = Device(kCudaDeviceType, sendDevices[k]);
@@ -569,7 +577,7 @@ PhaseResult RingBench::Impl::runMixedOn(const std::vector<std::shared_ptr<Pipe>>
     });
   };
 
-  if (recvPipes.size() == 1 && sendPipes.size() == 1) m.syncNeighbours();
+  if (recvPipes.size() == 1 && sendPipes.size() == 1) m.syncOn(sendPipes[0], recvPipes[0]);
   auto t0 = Clock::now();
   TPB_CUDA_CHECK(cudaEventRecord(m.evStart, m.recvStream));
   for (size_t k = 0; k < recvPipes.size(); ++k) (*armRead)(k, steps);
@@ -589,7 +597,7 @@ PhaseResult RingBench::Impl::runMixedOn(const std::vector<std::shared_ptr<Pipe>>
     r.deviceMs = ms;
   }
   r.hostMs = msSince(t0);
-  TPB_CUDA_CHECK(cudaStreamSynchronize(m.sendStream));
+  for (cudaStream_t st : sendStreams) TPB_CUDA_CHECK(cudaStreamSynchronize(st));
   r.kernelLaunches = kernels::launchCount() - launches0;
   return r;
 }

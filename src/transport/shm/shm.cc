@@ -205,7 +205,7 @@ class Reactor final : public ThreadLoop {
     ev.data.u64 = 0;
     ::epoll_ctl(epollFd_, EPOLL_CTL_ADD, eventFd_, &ev);
     const char* s = std::getenv("TPB_SHM_SPIN_US");
-    spinUs_ = s ? std::strtol(s, nullptr, 10) : 200;
+    spinUs_ = s ? std::strtol(s, nullptr, 10) : 2000;
     startThread("TP_SHM_reactor");
   }
   ~Reactor() override {
@@ -344,7 +344,7 @@ class Reactor final : public ThreadLoop {
   ReactorQueue queue_;
   int eventFd_ = -1;
   int epollFd_ = -1;
-  long spinUs_ = 200;
+  long spinUs_ = 2000;
   std::atomic<bool> closed_{false};
   std::atomic<bool> sleeping_{false};
   std::vector<std::function<void()>> functions_;

@@ -332,12 +332,14 @@ void layoutsCase(bool crossProc, int recvDevice, int sendDevice) {
     CK(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
     for (int round = 0; round < 2; ++round) {  // round 0 rendezvous, round 1 may go through the inbox
       Descriptor d = readDescriptorSync(*pipe);
-      EXPECT_EQ(d.tensors.size(), size_t(2));
+      EXPECT_EQ(d.tensors.size(), size_t(3));
       EXPECT_EQ(d.tensors[0].length, size_t(kRows * kCols * 4));
       uint16_t* bf;
       float* plain;
+      uint16_t* flat;  // contiguous source, converted on the way
       CK(cudaMalloc(&bf, kRows * kCols * 2));
       CK(cudaMalloc(&plain, kRows * kCols * 4));
+      CK(cudaMalloc(&flat, kRows * kCols * 2));
       Allocation a;
       Allocation::Tensor t0;
       t0.buffer = CudaBuffer{bf, stream, recvDevice};
@@ -345,9 +347,19 @@ void layoutsCase(bool crossProc, int recvDevice, int sendDevice) {
       t0.sourceDtype = DType::kF32;
       Allocation::Tensor t1;
       t1.buffer = CudaBuffer{plain, stream, recvDevice};
-      a.tensors = {t0, t1};
+      Allocation::Tensor t2;
+      t2.buffer = CudaBuffer{flat, stream, recvDevice};
+      t2.castTo = DType::kBF16;
+      t2.sourceDtype = DType::kF32;
+      a.tensors = {t0, t1, t2};
       readSync(*pipe, std::move(a));
       CK(cudaStreamSynchronize(stream));
+      std::vector<uint16_t> gotFlat(kRows * kCols);
+      CK(cudaMemcpy(gotFlat.data(), flat, gotFlat.size() * 2, cudaMemcpyDeviceToHost));
+      for (int64_t c = 0; c < kCols; ++c)
+        for (int64_t r = 0; r < kRows; ++r)
+          EXPECT_EQ(gotFlat[c * kRows + r], f32ToBf16(static_cast<float>(c * 1000 + r) * 0.37f + round));
+      cudaFree(flat);
       std::vector<uint16_t> gotBf(kRows * kCols);
       std::vector<float> gotPlain(kRows * kCols);
       CK(cudaMemcpy(gotBf.data(), bf, gotBf.size() * 2, cudaMemcpyDeviceToHost));
@@ -385,6 +397,14 @@ void layoutsCase(bool crossProc, int recvDevice, int sendDevice) {
         t.length = host.size() * 4;
         t.dtype = DType::kF32;
         t.view = StridedView{DType::kF32, kRows, kCols, 1, kRows};
+        t.targetDevice = Device(kCudaDeviceType, recvDevice);
+        m.tensors.push_back(t);
+      }
+      {
+        Message::Tensor t;  // the same storage, sent as it lies in memory
+        t.buffer = CudaBuffer{dev, stream, sendDevice};
+        t.length = host.size() * 4;
+        t.dtype = DType::kF32;
         t.targetDevice = Device(kCudaDeviceType, recvDevice);
         m.tensors.push_back(t);
       }

@@ -39,6 +39,7 @@ def parse_args():
     p.add_argument("--depth", type=int, default=2, help="writes kept in flight")
     p.add_argument("--no-sweep", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--e2e-only", action="store_true", help="skip everything but the end-to-end measurement")
     p.add_argument("--no-bulk", action="store_true", help="plain ld/st path instead of TMA bulk copies")
     p.add_argument("--max-sweep-bytes", type=int, default=1 << 30)
     return p.parse_args()
@@ -159,6 +160,13 @@ def run_native(args):
         dist.all_gather_object(out, obj)
         return out
 
+    if args.e2e_only:
+        e2e = run_e2e(args, tpb, torch, dist, rank, world, local_rank, barrier, max_over_ranks, gather)
+        if rank == 0:
+            print(json.dumps({"impl": "native", "n_gpus": world, "e2e": e2e}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     max_bytes = max(args.bytes, 0 if args.no_sweep else args.max_sweep_bytes)
     rb = _C.RingBench(device=local_rank, use_bulk_copy=not args.no_bulk, max_bytes=max_bytes)
     urls = gather(f"{rb.listen_url()}|{local_rank}")

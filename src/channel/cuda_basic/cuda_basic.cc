@@ -280,7 +280,9 @@ uint32_t* ChannelImpl::counterFor(int device, cudaStream_t stream) {
   if (it != counters_.end()) return it->second;
   void* p = nullptr;
   TPB_CUDA_CHECK(cudaMalloc(&p, 256));
-  TPB_CUDA_CHECK(cudaMemset(p, 0, 256));
+  // Zero it for certain before the first kernel that counts on it can run (that kernel goes to
+  // the user's stream, which a memset on the default stream would not be ordered with).
+  if (!cudaZeroNow(p, 256, device)) throw std::runtime_error("cannot clear the arrive counter");
   counters_[key] = static_cast<uint32_t*>(p);
   return static_cast<uint32_t*>(p);
 }

@@ -471,7 +471,9 @@ Arena* ChannelImpl::arenaFor(int device, Error& err) {
   CudaDeviceGuard g(device);
   void* p = nullptr;
   cudaError_t e = cudaMalloc(&p, kFlagsBytes + a.inboxBytes);
-  if (e == cudaSuccess) e = cudaMemset(p, 0, kFlagsBytes);
+  // The flags and counters must read zero BEFORE the peer learns this address: a memset queued
+  // on the default stream could run after the peer's first push has already set a flag.
+  if (e == cudaSuccess && !cudaZeroNow(p, kFlagsBytes, device)) e = cudaErrorUnknown;
   if (e == cudaSuccess && !sameProcess_) {
     cudaIpcMemHandle_t h;
     e = cudaIpcGetMemHandle(&h, p);
@@ -546,6 +548,8 @@ void ChannelImpl::sendBatchFromLoop(std::vector<SendItem> items) {
       op.ready = std::move(early->second);
       earlyReady_.erase(early);
     }
+    TPB_VLOG(6) << "Channel " << id_ << " send batch #" << op.seq << " (" << op.items.size() << " tensors)"
+                << (op.ready ? ", receiver already announced its buffers" : "");
     sendOps_.push_back(std::move(op));
   }
   pumpSends();
@@ -638,6 +642,7 @@ ChannelImpl::Eager ChannelImpl::tryEager(SendOp& op) {
   l.eager = 1;
   l.inboxOffset = offset;
   l.creditValue = peer.head;
+  TPB_VLOG(6) << "Channel " << id_ << " pushed batch #" << op.seq << " eagerly into the peer's inbox at " << offset;
   writePacket(l);
   finishSend(op, Error::kSuccess);
   return Eager::kLaunched;
@@ -737,6 +742,8 @@ void ChannelImpl::launchRendezvous(SendOp& op) {
       for (cudaStream_t s : others) ev.wait(s, op.srcDevice);
     }
   }
+  TPB_VLOG(6) << "Channel " << id_ << " launched the push of batch #" << op.seq << " (" << plan.entries.size()
+              << " entries, " << plan.totalBytesOut << " bytes)";
   writePacket(l);
   finishSend(op, Error::kSuccess);
 }
@@ -841,11 +848,14 @@ void ChannelImpl::sendReady(RecvOp& op) {
     return closeFromLoop(TPB_CREATE_ERROR(CudaError, ex.what()));
   }
   op.readySent = true;
+  TPB_VLOG(6) << "Channel " << id_ << " announces its buffers for receive batch #" << op.seq;
   writePacket(r);
 }
 
 void ChannelImpl::completeRecv(RecvOp& op) {
   const Launched& n = *op.notice;
+  TPB_VLOG(6) << "Channel " << id_ << " learnt that batch #" << op.seq << " is on its way"
+              << (n.eager ? " (eager)" : "") << "; making the stream wait";
   if (!n.error.empty()) return closeFromLoop(TPB_CREATE_ERROR(CudaError, n.error));
   try {
     CudaDeviceGuard g(op.device);

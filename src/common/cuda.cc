@@ -165,6 +165,19 @@ int cudaSmCount(int device) {
   return n;
 }
 
+bool cudaZeroNow(void* ptr, size_t bytes, int device) {
+  CudaDeviceGuard g(device);
+  cudaStream_t s = nullptr;
+  if (cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  bool ok = cudaMemsetAsync(ptr, 0, bytes, s) == cudaSuccess && cudaStreamSynchronize(s) == cudaSuccess;
+  cudaStreamDestroy(s);
+  if (!ok) cudaGetLastError();
+  return ok;
+}
+
 int cudaDeviceForPointerOrHint(const CudaBuffer& b) {
   if (b.deviceIndex >= 0) return b.deviceIndex;
   int d = cudaDeviceForPointer(b.ptr);

@@ -149,5 +149,9 @@ bool cudaAllocationInfo(const void* ptr, void** base, size_t* size, unsigned lon
 // Enable peer access from `device` to `peer` once (idempotent). Returns false if impossible.
 bool cudaEnablePeerAccessOnce(int device, int peer);
 int cudaSmCount(int device);
+// Zeroes device memory and returns only once that has happened, on a private stream: it neither
+// waits for nor queues behind whatever the user's streams (or the legacy default stream) hold.
+// For memory whose address is about to be handed to a peer that may write to it right away.
+bool cudaZeroNow(void* ptr, size_t bytes, int device);
 
 }  // namespace tpb

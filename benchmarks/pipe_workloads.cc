@@ -8,6 +8,10 @@
 //       two forked processes; every message = 64 KiB payload + four fp32 CPU tensors of shapes
 //       [1024], [256,256], [64,64,64], [1<<20]; the server echoes; the client verifies every byte
 //       and that callbacks arrive in order; prints p50 / p99 round-trip latency.
+//   --workload transport_pingpong  --transport uv|shm  [--bytes 64]  [--iters 20000]
+//       raw transport connections (no pipe): one frame each way per round trip, two forked
+//       processes; prints p50 / p99 round-trip latency (the reference's benchmark_transport,
+//       tensorpipe/benchmark/benchmark_transport.cc:30-199).
 //   --workload rpc_fanin  --ranks N  [--iters 20000]
 //       rank 0 serves, ranks 1..N-1 (one forked process each, GPU r mod #GPUs) issue requests of a
 //       256 B payload + one 4 KiB fp32 CUDA tensor and wait for a same-shaped reply; prints
@@ -48,6 +52,7 @@ using Clock = std::chrono::steady_clock;
 struct Options {
   std::string workload = "cpu_pingpong", transport = "uv", channel = "basic";
   int iters = 1000, ranks = 2, warmup = 20;
+  size_t bytes = 64;
 };
 
 static void die(const std::string& what) {
@@ -229,6 +234,102 @@ static int cpuPingPong(const Options& o, Shared* sh) {
             << ", \"rtt_mean_us\": " << sh->mean[0] << ", \"verified\": \"byte-exact, every round trip\"}" << std::endl;
   return 0;
 }
+
+// ---- raw transport ping-pong ------------------------------------------------------------------------
+#ifdef USE_REFERENCE
+// PyTorch ships the reference's public headers only; transport/connection.h and listener.h are
+// not among them, so the raw transport API cannot be driven from here.
+static int transportPingPong(const Options&, Shared*) {
+  std::cout << "{\"impl\": \"reference\", \"workload\": \"transport_pingpong\", \"unavailable\": "
+               "\"the reference's transport headers are not shipped with PyTorch\"}" << std::endl;
+  return 0;
+}
+#else
+static int transportPingPong(const Options& o, Shared* sh) {
+  const int total = o.iters + o.warmup * 10;
+  auto makeTransport = [&]() -> std::shared_ptr<lib::transport::Context> {
+    if (o.transport == "shm") return lib::transport::shm::create();
+    return lib::transport::uv::create();
+  };
+  pid_t server = fork();
+  if (server == 0) {
+    auto t = makeTransport();
+    auto listener = t->listen(o.transport == "shm" ? std::string("tpb-bench-") + std::to_string(getpid()) : std::string("127.0.0.1"));
+    std::strncpy(sh->url, listener->addr().c_str(), sizeof(sh->url) - 1);
+    sh->urlReady = 1;
+    std::promise<std::shared_ptr<lib::transport::Connection>> pc;
+    listener->accept([&](const lib::Error& e, std::shared_ptr<lib::transport::Connection> c) {
+      if (e) die("accept: " + e.what());
+      pc.set_value(c);
+    });
+    auto conn = pc.get_future().get();
+    std::vector<uint8_t> buf(o.bytes);
+    std::promise<void> done;
+    int count = 0;
+    std::function<void()> arm = [&]() {
+      conn->read(buf.data(), buf.size(), [&](const lib::Error& e, const void*, size_t) {
+        if (e) die("read: " + e.what());
+        conn->write(buf.data(), buf.size(), [&](const lib::Error& e2) {
+          if (e2) die("write: " + e2.what());
+        });
+        if (++count == total) done.set_value();
+        else arm();
+      });
+    };
+    arm();
+    done.get_future().wait();
+    while (sh->clientsDone.load() == 0) std::this_thread::sleep_for(std::chrono::milliseconds(1));
+    t->join();
+    _exit(0);
+  }
+  pid_t client = fork();
+  if (client == 0) {
+    while (sh->urlReady.load() == 0) std::this_thread::sleep_for(std::chrono::milliseconds(1));
+    auto t = makeTransport();
+    auto conn = t->connect(sh->url);
+    std::vector<uint8_t> out(o.bytes, 7), in(o.bytes);
+    std::vector<double> rtt;
+    rtt.reserve(o.iters);
+    std::promise<void> done;
+    int count = 0;
+    Clock::time_point t0;
+    std::function<void()> round = [&]() {
+      t0 = Clock::now();
+      conn->write(out.data(), out.size(), [&](const lib::Error& e) {
+        if (e) die("write: " + e.what());
+      });
+      conn->read(in.data(), in.size(), [&](const lib::Error& e, const void*, size_t) {
+        if (e) die("read: " + e.what());
+        if (count >= o.warmup * 10) rtt.push_back(std::chrono::duration<double, std::micro>(Clock::now() - t0).count());
+        if (++count == total) done.set_value();
+        else round();
+      });
+    };
+    round();
+    done.get_future().wait();
+    sh->p50[0] = percentile(rtt, 0.5);
+    sh->p99[0] = percentile(rtt, 0.99);
+    double sum = 0;
+    for (double v : rtt) sum += v;
+    sh->mean[0] = sum / rtt.size();
+    sh->clientsDone = 1;
+    t->join();
+    _exit(0);
+  }
+  int s1 = 0, s2 = 0;
+  waitpid(client, &s2, 0);
+  sh->clientsDone = 1;
+  waitpid(server, &s1, 0);
+  if (!WIFEXITED(s1) || WEXITSTATUS(s1) || !WIFEXITED(s2) || WEXITSTATUS(s2)) {
+    std::cout << "{\"impl\": \"" << kImpl << "\", \"workload\": \"transport_pingpong\", \"error\": \"a peer failed\"}" << std::endl;
+    return 1;
+  }
+  std::cout << "{\"impl\": \"" << kImpl << "\", \"workload\": \"transport_pingpong\", \"transport\": \"" << o.transport
+            << "\", \"bytes\": " << o.bytes << ", \"round_trips\": " << o.iters << ", \"rtt_p50_us\": " << sh->p50[0]
+            << ", \"rtt_p99_us\": " << sh->p99[0] << ", \"rtt_mean_us\": " << sh->mean[0] << "}" << std::endl;
+  return 0;
+}
+#endif
 
 // ---- workload 5 ---------------------------------------------------------------------------------
 static std::shared_ptr<lib::Context> makeCudaContext(const std::string& name) {
@@ -427,11 +528,13 @@ int main(int argc, char** argv) {
     else if (k == "--iters") o.iters = std::stoi(v);
     else if (k == "--ranks") o.ranks = std::stoi(v);
     else if (k == "--warmup") o.warmup = std::stoi(v);
+    else if (k == "--bytes") o.bytes = std::stoull(v);
   }
   auto* sh = static_cast<Shared*>(mmap(nullptr, sizeof(Shared), PROT_READ | PROT_WRITE, MAP_SHARED | MAP_ANONYMOUS, -1, 0));
   std::memset(static_cast<void*>(sh), 0, sizeof(Shared));
   if (o.workload == "cpu_pingpong") return cpuPingPong(o, sh);
   if (o.workload == "rpc_fanin") return rpcFanIn(o, sh);
+  if (o.workload == "transport_pingpong") return transportPingPong(o, sh);
   std::cerr << "unknown workload" << std::endl;
   return 2;
 }

@@ -236,3 +236,64 @@ TPB_TEST(Common, SystemProbes) {
   EXPECT_EQ(nextPow2(65), uint64_t(128));
   EXPECT_EQ(nextPow2(64), uint64_t(64));
 }
+
+#include "common/allocator.h"
+#include "common/queue.h"
+
+TPB_TEST(Common, AllocatorServesInOrderAndRecyclesChunks) {
+  std::vector<uint8_t> mem(4 * 100);
+  Allocator alloc(mem.data(), 4, 100);
+  std::vector<Allocator::TChunk> held;
+  std::vector<int> order;
+  int failedWaiters = 0;
+  for (int i = 0; i < 6; ++i) {
+    alloc.alloc(50, [&, i](const Error& e, Allocator::TChunk c) {
+      if (e) {
+        EXPECT_TRUE(e.isOfType<AllocatorClosedError>());
+        ++failedWaiters;
+        return;
+      }
+      order.push_back(i);
+      held.push_back(std::move(c));
+    });
+  }
+  // four chunks exist: requests 0-3 are served, 4 and 5 wait
+  EXPECT_EQ(order.size(), size_t(4));
+  EXPECT_EQ(alloc.numPending(), size_t(2));
+  // chunks are distinct and inside the pool
+  for (size_t i = 0; i < 4; ++i)
+    for (size_t j = i + 1; j < 4; ++j) EXPECT_TRUE(held[i].get() != held[j].get());
+  uint8_t* freed = held[1].get();
+  held[1].reset();  // returning one chunk serves request 4 with that very chunk
+  EXPECT_EQ(order.size(), size_t(5));
+  EXPECT_EQ(order.back(), 4);
+  EXPECT_TRUE(held.back().get() == freed);
+  // too large a request is an error, not a wait
+  bool failed = false;
+  alloc.alloc(101, [&](const Error& e, Allocator::TChunk) { failed = bool(e); });
+  EXPECT_TRUE(failed);
+  // closing fails the remaining waiter and every later request
+  Error closedError;
+  alloc.close();
+  EXPECT_EQ(alloc.numPending(), size_t(0));
+  EXPECT_EQ(failedWaiters, 1);  // request 5 never got a chunk
+  alloc.alloc(10, [&](const Error& e, Allocator::TChunk) { closedError = e; });
+  EXPECT_TRUE(closedError.isOfType<AllocatorClosedError>());
+  held.clear();  // chunks may outlive close()
+}
+
+TPB_TEST(Common, QueueBlocksProducersAtCapacity) {
+  Queue<int> q(2);
+  std::atomic<int> produced{0};
+  std::thread producer([&] {
+    for (int i = 0; i < 10; ++i) {
+      q.push(i);
+      ++produced;
+    }
+  });
+  std::this_thread::sleep_for(std::chrono::milliseconds(20));
+  EXPECT_TRUE(produced.load() <= 3);  // two queued (+ one in flight at most)
+  for (int i = 0; i < 10; ++i) EXPECT_EQ(q.pop(), i);
+  producer.join();
+  EXPECT_EQ(produced.load(), 10);
+}

@@ -44,6 +44,9 @@ std::mutex gTuningMutex;
 PushTuning gTuning;
 
 constexpr uint32_t kWarpTileBytes = kStridedTile * (kStridedTile / 2 + 1) * 8;  // 4352 B per warp: 32 x 17 x 8-byte, or 32 x 33 x 4-byte
+constexpr int kWidePitch = kWideTile + 2;                                        // 2-byte elements per staged column
+constexpr uint32_t kWideWarpTileBytes = kWideTile * kWidePitch * 2;              // 8448 B per warp
+constexpr size_t kMaxSmemPerCta = 227 * 1024;
 
 // ---- PTX wrappers -----------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smemAddr(const void* p) {
@@ -125,6 +128,7 @@ struct PushParams {
   uint32_t* status;
   uint32_t bulkTileBytes;
   uint32_t bulkStages;
+  uint32_t warpTileBytes;  // shared memory per register-path warp (0 when no entry needs staging)
 };
 
 template <int N>
@@ -240,30 +244,81 @@ __device__ __noinline__ void castTile(const PushEntry& e, uint32_t localTile, in
 // A warp stages TR x 32 raw source elements as tile[c][r] (row stride TR+1 words keeps both access
 // patterns free of bank conflicts for 4-byte elements), reading along whichever source dimension is
 // contiguous, then writes rows of the packed destination: 32 consecutive elements per store.
+// The entry lives in the kernel's parameter block and is reached through a generic pointer inside
+// the tile routines: its fields are read once per call into this pack, or every use inside the
+// loops would become a load behind the tile stores.
+struct StridedArgs {
+  const void* src;
+  void* dst;
+  int64_t rows, cols, rowStride, colStride;
+  uint32_t numTiles;
+};
+__device__ __forceinline__ StridedArgs loadStridedArgs(const PushEntry& e) {
+  return StridedArgs{e.src, e.dst, e.rows, e.cols, e.rowStride, e.colStride, e.numTiles};
+}
+
 template <typename S, typename D, bool kConvert>
-__device__ __forceinline__ void stridedTileTyped(const PushEntry& e, uint32_t localTile, int lane, uint8_t* tileMem) {
+__device__ __forceinline__ void stridedTileTyped(const StridedArgs& a, uint32_t localTile, int lane, uint8_t* tileMem) {
   constexpr int TC = kStridedTile;                                 // columns per tile
   constexpr int TR = sizeof(S) == 8 ? kStridedTile / 2 : kStridedTile;  // rows per tile
   S* tile = reinterpret_cast<S*>(tileMem);
-  const int64_t tilesPerRow = (e.cols + TC - 1) / TC;
-  const int64_t r0 = (localTile / tilesPerRow) * TR;
-  const int64_t c0 = (localTile % tilesPerRow) * TC;
-  const int nr = static_cast<int>(e.rows - r0 < TR ? e.rows - r0 : TR);
-  const int nc = static_cast<int>(e.cols - c0 < TC ? e.cols - c0 : TC);
-  const S* src = static_cast<const S*>(e.src);
-  D* dst = static_cast<D*>(e.dst);
-  const bool rowsFast = (e.rowStride == 1 || e.rows == 1) && e.colStride != 1;
+  const int64_t rows = a.rows, cols = a.cols, rowStride = a.rowStride, colStride = a.colStride;
+  const S* src = static_cast<const S*>(a.src);
+  D* dst = static_cast<D*>(a.dst);
+  const uint32_t tilesPerRow = static_cast<uint32_t>((cols + TC - 1) / TC);  // the tile count fits 32 bits
+  const int64_t r0 = static_cast<int64_t>(localTile / tilesPerRow) * TR;
+  const int64_t c0 = static_cast<int64_t>(localTile % tilesPerRow) * TC;
+  const int nr = static_cast<int>(rows - r0 < TR ? rows - r0 : TR);
+  const int nc = static_cast<int>(cols - c0 < TC ? cols - c0 : TC);
+  const bool rowsFast = (rowStride == 1 || rows == 1) && colStride != 1;
+  if (rowsFast && rowStride == 1 && nr == TR && nc == TC) {
+    // Full tile of a transposed matrix: no predicates, pointers stepped instead of recomputed,
+    // eight loads in flight per lane.
+    constexpr int kWide = 8;
+    const bool act = lane < TR;
+    const S* colPtr = src + (r0 + lane) + c0 * colStride;
+#pragma unroll 1
+    for (int c = 0; c < TC; c += kWide) {
+      S v[kWide];
+#pragma unroll
+      for (int k = 0; k < kWide; ++k)
+        if (act) v[k] = colPtr[k * colStride];
+      colPtr += kWide * colStride;
+#pragma unroll
+      for (int k = 0; k < kWide; ++k)
+        if (act) tile[(c + k) * (TR + 1) + lane] = v[k];
+    }
+    __syncwarp();
+    D* outPtr = dst + r0 * cols + c0 + lane;
+    const S* mine = tile + lane * (TR + 1);
+#pragma unroll 1
+    for (int r = 0; r < TR; r += kWide) {
+      S v[kWide];
+#pragma unroll
+      for (int k = 0; k < kWide; ++k) v[k] = mine[r + k];
+#pragma unroll
+      for (int k = 0; k < kWide; ++k) {
+        D out;
+        if constexpr (kConvert) out = fromFloat<D>(toFloat<S>(v[k]));
+        else out = v[k];
+        outPtr[k * cols] = out;
+      }
+      outPtr += kWide * cols;
+    }
+    __syncwarp();
+    return;
+  }
   constexpr int kBatch = 4;  // independent loads issued before their results are parked in the tile
   if (rowsFast) {
     // lanes walk down a source column: coalesced reads when the source is a transposed matrix
     for (int rb = 0; rb < nr; rb += 32) {
       const int r = rb + lane;
-      const S* colPtr = src + (r0 + r) * e.rowStride + c0 * e.colStride;
+      const S* colPtr = src + (r0 + r) * rowStride + c0 * colStride;
       for (int c = 0; c < nc; c += kBatch) {
         S v[kBatch];
 #pragma unroll
         for (int k = 0; k < kBatch; ++k)
-          if (r < nr && c + k < nc) v[k] = colPtr[static_cast<int64_t>(c + k) * e.colStride];
+          if (r < nr && c + k < nc) v[k] = colPtr[static_cast<int64_t>(c + k) * colStride];
 #pragma unroll
         for (int k = 0; k < kBatch; ++k)
           if (r < nr && c + k < nc) tile[(c + k) * (TR + 1) + r] = v[k];
@@ -272,12 +327,12 @@ __device__ __forceinline__ void stridedTileTyped(const PushEntry& e, uint32_t lo
   } else {
     for (int cb = 0; cb < nc; cb += 32) {
       const int c = cb + lane;
-      const S* rowPtr = src + r0 * e.rowStride + (c0 + c) * e.colStride;
+      const S* rowPtr = src + r0 * rowStride + (c0 + c) * colStride;
       for (int r = 0; r < nr; r += kBatch) {
         S v[kBatch];
 #pragma unroll
         for (int k = 0; k < kBatch; ++k)
-          if (c < nc && r + k < nr) v[k] = rowPtr[static_cast<int64_t>(r + k) * e.rowStride];
+          if (c < nc && r + k < nr) v[k] = rowPtr[static_cast<int64_t>(r + k) * rowStride];
 #pragma unroll
         for (int k = 0; k < kBatch; ++k)
           if (c < nc && r + k < nr) tile[c * (TR + 1) + r + k] = v[k];
@@ -287,7 +342,7 @@ __device__ __forceinline__ void stridedTileTyped(const PushEntry& e, uint32_t lo
   __syncwarp();
   {
     const int c = lane;  // TC == 32: one column per lane
-    D* rowPtr = dst + r0 * e.cols + c0 + c;
+    D* rowPtr = dst + r0 * cols + c0 + c;
     for (int r = 0; r < nr; r += kBatch) {
       S v[kBatch];
 #pragma unroll
@@ -299,7 +354,7 @@ __device__ __forceinline__ void stridedTileTyped(const PushEntry& e, uint32_t lo
           D out;
           if constexpr (kConvert) out = fromFloat<D>(toFloat<S>(v[k]));
           else out = v[k];
-          rowPtr[static_cast<int64_t>(r + k) * e.cols] = out;
+          rowPtr[static_cast<int64_t>(r + k) * cols] = out;
         }
       }
     }
@@ -307,15 +362,26 @@ __device__ __forceinline__ void stridedTileTyped(const PushEntry& e, uint32_t lo
   __syncwarp();  // the tile is reused by this warp's next strided tile
 }
 
-// Not inlined: ten instantiations of the tile routine would otherwise set the register budget of
-// the whole kernel, including the copy loops that want many loads in flight.
-__device__ __noinline__ void stridedTile(const PushEntry& e, uint32_t localTile, int lane, uint8_t* tileMem) {
+// Not inlined, one function per element type: inlined they would set the register budget of the
+// whole kernel, including the copy loops that want many loads in flight. One call covers all
+// of this warp's tiles of the entry (first, first + step, ...): a call saves and restores the
+// registers it uses, which per tile would cost more local-memory traffic than the tile's payload.
+template <typename S, typename D, bool kConvert>
+__device__ __noinline__ void stridedTilesTyped(const PushEntry& a_, uint32_t first, uint32_t step, int lane,
+                                               uint8_t* tileMem) {
+  const StridedArgs a = loadStridedArgs(a_);
+#pragma unroll 1
+  for (uint32_t t = first; t < a.numTiles; t += step) stridedTileTyped<S, D, kConvert>(a, t, lane, tileMem);
+}
+
+__device__ __forceinline__ void stridedTiles(const PushEntry& a, uint32_t first, uint32_t step, int lane, uint8_t* tileMem) {
+  const PushEntry& e = a;
   if (e.srcDtype == e.dstDtype || e.dstDtype == static_cast<uint8_t>(DType::kBytes)) {
     switch (e.srcElemSize) {
-      case 1: stridedTileTyped<uint8_t, uint8_t, false>(e, localTile, lane, tileMem); break;
-      case 2: stridedTileTyped<uint16_t, uint16_t, false>(e, localTile, lane, tileMem); break;
-      case 4: stridedTileTyped<uint32_t, uint32_t, false>(e, localTile, lane, tileMem); break;
-      default: stridedTileTyped<uint64_t, uint64_t, false>(e, localTile, lane, tileMem); break;
+      case 1: stridedTilesTyped<uint8_t, uint8_t, false>(a, first, step, lane, tileMem); break;
+      case 2: stridedTilesTyped<uint16_t, uint16_t, false>(a, first, step, lane, tileMem); break;
+      case 4: stridedTilesTyped<uint32_t, uint32_t, false>(a, first, step, lane, tileMem); break;
+      default: stridedTilesTyped<uint64_t, uint64_t, false>(a, first, step, lane, tileMem); break;
     }
     return;
   }
@@ -323,26 +389,117 @@ __device__ __noinline__ void stridedTile(const PushEntry& e, uint32_t localTile,
   constexpr uint32_t F32 = static_cast<uint32_t>(DType::kF32), BF = static_cast<uint32_t>(DType::kBF16),
                      F16 = static_cast<uint32_t>(DType::kF16);
   switch (key) {
-    case (F32 << 8) | BF: stridedTileTyped<float, __nv_bfloat16, true>(e, localTile, lane, tileMem); break;
-    case (F32 << 8) | F16: stridedTileTyped<float, __half, true>(e, localTile, lane, tileMem); break;
-    case (BF << 8) | F32: stridedTileTyped<__nv_bfloat16, float, true>(e, localTile, lane, tileMem); break;
-    case (F16 << 8) | F32: stridedTileTyped<__half, float, true>(e, localTile, lane, tileMem); break;
-    case (BF << 8) | F16: stridedTileTyped<__nv_bfloat16, __half, true>(e, localTile, lane, tileMem); break;
-    case (F16 << 8) | BF: stridedTileTyped<__half, __nv_bfloat16, true>(e, localTile, lane, tileMem); break;
+    case (F32 << 8) | BF: stridedTilesTyped<float, __nv_bfloat16, true>(a, first, step, lane, tileMem); break;
+    case (F32 << 8) | F16: stridedTilesTyped<float, __half, true>(a, first, step, lane, tileMem); break;
+    case (BF << 8) | F32: stridedTilesTyped<__nv_bfloat16, float, true>(a, first, step, lane, tileMem); break;
+    case (F16 << 8) | F32: stridedTilesTyped<__half, float, true>(a, first, step, lane, tileMem); break;
+    case (BF << 8) | F16: stridedTilesTyped<__nv_bfloat16, __half, true>(a, first, step, lane, tileMem); break;
+    case (F16 << 8) | BF: stridedTilesTyped<__half, __nv_bfloat16, true>(a, first, step, lane, tileMem); break;
     default: break;
   }
+}
+
+// Transposed matrix of 2-byte elements (rowStride == 1), with the source, the destination, both
+// extents and the column stride all even: a warp moves a 64x64 tile, reading 32-bit words down the
+// source columns (128 B per instruction instead of 64) and writing 32-bit words along the packed
+// rows. Staged as tile[c][r] with an even pitch, so a word of two rows lands on an aligned word.
+__device__ __forceinline__ void stridedWide16Tile(const StridedArgs& a, uint32_t localTile, int lane, uint8_t* tileMem) {
+  constexpr int T = kWideTile, P = kWidePitch;
+  const uint16_t* tile = reinterpret_cast<const uint16_t*>(tileMem);
+  uint32_t* tileWords = reinterpret_cast<uint32_t*>(tileMem);
+  const int64_t rows = a.rows, cols = a.cols, colStride = a.colStride;
+  const uint16_t* src = static_cast<const uint16_t*>(a.src);
+  uint16_t* dst = static_cast<uint16_t*>(a.dst);
+  const uint32_t tilesPerRow = static_cast<uint32_t>((cols + T - 1) / T);
+  const int64_t r0 = static_cast<int64_t>(localTile / tilesPerRow) * T;
+  const int64_t c0 = static_cast<int64_t>(localTile % tilesPerRow) * T;
+  const int nr = static_cast<int>(rows - r0 < T ? rows - r0 : T);  // even
+  const int nc = static_cast<int>(cols - c0 < T ? cols - c0 : T);  // even
+  constexpr int kBatch = 8;
+  const uint16_t* colPtr = src + (r0 + 2 * lane) + c0 * colStride;
+  uint32_t* rowPtr = reinterpret_cast<uint32_t*>(dst + r0 * cols + c0) + lane;
+  const int64_t rowWords = cols / 2;
+  const uint16_t* lo = tile + (2 * lane) * P;
+  const uint16_t* hi = lo + P;
+  if (nr == T && nc == T) {
+    // Full tile: no predicates, constant trip counts.
+#pragma unroll 1
+    for (int c = 0; c < T; c += kBatch) {
+      uint32_t v[kBatch];
+#pragma unroll
+      for (int k = 0; k < kBatch; ++k) v[k] = *reinterpret_cast<const uint32_t*>(colPtr + k * colStride);
+      colPtr += kBatch * colStride;
+#pragma unroll
+      for (int k = 0; k < kBatch; ++k) tileWords[(c + k) * (P / 2) + lane] = v[k];
+    }
+    __syncwarp();
+#pragma unroll 1
+    for (int r = 0; r < T; r += kBatch) {
+      uint32_t v[kBatch];
+#pragma unroll
+      for (int k = 0; k < kBatch; ++k) v[k] = static_cast<uint32_t>(lo[r + k]) | (static_cast<uint32_t>(hi[r + k]) << 16);
+#pragma unroll
+      for (int k = 0; k < kBatch; ++k) rowPtr[k * rowWords] = v[k];
+      rowPtr += kBatch * rowWords;
+    }
+    __syncwarp();
+    return;
+  }
+  {
+    const bool active = 2 * lane < nr;
+    for (int c = 0; c < nc; c += kBatch) {
+      uint32_t v[kBatch];
+#pragma unroll
+      for (int k = 0; k < kBatch; ++k)
+        if (active && c + k < nc) v[k] = *reinterpret_cast<const uint32_t*>(colPtr + static_cast<int64_t>(c + k) * colStride);
+#pragma unroll
+      for (int k = 0; k < kBatch; ++k)
+        if (active && c + k < nc) tileWords[(c + k) * (P / 2) + lane] = v[k];
+    }
+  }
+  __syncwarp();
+  {
+    const bool active = 2 * lane < nc;
+    for (int r = 0; r < nr; r += kBatch) {
+      uint32_t v[kBatch];
+#pragma unroll
+      for (int k = 0; k < kBatch; ++k)
+        if (active && r + k < nr) v[k] = static_cast<uint32_t>(lo[r + k]) | (static_cast<uint32_t>(hi[r + k]) << 16);
+#pragma unroll
+      for (int k = 0; k < kBatch; ++k)
+        if (active && r + k < nr) rowPtr[static_cast<int64_t>(r + k) * rowWords] = v[k];
+    }
+  }
+  __syncwarp();
+}
+
+__device__ __noinline__ void stridedWide16Tiles(const PushEntry& e, uint32_t first, uint32_t step, int lane,
+                                                uint8_t* tileMem) {
+  const StridedArgs a = loadStridedArgs(e);
+#pragma unroll 1
+  for (uint32_t t = first; t < a.numTiles; t += step) stridedWide16Tile(a, t, lane, tileMem);
 }
 
 // Warp tiles t = firstWarp, firstWarp + totalWarps, ... of the plain class.
 template <int N>
 __device__ __forceinline__ void runPlainWarp(const PushParams<N>& p, uint32_t firstWarp, uint32_t totalWarps, int lane,
                                              uint8_t* tileMem) {
-  for (uint32_t t = firstWarp; t < p.plainTiles; t += totalWarps) {
+  uint32_t t = firstWarp;
+  while (t < p.plainTiles) {
     const PushEntry* e = findEntry(p, t, false);
     const uint32_t local = t - e->tileStart;
-    if (e->kind == kCopyPlain) copyPlainTile(*e, local, lane);
-    else if (e->kind == kCastPlain) castTile(*e, local, lane);
-    else stridedTile(*e, local, lane, tileMem);
+    if (e->kind == kCopyPlain) {
+      copyPlainTile(*e, local, lane);
+      t += totalWarps;
+    } else if (e->kind == kCastPlain) {
+      castTile(*e, local, lane);
+      t += totalWarps;
+    } else {
+      // One call handles every tile of this entry that falls to this warp.
+      if (e->kind == kStridedWide16) stridedWide16Tiles(*e, local, totalWarps, lane, tileMem);
+      else stridedTiles(*e, local, totalWarps, lane, tileMem);
+      t += (e->numTiles - local + totalWarps - 1) / totalWarps * totalWarps;
+    }
   }
 }
 
@@ -376,7 +533,7 @@ __global__ void __launch_bounds__(kThreads, 1) tpb_push_pack(const __grid_consta
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 127) & ~static_cast<uintptr_t>(127));
   uint8_t* stages = base;
   uint8_t* warpTiles = base + static_cast<size_t>(p.bulkStages) * p.bulkTileBytes;
-  uint64_t* full = reinterpret_cast<uint64_t*>(warpTiles + (kThreads / 32 - 1) * kWarpTileBytes);
+  uint64_t* full = reinterpret_cast<uint64_t*>(warpTiles + (kThreads / 32 - 1) * p.warpTileBytes);
 
   const int tid = threadIdx.x;
   const int S = static_cast<int>(p.bulkStages);
@@ -443,17 +600,17 @@ __global__ void __launch_bounds__(kThreads, 1) tpb_push_pack(const __grid_consta
     constexpr uint32_t kPlainWarps = kThreads / 32 - 1;
     const uint32_t warp = tid / 32 - 1;
     runPlainWarp(p, blockIdx.x * kPlainWarps + warp, gridDim.x * kPlainWarps, tid & 31,
-                 warpTiles + warp * kWarpTileBytes);
+                 warpTiles + warp * p.warpTileBytes);
   }
   publish(p);
 }
 
 template <int N>
 __global__ void __launch_bounds__(kLightThreads, 2) tpb_push_pack_light(const __grid_constant__ PushParams<N> p) {
-  __shared__ __align__(16) uint8_t warpTiles[(kLightThreads / 32) * kWarpTileBytes];
+  extern __shared__ __align__(16) uint8_t lightTiles[];  // kWarps * p.warpTileBytes, none for plain copies
   constexpr uint32_t kWarps = kLightThreads / 32;
   const uint32_t warp = threadIdx.x / 32;
-  runPlainWarp(p, blockIdx.x * kWarps + warp, gridDim.x * kWarps, threadIdx.x & 31, warpTiles + warp * kWarpTileBytes);
+  runPlainWarp(p, blockIdx.x * kWarps + warp, gridDim.x * kWarps, threadIdx.x & 31, lightTiles + warp * p.warpTileBytes);
   publish(p);
 }
 
@@ -540,22 +697,38 @@ void launchOne(const PushEntry* entries, uint32_t n, uint32_t bulkTiles, uint32_
   p.status = status;
   p.bulkTileBytes = bulkTileBytes;
   p.bulkStages = bulkStages;
+  p.warpTileBytes = 0;
+  for (uint32_t i = 0; i < n; ++i) {
+    const uint32_t need = entries[i].kind == kStridedWide16 ? kWideWarpTileBytes
+        : entries[i].kind == kStrided                        ? kWarpTileBytes
+                                                             : 0;
+    if (need > p.warpTileBytes) p.warpTileBytes = need;
+  }
+  int dev = 0;
+  check(cudaGetDevice(&dev), "cudaGetDevice");
   if (bulkTiles == 0) {
-    // Light kernel: 8 warps per CTA, static shared memory only.
+    // Light kernel: 8 warps per CTA, shared memory only when an entry is staged through it.
     constexpr uint32_t kWarps = kLightThreads / 32;
     uint32_t grid = (plainTiles + kWarps - 1) / kWarps;
     if (grid > static_cast<uint32_t>(maxCtas) * 2) grid = static_cast<uint32_t>(maxCtas) * 2;
     if (grid == 0) grid = 1;
-    tpb_push_pack_light<N><<<grid, kLightThreads, 0, stream>>>(p);
+    const size_t lightSmem = static_cast<size_t>(kWarps) * p.warpTileBytes;
+    static size_t lightConfigured[64] = {};
+    if (lightSmem > 48 * 1024 && dev < 64 && lightConfigured[dev] < lightSmem) {
+      check(cudaFuncSetAttribute(tpb_push_pack_light<N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(lightSmem)),
+            "cudaFuncSetAttribute");
+      lightConfigured[dev] = lightSmem;
+    }
+    tpb_push_pack_light<N><<<grid, kLightThreads, lightSmem, stream>>>(p);
     check(cudaGetLastError(), "tpb_push_pack_light launch");
     ++gLaunches;
     return;
   }
-  const size_t smem = static_cast<size_t>(bulkStages) * bulkTileBytes + (kThreads / 32 - 1) * kWarpTileBytes +
+  const size_t smem = static_cast<size_t>(bulkStages) * bulkTileBytes + (kThreads / 32 - 1) * p.warpTileBytes +
       kMaxBulkStages * sizeof(uint64_t) + 128;
+  if (smem > kMaxSmemPerCta) throw std::runtime_error("push plan needs more shared memory than a CTA has");
   static size_t configured[64] = {};
-  int dev = 0;
-  check(cudaGetDevice(&dev), "cudaGetDevice");
   if (dev < 64 && configured[dev] < smem) {
     check(cudaFuncSetAttribute(tpb_push_pack<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)),
           "cudaFuncSetAttribute");
@@ -613,6 +786,11 @@ void pushEntry(PushPlan& plan, PushEntry e) {
     e.numTiles = static_cast<uint32_t>((e.count + perTile - 1) / perTile);
     e.tileStart = plan.plainTiles;
     plan.plainTiles += e.numTiles;
+  } else if (e.kind == kStridedWide16) {
+    const uint64_t tr = (e.rows + kWideTile - 1) / kWideTile, tc = (e.cols + kWideTile - 1) / kWideTile;
+    e.numTiles = static_cast<uint32_t>(tr * tc);
+    e.tileStart = plan.plainTiles;
+    plan.plainTiles += e.numTiles;
   } else {
     const int tileRows = e.srcElemSize == 8 ? kStridedTile / 2 : kStridedTile;
     const uint64_t tr = (e.rows + tileRows - 1) / tileRows, tc = (e.cols + kStridedTile - 1) / kStridedTile;
@@ -653,6 +831,17 @@ void appendToPlan(PushPlan& plan, const CopyItem& item, bool useBulk) {
     e.src = item.src;
     e.dst = item.dst;
     e.kind = kStrided;
+    {
+      // The word-wide variant needs even everything; it also needs its larger staging area to fit
+      // next to the bulk stages this plan was sized with.
+      const uintptr_t both = reinterpret_cast<uintptr_t>(item.src) | reinterpret_cast<uintptr_t>(item.dst);
+      const size_t smemWithWide = static_cast<size_t>(plan.bulkStages) * plan.bulkTileBytes +
+          (kThreads / 32 - 1) * kWideWarpTileBytes + kMaxBulkStages * sizeof(uint64_t) + 128;
+      if (!convert && e.srcElemSize == 2 && v.rowStride == 1 && v.colStride != 1 && v.rows >= kWideTile &&
+          v.cols >= kWideTile && v.rows % 2 == 0 && v.cols % 2 == 0 && v.colStride % 2 == 0 && (both & 3) == 0 &&
+          smemWithWide <= kMaxSmemPerCta)
+        e.kind = kStridedWide16;
+    }
     e.rows = v.rows;
     e.cols = v.cols;
     e.rowStride = v.rowStride;

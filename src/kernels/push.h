@@ -29,6 +29,7 @@ enum EntryKind : uint32_t {
   kCopyPlain = 1,    // contiguous, any alignment: vectorised ld/st
   kCastPlain = 2,    // contiguous with dtype conversion
   kStrided = 3,      // 2-D strided source -> packed destination (optional conversion)
+  kStridedWide16 = 4,  // transposed 2-byte elements, everything 4-byte aligned: 64x64 tiles moved as 32-bit words
 };
 
 struct alignas(16) PushEntry {
@@ -47,6 +48,7 @@ constexpr int kMaxEntriesSmall = 8;
 constexpr int kMaxEntriesLarge = 96;
 constexpr uint32_t kPlainTileBytes = 8 * 1024;  // one warp's unit of work (destination bytes)
 constexpr int kStridedTile = 32;                // a warp transposes 32x32 elements (16x32 for 8-byte ones)
+constexpr int kWideTile = 64;                   // kStridedWide16: 64x64 two-byte elements per warp tile
 constexpr int kThreads = 512;                   // full kernel: warp 0 drives TMA, warps 1..15 use registers
 constexpr int kLightThreads = 256;              // light kernel (no bulk pipeline, static shared memory only)
 constexpr int kMaxBulkStages = 8;

@@ -204,6 +204,90 @@ TPB_GPU_TEST(Kernel, StridedViewsPackLikeACpuGather, 1) {
   }
 }
 
+// Even-sized transposed matrices of 2-byte elements take the word-wide 64x64 tile path; alone they
+// run in the light kernel, next to a large contiguous tensor in the full kernel (bulk pipeline on
+// warp 0, the transposition on the other warps with the larger staging area).
+TPB_GPU_TEST(Kernel, WideTransposeOfTwoByteElements, 1) {
+  struct Case {
+    int64_t rows, cols;
+    bool withBulk;
+  };
+  for (Case c : {Case{64, 64, false}, Case{130, 198, false}, Case{1024, 258, false}, Case{2050, 514, true},
+                 Case{66, 4096, true}}) {
+    std::vector<uint16_t> host(c.rows * c.cols);
+    std::mt19937 rng(static_cast<uint32_t>(c.rows * 7 + c.cols));
+    for (auto& b : host) b = static_cast<uint16_t>(rng());
+    const size_t packed = host.size() * 2;
+    const size_t bulkBytes = 3 * 1024 * 1024 + 16;
+    DeviceBuf src(packed), dst(packed + 2 * kGuard), bsrc(bulkBytes), bdst(bulkBytes);
+    CK(cudaMemcpy(src.p, host.data(), packed, cudaMemcpyHostToDevice));
+    CK(cudaMemset(dst.p, 0xCD, dst.n));
+    launchFill(nullptr, bsrc.p, bulkBytes, 99);
+    CK(cudaMemset(bdst.p, 0, bulkBytes));
+    PushPlan plan;
+    if (c.withBulk) {
+      CopyItem b;
+      b.src = bsrc.p;
+      b.dst = bdst.p;
+      b.srcBytes = bulkBytes;
+      appendToPlan(plan, b, true);
+    }
+    CopyItem it;
+    it.src = src.p;
+    it.dst = dst.p + kGuard;
+    it.srcBytes = packed;
+    it.srcDtype = DType::kF16;
+    it.dstDtype = DType::kF16;
+    it.strided = true;
+    it.view = StridedView{DType::kF16, c.rows, c.cols, 1, c.rows};
+    appendToPlan(plan, it, true);
+    EXPECT_EQ(int(plan.entries.back().kind), int(kStridedWide16));
+    if (c.withBulk) EXPECT_TRUE(plan.bulkTiles > 0);
+    launchPush(plan, nullptr, 148, nullptr, 0, nullptr, nullptr);
+    CK(cudaDeviceSynchronize());
+    auto out = download(dst.p, dst.n);
+    for (int64_t r = 0; r < c.rows; ++r)
+      for (int64_t col = 0; col < c.cols; ++col) {
+        uint16_t got;
+        std::memcpy(&got, &out[kGuard + (r * c.cols + col) * 2], 2);
+        if (got != host[col * c.rows + r])
+          throw tpbtest::TestFailure("wide transpose mismatch at (" + std::to_string(r) + "," + std::to_string(col) +
+                                     ") of " + std::to_string(c.rows) + "x" + std::to_string(c.cols));
+      }
+    EXPECT_EQ(int(out[kGuard - 1]), 0xCD);
+    EXPECT_EQ(int(out[kGuard + packed]), 0xCD);
+    if (c.withBulk) {
+      DeviceBuf bad(8);
+      CK(cudaMemset(bad.p, 0, 8));
+      launchVerify(nullptr, bdst.p, bulkBytes, 99, reinterpret_cast<unsigned long long*>(bad.p));
+      CK(cudaDeviceSynchronize());
+      auto n = download(bad.p, 8);
+      unsigned long long mism;
+      std::memcpy(&mism, n.data(), 8);
+      EXPECT_EQ(mism, 0ull);
+    }
+  }
+  // Odd extents, an odd column stride or a misaligned destination fall back to the element-wise tiles.
+  {
+    PushPlan plan;
+    DeviceBuf src(65 * 64 * 2), dst(65 * 64 * 2 + 64);
+    CopyItem it;
+    it.src = src.p;
+    it.dst = dst.p;
+    it.srcBytes = 65 * 64 * 2;
+    it.srcDtype = it.dstDtype = DType::kBF16;
+    it.strided = true;
+    it.view = StridedView{DType::kBF16, 65, 64, 1, 65};
+    appendToPlan(plan, it, true);
+    EXPECT_EQ(int(plan.entries.back().kind), int(kStrided));
+    it.srcBytes = 64 * 64 * 2;
+    it.view = StridedView{DType::kBF16, 64, 64, 1, 64};
+    it.dst = dst.p + 2;
+    appendToPlan(plan, it, true);
+    EXPECT_EQ(int(plan.entries.back().kind), int(kStrided));
+  }
+}
+
 TPB_GPU_TEST(Kernel, StridedWithCast, 1) {
   const int64_t rows = 130, cols = 70;
   std::vector<float> host(rows * cols);

@@ -164,6 +164,73 @@ class MappingCache {
   std::map<Handle, void*> map_;
 };
 
+// ---- process-wide cache of exported IPC handles ---------------------------------------------
+// Exporting a handle is a driver round trip per call; a message of many tensors carved out of a
+// few allocations (a caching allocator's blocks) would pay it per tensor per message. Entries are
+// keyed by allocation range and checked against the driver's buffer id, which is unique for the
+// life of the process, so a freed and re-used address range is noticed and re-exported.
+class ExportCache {
+ public:
+  struct Entry {
+    uintptr_t base = 0;
+    size_t size = 0;
+    unsigned long long id = 0;
+    Handle handle{};
+  };
+  static ExportCache& get() {
+    static ExportCache c;
+    return c;
+  }
+  // The device that owns `ptr` must be current. False if the pointer cannot be exported.
+  bool lookup(const void* ptr, Entry* out) {
+    const CudaLib& lib = CudaLib::get();
+    if (!lib.ok) return false;
+    unsigned long long id = 0;
+    if (lib.cuPointerGetAttribute(&id, CudaLib::kAttrBufferId, reinterpret_cast<CUdeviceptr_t>(ptr)) != 0) return false;
+    const uintptr_t a = reinterpret_cast<uintptr_t>(ptr);
+    std::unique_lock<std::mutex> lock(m_);
+    auto it = byBase_.upper_bound(a);
+    if (it != byBase_.begin()) {
+      --it;
+      if (a - it->second.base < it->second.size && it->second.id == id) {
+        *out = it->second;
+        return true;
+      }
+    }
+    void* base = nullptr;
+    size_t size = 0;
+    unsigned long long id2 = 0;
+    if (!cudaAllocationInfo(ptr, &base, &size, &id2)) return false;
+    cudaIpcMemHandle_t h;
+    if (cudaIpcGetMemHandle(&h, base) != cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    Entry e;
+    e.base = reinterpret_cast<uintptr_t>(base);
+    e.size = size;
+    e.id = id2;
+    std::memcpy(e.handle.data(), &h, sizeof(h));
+    // Drop whatever used to live in this address range.
+    auto first = byBase_.lower_bound(e.base);
+    if (first != byBase_.begin()) {
+      auto prev = std::prev(first);
+      if (prev->second.base + prev->second.size > e.base) first = prev;
+    }
+    auto last = first;
+    while (last != byBase_.end() && last->second.base < e.base + e.size) ++last;
+    byBase_.erase(first, last);
+    if (byBase_.size() > 8192) byBase_.clear();
+    byBase_[e.base] = e;
+    *out = e;
+    return true;
+  }
+
+ private:
+  std::mutex m_;
+  std::map<uintptr_t, Entry> byBase_;
+};
+
 class ContextImpl;
 
 struct Arena {
@@ -813,6 +880,9 @@ void ChannelImpl::sendReady(RecvOp& op) {
         a->announcedSeq = static_cast<int64_t>(op.seq);
       }
     }
+    // The driver queries below need this device's context current on the calling thread, which
+    // may be a transport thread that never touched CUDA.
+    CudaDeviceGuard g(op.device);
     for (auto& it : op.items) {
       TargetWire t;
       void* ptr = it.buffer.unwrap<CudaBuffer>().ptr;
@@ -823,23 +893,12 @@ void ChannelImpl::sendReady(RecvOp& op) {
       if (sameProcess_) {
         t.ptr = reinterpret_cast<uint64_t>(ptr);
       } else {
-        void* base = nullptr;
-        size_t size = 0;
-        unsigned long long id = 0;
-        // The driver queries below need this device's context current on the calling thread,
-        // which may be a transport thread that never touched CUDA.
-        CudaDeviceGuard g(op.device);
-        if (cudaAllocationInfo(ptr, &base, &size, &id)) {
-          cudaIpcMemHandle_t h;
-          cudaError_t e = cudaIpcGetMemHandle(&h, base);
-          if (e == cudaSuccess) {
-            std::memcpy(t.handle.data(), &h, sizeof(h));
-            t.hasHandle = 1;
-            t.bufferId = id;
-            t.ptr = static_cast<uint64_t>(static_cast<uint8_t*>(ptr) - static_cast<uint8_t*>(base));
-          } else {
-            cudaGetLastError();
-          }
+        ExportCache::Entry exported;
+        if (ExportCache::get().lookup(ptr, &exported)) {
+          t.handle = exported.handle;
+          t.hasHandle = 1;
+          t.bufferId = exported.id;
+          t.ptr = static_cast<uint64_t>(reinterpret_cast<uintptr_t>(ptr) - exported.base);
         }
       }
       r.targets.push_back(t);

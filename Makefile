@@ -15,6 +15,14 @@ NVCCFLAGS := -std=c++17 -O3 -gencode arch=compute_100a,code=sm_100a -lineinfo \
              -Xcompiler -fPIC -Iinclude -Isrc --expt-relaxed-constexpr
 LDLIBS := -L$(CUDA_HOME)/lib64 -lcudart_static -ldl -lrt -lpthread
 
+# make SANITIZE=thread BUILD=build-tsan build-tsan/bin/tpb_test   (or SANITIZE=address): the host code
+# of the library and of the C++ tests under a sanitizer, as the reference's cmake/Sanitize.cmake does.
+ifdef SANITIZE
+CXXFLAGS += -fsanitize=$(SANITIZE) -fno-omit-frame-pointer -O1
+NVCCFLAGS += -Xcompiler -fsanitize=$(SANITIZE)
+LDLIBS += -fsanitize=$(SANITIZE)
+endif
+
 PYINC := $(shell $(PYTHON) -c "import sysconfig,pybind11;print('-I'+sysconfig.get_paths()['include'],'-I'+pybind11.get_include())")
 PYEXT := $(shell $(PYTHON) -c "import sysconfig;print(sysconfig.get_config_var('EXT_SUFFIX'))")
 

@@ -119,6 +119,8 @@ namespace cuda_basic {
 std::shared_ptr<Context> create(std::shared_ptr<Context> cpuContext);
 }
 namespace cuda_p2p {
+// Every field can be overridden from the environment when the channel is created:
+// TPB_CUDA_P2P_EAGER_THRESHOLD, _INBOX_BYTES, _MAX_CTAS, _WAIT_KERNEL (0/1), _WAIT_TIMEOUT_MS, _BULK (0/1).
 struct Options {
   size_t eagerThreshold = 64 * 1024;     // batches up to this many bytes go through the inbox
   size_t inboxBytes = 8u << 20;          // per-peer inbox ring in device memory
@@ -131,6 +133,8 @@ struct Options {
 // the receiver's memory (same process: raw pointers; other process: IPC-mapped) and publishes a
 // release-ordered flag. Replaces both cuda_xth and cuda_ipc of the reference.
 std::shared_ptr<Context> create(Options options = Options());
+// The options after the environment overrides (what create() will use).
+Options applyEnvironment(Options options);
 }  // namespace cuda_p2p
 namespace cuda_xth {
 inline std::shared_ptr<Context> create() { return cuda_p2p::create(); }

@@ -9,3 +9,4 @@
 #include <tpb/message.h>
 #include <tpb/pipe.h>
 #include <tpb/transport.h>
+#include <tpb/trace.h>

@@ -309,6 +309,11 @@ PYBIND11_MODULE(_C, m) {
       });
 
   m.def("kernel_launch_count", &kernels::launchCount);
+  m.def("trace_enable", &traceEnable, py::arg("path"),
+        "Start recording pipe / channel / kernel-launch events; trace_dump() writes chrome://tracing JSON.");
+  m.def("trace_disable", &traceDisable);
+  m.def("trace_dump", &traceDump, py::arg("path") = "");
+  m.def("trace_event_count", &traceEventCount);
   // Direct access to the push/pack kernel for tests and tools: copy byte ranges between device
   // addresses on the current device with one launch; optionally publish a completion flag
   // (then `counter_ptr` must point to a zeroed 32-bit word in device memory).

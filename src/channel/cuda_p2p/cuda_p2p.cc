@@ -47,6 +47,7 @@
 #include <tpb/channel.h>
 
 #include "common/cuda.h"
+#include "common/trace.h"
 #include "common/defs.h"
 #include "common/loop.h"
 #include "common/nop.h"
@@ -716,6 +717,7 @@ ChannelImpl::Eager ChannelImpl::tryEager(SendOp& op) {
 }
 
 void ChannelImpl::launchRendezvous(SendOp& op) {
+  trace::Scope traced("cuda_p2p.launchRendezvous", op.seq);
   const RecvReady& ready = *op.ready;
   if (ready.targets.size() != op.items.size()) {
     return closeFromLoop(TPB_CREATE_ERROR(LogicError, "peer announced a different number of tensors"));
@@ -863,6 +865,7 @@ void ChannelImpl::recvBatchFromLoop(std::vector<RecvItem> items) {
 
 void ChannelImpl::sendReady(RecvOp& op) {
   if (error_) return;
+  trace::Scope traced("cuda_p2p.sendReady", op.seq);
   RecvReady r;
   r.seq = op.seq;
   r.deviceIdx = op.device;
@@ -912,6 +915,7 @@ void ChannelImpl::sendReady(RecvOp& op) {
 }
 
 void ChannelImpl::completeRecv(RecvOp& op) {
+  trace::Scope traced("cuda_p2p.completeRecv", op.seq);
   const Launched& n = *op.notice;
   TPB_VLOG(6) << "Channel " << id_ << " learnt that batch #" << op.seq << " is on its way"
               << (n.eager ? " (eager)" : "") << "; making the stream wait";
@@ -1103,7 +1107,27 @@ void ChannelImpl::closeFromLoop(const Error& e) {
 
 }  // namespace
 
-std::shared_ptr<Context> create(Options options) { return std::make_shared<ContextImpl>(options); }
+Options applyEnvironment(Options o) {
+  auto num = [](const char* name, auto& field) {
+    const char* s = std::getenv(name);
+    if (!s || !*s) return;
+    char* end = nullptr;
+    const unsigned long long v = std::strtoull(s, &end, 0);
+    if (end && *end == 0) field = static_cast<std::decay_t<decltype(field)>>(v);
+    else TPB_LOG_WARNING << name << "=" << s << " is not a number; ignored";
+  };
+  num("TPB_CUDA_P2P_EAGER_THRESHOLD", o.eagerThreshold);
+  num("TPB_CUDA_P2P_INBOX_BYTES", o.inboxBytes);
+  num("TPB_CUDA_P2P_MAX_CTAS", o.maxCtas);
+  num("TPB_CUDA_P2P_WAIT_KERNEL", o.waitWithKernel);
+  num("TPB_CUDA_P2P_BULK", o.useBulkCopy);
+  unsigned long long ms = o.waitTimeoutNs / 1'000'000ull;
+  num("TPB_CUDA_P2P_WAIT_TIMEOUT_MS", ms);
+  o.waitTimeoutNs = ms * 1'000'000ull;
+  return o;
+}
+
+std::shared_ptr<Context> create(Options options) { return std::make_shared<ContextImpl>(applyEnvironment(options)); }
 
 }  // namespace cuda_p2p
 }  // namespace channel

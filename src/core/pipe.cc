@@ -9,6 +9,7 @@
 #include <algorithm>
 
 #include "core/core_impl.h"
+#include "common/trace.h"
 #include "transport/nop_io.h"
 
 namespace tpb {
@@ -329,6 +330,7 @@ void PipeImpl::readDescriptor(Pipe::read_descriptor_callback_fn fn) {
 
 void PipeImpl::readDescriptorFromLoop(Pipe::read_descriptor_callback_fn fn) {
   ReadOperation& op = readOps_.emplaceBack();
+  trace::instant("pipe.readDescriptor", op.sequenceNumber);
   TPB_VLOG(1) << "Pipe " << id_ << " received a readDescriptor request (#" << op.sequenceNumber << ")";
   op.readDescriptorCallback = std::move(fn);
   readOps_.advanceOperation(op);
@@ -352,6 +354,7 @@ void PipeImpl::readFromLoop(Allocation allocation, Pipe::read_callback_fn fn) {
   TPB_THROW_ASSERT_IF(op == nullptr, "internal: lost read operation");
   checkAllocationCompatibility(op->descriptor, allocation);
   awaitingRead_.pop_front();
+  trace::instant("pipe.read", op->sequenceNumber);
   TPB_VLOG(1) << "Pipe " << id_ << " received a read request (#" << op->sequenceNumber << ")";
   op->allocation = std::move(allocation);
   op->readCallback = std::move(fn);
@@ -371,6 +374,7 @@ void PipeImpl::write(Message message, Pipe::write_callback_fn fn) {
 
 void PipeImpl::writeFromLoop(Message message, Pipe::write_callback_fn fn) {
   WriteOperation& op = writeOps_.emplaceBack();
+  trace::instant("pipe.write", op.sequenceNumber);
   TPB_VLOG(1) << "Pipe " << id_ << " received a write request (#" << op.sequenceNumber << ")";
   op.message = std::move(message);
   op.writeCallback = std::move(fn);
@@ -444,6 +448,7 @@ void PipeImpl::advanceReadOperation(ReadOperation& op, ReadOperation::State prev
                        op.numPayloadsBeingRead == 0 && op.numTensorsBeingReceived == 0 &&
                            prev == R::FINISHED,
                        [&]() {
+                         trace::instant("pipe.read.done", op.sequenceNumber);
                          TPB_VLOG(1) << "Pipe " << id_ << " is calling a read callback (#"
                                      << op.sequenceNumber << ")";
                          if (!error_) {
@@ -582,6 +587,7 @@ void PipeImpl::advanceWriteOperation(WriteOperation& op, WriteOperation::State p
                        op.numPayloadsBeingWritten == 0 && op.numTensorsBeingSent == 0 &&
                            prev == W::FINISHED,
                        [&]() {
+                         trace::instant("pipe.write.done", op.sequenceNumber);
                          TPB_VLOG(1) << "Pipe " << id_ << " is calling a write callback (#"
                                      << op.sequenceNumber << ")";
                          if (!error_) {

@@ -29,6 +29,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include "common/trace.h"
+
 #include <atomic>
 #include <mutex>
 #include <stdexcept>
@@ -904,6 +906,7 @@ void appendToPlan(PushPlan& plan, const CopyItem& item, bool useBulk) {
 int launchPush(const PushPlan& plan, cudaStream_t stream, int maxCtas, uint32_t* flag, uint32_t flagValue,
                uint32_t* counter, uint32_t* status) {
   const size_t n = plan.entries.size();
+  trace::Scope traced("tpb_push_pack launch", plan.totalBytesOut);
   if (maxCtas <= 0) maxCtas = 1;
   const uint32_t tileBytes = plan.bulkTileBytes ? plan.bulkTileBytes : 32768;
   const uint32_t stages = plan.bulkStages ? plan.bulkStages : 4;

@@ -443,3 +443,30 @@ TPB_TEST(Channel, PipeSelectsCmaAcrossProcessesAndXthInside) {
         ctx->join();
       });
 }
+
+// The CUDA channel's options can be overridden from the environment (no GPU needed to check).
+TPB_TEST(Channel, CudaP2pOptionsFollowTheEnvironment) {
+  namespace p2p = tpb::channel::cuda_p2p;
+  ::setenv("TPB_CUDA_P2P_EAGER_THRESHOLD", "4096", 1);
+  ::setenv("TPB_CUDA_P2P_INBOX_BYTES", "0x100000", 1);
+  ::setenv("TPB_CUDA_P2P_MAX_CTAS", "37", 1);
+  ::setenv("TPB_CUDA_P2P_WAIT_KERNEL", "1", 1);
+  ::setenv("TPB_CUDA_P2P_WAIT_TIMEOUT_MS", "250", 1);
+  ::setenv("TPB_CUDA_P2P_BULK", "0", 1);
+  p2p::Options o = p2p::applyEnvironment(p2p::Options());
+  EXPECT_EQ(o.eagerThreshold, size_t(4096));
+  EXPECT_EQ(o.inboxBytes, size_t(1) << 20);
+  EXPECT_EQ(o.maxCtas, 37);
+  EXPECT_TRUE(o.waitWithKernel);
+  EXPECT_EQ(o.waitTimeoutNs, uint64_t(250) * 1000 * 1000);
+  EXPECT_FALSE(o.useBulkCopy);
+  ::setenv("TPB_CUDA_P2P_MAX_CTAS", "many", 1);  // not a number: ignored with a warning
+  p2p::Options keep;
+  keep.maxCtas = 5;
+  EXPECT_EQ(p2p::applyEnvironment(keep).maxCtas, 5);
+  for (const char* n : {"TPB_CUDA_P2P_EAGER_THRESHOLD", "TPB_CUDA_P2P_INBOX_BYTES", "TPB_CUDA_P2P_MAX_CTAS",
+                        "TPB_CUDA_P2P_WAIT_KERNEL", "TPB_CUDA_P2P_WAIT_TIMEOUT_MS", "TPB_CUDA_P2P_BULK"})
+    ::unsetenv(n);
+  p2p::Options d = p2p::applyEnvironment(p2p::Options());
+  EXPECT_EQ(d.eagerThreshold, size_t(64 * 1024));
+}

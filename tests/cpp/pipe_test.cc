@@ -398,3 +398,37 @@ TPB_TEST(Pipe, ManyMessagesOverShm) {
           [&](Pipe& p) { for (int i = 0; i < kN; ++i) { writeSync(p, msg.view(true)); expectSame(msg, readSync(p)); } },
           {"uv://127.0.0.1", "shm://"}, true);
 }
+
+// Tracing: a traced ping records the pipe's write / read events, and the dump is a JSON array
+// whose entries carry the sequence number of the message.
+#include <tpb/trace.h>
+
+#include <fstream>
+#include <sstream>
+
+TPB_TEST(Pipe, TraceRecordsWritesAndReadsAndDumpsJson) {
+  char path[] = "/tmp/tpb_trace_test_XXXXXX";
+  int fd = ::mkstemp(path);
+  EXPECT_TRUE(fd >= 0);
+  ::close(fd);
+  const uint64_t before = traceEventCount();
+  traceEnable(path);
+  auto msg = makeMessage(77, {16}, {4096});
+  runPair([&](Pipe& p) { expectSame(msg, readSync(p)); }, [&](Pipe& p) { writeSync(p, msg.view(false)); });
+  traceDisable();
+  EXPECT_TRUE(traceEventCount() >= before + 5);  // write, write.done, readDescriptor, read, read.done
+  EXPECT_TRUE(traceDump());
+  std::ifstream in(path);
+  std::stringstream ss;
+  ss << in.rdbuf();
+  const std::string json = ss.str();
+  ::unlink(path);
+  EXPECT_TRUE(json.size() > 2 && json[0] == '[');
+  for (const char* name : {"pipe.write", "pipe.write.done", "pipe.readDescriptor", "pipe.read", "pipe.read.done"})
+    EXPECT_TRUE(json.find(std::string("\"name\":\"") + name + "\"") != std::string::npos);
+  EXPECT_TRUE(json.find("\"ph\":\"i\"") != std::string::npos);
+  // Events recorded while tracing is off are dropped.
+  const uint64_t after = traceEventCount();
+  runPair([&](Pipe& p) { expectSame(msg, readSync(p)); }, [&](Pipe& p) { writeSync(p, msg.view(false)); });
+  EXPECT_EQ(traceEventCount(), after);
+}

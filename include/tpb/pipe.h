@@ -4,6 +4,7 @@
 // given pipe fire in the order the operations were issued.
 #pragma once
 
+#include <chrono>
 #include <functional>
 #include <memory>
 #include <string>
@@ -16,6 +17,15 @@ namespace tpb {
 class ContextImpl;
 class ListenerImpl;
 class PipeImpl;
+
+// Optional deadlines (not in the reference, where a silent peer hangs an operation forever).
+// Zero means "wait forever". When a deadline passes the pipe fails with TimeoutError: the late
+// operation and everything queued behind it get that error, as after any other pipe error.
+struct PipeTimeouts {
+  std::chrono::milliseconds write{0};       // write() call -> its callback
+  std::chrono::milliseconds read{0};        // read() call -> its callback
+  std::chrono::milliseconds descriptor{0};  // readDescriptor() call -> its callback (an idle limit)
+};
 
 class Pipe final {
   // Only the context and the listener create pipes.
@@ -38,6 +48,9 @@ class Pipe final {
   void read(Allocation allocation, read_callback_fn fn);
   // Send a message. The memory it points to must stay valid until the callback fires.
   void write(Message message, write_callback_fn fn);
+
+  // Applies to operations issued after the call.
+  void setTimeouts(PipeTimeouts timeouts);
 
   // Name the peer gave to its context (or the name passed to connect()).
   const std::string& getRemoteName();

@@ -239,6 +239,16 @@ PYBIND11_MODULE(_C, m) {
              self.read(std::move(copy), [cb](const Error& e) { cb(errorString(e)); });
            })
       .def("remote_name", [](Pipe& self) { return self.getRemoteName(); })
+      .def("set_timeouts",
+           [](Pipe& self, int64_t writeMs, int64_t readMs, int64_t descriptorMs) {
+             PipeTimeouts t;
+             t.write = std::chrono::milliseconds(writeMs);
+             t.read = std::chrono::milliseconds(readMs);
+             t.descriptor = std::chrono::milliseconds(descriptorMs);
+             self.setTimeouts(t);
+           },
+           py::arg("write_ms") = 0, py::arg("read_ms") = 0, py::arg("descriptor_ms") = 0,
+           "Deadlines for operations issued from now on (0 = wait forever); a missed one fails the pipe with 'timeout'.")
       .def("channel_supports_layouts",
            [](Pipe& self, const std::string& local, const std::string& remote) {
              Device l = parseDevice(local), r = parseDevice(remote);

@@ -3,7 +3,8 @@
 // with hierarchical ids, tensorpipe/core/pipe_impl.cc:240,1117-1199, and the state-machine dump
 // tool); this keeps those and adds a timeline.
 //
-//   TPB_TRACE=/path/trace.json   record from start-up and write a chrome://tracing file at exit
+//   TPB_TRACE=/path/trace.%p.json   record from start-up and write a chrome://tracing file at exit
+//                                   (%p = process id)
 //   tpb::trace::enable(path) / tpb::trace::dump()   the same from code (Python: trace_enable / trace_dump)
 //
 // Events are fixed-size slots claimed with one fetch_add; the ring keeps the most recent
@@ -51,6 +52,10 @@ class Tracer {
     std::unique_lock<std::mutex> lock(m_);
     if (!ring_) ring_.reset(new Event[kCapacity]());
     path_ = path;
+    // "%p" in the path becomes the process id, so that ranks sharing an environment do not
+    // overwrite one another's file.
+    const size_t at = path_.find("%p");
+    if (at != std::string::npos) path_.replace(at, 2, std::to_string(::getpid()));
     enabled_.store(true, std::memory_order_release);
   }
   void disable() { enabled_.store(false, std::memory_order_release); }

@@ -193,6 +193,7 @@ class PipeImpl final : public std::enable_shared_from_this<PipeImpl> {
   void readDescriptor(Pipe::read_descriptor_callback_fn fn);
   void read(Allocation allocation, Pipe::read_callback_fn fn);
   void write(Message message, Pipe::write_callback_fn fn);
+  void setTimeouts(PipeTimeouts timeouts);
   const std::string& getRemoteName() { return remoteName_; }
   bool channelSupportsLayouts(const Device& local, const Device& remote);
   void close();
@@ -205,6 +206,9 @@ class PipeImpl final : public std::enable_shared_from_this<PipeImpl> {
   void readFromLoop(Allocation allocation, Pipe::read_callback_fn fn);
   void writeFromLoop(Message message, Pipe::write_callback_fn fn);
   void handleError();
+  // Fails the pipe with TimeoutError if the operation is still pending after `delay`.
+  enum class Deadline { kWrite, kRead, kDescriptor };
+  void armDeadline(Deadline kind, int64_t seq, std::chrono::milliseconds delay);
 
   void advanceReadOperation(ReadOperation& op, ReadOperation::State prev);
   void advanceWriteOperation(WriteOperation& op, WriteOperation::State prev);
@@ -245,6 +249,7 @@ class PipeImpl final : public std::enable_shared_from_this<PipeImpl> {
   std::unordered_map<std::string, std::vector<std::shared_ptr<transport::Connection>>>
       channelReceivedConnections_;
   Error error_;
+  PipeTimeouts timeouts_;  // loop only
 
   OpQueue<ReadOperation> readOps_;
   OpQueue<WriteOperation> writeOps_;

@@ -9,6 +9,7 @@
 #include <algorithm>
 
 #include "core/core_impl.h"
+#include "common/timer.h"
 #include "common/trace.h"
 #include "transport/nop_io.h"
 
@@ -333,6 +334,7 @@ void PipeImpl::readDescriptorFromLoop(Pipe::read_descriptor_callback_fn fn) {
   trace::instant("pipe.readDescriptor", op.sequenceNumber);
   TPB_VLOG(1) << "Pipe " << id_ << " received a readDescriptor request (#" << op.sequenceNumber << ")";
   op.readDescriptorCallback = std::move(fn);
+  if (timeouts_.descriptor.count() > 0) armDeadline(Deadline::kDescriptor, op.sequenceNumber, timeouts_.descriptor);
   readOps_.advanceOperation(op);
 }
 
@@ -359,6 +361,7 @@ void PipeImpl::readFromLoop(Allocation allocation, Pipe::read_callback_fn fn) {
   op->allocation = std::move(allocation);
   op->readCallback = std::move(fn);
   op->doneGettingAllocation = true;
+  if (timeouts_.read.count() > 0) armDeadline(Deadline::kRead, op->sequenceNumber, timeouts_.read);
   // Never call back from inside read(): advance from a fresh loop iteration.
   auto self = shared_from_this();
   int64_t seq = op->sequenceNumber;
@@ -386,7 +389,39 @@ void PipeImpl::writeFromLoop(Message message, Pipe::write_callback_fn fn) {
     op.targetDevices.push_back(t.targetDevice);
     if (!t.targetDevice.has_value()) op.hasMissingTargetDevices = true;
   }
+  if (timeouts_.write.count() > 0) armDeadline(Deadline::kWrite, op.sequenceNumber, timeouts_.write);
   writeOps_.advanceOperation(op);
+}
+
+void PipeImpl::setTimeouts(PipeTimeouts timeouts) {
+  auto self = shared_from_this();
+  context_->deferToLoop([self, timeouts]() { self->timeouts_ = timeouts; });
+}
+
+void PipeImpl::armDeadline(Deadline kind, int64_t seq, std::chrono::milliseconds delay) {
+  std::weak_ptr<PipeImpl> weak = shared_from_this();
+  TimerThread::get().schedule(delay, [weak, kind, seq]() {
+    auto self = weak.lock();
+    if (!self) return;
+    self->context_->deferToLoop([self, kind, seq]() {
+      if (self->error_) return;
+      bool pending;
+      if (kind == Deadline::kWrite) {
+        WriteOperation* op = self->writeOps_.findOperation(seq);
+        pending = op != nullptr && op->state != WriteOperation::FINISHED;
+      } else {
+        ReadOperation* op = self->readOps_.findOperation(seq);
+        // A descriptor deadline is met once the descriptor has been handed to the user.
+        pending = op != nullptr && op->state != ReadOperation::FINISHED &&
+            (kind == Deadline::kRead || !op->descriptorDelivered);
+      }
+      if (!pending) return;
+      TPB_VLOG(1) << "Pipe " << self->id_ << " gives up on "
+                  << (kind == Deadline::kWrite ? "write" : kind == Deadline::kRead ? "read" : "readDescriptor") << " #"
+                  << seq << ": deadline passed";
+      self->setError(TPB_CREATE_ERROR(TimeoutError));
+    });
+  });
 }
 
 // ---- read state machine ---------------------------------------------------------------------
@@ -739,6 +774,7 @@ Pipe::Pipe(ConstructorToken, std::shared_ptr<PipeImpl> impl) : impl_(std::move(i
 void Pipe::readDescriptor(read_descriptor_callback_fn fn) { impl_->readDescriptor(std::move(fn)); }
 void Pipe::read(Allocation allocation, read_callback_fn fn) { impl_->read(std::move(allocation), std::move(fn)); }
 void Pipe::write(Message message, write_callback_fn fn) { impl_->write(std::move(message), std::move(fn)); }
+void Pipe::setTimeouts(PipeTimeouts timeouts) { impl_->setTimeouts(timeouts); }
 const std::string& Pipe::getRemoteName() { return impl_->getRemoteName(); }
 bool Pipe::channelSupportsLayouts(const Device& l, const Device& r) { return impl_->channelSupportsLayouts(l, r); }
 void Pipe::close() { impl_->close(); }

@@ -502,7 +502,9 @@ PhaseResult RingBench::Impl::runMixedOn(const std::vector<std::shared_ptr<Pipe>>
   auto st = std::make_shared<State>();
   Impl* mp = &m;
 
-  // One receive chain per incoming pipe, each into its own region of the destination buffer.
+  // Two receive chains per incoming pipe (two messages in flight, like the single-tensor stream),
+  // alternating between the two destination buffers; each pipe has its own region in both.
+  auto readsIssued = std::make_shared<std::vector<int>>(recvPipes.size(), 0);
   auto armRead = std::make_shared<std::function<void(size_t, int)>>();
   *armRead = [=](size_t k, int remaining) {
     if (remaining == 0) return;
@@ -514,10 +516,12 @@ PhaseResult RingBench::Impl::runMixedOn(const std::vector<std::shared_ptr<Pipe>>
         if (!st->recvSet) { st->recvSet = true; st->recvDone.set_value(); }
       };
       if (e) return fail(e);
+      // Descriptor callbacks of one context run one at a time: no lock needed for the counter.
+      uint8_t* base = mp->dst[(*readsIssued)[k]++ & 1] + k * layout->dstTotal;
       Allocation a;
       for (const MixedSpec& s : layout->specs) {
         Allocation::Tensor t;
-        t.buffer = CudaBuffer{mp->dst[0] + k * layout->dstTotal + s.dstOff, mp->recvStream, mp->opts.device};
+        t.buffer = CudaBuffer{base + s.dstOff, mp->recvStream, mp->opts.device};
         if (s.cast) {
           t.castTo = DType::kBF16;
           t.sourceDtype = DType::kF32;
@@ -542,7 +546,7 @@ PhaseResult RingBench::Impl::runMixedOn(const std::vector<std::shared_ptr<Pipe>>
       });
     });
   };
-  // One send chain per outgoing pipe; all of them read the same source tensors.
+  // Two send chains per outgoing pipe; all of them read the same source tensors.
   auto sendOne = std::make_shared<std::function<void(size_t, int)>>();
   *sendOne = [=](size_t k, int remaining) {
     if (remaining == 0) return;
@@ -580,8 +584,14 @@ PhaseResult RingBench::Impl::runMixedOn(const std::vector<std::shared_ptr<Pipe>>
   if (recvPipes.size() == 1 && sendPipes.size() == 1) m.syncOn(sendPipes[0], recvPipes[0]);
   auto t0 = Clock::now();
   TPB_CUDA_CHECK(cudaEventRecord(m.evStart, m.recvStream));
-  for (size_t k = 0; k < recvPipes.size(); ++k) (*armRead)(k, steps);
-  for (size_t k = 0; k < sendPipes.size(); ++k) (*sendOne)(k, steps);
+  for (int chain = 0; chain < 2; ++chain) {
+    const int share = chain == 0 ? (steps + 1) / 2 : steps / 2;
+    for (size_t k = 0; k < recvPipes.size(); ++k) (*armRead)(k, share);
+  }
+  for (int chain = 0; chain < 2; ++chain) {
+    const int share = chain == 0 ? (steps + 1) / 2 : steps / 2;
+    for (size_t k = 0; k < sendPipes.size(); ++k) (*sendOne)(k, share);
+  }
   auto fr = st->recvDone.get_future();
   auto fs = st->sendDone.get_future();
   if (totalRecv > 0) waitOrThrow(fr, 300, "receiving");

@@ -90,6 +90,11 @@ class Pipe:
     def close(self) -> None:
         self._p.close()
 
+    def set_timeouts(self, write: float = 0.0, read: float = 0.0, descriptor: float = 0.0) -> None:
+        """Deadlines in seconds for operations issued from now on (0 = wait forever). A missed
+        deadline fails the pipe: the late operation and all later ones report "timeout"."""
+        self._p.set_timeouts(int(write * 1000), int(read * 1000), int(descriptor * 1000))
+
     # ---- native-shaped API ----
     def write(self, message: Message, callback: Callable[[str], None]) -> None:
         out = _C.OutgoingMessage(bytes(message.metadata))

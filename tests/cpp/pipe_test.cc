@@ -432,3 +432,37 @@ TPB_TEST(Pipe, TraceRecordsWritesAndReadsAndDumpsJson) {
   runPair([&](Pipe& p) { expectSame(msg, readSync(p)); }, [&](Pipe& p) { writeSync(p, msg.view(false)); });
   EXPECT_EQ(traceEventCount(), after);
 }
+
+// Optional deadlines: a peer that never answers fails the operation with TimeoutError instead of
+// hanging it; operations that finish in time are unaffected.
+TPB_TEST(Pipe, DeadlinesFailASilentPeerAndSpareAPromptOne) {
+  auto msg = makeMessage(91, {8}, {256});
+  std::atomic<bool> timedOut{false}, laterAlsoFailed{false};
+  runPair(
+      [&](Pipe& p) {
+        // Serve one message promptly, then go silent: never write again.
+        expectSame(msg, readSync(p));
+        writeSync(p, msg.view(false));
+        std::this_thread::sleep_for(std::chrono::milliseconds(700));
+      },
+      [&](Pipe& p) {
+        PipeTimeouts t;
+        t.write = std::chrono::milliseconds(5000);
+        t.read = std::chrono::milliseconds(5000);
+        t.descriptor = std::chrono::milliseconds(300);
+        p.setTimeouts(t);
+        writeSync(p, msg.view(false));
+        expectSame(msg, readSync(p));  // answered well inside every deadline
+        std::promise<Error> first, second;
+        p.readDescriptor([&](const Error& e, Descriptor) { first.set_value(e); });
+        p.readDescriptor([&](const Error& e, Descriptor) { second.set_value(e); });
+        auto f1 = first.get_future();
+        auto f2 = second.get_future();
+        Error e1 = waitFor(f1);
+        Error e2 = waitFor(f2);
+        timedOut = e1.isOfType<TimeoutError>();
+        laterAlsoFailed = bool(e2);
+      });
+  EXPECT_TRUE(timedOut.load());
+  EXPECT_TRUE(laterAlsoFailed.load());
+}

@@ -60,6 +60,27 @@ def test_callbacks_are_ordered_and_errors_reach_python(built):
     b.join()
 
 
+def test_deadlines_and_trace_from_python(built, tmp_path):
+    from tensorpipe_b200 import _C
+    trace_file = str(tmp_path / "trace.json")
+    _C.trace_enable(trace_file)
+    a, b, listener, out_pipe, in_pipe = connected_pair(cuda=False)
+    in_pipe.set_timeouts(descriptor=0.3)
+    sent = out_pipe.send([torch.ones(8)])
+    assert torch.equal(in_pipe.recv().result(30).tensors[0], torch.ones(8))  # in time: unaffected
+    sent.result(30)
+    late = in_pipe.recv()  # nothing is ever sent again
+    with pytest.raises(RuntimeError, match="timeout"):
+        late.result(30)
+    _C.trace_disable()
+    assert _C.trace_dump()
+    import json
+    events = json.load(open(trace_file))
+    assert {"pipe.write", "pipe.read.done"} <= {e["name"] for e in events}
+    a.join()
+    b.join()
+
+
 def test_mpt_lanes_carry_tensors(built):
     a = tpb.Context("a")
     b = tpb.Context("b")

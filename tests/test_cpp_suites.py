@@ -7,7 +7,7 @@ import subprocess
 import pytest
 
 CPU_SUITES = ["Nop.", "Transport.", "TransportShm.", "TransportUv.", "Pipe.", "Context.", "Listener.",
-              "Channel.", "Common.", "Faults."]
+              "Channel.", "Common.", "Faults.", "Plan."]
 GPU_SUITES = ["Kernel.", "CudaPipe.", "CudaBasic.", "CudaChannel."]
 
 

@@ -23,6 +23,12 @@ NVCCFLAGS += -Xcompiler -fsanitize=$(SANITIZE)
 LDLIBS += -fsanitize=$(SANITIZE)
 endif
 
+# make DEBUG_KERNELS=1 BUILD=build-dbg build-dbg/bin/tpb_test: kernels that check every address they
+# compute against their table entry and count what lies outside (see src/kernels/push.h).
+ifdef DEBUG_KERNELS
+NVCCFLAGS += -DTPB_DEBUG_KERNELS
+endif
+
 PYINC := $(shell $(PYTHON) -c "import sysconfig,pybind11;print('-I'+sysconfig.get_paths()['include'],'-I'+pybind11.get_include())")
 PYEXT := $(shell $(PYTHON) -c "import sysconfig;print(sysconfig.get_config_var('EXT_SUFFIX'))")
 

@@ -10,6 +10,11 @@
 //   latency <bytes> <laps>               -> "ok <n> <sample_us>..."   (rank 0 only has samples)
 //   e2e <bytes> <steps>                  -> "ok <host_ms>"  (H2D from pinned memory every step,
 //                                            D2H of a 4-byte result every step)
+//   mixed <steps> <depth> <seed>         -> "ok <device_ms> <bytes_per_message>"  (64 tensors per
+//                                            message with the sizes the native mixed message
+//                                            DELIVERS; all contiguous and unconverted, because
+//                                            the reference has neither views nor casts: the layout
+//                                            work is left out in the reference's favour)
 //   quit
 // Protocol per step and timing points are the same as in src/tools/ring_bench.cc.
 #include <cuda_runtime.h>
@@ -19,7 +24,9 @@
 #include <functional>
 #include <future>
 #include <iostream>
+#include <cmath>
 #include <mutex>
+#include <random>
 #include <sstream>
 #include <string>
 #include <thread>
@@ -95,7 +102,41 @@ struct Bench {
     recvPipe = accepted.get_future().get();
   }
 
+  struct Segment {
+    size_t offset, bytes;
+  };
+
   double stream(size_t bytes, int steps, int depth, double* hostMs) {
+    return streamSegments({Segment{0, bytes}}, steps, depth, hostMs);
+  }
+
+  // The sizes of the 64-tensor mixed message as delivered: dtype cycles fp32, bf16, int64; sizes
+  // log-uniform in [1 KiB, 16 MiB] rounded to rows of 64 elements; every other fp32 tensor arrives
+  // as bf16. Same generator and seed as the native benchmark, so both sides move the same bytes.
+  static std::vector<Segment> mixedSegments(uint64_t seed, size_t* delivered) {
+    std::vector<Segment> segs;
+    std::mt19937_64 rng(seed);
+    int fp32Count = 0;
+    size_t offset = 0;
+    *delivered = 0;
+    for (int i = 0; i < 64; ++i) {
+      const size_t es = i % 3 == 0 ? 4 : (i % 3 == 1 ? 2 : 8);
+      const double lg = std::log(1024.0) + (std::log(16.0 * 1024 * 1024) - std::log(1024.0)) *
+                                                (static_cast<double>(rng() % 100000) / 100000.0);
+      const uint64_t bytes = static_cast<uint64_t>(std::exp(lg));
+      const uint64_t rows = std::max<uint64_t>(1, bytes / es / 64);
+      const uint64_t elems = rows * 64;
+      bool cast = false;
+      if (es == 4) cast = (fp32Count++ % 2) == 0;
+      const size_t out = cast ? elems * 2 : elems * es;
+      segs.push_back(Segment{offset, out});
+      offset += (out + 255) / 256 * 256;
+      *delivered += out;
+    }
+    return segs;
+  }
+
+  double streamSegments(std::vector<Segment> segs, int steps, int depth, double* hostMs) {
     struct State {
       std::mutex mu;
       int sent = 0, inflight = 0, received = 0, armed = 0, descs = 0;
@@ -114,9 +155,11 @@ struct Bench {
         int k;
         { std::unique_lock<std::mutex> l(st->mu); k = st->descs++; }
         tp::Allocation a;
-        tp::Allocation::Tensor t;
-        t.buffer = tp::CudaBuffer{dst[k & 1], recvStream};
-        a.tensors.push_back(t);
+        for (const Segment& seg : segs) {
+          tp::Allocation::Tensor t;
+          t.buffer = tp::CudaBuffer{dst[k & 1] + seg.offset, recvStream};
+          a.tensors.push_back(t);
+        }
         recvPipe->read(std::move(a), [=](const tp::Error& e2) {
           if (e2) { std::cerr << "read: " << e2.what() << "\n"; std::exit(4); }
           bool last;
@@ -140,11 +183,13 @@ struct Bench {
           ++st->inflight;
         }
         tp::Message m;
-        tp::Message::Tensor t;
-        t.buffer = tp::CudaBuffer{src, sendStream};
-        t.length = bytes;
-        t.targetDevice = tp::Device(tp::kCudaDeviceType, args.nextDevice);
-        m.tensors.push_back(t);
+        for (const Segment& seg : segs) {
+          tp::Message::Tensor t;
+          t.buffer = tp::CudaBuffer{src + seg.offset, sendStream};
+          t.length = seg.bytes;
+          t.targetDevice = tp::Device(tp::kCudaDeviceType, args.nextDevice);
+          m.tensors.push_back(t);
+        }
         sendPipe->write(std::move(m), [=](const tp::Error& e) {
           if (e) { std::cerr << "write: " << e.what() << "\n"; std::exit(4); }
           bool done;
@@ -316,6 +361,15 @@ int main(int argc, char** argv) {
       double host = 0;
       double ms = b.stream(bytes, steps, depth, &host);
       std::cout << "ok " << ms << " " << host << std::endl;
+    } else if (cmd == "mixed") {
+      int steps, depth;
+      uint64_t seed;
+      in >> steps >> depth >> seed;
+      size_t delivered = 0;
+      auto segs = Bench::mixedSegments(seed, &delivered);
+      double host = 0;
+      double ms = b.streamSegments(segs, steps, depth, &host);
+      std::cout << "ok " << ms << " " << delivered << std::endl;
     } else if (cmd == "latency") {
       size_t bytes;
       int laps;

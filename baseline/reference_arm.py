@@ -1,7 +1,7 @@
 """Reference arm of bench.py: runs the reference's own build for the same metric and config.
 
-/root/reference cannot be built offline (its third_party submodule directories are empty and its
-setup.py insists on clang-6.0; `pip install --no-index ... /root/reference` fails in cmake), so this
+The reference's source tree cannot be built offline (its third_party submodule directories are empty
+and its setup.py insists on clang-6.0; `pip install --no-index` of the tree fails in cmake), so this
 arm uses the reference as PyTorch ships it: the TensorPipe public headers under
 torch/include/tensorpipe and the compiled library inside libtorch_cpu.so / libtorch_cuda.so.
 baseline/ref_pipe_bench.cc is a small harness over that public C++ API (Context, Listener, Pipe;
@@ -15,6 +15,8 @@ import select
 import subprocess
 import sys
 import time
+
+MIXED_SEED = 1  # the seed bench.py gives the native mixed message
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REPO = os.path.dirname(HERE)
@@ -178,6 +180,19 @@ def main(args, metric):
                        "p99_us": round(percentile(lat, 0.99), 2), "mean_us": round(sum(lat) / len(lat), 2),
                        "hops": world}
 
+        # The 64-tensor message with the delivered sizes of the native mixed message, contiguous and
+        # unconverted (the reference has neither views nor casts): its layout work is left out.
+        mixed = None
+        mixed_steps = 20
+        h.command(f"mixed 3 2 {MIXED_SEED}")
+        barrier()
+        out = h.command(f"mixed {mixed_steps} 2 {MIXED_SEED}")
+        barrier()
+        mixed_ms = max_over_ranks(float(out[0])) / mixed_steps
+        mixed = {"tensors": 64, "bytes_per_msg": int(out[1]), "ms_per_msg": round(mixed_ms, 4),
+                 "GBps": round(world * int(out[1]) / (mixed_ms * 1e-3) / 1e9, 2),
+                 "note": "contiguous tensors of the delivered sizes; no transposed views, no conversion"}
+
         e2e = None
         if not args.no_e2e:
             steps = max(5, min(args.steps, 20))
@@ -214,6 +229,7 @@ def main(args, metric):
                        "l2": "inputs larger than L2 (no flush)", "writes_in_flight": args.depth,
                        "channels": "cuda_xth (same process) / cuda_ipc (other process) / cuda_basic"},
             "clocks": clocks, "gpu_launches": 0, "e2e": e2e, "sweep": sweep, "latency": latency,
+            "mixed_64_tensor_message": mixed,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -37,6 +37,8 @@ const CudaLib& CudaLib::get() {
         loadSym(l.handle, l.cuMemGetAddressRange, {"cuMemGetAddressRange_v2"}) &&
         loadSym(l.handle, l.cuGetErrorString, {"cuGetErrorString"}) &&
         loadSym(l.handle, l.cuCtxGetCurrent, {"cuCtxGetCurrent"});
+    loadSym(l.handle, l.cuDeviceGet, {"cuDeviceGet"});
+    loadSym(l.handle, l.cuDevicePrimaryCtxGetState, {"cuDevicePrimaryCtxGetState"});
     // Stream memory operations are optional (the wait kernel is the fallback).
     loadSym(l.handle, l.cuStreamWaitValue32, {"cuStreamWaitValue32_v2", "cuStreamWaitValue32"});
     loadSym(l.handle, l.cuStreamWriteValue32, {"cuStreamWriteValue32_v2", "cuStreamWriteValue32"});
@@ -163,6 +165,17 @@ int cudaSmCount(int device) {
   TPB_CUDA_CHECK(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device));
   cache[device] = n;
   return n;
+}
+
+int cudaPrimaryContextActive(int device) {
+  const CudaLib& lib = CudaLib::get();
+  if (!lib.ok || !lib.cuDeviceGet || !lib.cuDevicePrimaryCtxGetState) return -1;
+  int dev = 0;
+  if (lib.cuDeviceGet(&dev, device) != 0) return -1;
+  unsigned flags = 0;
+  int active = 0;
+  if (lib.cuDevicePrimaryCtxGetState(dev, &flags, &active) != 0) return -1;
+  return active;
 }
 
 bool cudaZeroNow(void* ptr, size_t bytes, int device) {

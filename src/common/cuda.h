@@ -109,6 +109,8 @@ struct CudaLib {
   int (*cuStreamWriteValue32)(void* stream, CUdeviceptr_t addr, uint32_t value, unsigned flags) = nullptr;
   int (*cuGetErrorString)(int, const char**) = nullptr;
   int (*cuCtxGetCurrent)(void**) = nullptr;
+  int (*cuDeviceGet)(int* device, int ordinal) = nullptr;
+  int (*cuDevicePrimaryCtxGetState)(int device, unsigned* flags, int* active) = nullptr;
   bool ok = false;
   std::string why;
 
@@ -149,6 +151,9 @@ bool cudaAllocationInfo(const void* ptr, void** base, size_t* size, unsigned lon
 // Enable peer access from `device` to `peer` once (idempotent). Returns false if impossible.
 bool cudaEnablePeerAccessOnce(int device, int peer);
 int cudaSmCount(int device);
+// Whether this process has created (and not released) the primary context of `device`. Lets
+// tests prove that moving tensors of one GPU never initialises another one. -1 if unknown.
+int cudaPrimaryContextActive(int device);
 // Zeroes device memory and returns only once that has happened, on a private stream: it neither
 // waits for nor queues behind whatever the user's streams (or the legacy default stream) hold.
 // For memory whose address is about to be handed to a peer that may write to it right away.

@@ -29,6 +29,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include "common/cuda.h"
 #include "common/trace.h"
 
 #include <atomic>
@@ -117,6 +118,24 @@ __device__ __forceinline__ uint64_t globalTimerNs() {
   return t;
 }
 
+// ---- self-checking build ------------------------------------------------------------------------
+// With -DTPB_DEBUG_KERNELS every address the copy paths compute is compared with the byte range
+// its table entry declares before it is used; an address outside is counted and the access is
+// skipped, so a wrong index shows up as a number the host can read (boundsViolations()) and never
+// as a fault. compute-sanitizer plays this role elsewhere; here the kernel checks itself.
+#ifdef TPB_DEBUG_KERNELS
+__device__ unsigned long long gBoundsViolations = 0;
+__device__ __forceinline__ bool dbgInside(const void* p, uint64_t n, const void* base, uint64_t span) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(p), b = reinterpret_cast<uintptr_t>(base);
+  if (a >= b && a - b <= span && n <= span - (a - b)) return true;
+  atomicAdd(&gBoundsViolations, 1ull);
+  return false;
+}
+#define TPB_DBG_INSIDE(p, n, base, span) dbgInside(p, n, base, span)
+#else
+#define TPB_DBG_INSIDE(p, n, base, span) true
+#endif
+
 // ---- parameters ---------------------------------------------------------------------------------
 template <int N>
 struct PushParams {
@@ -191,6 +210,7 @@ __device__ __forceinline__ void copyPlainTile(const PushEntry& e, uint32_t local
   const uint32_t bytes = left > kPlainTileBytes ? kPlainTileBytes : static_cast<uint32_t>(left);
   const uint8_t* src = static_cast<const uint8_t*>(e.src) + off;
   uint8_t* dst = static_cast<uint8_t*>(e.dst) + off;
+  if (!TPB_DBG_INSIDE(src, bytes, e.src, e.count) || !TPB_DBG_INSIDE(dst, bytes, e.dst, e.count)) return;
   const uintptr_t a = reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst);
   if ((a & 15) == 0) copyVec<uint4>(src, dst, bytes, lane);
   else if ((a & 7) == 0) copyVec<uint2>(src, dst, bytes, lane);
@@ -209,6 +229,9 @@ __device__ __forceinline__ void castTileTyped(const PushEntry& e, uint32_t local
   const uint32_t n = left > perTile ? perTile : static_cast<uint32_t>(left);
   const S* s = static_cast<const S*>(e.src) + first;
   D* d = static_cast<D*>(e.dst) + first;
+  if (!TPB_DBG_INSIDE(s, uint64_t(n) * sizeof(S), e.src, e.count * sizeof(S)) ||
+      !TPB_DBG_INSIDE(d, uint64_t(n) * sizeof(D), e.dst, e.count * sizeof(D)))
+    return;
   constexpr int kVec = 16 / sizeof(D) < 16 / sizeof(S) ? 16 / sizeof(S) : 16 / sizeof(D);  // elements per step
   const bool aligned = ((reinterpret_cast<uintptr_t>(s) & 15) == 0) && ((reinterpret_cast<uintptr_t>(d) & 15) == 0);
   const uint32_t vecElems = aligned ? (n / kVec) * kVec : 0;
@@ -254,10 +277,26 @@ struct StridedArgs {
   void* dst;
   int64_t rows, cols, rowStride, colStride;
   uint32_t numTiles;
+#ifdef TPB_DEBUG_KERNELS
+  uint64_t srcSpan, dstSpan;  // bytes the view covers from src / the packed result covers from dst
+#endif
 };
 __device__ __forceinline__ StridedArgs loadStridedArgs(const PushEntry& e) {
-  return StridedArgs{e.src, e.dst, e.rows, e.cols, e.rowStride, e.colStride, e.numTiles};
+  StridedArgs a{e.src, e.dst, e.rows, e.cols, e.rowStride, e.colStride, e.numTiles};
+#ifdef TPB_DEBUG_KERNELS
+  // Views with non-negative strides only (what the host accepts): the last element is the farthest.
+  a.srcSpan = static_cast<uint64_t>((e.rows - 1) * e.rowStride + (e.cols - 1) * e.colStride + 1) * e.srcElemSize;
+  a.dstSpan = static_cast<uint64_t>(e.rows) * e.cols * e.dstElemSize;
+#endif
+  return a;
 }
+#ifdef TPB_DEBUG_KERNELS
+#define TPB_DBG_SRC(a, p, n) dbgInside(p, n, (a).src, (a).srcSpan)
+#define TPB_DBG_DST(a, p, n) dbgInside(p, n, (a).dst, (a).dstSpan)
+#else
+#define TPB_DBG_SRC(a, p, n) true
+#define TPB_DBG_DST(a, p, n) true
+#endif
 
 template <typename S, typename D, bool kConvert>
 __device__ __forceinline__ void stridedTileTyped(const StridedArgs& a, uint32_t localTile, int lane, uint8_t* tileMem) {
@@ -275,8 +314,8 @@ __device__ __forceinline__ void stridedTileTyped(const StridedArgs& a, uint32_t 
   const bool rowsFast = (rowStride == 1 || rows == 1) && colStride != 1;
   if (rowsFast && rowStride == 1 && nr == TR && nc == TC) {
     // Full tile of a transposed matrix: no predicates, pointers stepped instead of recomputed,
-    // eight loads in flight per lane.
-    constexpr int kWide = 8;
+    // sixteen loads in flight per lane.
+    constexpr int kWide = 16;
     const bool act = lane < TR;
     const S* colPtr = src + (r0 + lane) + c0 * colStride;
 #pragma unroll 1
@@ -284,7 +323,7 @@ __device__ __forceinline__ void stridedTileTyped(const StridedArgs& a, uint32_t 
       S v[kWide];
 #pragma unroll
       for (int k = 0; k < kWide; ++k)
-        if (act) v[k] = colPtr[k * colStride];
+        if (act && TPB_DBG_SRC(a, colPtr + k * colStride, sizeof(S))) v[k] = colPtr[k * colStride];
       colPtr += kWide * colStride;
 #pragma unroll
       for (int k = 0; k < kWide; ++k)
@@ -303,7 +342,7 @@ __device__ __forceinline__ void stridedTileTyped(const StridedArgs& a, uint32_t 
         D out;
         if constexpr (kConvert) out = fromFloat<D>(toFloat<S>(v[k]));
         else out = v[k];
-        outPtr[k * cols] = out;
+        if (TPB_DBG_DST(a, outPtr + k * cols, sizeof(D))) outPtr[k * cols] = out;
       }
       outPtr += kWide * cols;
     }
@@ -320,7 +359,8 @@ __device__ __forceinline__ void stridedTileTyped(const StridedArgs& a, uint32_t 
         S v[kBatch];
 #pragma unroll
         for (int k = 0; k < kBatch; ++k)
-          if (r < nr && c + k < nc) v[k] = colPtr[static_cast<int64_t>(c + k) * colStride];
+          if (r < nr && c + k < nc && TPB_DBG_SRC(a, colPtr + static_cast<int64_t>(c + k) * colStride, sizeof(S)))
+            v[k] = colPtr[static_cast<int64_t>(c + k) * colStride];
 #pragma unroll
         for (int k = 0; k < kBatch; ++k)
           if (r < nr && c + k < nc) tile[(c + k) * (TR + 1) + r] = v[k];
@@ -334,7 +374,8 @@ __device__ __forceinline__ void stridedTileTyped(const StridedArgs& a, uint32_t 
         S v[kBatch];
 #pragma unroll
         for (int k = 0; k < kBatch; ++k)
-          if (c < nc && r + k < nr) v[k] = rowPtr[static_cast<int64_t>(r + k) * rowStride];
+          if (c < nc && r + k < nr && TPB_DBG_SRC(a, rowPtr + static_cast<int64_t>(r + k) * rowStride, sizeof(S)))
+            v[k] = rowPtr[static_cast<int64_t>(r + k) * rowStride];
 #pragma unroll
         for (int k = 0; k < kBatch; ++k)
           if (c < nc && r + k < nr) tile[c * (TR + 1) + r + k] = v[k];
@@ -356,7 +397,8 @@ __device__ __forceinline__ void stridedTileTyped(const StridedArgs& a, uint32_t 
           D out;
           if constexpr (kConvert) out = fromFloat<D>(toFloat<S>(v[k]));
           else out = v[k];
-          rowPtr[static_cast<int64_t>(r + k) * cols] = out;
+          if (TPB_DBG_DST(a, rowPtr + static_cast<int64_t>(r + k) * cols, sizeof(D)))
+            rowPtr[static_cast<int64_t>(r + k) * cols] = out;
         }
       }
     }
@@ -417,7 +459,7 @@ __device__ __forceinline__ void stridedWide16Tile(const StridedArgs& a, uint32_t
   const int64_t c0 = static_cast<int64_t>(localTile % tilesPerRow) * T;
   const int nr = static_cast<int>(rows - r0 < T ? rows - r0 : T);  // even
   const int nc = static_cast<int>(cols - c0 < T ? cols - c0 : T);  // even
-  constexpr int kBatch = 8;
+  constexpr int kBatch = 16;
   const uint16_t* colPtr = src + (r0 + 2 * lane) + c0 * colStride;
   uint32_t* rowPtr = reinterpret_cast<uint32_t*>(dst + r0 * cols + c0) + lane;
   const int64_t rowWords = cols / 2;
@@ -429,7 +471,8 @@ __device__ __forceinline__ void stridedWide16Tile(const StridedArgs& a, uint32_t
     for (int c = 0; c < T; c += kBatch) {
       uint32_t v[kBatch];
 #pragma unroll
-      for (int k = 0; k < kBatch; ++k) v[k] = *reinterpret_cast<const uint32_t*>(colPtr + k * colStride);
+      for (int k = 0; k < kBatch; ++k)
+        if (TPB_DBG_SRC(a, colPtr + k * colStride, 4)) v[k] = *reinterpret_cast<const uint32_t*>(colPtr + k * colStride);
       colPtr += kBatch * colStride;
 #pragma unroll
       for (int k = 0; k < kBatch; ++k) tileWords[(c + k) * (P / 2) + lane] = v[k];
@@ -441,7 +484,8 @@ __device__ __forceinline__ void stridedWide16Tile(const StridedArgs& a, uint32_t
 #pragma unroll
       for (int k = 0; k < kBatch; ++k) v[k] = static_cast<uint32_t>(lo[r + k]) | (static_cast<uint32_t>(hi[r + k]) << 16);
 #pragma unroll
-      for (int k = 0; k < kBatch; ++k) rowPtr[k * rowWords] = v[k];
+      for (int k = 0; k < kBatch; ++k)
+        if (TPB_DBG_DST(a, rowPtr + k * rowWords, 4)) rowPtr[k * rowWords] = v[k];
       rowPtr += kBatch * rowWords;
     }
     __syncwarp();
@@ -453,7 +497,8 @@ __device__ __forceinline__ void stridedWide16Tile(const StridedArgs& a, uint32_t
       uint32_t v[kBatch];
 #pragma unroll
       for (int k = 0; k < kBatch; ++k)
-        if (active && c + k < nc) v[k] = *reinterpret_cast<const uint32_t*>(colPtr + static_cast<int64_t>(c + k) * colStride);
+        if (active && c + k < nc && TPB_DBG_SRC(a, colPtr + static_cast<int64_t>(c + k) * colStride, 4))
+          v[k] = *reinterpret_cast<const uint32_t*>(colPtr + static_cast<int64_t>(c + k) * colStride);
 #pragma unroll
       for (int k = 0; k < kBatch; ++k)
         if (active && c + k < nc) tileWords[(c + k) * (P / 2) + lane] = v[k];
@@ -469,7 +514,8 @@ __device__ __forceinline__ void stridedWide16Tile(const StridedArgs& a, uint32_t
         if (active && r + k < nr) v[k] = static_cast<uint32_t>(lo[r + k]) | (static_cast<uint32_t>(hi[r + k]) << 16);
 #pragma unroll
       for (int k = 0; k < kBatch; ++k)
-        if (active && r + k < nr) rowPtr[static_cast<int64_t>(r + k) * rowWords] = v[k];
+        if (active && r + k < nr && TPB_DBG_DST(a, rowPtr + static_cast<int64_t>(r + k) * rowWords, 4))
+          rowPtr[static_cast<int64_t>(r + k) * rowWords] = v[k];
     }
   }
   __syncwarp();
@@ -554,6 +600,21 @@ __global__ void __launch_bounds__(kThreads, 1) tpb_push_pack(const __grid_consta
       const uint32_t mine = (p.bulkTiles - first + step - 1) / step;  // tiles this CTA owns
       const uint32_t tileBytes = p.bulkTileBytes;
       bool failed = false;
+#ifdef TPB_DEBUG_KERNELS
+      // A bulk copy off the 16-byte grid is an illegal instruction: check the whole table first
+      // and leave the pipeline alone if any entry is wrong.
+      bool tableOk = true;
+      for (uint32_t i = 0; i < p.numEntries; ++i) {
+        const PushEntry& e = p.entries[i];
+        if (e.kind != kCopyBulk) continue;
+        if ((reinterpret_cast<uintptr_t>(e.src) | reinterpret_cast<uintptr_t>(e.dst) | e.count) & 15) {
+          atomicAdd(&gBoundsViolations, 1ull);
+          tableOk = false;
+        }
+      }
+#else
+      constexpr bool tableOk = true;
+#endif
       auto describe = [&](uint32_t i, const uint8_t*& src, uint8_t*& dst, uint32_t& bytes) {
         const uint32_t t = first + i * step;
         const PushEntry* e = findEntry(p, t, true);
@@ -572,9 +633,9 @@ __global__ void __launch_bounds__(kThreads, 1) tpb_push_pack(const __grid_consta
         mbarExpectTx(&full[s], bytes);
         bulkLoad(stages + static_cast<size_t>(s) * tileBytes, src, bytes, &full[s]);
       };
-      const uint32_t prologue = mine < static_cast<uint32_t>(S) ? mine : S;
+      const uint32_t prologue = !tableOk ? 0 : mine < static_cast<uint32_t>(S) ? mine : S;
       for (uint32_t i = 0; i < prologue; ++i) issueLoad(i);
-      for (uint32_t c = 0; c < mine; ++c) {
+      for (uint32_t c = 0; tableOk && c < mine; ++c) {
         const int s = c % S;
         if (!mbarWaitBounded(&full[s], (c / S) & 1)) {
           failed = true;
@@ -983,6 +1044,33 @@ uint8_t patternByte(uint64_t seed, uint64_t index) {
 }
 
 uint64_t launchCount() { return gLaunches.load(); }
+
+bool debugKernels() {
+#ifdef TPB_DEBUG_KERNELS
+  return true;
+#else
+  return false;
+#endif
+}
+
+uint64_t boundsViolations() {
+#ifdef TPB_DEBUG_KERNELS
+  // Summed over the devices this process has a context on (and only those: asking a device
+  // without one would create it).
+  unsigned long long total = 0;
+  const int n = cudaDeviceCountNoThrow();
+  for (int d = 0; d < n; ++d) {
+    if (cudaPrimaryContextActive(d) != 1) continue;
+    CudaDeviceGuard g(d);
+    unsigned long long v = 0;
+    check(cudaMemcpyFromSymbol(&v, gBoundsViolations, sizeof(v)), "reading the violation counter");
+    total += v;
+  }
+  return total;
+#else
+  return 0;
+#endif
+}
 
 }  // namespace kernels
 }  // namespace tpb

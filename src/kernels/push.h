@@ -123,5 +123,12 @@ uint8_t patternByte(uint64_t seed, uint64_t index);
 // Total kernel launches made by this process (for benchmarks' accounting).
 uint64_t launchCount();
 
+// True when the library was built with -DTPB_DEBUG_KERNELS: the copy paths then compare every
+// address they compute with the range its table entry declares, skip what lies outside and count it.
+bool debugKernels();
+// Violations counted so far, over every device this process has a context on (always 0 in a
+// regular build).
+uint64_t boundsViolations();
+
 }  // namespace kernels
 }  // namespace tpb

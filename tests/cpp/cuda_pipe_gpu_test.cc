@@ -197,6 +197,33 @@ TPB_GPU_TEST(CudaPipe, SameProcessSameDevice, 1) {
       });
 }
 
+// Moving tensors that live on the second GPU must not create a context on the first one (the
+// reference checks the same through NVML's process list, tensorpipe/test/channel/cuda_helpers.h:50-95;
+// the driver's primary-context state is exact and also works inside a pid namespace).
+TPB_GPU_TEST(CudaPipe, NoContextOnADeviceTheUserNeverTouched, 2) {
+  EXPECT_EQ(cudaPrimaryContextActive(0), 0);
+  ThreadPeers peers;
+  peers.run(
+      [&](ThreadPeers& pg) {
+        auto ctx = makeContext("server");
+        auto listener = ctx->listen({"uv://127.0.0.1"});
+        pg.sendToClient(listener->url("uv"));
+        auto pipe = acceptSync(*listener);
+        receiverSide(*pipe, 1, 1000, 3);
+        pg.recvFromClient();
+        ctx->join();
+      },
+      [&](ThreadPeers& pg) {
+        auto ctx = makeContext("client");
+        auto pipe = ctx->connect(pg.recvFromServer());
+        senderSide(*pipe, 1, 1, 1000, 3);
+        pg.sendToServer("done");
+        ctx->join();
+      });
+  EXPECT_EQ(cudaPrimaryContextActive(1), 1);
+  EXPECT_EQ(cudaPrimaryContextActive(0), 0);
+}
+
 TPB_GPU_TEST(CudaPipe, ReceiverWaitsForWorkOnTheSendersStream, 1) {
   // The sender's stream first spends ~30 ms scribbling garbage over the tensor and only then
   // writes the real data; the pipe write is issued while all of that is still queued.

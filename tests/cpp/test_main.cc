@@ -4,6 +4,7 @@
 
 #include <cuda_runtime.h>
 
+#include "kernels/push.h"
 #include "test_util.h"
 
 namespace tpbtest {
@@ -79,6 +80,11 @@ int main(int argc, char** argv) {
           int rc = 0;
           try {
             t.fn();
+            // In a build with self-checking kernels, an address outside its entry fails the test.
+            if (tpb::kernels::debugKernels()) {
+              const uint64_t bad = tpb::kernels::boundsViolations();
+              if (bad) throw tpbtest::TestFailure(std::to_string(bad) + " out-of-range addresses computed by the kernels");
+            }
           } catch (const tpbtest::TestSkipped& e) {
             std::cout << "  skipped: " << e.what() << std::endl;
             rc = 77;

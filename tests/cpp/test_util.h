@@ -19,6 +19,13 @@
 #include <thread>
 #include <vector>
 
+namespace tpb {
+namespace kernels {
+bool debugKernels();
+uint64_t boundsViolations();
+}  // namespace kernels
+}  // namespace tpb
+
 namespace tpbtest {
 
 struct TestCase {
@@ -211,6 +218,8 @@ class ProcessPeers {
       int rc = 0;
       try {
         body();
+        if (tpb::kernels::debugKernels() && tpb::kernels::boundsViolations() != 0)
+          throw TestFailure("out-of-range addresses computed by the kernels in a peer process");
       } catch (const std::exception& e) {
         std::cerr << "  [child " << ::getpid() << "] " << e.what() << std::endl;
         rc = 1;

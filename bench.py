@@ -194,8 +194,31 @@ def run_native(args):
     ms_per_step = ms / args.steps
     value = world * args.bytes / (ms_per_step * 1e-3) / 1e9
 
-    sweep = []
-    if not args.no_sweep:
+    # End to end right after the headline, on contexts of its own.
+    e2e = None
+    if not args.no_e2e:
+        e2e = run_e2e(args, tpb, torch, dist, rank, world, local_rank, barrier, max_over_ranks, gather)
+
+    # The remaining phases explain the headline; a failure in one of them is reported in its place
+    # and ends the auxiliary phases on every rank, but never costs the headline line.
+    aux_failed = []
+
+    def auxiliary(name, fn):
+        if aux_failed:
+            return {"skipped": f"after the failure of {aux_failed[0]}"}
+        error = None
+        result = None
+        try:
+            result = fn()
+        except Exception as exc:  # noqa: BLE001
+            error = f"{type(exc).__name__}: {exc}"
+        if max_over_ranks(1.0 if error else 0.0) > 0:
+            aux_failed.append(name)
+            return {"error": error or "failed on another rank"}
+        return result
+
+    def run_sweep():
+        out = []
         size = 4096
         while size <= args.max_sweep_bytes:
             iters = 100 if size <= (64 << 20) else 20
@@ -204,35 +227,38 @@ def run_native(args):
             r = rb.run_stream(size, iters, args.depth, False)
             barrier()
             t = max_over_ranks(r.device_ms) / iters
-            sweep.append({"bytes": size, "us_per_msg": round(t * 1e3, 2),
-                          "GBps": round(world * size / (t * 1e-3) / 1e9, 2)})
+            out.append({"bytes": size, "us_per_msg": round(t * 1e3, 2),
+                        "GBps": round(world * size / (t * 1e-3) / 1e9, 2)})
             size *= 2
+        return out
 
-    # Small-message latency: one token around the ring, host clock, data visible on the device.
-    barrier()
-    rb.run_latency(4096, 50, rank, world)
-    barrier()
-    lat = rb.run_latency(4096, 1000, rank, world)
-    barrier()
-    latency = None
-    if rank == 0 and lat:
-        latency = {"bytes": 4096, "p50_us": round(percentile(lat, 0.5), 2), "p99_us": round(percentile(lat, 0.99), 2),
-                   "mean_us": round(sum(lat) / len(lat), 2), "hops": world}
+    def run_latency():
+        # Small-message latency: one token around the ring, host clock, data visible on the device.
+        barrier()
+        rb.run_latency(4096, 50, rank, world)
+        barrier()
+        lat = rb.run_latency(4096, 1000, rank, world)
+        barrier()
+        if rank == 0 and lat:
+            return {"bytes": 4096, "p50_us": round(percentile(lat, 0.5), 2), "p99_us": round(percentile(lat, 0.99), 2),
+                    "mean_us": round(sum(lat) / len(lat), 2), "hops": world}
+        return None
 
-    # 64-tensor mixed-dtype message (strided views + receiver-requested casts), one fused launch.
-    barrier()
-    rb.run_mixed(3, 1)
-    barrier()
-    mres, mixed_bytes = rb.run_mixed(10, 1)
-    barrier()
-    mixed_ms = max_over_ranks(mres.device_ms) / 10
-    mixed = {"tensors": 64, "bytes_per_msg": mixed_bytes, "ms_per_msg": round(mixed_ms, 4),
-             "GBps": round(world * mixed_bytes / (mixed_ms * 1e-3) / 1e9, 2),
-             "kernel_launches_per_msg": mres.kernel_launches / 10}
+    def run_mixed():
+        # 64-tensor mixed-dtype message (strided views + receiver-requested casts), one fused launch.
+        barrier()
+        rb.run_mixed(3, 1)
+        barrier()
+        mres, mixed_bytes = rb.run_mixed(10, 1)
+        barrier()
+        mixed_ms = max_over_ranks(mres.device_ms) / 10
+        return {"tensors": 64, "bytes_per_msg": mixed_bytes, "ms_per_msg": round(mixed_ms, 4),
+                "GBps": round(world * mixed_bytes / (mixed_ms * 1e-3) / 1e9, 2),
+                "kernel_launches_per_msg": mres.kernel_launches / 10}
 
-    e2e = None
-    if not args.no_e2e:
-        e2e = run_e2e(args, tpb, torch, dist, rank, world, local_rank, barrier, max_over_ranks, gather)
+    sweep = [] if args.no_sweep else auxiliary("sweep", run_sweep)
+    latency = auxiliary("latency", run_latency)
+    mixed = auxiliary("mixed_64_tensor_message", run_mixed)
 
     del rb
     if world > 1:

@@ -135,6 +135,9 @@ struct Options {
 std::shared_ptr<Context> create(Options options = Options());
 // The options after the environment overrides (what create() will use).
 Options applyEnvironment(Options options);
+// Tensors this process received through a staging buffer because CUDA IPC could not export the
+// user's buffer (memory from cudaMallocAsync pools or virtual-memory allocations): a statistic.
+uint64_t stagedReceives();
 }  // namespace cuda_p2p
 namespace cuda_xth {
 inline std::shared_ptr<Context> create() { return cuda_p2p::create(); }

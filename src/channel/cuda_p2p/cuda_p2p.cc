@@ -278,10 +278,22 @@ struct SendOp {
   std::optional<RecvReady> ready;
 };
 
+// A receive buffer that CUDA IPC cannot export (memory from a stream-ordered pool, a virtual-memory
+// allocation, ...) is replaced, for the sender's eyes, by an exportable buffer of this channel; the
+// receiver copies from it to the user's buffer on the user's stream once the data has landed.
+struct StagingBuffer {
+  uint8_t* ptr = nullptr;
+  size_t bytes = 0;
+  bool busy = false;                 // handed to a receive that has not been completed yet
+  std::unique_ptr<CudaEvent> drained;  // recorded after the copy out of it; reusable once it has fired
+};
+std::atomic<uint64_t> gStagedReceives{0};
+
 struct RecvOp {
   uint64_t seq = 0;
   int device = -1;
   std::vector<RecvItem> items;
+  std::vector<std::pair<size_t, size_t>> staged;  // (item index, staging buffer index on `device`)
   bool readySent = false;
   bool expectEager = false;
   std::optional<Launched> notice;
@@ -334,6 +346,7 @@ class ChannelImpl final : public Channel, public std::enable_shared_from_this<Ch
   Eager tryEager(SendOp& op);
   uint64_t alignedTotal(const std::vector<SendItem>& items) const;
   std::unique_ptr<CudaEvent> takeEvent(int device);
+  uint8_t* takeStaging(int device, size_t bytes, size_t* index);
   void watchLastCredit();
   bool creditWanted_ = false;
   void launchRendezvous(SendOp& op);
@@ -371,6 +384,7 @@ class ChannelImpl final : public Channel, public std::enable_shared_from_this<Ch
   // Events handed to the peer (same process) must outlive their use.
   std::deque<std::unique_ptr<CudaEvent>> eventPool_;
   std::map<int, std::vector<std::unique_ptr<CudaEvent>>> freeEvents_;  // recycled credit events
+  std::map<int, std::vector<StagingBuffer>> staging_;                  // per device, kept until the channel dies
   std::vector<std::pair<uint32_t*, uint32_t>> enqueuedWaits_;  // for cancellation on error
 };
 
@@ -466,6 +480,16 @@ class ContextImpl final : public Context, public std::enable_shared_from_this<Co
 // ---- channel --------------------------------------------------------------------------------
 ChannelImpl::~ChannelImpl() {
   conn_->close();
+  for (auto& perDevice : staging_) {
+    int prev = -1;
+    cudaGetDevice(&prev);
+    cudaSetDevice(perDevice.first);
+    for (auto& b : perDevice.second) {
+      b.drained.reset();
+      if (b.ptr) cudaFree(b.ptr);
+    }
+    if (prev >= 0) cudaSetDevice(prev);
+  }
   for (auto& a : arenas_) {
     if (a.second.base) {
       // Freeing synchronises the device; this only happens when a pipe goes away.
@@ -902,6 +926,22 @@ void ChannelImpl::sendReady(RecvOp& op) {
           t.hasHandle = 1;
           t.bufferId = exported.id;
           t.ptr = static_cast<uint64_t>(reinterpret_cast<uintptr_t>(ptr) - exported.base);
+        } else {
+          // Not exportable: let the sender write into a staging buffer of ours instead.
+          size_t index = 0;
+          uint8_t* stage = takeStaging(op.device, t.bytes, &index);
+          if (stage && ExportCache::get().lookup(stage, &exported)) {
+            t.handle = exported.handle;
+            t.hasHandle = 1;
+            t.bufferId = exported.id;
+            t.ptr = static_cast<uint64_t>(reinterpret_cast<uintptr_t>(stage) - exported.base);
+            op.staged.emplace_back(static_cast<size_t>(&it - op.items.data()), index);
+            ++gStagedReceives;
+            TPB_VLOG(5) << "Channel " << id_ << " stages a tensor of batch #" << op.seq
+                        << " whose buffer CUDA IPC cannot export";
+          } else if (stage) {
+            staging_[op.device][index].busy = false;
+          }
         }
       }
       r.targets.push_back(t);
@@ -973,6 +1013,29 @@ void ChannelImpl::completeRecv(RecvOp& op) {
         pendingCredits_.push_back(std::move(pc));
         if (creditWanted_) watchLastCredit();
       }
+      if (!op.staged.empty()) {
+        // The sender wrote (and converted) into our staging buffers: move the bytes to where the
+        // user wants them, behind the wait that was just enqueued.
+        kernels::PushPlan plan;
+        auto& pool = staging_[op.device];
+        for (auto& [item, index] : op.staged) {
+          RecvItem& it = op.items[item];
+          kernels::CopyItem c;
+          c.src = pool[index].ptr;
+          c.dst = it.buffer.unwrap<CudaBuffer>().ptr;
+          c.srcBytes = it.castTo ? kernels::convertedBytes(it.length, it.srcDtype, *it.castTo) : it.length;
+          kernels::appendToPlan(plan, c, opts_.useBulkCopy);
+        }
+        const int ctas = opts_.maxCtas > 0 ? opts_.maxCtas : cudaSmCount(op.device);
+        kernels::launchPush(plan, stream, ctas, nullptr, 0, nullptr, nullptr);
+        for (auto& [item, index] : op.staged) {
+          (void)item;
+          if (!pool[index].drained) pool[index].drained = std::make_unique<CudaEvent>(op.device);
+          pool[index].drained->record(stream);
+          pool[index].busy = false;
+        }
+        op.staged.clear();
+      }
       if (!others.empty()) {
         CudaEvent ev(op.device);
         ev.record(stream);
@@ -983,6 +1046,33 @@ void ChannelImpl::completeRecv(RecvOp& op) {
     return closeFromLoop(TPB_CREATE_ERROR(CudaError, ex.what()));
   }
   finishRecv(op, Error::kSuccess);
+}
+
+uint8_t* ChannelImpl::takeStaging(int device, size_t bytes, size_t* index) {
+  constexpr size_t kGranule = 2u << 20;
+  const size_t want = (std::max<size_t>(bytes, 1) + kGranule - 1) / kGranule * kGranule;
+  auto& pool = staging_[device];
+  for (size_t i = 0; i < pool.size(); ++i) {
+    StagingBuffer& b = pool[i];
+    if (b.busy || b.bytes < bytes || b.bytes > 2 * want) continue;
+    if (b.drained && !b.drained->query()) continue;  // the copy out of it is still queued
+    b.busy = true;
+    *index = i;
+    return b.ptr;
+  }
+  CudaDeviceGuard g(device);
+  void* p = nullptr;
+  if (cudaMalloc(&p, want) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  StagingBuffer b;
+  b.ptr = static_cast<uint8_t*>(p);
+  b.bytes = want;
+  b.busy = true;
+  pool.push_back(std::move(b));
+  *index = pool.size() - 1;
+  return pool.back().ptr;
 }
 
 void ChannelImpl::finishRecv(RecvOp& op, const Error& e) {
@@ -1106,6 +1196,8 @@ void ChannelImpl::closeFromLoop(const Error& e) {
 }
 
 }  // namespace
+
+uint64_t stagedReceives() { return gStagedReceives.load(); }
 
 Options applyEnvironment(Options o) {
   auto num = [](const char* name, auto& field) {

@@ -105,7 +105,7 @@ void senderSide(Pipe& pipe, int device, int targetDevice, uint64_t seedBase, int
 }
 
 void receiverSide(Pipe& pipe, int device, uint64_t seedBase, int rounds,
-                  const std::vector<size_t>& kSizes = kDefaultSizes) {
+                  const std::vector<size_t>& kSizes = kDefaultSizes, bool poolMemory = false) {
   CK(cudaSetDevice(device));
   cudaStream_t stream;
   CK(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
@@ -121,7 +121,9 @@ void receiverSide(Pipe& pipe, int device, uint64_t seedBase, int rounds,
     for (size_t i = 0; i < kSizes.size(); ++i) {
       EXPECT_EQ(d.tensors[i].length, kSizes[i]);
       uint8_t* p = nullptr;
-      CK(cudaMalloc(&p, kSizes[i] + 512));
+      // Stream-ordered pool memory has no legacy IPC handle: the channel must stage such buffers.
+      if (poolMemory) CK(cudaMallocAsync(reinterpret_cast<void**>(&p), kSizes[i] + 512, stream));
+      else CK(cudaMalloc(&p, kSizes[i] + 512));
       CK(cudaMemsetAsync(p, 0xCD, kSizes[i] + 512, stream));
       bufs.push_back(p);
       Allocation::Tensor t;
@@ -141,7 +143,8 @@ void receiverSide(Pipe& pipe, int device, uint64_t seedBase, int rounds,
       CK(cudaMemcpy(&guard[1], bufs[i] + 256 + kSizes[i], 1, cudaMemcpyDeviceToHost));
       EXPECT_EQ(int(guard[0]), 0xCD);
       EXPECT_EQ(int(guard[1]), 0xCD);
-      cudaFree(bufs[i]);
+      if (poolMemory) cudaFreeAsync(bufs[i], stream);
+      else cudaFree(bufs[i]);
     }
   }
   cudaFree(bad);
@@ -289,6 +292,47 @@ TPB_GPU_TEST(CudaPipe, TwoProcessesOneDeviceWithoutBulkCopiesOrEager, 1) {
 }
 
 TPB_GPU_TEST(CudaPipe, TwoProcessesTwoDevices, 2) { crossProcess(0, 1, {}); }
+
+// The receiver's buffers come from a stream-ordered memory pool, which CUDA IPC cannot export:
+// the channel lets the sender write into exportable staging buffers of its own and copies out on
+// the receiver's stream. (The reference never exports user memory for this reason,
+// tensorpipe/channel/cuda_ipc/context_impl.h:101-115, and always pays the staging copy.)
+TPB_GPU_TEST(CudaPipe, ReceiveIntoMemoryThatCannotBeExported, 1) {
+  channel::cuda_p2p::Options o;
+  o.eagerThreshold = 0;  // everything by rendezvous, so every tensor needs a destination handle
+  const std::vector<size_t> sizes = {4096, 70001, (1u << 20) + 3, 8u << 20};
+  ProcessPeers::run(
+      [=](const ProcessPeers::Side& me) {
+        auto ctx = makeContext("server", o);
+        auto listener = ctx->listen({"uv://127.0.0.1", "shm://"});
+        me.send(listener->url("uv"));
+        auto pipe = acceptSync(*listener);
+        // Does this driver refuse a legacy IPC handle for pool memory? (It should.)
+        CK(cudaSetDevice(0));
+        void* probe = nullptr;
+        CK(cudaMallocAsync(&probe, 4096, nullptr));
+        CK(cudaStreamSynchronize(nullptr));
+        cudaIpcMemHandle_t h;
+        const bool exportable = cudaIpcGetMemHandle(&h, probe) == cudaSuccess;
+        cudaGetLastError();
+        CK(cudaFreeAsync(probe, nullptr));
+        std::cout << "  a legacy IPC handle for pool memory: " << (exportable ? "granted" : "refused") << std::endl;
+        const uint64_t before = channel::cuda_p2p::stagedReceives();
+        receiverSide(*pipe, 0, 1000, 3, sizes, true);
+        if (!exportable) EXPECT_EQ(channel::cuda_p2p::stagedReceives() - before, uint64_t(3 * sizes.size()));
+        me.recv();
+        me.send("bye");
+        ctx->join();
+      },
+      [=](const ProcessPeers::Side& me) {
+        auto ctx = makeContext("client", o);
+        auto pipe = ctx->connect(me.recv());
+        senderSide(*pipe, 0, 0, 1000, 3, sizes);
+        me.send("done");
+        me.recv();
+        ctx->join();
+      });
+}
 
 TPB_GPU_TEST(CudaPipe, EagerInboxWrapsAndRunsOutOfCredits, 1) {
   // Small messages go through the peer's inbox ring without waiting for the receiver; a tiny

@@ -193,11 +193,11 @@ class ChannelImpl final : public Channel, public std::enable_shared_from_this<Ch
  public:
   ~ChannelImpl() override {
     for (auto& c : counters_) {
-      int prev = -1;
-      cudaGetDevice(&prev);
-      cudaSetDevice(c.first.first);
-      cudaFree(c.second);
-      if (prev >= 0) cudaSetDevice(prev);
+      try {
+        CudaDeviceGuard g(c.first.first);
+        cudaFree(c.second);
+      } catch (...) {
+      }
     }
   }
 };

@@ -481,23 +481,23 @@ class ContextImpl final : public Context, public std::enable_shared_from_this<Co
 ChannelImpl::~ChannelImpl() {
   conn_->close();
   for (auto& perDevice : staging_) {
-    int prev = -1;
-    cudaGetDevice(&prev);
-    cudaSetDevice(perDevice.first);
-    for (auto& b : perDevice.second) {
-      b.drained.reset();
-      if (b.ptr) cudaFree(b.ptr);
+    try {
+      CudaDeviceGuard g(perDevice.first);
+      for (auto& b : perDevice.second) {
+        b.drained.reset();
+        if (b.ptr) cudaFree(b.ptr);
+      }
+    } catch (...) {
     }
-    if (prev >= 0) cudaSetDevice(prev);
   }
   for (auto& a : arenas_) {
     if (a.second.base) {
       // Freeing synchronises the device; this only happens when a pipe goes away.
-      int prev = -1;
-      cudaGetDevice(&prev);
-      cudaSetDevice(a.second.device);
-      cudaFree(a.second.base);
-      if (prev >= 0) cudaSetDevice(prev);
+      try {
+        CudaDeviceGuard g(a.second.device);
+        cudaFree(a.second.base);
+      } catch (...) {
+      }
     }
   }
 }

@@ -38,6 +38,9 @@ const CudaLib& CudaLib::get() {
         loadSym(l.handle, l.cuGetErrorString, {"cuGetErrorString"}) &&
         loadSym(l.handle, l.cuCtxGetCurrent, {"cuCtxGetCurrent"});
     loadSym(l.handle, l.cuDeviceGet, {"cuDeviceGet"});
+    loadSym(l.handle, l.cuDevicePrimaryCtxRetain, {"cuDevicePrimaryCtxRetain"});
+    loadSym(l.handle, l.cuCtxPushCurrent, {"cuCtxPushCurrent_v2", "cuCtxPushCurrent"});
+    loadSym(l.handle, l.cuCtxPopCurrent, {"cuCtxPopCurrent_v2", "cuCtxPopCurrent"});
     loadSym(l.handle, l.cuDevicePrimaryCtxGetState, {"cuDevicePrimaryCtxGetState"});
     // Stream memory operations are optional (the wait kernel is the fallback).
     loadSym(l.handle, l.cuStreamWaitValue32, {"cuStreamWaitValue32_v2", "cuStreamWaitValue32"});
@@ -87,6 +90,55 @@ bool NvmlLib::p2pOk(const std::string& uuidA, const std::string& uuidB) const {
   int rd = -1, wr = -1;
   if (deviceGetP2PStatus(a, b, 0, &rd) != 0 || deviceGetP2PStatus(a, b, 1, &wr) != 0) return false;
   return rd == 0 && wr == 0;
+}
+
+namespace {
+// The primary context of each device, retained once and kept for the life of the process.
+void* primaryContext(int device) {
+  static std::mutex m;
+  static std::map<int, void*> cache;
+  std::unique_lock<std::mutex> lock(m);
+  auto it = cache.find(device);
+  if (it != cache.end()) return it->second;
+  const CudaLib& lib = CudaLib::get();
+  void* ctx = nullptr;
+  int dev = 0;
+  if (!lib.ok || !lib.cuDeviceGet || !lib.cuDevicePrimaryCtxRetain || lib.cuDeviceGet(&dev, device) != 0 ||
+      lib.cuDevicePrimaryCtxRetain(&ctx, dev) != 0)
+    ctx = nullptr;
+  cache[device] = ctx;
+  return ctx;
+}
+}  // namespace
+
+CudaDeviceGuard::CudaDeviceGuard(int device) {
+  if (device < 0) return;
+  const CudaLib& lib = CudaLib::get();
+  if (lib.ok && lib.cuCtxPushCurrent && lib.cuCtxPopCurrent) {
+    if (void* ctx = primaryContext(device)) {
+      void* current = nullptr;
+      lib.cuCtxGetCurrent(&current);
+      if (current == ctx) return;
+      if (lib.cuCtxPushCurrent(ctx) == 0) {
+        pushed_ = true;
+        return;
+      }
+    }
+  }
+  TPB_CUDA_CHECK(cudaGetDevice(&prev_));
+  if (device != prev_) {
+    TPB_CUDA_CHECK(cudaSetDevice(device));
+    changed_ = true;
+  }
+}
+
+CudaDeviceGuard::~CudaDeviceGuard() {
+  if (pushed_) {
+    void* popped = nullptr;
+    CudaLib::get().cuCtxPopCurrent(&popped);
+  } else if (changed_) {
+    cudaSetDevice(prev_);
+  }
 }
 
 int cudaDeviceCountNoThrow() {

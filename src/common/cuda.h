@@ -37,23 +37,22 @@ inline Error cudaErrorToError(cudaError_t e, const char* what) {
   return TPB_CREATE_ERROR(CudaError, std::string(what) + ": " + cudaGetErrorString(e));
 }
 
+// Makes `device` current for the scope and puts back what was current before. Implemented with the
+// driver's context stack (push the device's primary context, pop it again), because restoring
+// with cudaSetDevice(previous) CREATES a primary context on the previous device if the thread
+// never used it (since CUDA 12 cudaSetDevice initialises the device): a library thread whose
+// default device is 0 would quietly open a context on GPU 0 while only moving tensors of GPU 1.
+// Falls back to the runtime calls when the driver entry points are missing.
 class CudaDeviceGuard {
  public:
-  explicit CudaDeviceGuard(int device) {
-    TPB_CUDA_CHECK(cudaGetDevice(&prev_));
-    if (device >= 0 && device != prev_) {
-      TPB_CUDA_CHECK(cudaSetDevice(device));
-      changed_ = true;
-    }
-  }
-  ~CudaDeviceGuard() {
-    if (changed_) cudaSetDevice(prev_);
-  }
+  explicit CudaDeviceGuard(int device);
+  ~CudaDeviceGuard();
   CudaDeviceGuard(const CudaDeviceGuard&) = delete;
   CudaDeviceGuard& operator=(const CudaDeviceGuard&) = delete;
 
  private:
-  int prev_ = 0;
+  int prev_ = -1;
+  bool pushed_ = false;
   bool changed_ = false;
 };
 
@@ -66,11 +65,12 @@ class CudaEvent {
   }
   ~CudaEvent() {
     if (ev_) {
-      int prev = -1;
-      cudaGetDevice(&prev);
-      cudaSetDevice(device_);
-      cudaEventDestroy(ev_);
-      if (prev >= 0) cudaSetDevice(prev);
+      try {
+        CudaDeviceGuard g(device_);
+        cudaEventDestroy(ev_);
+      } catch (...) {
+        cudaEventDestroy(ev_);
+      }
     }
   }
   CudaEvent(const CudaEvent&) = delete;
@@ -110,6 +110,9 @@ struct CudaLib {
   int (*cuGetErrorString)(int, const char**) = nullptr;
   int (*cuCtxGetCurrent)(void**) = nullptr;
   int (*cuDeviceGet)(int* device, int ordinal) = nullptr;
+  int (*cuDevicePrimaryCtxRetain)(void** ctx, int device) = nullptr;
+  int (*cuCtxPushCurrent)(void* ctx) = nullptr;
+  int (*cuCtxPopCurrent)(void** ctx) = nullptr;
   int (*cuDevicePrimaryCtxGetState)(int device, unsigned* flags, int* active) = nullptr;
   bool ok = false;
   std::string why;

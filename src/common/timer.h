@@ -4,6 +4,9 @@
 // (no operation ever times out there); this backs the optional per-pipe deadlines.
 #pragma once
 
+#include <pthread.h>
+
+#include <atomic>
 #include <chrono>
 #include <condition_variable>
 #include <functional>
@@ -20,7 +23,16 @@ class TimerThread {
   using Clock = std::chrono::steady_clock;
 
   static TimerThread& get() {
-    static TimerThread* t = new TimerThread();  // never destroyed: lives as long as the process
+    // Never destroyed: lives as long as the process. A forked child starts over with a fresh one
+    // (the parent's thread does not exist there, and its mutex may have been held at the fork).
+    static std::once_flag once;
+    std::call_once(once, []() { ::pthread_atfork(nullptr, nullptr, []() { instance().store(nullptr); }); });
+    TimerThread* t = instance().load(std::memory_order_acquire);
+    if (t == nullptr) {
+      auto* fresh = new TimerThread();
+      if (instance().compare_exchange_strong(t, fresh)) return *fresh;
+      delete fresh;
+    }
     return *t;
   }
 
@@ -35,6 +47,11 @@ class TimerThread {
   }
 
  private:
+  static std::atomic<TimerThread*>& instance() {
+    static std::atomic<TimerThread*> p{nullptr};
+    return p;
+  }
+
   void run() {
     setThreadName("TP_timer");
     std::unique_lock<std::mutex> lock(m_);

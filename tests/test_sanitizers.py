@@ -15,7 +15,8 @@ pytestmark = pytest.mark.skipif(os.environ.get("TPB_RUN_SANITIZERS") != "1",
 
 
 @pytest.mark.parametrize("kind,env,needle", [
-    ("thread", {"TSAN_OPTIONS": "halt_on_error=0"}, "WARNING: ThreadSanitizer"),
+    # die_after_fork=0: some tests fork peer processes after earlier tests have started the timer thread.
+    ("thread", {"TSAN_OPTIONS": "halt_on_error=0:die_after_fork=0"}, "WARNING: ThreadSanitizer"),
     ("address", {"ASAN_OPTIONS": "protect_shadow_gap=0"}, "ERROR: AddressSanitizer"),
 ])
 def test_cpu_suites_are_clean_under_sanitizer(kind, env, needle):

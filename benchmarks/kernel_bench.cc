@@ -9,7 +9,9 @@
 
 #include <cstdio>
 #include <cstdlib>
+#include <cmath>
 #include <cstring>
+#include <random>
 #include <string>
 #include <vector>
 
@@ -141,6 +143,47 @@ int main(int argc, char** argv) {
       appendToPlan(plan, it, true);
       double ms = timer.run(2, iters / 2 + 1, [&] { launchPush(plan, nullptr, sms, nullptr, 0, nullptr, nullptr); });
       report("transposed view, " + std::to_string(es) + "-byte elements", it.srcBytes, ms);
+    }
+  }
+  if (want("mixed")) {
+    // The 64-tensor message of the pipe benchmarks as ONE launch of the full kernel on one GPU:
+    // dtype cycles fp32 / bf16 / int64, sizes log-uniform in [1 KiB, 16 MiB], every fourth tensor a
+    // transposed [rows, 64] view, every other fp32 tensor converted to bf16. The bulk pipeline and
+    // the register paths run side by side in the same CTAs.
+    std::mt19937_64 rng(1);
+    PushPlan plan;
+    uint64_t srcOff = 0, dstOff = 0, delivered = 0, read = 0;
+    int fp32Count = 0;
+    for (int i = 0; i < 64; ++i) {
+      const DType dt = i % 3 == 0 ? DType::kF32 : (i % 3 == 1 ? DType::kBF16 : DType::kI64);
+      const double lg = std::log(1024.0) + (std::log(16.0 * 1024 * 1024) - std::log(1024.0)) *
+                                                (static_cast<double>(rng() % 100000) / 100000.0);
+      const uint64_t es = dtypeSize(dt);
+      const int64_t rows = static_cast<int64_t>(std::max<uint64_t>(1, static_cast<uint64_t>(std::exp(lg)) / es / 64));
+      const uint64_t elems = static_cast<uint64_t>(rows) * 64;
+      const bool cast = dt == DType::kF32 && (fp32Count++ % 2) == 0;
+      CopyItem it;
+      it.src = src + srcOff;
+      it.dst = dst + dstOff;
+      it.srcBytes = elems * es;
+      it.srcDtype = dt;
+      it.dstDtype = cast ? DType::kBF16 : dt;
+      if (i % 4 == 3) {
+        it.strided = true;
+        it.view = StridedView{dt, rows, 64, 1, rows};
+      }
+      appendToPlan(plan, it, true);
+      srcOff += (it.srcBytes + 255) / 256 * 256;
+      const uint64_t out = cast ? elems * 2 : elems * es;
+      dstOff += (out + 255) / 256 * 256;
+      delivered += out;
+      read += it.srcBytes;
+    }
+    if (srcOff <= bytes && dstOff <= bytes) {
+      double ms = timer.run(3, iters, [&] { launchPush(plan, nullptr, sms, words, 1, words + 16, nullptr); });
+      std::printf("%-44s %10.1f us  %8.1f GB/s delivered  %8.1f GB/s read+write  (%zu entries, %u bulk + %u warp tiles)\n",
+                  "64-tensor mixed message, one launch", ms * 1e3, delivered / (ms * 1e-3) / 1e9,
+                  (read + delivered) / (ms * 1e-3) / 1e9, plan.entries.size(), plan.bulkTiles, plan.plainTiles);
     }
   }
   if (want("small")) {

@@ -443,8 +443,12 @@ void RingBench::connectMesh(const std::vector<std::string>& urls, int rank) {
     });
   };
   if (world > 1) arm();
-  for (int j = 0; j < world; ++j) {
-    if (j == rank) continue;
+  // Peers in rotation order (rank+1, rank+2, ...): the sends of one round are launched in this
+  // order, so at any moment the ranks target distinct receivers instead of all converging on rank 0
+  // first (an all-to-all's usual schedule; with every rank starting at peer 0 the receivers' links
+  // take turns being oversubscribed sevenfold while the others idle).
+  for (int d = 1; d < world; ++d) {
+    const int j = (rank + d) % world;
     std::string url = urls[j];
     int dev = m.opts.device;
     auto bar = url.rfind('|');

@@ -31,6 +31,7 @@ DTYPE_CODES = {
 }
 _CASTABLE = (torch.float32, torch.bfloat16, torch.float16)
 _DTYPE_BY_NAME = {str(d).replace("torch.", ""): d for d in DTYPE_CODES}
+_DTYPE_NAMES = {d: name for name, d in _DTYPE_BY_NAME.items()}
 
 
 def kernel_launch_count() -> int:
@@ -82,6 +83,7 @@ class Pipe:
     def __init__(self, native: "_C.Pipe"):
         self._p = native
         self._lock = threading.Lock()
+        self._layouts: Dict[tuple, bool] = {}
 
     @property
     def remote_name(self) -> str:
@@ -103,11 +105,21 @@ class Pipe:
             out.add_payload(p if isinstance(p, (bytes, bytearray, memoryview)) else bytes(p), bytes(pm))
         targets = message.target_devices or [None] * len(message.tensors)
         tmeta = message.tensor_metadata or [None] * len(message.tensors)
+        streams: Dict[torch.device, int] = {}  # one current-stream lookup per device and message
         for t, target, tm in zip(message.tensors, targets, tmeta):
-            self._add_tensor(out, t, target, tm)
+            self._add_tensor(out, t, target, tm, streams)
         self._p.write(out, callback)
 
-    def _add_tensor(self, out, t: torch.Tensor, target: Optional[str], metadata: Optional[bytes] = None) -> None:
+    def _supports_layouts(self, local: str, target: str) -> bool:
+        # Fixed once the pipe is established: asked once per device pair, not per tensor.
+        key = (local, target)
+        known = self._layouts.get(key)
+        if known is None:
+            known = self._layouts[key] = bool(self._p.channel_supports_layouts(local, target))
+        return known
+
+    def _add_tensor(self, out, t: torch.Tensor, target: Optional[str], metadata: Optional[bytes] = None,
+                    streams: Optional[Dict[torch.device, int]] = None) -> None:
         local = _device_str(t.device)
         view = None
         code = DTYPE_CODES.get(t.dtype, 0)
@@ -117,21 +129,28 @@ class Pipe:
                 and t.numel() > 0
                 and t.device.type == "cuda"
                 and target is not None
-                and self._p.channel_supports_layouts(local, target)
+                and self._supports_layouts(local, target)
             )
             if packable:
                 view = (t.shape[0], t.shape[1], t.stride(0), t.stride(1))
             else:
                 t = t.contiguous()
-        meta = metadata if metadata is not None else json.dumps(
-            {"dtype": str(t.dtype).replace("torch.", ""), "shape": list(t.shape)}).encode()
+        meta = metadata if metadata is not None else (
+            '{"dtype": "%s", "shape": %s}' % (_DTYPE_NAMES.get(t.dtype) or str(t.dtype).replace("torch.", ""),
+                                              list(t.shape))).encode()
         dev_type, dev_index = local.split(":")
+        if streams is None:
+            stream = _stream_handle(t.device)
+        else:
+            stream = streams.get(t.device)
+            if stream is None:
+                stream = streams[t.device] = _stream_handle(t.device)
         out.add_tensor(
             t.data_ptr(),
             t.numel() * t.element_size(),
             dev_type,
             int(dev_index),
-            _stream_handle(t.device),
+            stream,
             meta,
             code,
             view,

@@ -21,6 +21,7 @@ import statistics
 import subprocess
 import sys
 import tempfile
+import threading
 import time
 
 REPO = os.path.dirname(os.path.abspath(__file__))
@@ -32,7 +33,7 @@ METRIC = "pipe_gpu_to_gpu_GBps"
 def parse_args():
     p = argparse.ArgumentParser()
     p.add_argument("--gpus", type=int, default=1)
-    p.add_argument("--steps", type=int, default=50)
+    p.add_argument("--steps", type=int, default=200)
     p.add_argument("--warmup", type=int, default=5)
     p.add_argument("--impl", default="native", choices=["native", "reference"])
     p.add_argument("--bytes", type=int, default=256 << 20)
@@ -46,18 +47,64 @@ def parse_args():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    """Samples SM clocks and throttle reasons of one GPU while a region runs.
+
+    Reads NVML from a thread every millisecond (the timed region of the default run lasts a few
+    milliseconds, less than nvidia-smi needs to print its first line); falls back to an
+    `nvidia-smi -lms` child process when the NVML module is missing. Read-only either way."""
 
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20,
+                   "sw_power_cap": 0x4}
 
     def __init__(self, device_index):
         self.device_index = device_index
         self.proc = None
         self.path = None
+        self.thread = None
+        self.stop_flag = threading.Event()
+        self.sm, self.sm_max, self.reasons = [], [], set()
+        self.handle = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            # NVML numbers physical GPUs; honour CUDA_VISIBLE_DEVICES when it lists indices.
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+            index = device_index
+            if visible and all(v.strip().isdigit() for v in visible.split(",")):
+                index = int(visible.split(",")[device_index])
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.nvml = pynvml
+        except Exception:  # noqa: BLE001
+            self.handle = None
+
+    def _sample(self):
+        n = self.nvml
+        self.sm.append(float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)))
+        self.sm_max.append(float(n.nvmlDeviceGetMaxClockInfo(self.handle, n.NVML_CLOCK_SM)))
+        try:
+            bits = n.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+        except Exception:  # noqa: BLE001
+            bits = n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+        for name, bit in self.REASON_BITS.items():
+            if bits & bit:
+                self.reasons.add(name)
+
+    def _poll(self):
+        while not self.stop_flag.is_set():
+            try:
+                self._sample()
+            except Exception:  # noqa: BLE001
+                return
+            time.sleep(0.001)
 
     def start(self):
+        if self.handle is not None:
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
         try:
             fd, self.path = tempfile.mkstemp(prefix="tpb_clocks_", suffix=".csv")
             os.close(fd)
@@ -70,6 +117,16 @@ class ClockSampler:
             self.proc = None
 
     def stop(self):
+        if self.thread is not None:
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
+            return {
+                "sm_mhz": statistics.median(self.sm) if self.sm else None,
+                "sm_max_mhz": max(self.sm_max) if self.sm_max else None,
+                "samples": len(self.sm),
+                "reasons": sorted(self.reasons),
+                "source": "NVML, 1 ms period",
+            }
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
@@ -100,6 +157,7 @@ class ClockSampler:
             "sm_max_mhz": max(sm_max) if sm_max else None,
             "samples": len(sm),
             "reasons": sorted(reasons),
+            "source": "nvidia-smi -lms 100",
         }
 
 

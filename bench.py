@@ -77,13 +77,14 @@ class ClockSampler:
                 index = int(visible.split(",")[device_index])
             self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
             self.nvml = pynvml
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
         except Exception:  # noqa: BLE001
             self.handle = None
 
     def _sample(self):
         n = self.nvml
         self.sm.append(float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)))
-        self.sm_max.append(float(n.nvmlDeviceGetMaxClockInfo(self.handle, n.NVML_CLOCK_SM)))
+        self.sm_max.append(self.max_mhz)  # a property of the board, read once
         try:
             bits = n.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
         except Exception:  # noqa: BLE001

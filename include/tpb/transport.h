@@ -18,6 +18,10 @@
 namespace tpb {
 namespace transport {
 
+// Largest frame a transport allocates memory for on the peer's word (reads without a caller
+// buffer: control messages). A longer one fails the connection instead of the allocation.
+constexpr uint64_t kMaxAllocatedFrame = 1ull << 30;
+
 class Connection {
  public:
   using read_callback_fn = std::function<void(const Error&, const void* ptr, size_t length)>;

@@ -557,6 +557,13 @@ void ConnectionImpl::processReads() {
           return;
         }
       } else {
+        // A length the peer chose: bound what is allocated on its word.
+        if (op.frameLen > kMaxAllocatedFrame) {
+          if (!peerGone_) pokePeer(peerOutboxToken_);
+          closeFromLoop(TPB_CREATE_ERROR(MessageError, "incoming frame of " + std::to_string(op.frameLen) +
+                                                           " bytes exceeds the limit for unsolicited frames"));
+          return;
+        }
         op.owned.resize(op.frameLen);
         op.ptr = op.owned.data();
       }

@@ -316,6 +316,13 @@ void ConnectionImpl::processReads() {
           return;
         }
       } else {
+        // The length comes from the peer: a corrupt or hostile header must fail the connection,
+        // not exhaust memory. Frames the library allocates for are control messages.
+        if (op.frameLen > kMaxAllocatedFrame) {
+          closeFromLoop(TPB_CREATE_ERROR(MessageError, "incoming frame of " + std::to_string(op.frameLen) +
+                                                           " bytes exceeds the limit for unsolicited frames"));
+          return;
+        }
         op.owned.resize(op.frameLen);
         op.ptr = op.owned.data();
       }

@@ -121,3 +121,97 @@ TPB_TEST(Nop, RejectsMalformed) {
   uint8_t big[] = {0x83, 0, 0, 0, 0, 1, 0, 0, 0};
   EXPECT_FALSE(nop::decode(big, sizeof(big), small));
 }
+
+// Whatever arrives on the wire, decoding either succeeds or says no: it never crashes, never loops
+// and never allocates more than the input could justify. Valid encodings of every core structure
+// are mutated (bit flips, truncations, spliced garbage) and random bytes are thrown in as well.
+#include <random>
+
+TPB_TEST(Nop, DecodersSurviveMutatedAndRandomInput) {
+  std::vector<std::vector<uint8_t>> seeds;
+  {
+    Packet hello = SpontaneousConnection{"some-context"};
+    seeds.push_back(nop::encode(hello));
+    Packet req = RequestedConnection{123456789};
+    seeds.push_back(nop::encode(req));
+    Brochure b;
+    b.transportDomainDescriptors["uv"] = "uv:*";
+    b.transportDomainDescriptors["shm"] = "tpbshm1:abc";
+    b.channelDeviceDescriptors["basic"][Device("cpu", 0)] = "any";
+    b.channelDeviceDescriptors["cuda_p2p"][Device("cuda", 1)] = "GPU-xyz";
+    seeds.push_back(nop::encode(b));
+    BrochureAnswer a;
+    a.transport = "uv";
+    a.address = "127.0.0.1:1";
+    a.transportRegistrationIds[1] = 7;
+    a.channelRegistrationIds["basic"] = {3, 4, 5};
+    a.channelForDevicePair[{Device("cpu", 0), Device("cuda", 2)}] = "cuda_basic";
+    seeds.push_back(nop::encode(a));
+    Descriptor d;
+    d.metadata = std::string(40, 'm');
+    d.payloads.push_back({4, "p"});
+    d.payloads.push_back({1u << 20, ""});
+    for (int i = 0; i < 5; ++i) {
+      Descriptor::Tensor t;
+      t.length = 1024u * (i + 1);
+      t.sourceDevice = Device(i % 2 ? "cuda" : "cpu", i);
+      if (i % 2) t.targetDevice = Device("cuda", 7 - i);
+      t.metadata = std::string(i, 't');
+      d.tensors.push_back(t);
+    }
+    seeds.push_back(nop::encode(d));
+    DescriptorReply r;
+    r.targetDevices.push_back(Device("cuda", 0));
+    r.targetDevices.push_back(Device("cpu", 0));
+    seeds.push_back(nop::encode(r));
+  }
+  std::mt19937 rng(20240607);
+  size_t accepted = 0, rejected = 0;
+  auto tryAll = [&](const std::vector<uint8_t>& bytes) {
+    Packet p;
+    Brochure b;
+    BrochureAnswer a;
+    Descriptor d;
+    DescriptorReply r;
+    std::string s;
+    std::vector<uint64_t> v;
+    bool any = nop::decode(bytes.data(), bytes.size(), p);
+    any |= nop::decode(bytes.data(), bytes.size(), b);
+    any |= nop::decode(bytes.data(), bytes.size(), a);
+    any |= nop::decode(bytes.data(), bytes.size(), d);
+    any |= nop::decode(bytes.data(), bytes.size(), r);
+    any |= nop::decode(bytes.data(), bytes.size(), s);
+    any |= nop::decode(bytes.data(), bytes.size(), v);
+    (any ? accepted : rejected)++;
+    // A decoded descriptor never claims more entries than the input has bytes.
+    EXPECT_TRUE(d.tensors.size() <= bytes.size() && d.payloads.size() <= bytes.size());
+  };
+  for (int iter = 0; iter < 20000; ++iter) {
+    std::vector<uint8_t> bytes = seeds[rng() % seeds.size()];
+    switch (rng() % 5) {
+      case 0:  // flip a few bits
+        for (int k = 0, n = 1 + rng() % 4; k < n && !bytes.empty(); ++k) bytes[rng() % bytes.size()] ^= 1u << (rng() % 8);
+        break;
+      case 1:  // truncate
+        bytes.resize(rng() % (bytes.size() + 1));
+        break;
+      case 2:  // overwrite a run with garbage (length fields become huge)
+        for (size_t k = rng() % bytes.size(), n = 0; k < bytes.size() && n < 9; ++k, ++n) bytes[k] = static_cast<uint8_t>(rng());
+        break;
+      case 3:  // splice two encodings
+        bytes.resize(rng() % (bytes.size() + 1));
+        {
+          const auto& other = seeds[rng() % seeds.size()];
+          bytes.insert(bytes.end(), other.begin() + rng() % other.size(), other.end());
+        }
+        break;
+      default:  // pure noise
+        bytes.resize(rng() % 64);
+        for (auto& x : bytes) x = static_cast<uint8_t>(rng());
+    }
+    tryAll(bytes);
+  }
+  for (const auto& s : seeds) tryAll(s);
+  EXPECT_TRUE(accepted >= seeds.size());  // the untouched encodings, at the very least
+  EXPECT_TRUE(rejected > 10000);          // and most mutations are refused
+}

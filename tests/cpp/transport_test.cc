@@ -364,3 +364,38 @@ TPB_TEST(TransportUv, AddressHelpers) {
   }
   ctx->join();
 }
+
+// A frame header is the peer's word: one that announces more than the transport is willing to
+// allocate fails the connection (and the pending read) instead of the process.
+#include <arpa/inet.h>
+#include <netinet/in.h>
+#include <sys/socket.h>
+#include <unistd.h>
+
+TPB_TEST(TransportUv, AbsurdFrameLengthFailsTheConnectionNotTheProcess) {
+  auto ctx = transport::uv::create();
+  auto l = ctx->listen("127.0.0.1");
+  const std::string addr = l->addr();  // "127.0.0.1:port"
+  const int port = std::stoi(addr.substr(addr.rfind(':') + 1));
+  // A raw socket plays the corrupt peer.
+  int fd = ::socket(AF_INET, SOCK_STREAM, 0);
+  EXPECT_TRUE(fd >= 0);
+  sockaddr_in sa{};
+  sa.sin_family = AF_INET;
+  sa.sin_port = htons(static_cast<uint16_t>(port));
+  ::inet_pton(AF_INET, "127.0.0.1", &sa.sin_addr);
+  EXPECT_EQ(::connect(fd, reinterpret_cast<sockaddr*>(&sa), sizeof(sa)), 0);
+  auto server = acceptSync(*l);
+  std::promise<Error> got;
+  server->read([&](const Error& e, const void*, size_t) { got.set_value(e); });
+  const uint64_t absurd = transport::kMaxAllocatedFrame + 1;
+  EXPECT_EQ(::write(fd, &absurd, sizeof(absurd)), ssize_t(sizeof(absurd)));
+  auto f = got.get_future();
+  Error e = waitFor(f);
+  EXPECT_TRUE(bool(e));
+  EXPECT_TRUE(e.what().find("exceeds the limit") != std::string::npos);
+  // A frame right at the limit is not refused for its size (the peer hangs up before sending
+  // the body, so it ends in EOF; what matters is that the limit itself is inclusive).
+  ::close(fd);
+  ctx->join();
+}

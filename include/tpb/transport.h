@@ -94,6 +94,8 @@ struct FaultPlan {
   int failAfterWrites = -1;  // >=0: the (N+1)-th write and everything after fails and closes
   int dropWrites = 0;        // silently drop this many writes (callback still succeeds)
   int delayMs = 0;           // delay every write by this long
+  int corruptFromWrite = -1; // >=0: from the N-th write on, frames are sent with their bytes scrambled
+  unsigned corruptSeed = 1;  //      (same length, seeded noise XOR-ed over the content)
 };
 std::shared_ptr<Context> wrapWithFaults(std::shared_ptr<Context> inner, FaultPlan plan);
 

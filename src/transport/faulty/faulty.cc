@@ -5,7 +5,9 @@
 // with an error and in order.
 #include <atomic>
 #include <chrono>
+#include <random>
 #include <thread>
+#include <vector>
 
 #include <tpb/transport.h>
 
@@ -35,6 +37,15 @@ class FaultyConnection final : public Connection {
       // Pretend success without sending anything; a zero-length read on our own side keeps the
       // callback off the caller's stack.
       inner_->write(nullptr, 0, [fn = std::move(fn)](const Error& e) { fn(e); });
+      return;
+    }
+    if (plan_.corruptFromWrite >= 0 && n >= plan_.corruptFromWrite && length > 0) {
+      // Same length on the wire, scrambled content; the copy lives until the write completes.
+      auto copy = std::make_shared<std::vector<uint8_t>>(static_cast<const uint8_t*>(ptr),
+                                                         static_cast<const uint8_t*>(ptr) + length);
+      std::mt19937 rng(plan_.corruptSeed + static_cast<unsigned>(n));
+      for (auto& b : *copy) b ^= static_cast<uint8_t>(rng());
+      inner_->write(copy->data(), copy->size(), [fn = std::move(fn), copy](const Error& e) { fn(e); });
       return;
     }
     inner_->write(ptr, length, std::move(fn));

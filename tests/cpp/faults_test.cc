@@ -213,3 +213,59 @@ TPB_TEST(Faults, DroppedFramesDoNotCrashThePeer) {
   auto fa = accepted.get_future();
   waitFor(fa);  // fired one way or the other
 }
+
+// A peer whose frames arrive scrambled (same lengths, noise for content) at every possible point
+// of the conversation: during the handshake, in a descriptor, in a payload. The healthy side must
+// end every operation with an error or with data, never crash or hang, and stay joinable.
+TPB_TEST(Faults, ScrambledFramesAtAnyPointNeverCrashThePeer) {
+  for (int from = 0; from < 10; ++from) {
+    auto a = plain("a");
+    auto b = std::make_shared<Context>(ContextOptions().name("b"));
+    transport::FaultPlan plan;
+    plan.corruptFromWrite = from;
+    plan.corruptSeed = 1000 + from;
+    b->registerTransport(0, "uv", transport::wrapWithFaults(transport::uv::create(), plan));
+    b->registerChannel(0, "basic", channel::basic::create());
+    auto l = a->listen({"uv://127.0.0.1"});
+    std::atomic<int> called{0};
+    std::shared_ptr<Pipe> server;
+    std::vector<uint8_t> inPayload(64), inTensor(4096);
+    l->accept([&](const Error& e, std::shared_ptr<Pipe> p) {
+      ++called;
+      if (e) return;
+      server = p;
+      // Try to receive whatever the scrambling peer manages to say.
+      p->readDescriptor([&, p](const Error& e2, Descriptor d) {
+        ++called;
+        if (e2) return;
+        if (d.payloads.size() != 1 || d.tensors.size() != 1 || d.payloads[0].length != inPayload.size() ||
+            d.tensors[0].length != inTensor.size())
+          return;  // a descriptor that decoded into something else: leave it unread, close will clean up
+        Allocation al;
+        al.payloads.push_back({inPayload.data()});
+        Allocation::Tensor t;
+        t.buffer = CpuBuffer{inTensor.data()};
+        al.tensors.push_back(t);
+        p->read(std::move(al), [&](const Error&) { ++called; });
+      });
+    });
+    auto out = b->connect(l->url("uv"));
+    std::vector<uint8_t> payload(64, 7), tensor(4096, 9);
+    std::promise<Error> w;
+    Message m;
+    m.metadata = "meta";
+    m.payloads.push_back({payload.data(), payload.size(), ""});
+    Message::Tensor mt;
+    mt.buffer = CpuBuffer{tensor.data()};
+    mt.length = tensor.size();
+    m.tensors.push_back(mt);
+    out->write(std::move(m), [&](const Error& e) { w.set_value(e); });
+    std::this_thread::sleep_for(std::chrono::milliseconds(60));
+    b->join();
+    auto fw = w.get_future();
+    waitFor(fw);  // fired one way or the other
+    a->join();
+    EXPECT_TRUE(called.load() >= 1);
+    server.reset();
+  }
+}

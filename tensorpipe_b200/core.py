@@ -39,6 +39,28 @@ def kernel_launch_count() -> int:
     return _C.kernel_launch_count()
 
 
+def _parse_tensor_metadata(raw: bytes):
+    """(dtype name, shape) out of the metadata this module attaches to tensors, or None for anything
+    else (a foreign peer's metadata). The exact bytes `_add_tensor` writes are recognised without a
+    JSON parser; anything that merely is JSON with those two keys still goes through json."""
+    if raw.startswith(b'{"dtype": "') and raw.endswith(b']}'):
+        try:
+            end = raw.index(b'"', 11)
+            if raw[end:end + 13] == b'", "shape": [':
+                body = raw[end + 13:-2]
+                shape = [int(x) for x in body.split(b",")] if body.strip() else []
+                return raw[11:end].decode(), shape
+        except ValueError:
+            pass
+    try:
+        meta = json.loads(raw.decode())
+    except (ValueError, UnicodeDecodeError):
+        return None
+    if isinstance(meta, dict) and isinstance(meta.get("shape"), list) and isinstance(meta.get("dtype"), str):
+        return meta["dtype"], meta["shape"]
+    return None
+
+
 def _stream_handle(device: torch.device) -> int:
     if device.type != "cuda":
         return 0
@@ -202,14 +224,11 @@ class Pipe:
                     alloc.add_payload(buf)
                 for i, td in enumerate(desc["tensors"]):
                     msg.tensor_metadata.append(td["metadata"])
-                    try:
-                        meta = json.loads(td["metadata"].decode())
-                        if not (isinstance(meta, dict) and meta.get("dtype") in _DTYPE_BY_NAME and "shape" in meta):
-                            meta = None
-                    except (ValueError, UnicodeDecodeError):
+                    meta = _parse_tensor_metadata(td["metadata"])
+                    if meta is not None and meta[0] not in _DTYPE_BY_NAME:
                         meta = None  # a foreign peer's metadata: deliver the bytes as they are
-                    src_dtype = _DTYPE_BY_NAME[meta["dtype"]] if meta else torch.uint8
-                    shape = meta["shape"] if meta else [td["length"]]
+                    src_dtype = _DTYPE_BY_NAME[meta[0]] if meta else torch.uint8
+                    shape = meta[1] if meta else [td["length"]]
                     want = cast.get(i)
                     dst_dtype = want if want is not None else src_dtype
                     where = td["target_device"] or device or (

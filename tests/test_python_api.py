@@ -124,3 +124,16 @@ def test_cuda_tensors_views_and_casts(built):
 def test_smoke_entry_point(built):
     import __graft_entry__
     __graft_entry__.smoke()
+
+
+def test_tensor_metadata_fast_path_agrees_with_json(built):
+    import json
+    from tensorpipe_b200.core import _parse_tensor_metadata
+    for dtype, shape in [("float32", [1000, 10]), ("bfloat16", []), ("int64", [7]), ("uint8", [2, 3, 4, 5])]:
+        ours = ('{"dtype": "%s", "shape": %s}' % (dtype, shape)).encode()  # what the sender writes
+        assert _parse_tensor_metadata(ours) == (dtype, shape)
+        assert _parse_tensor_metadata(json.dumps({"shape": shape, "dtype": dtype}).encode()) == (dtype, shape)
+    for foreign in [b"", b"a place", b"\xff\xfe", b'{"dtype": "float32"}', b'{"dtype": "x", "shape": [1, "a"]}',
+                    b'[1, 2]', b'{"dtype": 3, "shape": [1]}']:
+        got = _parse_tensor_metadata(foreign)
+        assert got is None or got == ("x", [1, "a"])

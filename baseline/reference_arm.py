@@ -33,6 +33,21 @@ def build():
     src = os.path.join(HERE, "ref_pipe_bench.cc")
     if os.path.exists(BIN) and os.path.getmtime(BIN) >= os.path.getmtime(src):
         return None
+    # Every rank lands here at once: one compiles (into a temporary name, renamed when complete),
+    # the others wait for the lock and then find the binary in place.
+    import fcntl
+    os.makedirs(os.path.dirname(BIN), exist_ok=True)
+    with open(BIN + ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if os.path.exists(BIN) and os.path.getmtime(BIN) >= os.path.getmtime(src):
+                return None
+            return _compile(src)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _compile(src):
     import torch
     tdir = os.path.dirname(torch.__file__)
     nv = os.path.join(os.path.dirname(tdir), "nvidia", "cuda_runtime", "lib")
@@ -40,12 +55,16 @@ def build():
         return "torch does not ship the TensorPipe headers"
     os.makedirs(os.path.dirname(BIN), exist_ok=True)
     cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++"
-    cmd = [cxx, "-std=c++17", "-O2", f"-I{tdir}/include", "-I/usr/local/cuda/include", src, "-o", BIN,
+    tmp = f"{BIN}.{os.getpid()}.tmp"
+    cmd = [cxx, "-std=c++17", "-O2", f"-I{tdir}/include", "-I/usr/local/cuda/include", src, "-o", tmp,
            f"-L{tdir}/lib", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda", f"-Wl,-rpath,{tdir}/lib",
            f"-L{nv}", "-l:libcudart.so.12", f"-Wl,-rpath,{nv}", "-lpthread"]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
+        if os.path.exists(tmp):
+            os.unlink(tmp)
         return "harness does not compile: " + proc.stderr.strip().splitlines()[-1][:200]
+    os.replace(tmp, BIN)
     return None
 
 

@@ -183,7 +183,26 @@ def run_reference(args):
     reference_arm.main(args, METRIC)
 
 
+def ensure_built():
+    """The native module normally arrives built; if it is missing, one rank builds it (under a lock)
+    while the others wait, so a bare source tree still runs."""
+    import glob
+    here = os.path.dirname(os.path.abspath(__file__))
+    if glob.glob(os.path.join(here, "tensorpipe_b200", "_C*.so")):
+        return
+    import fcntl
+    with open(os.path.join(here, ".build.lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not glob.glob(os.path.join(here, "tensorpipe_b200", "_C*.so")):
+                subprocess.check_call(["make", "-j", str(os.cpu_count() or 4)], cwd=here,
+                                      stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
 def run_native(args):
+    ensure_built()
     import torch
     import torch.distributed as dist
     import tensorpipe_b200 as tpb

@@ -793,6 +793,7 @@ void ChannelImpl::launchRendezvous(SendOp& op) {
       c.strided = true;
       c.view = *it.view;
     }
+    c.remote = ready.deviceIdx != op.srcDevice;
     if (c.dstDtype != c.srcDtype && !kernels::castSupported(c.srcDtype, c.dstDtype))
       return closeFromLoop(TPB_CREATE_ERROR(LogicError, "unsupported dtype conversion requested by the receiver"));
     if (kernels::convertedBytes(it.length, c.srcDtype, c.dstDtype) != t.bytes)

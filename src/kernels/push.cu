@@ -33,6 +33,7 @@
 #include "common/trace.h"
 
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 #include <stdexcept>
 #include <string>
@@ -44,7 +45,14 @@ namespace {
 
 std::atomic<uint64_t> gLaunches{0};
 std::mutex gTuningMutex;
-PushTuning gTuning;
+PushTuning initialTuning() {
+  PushTuning t;
+  if (const char* e = std::getenv("TPB_PUSH_NARROW")) {
+    if (e[0] >= '0' && e[0] <= '2' && e[1] == 0) t.narrowRows = static_cast<uint32_t>(e[0] - '0');
+  }
+  return t;
+}
+PushTuning gTuning = initialTuning();
 
 constexpr uint32_t kWarpTileBytes = kStridedTile * (kStridedTile / 2 + 1) * 8;  // 4352 B per warp: 32 x 17 x 8-byte, or 32 x 33 x 4-byte
 constexpr int kWidePitch = kWideTile + 2;                                        // 2-byte elements per staged column
@@ -443,6 +451,117 @@ __device__ __forceinline__ void stridedTiles(const PushEntry& a, uint32_t first,
   }
 }
 
+// Transposed matrix with few columns (cols <= 64, rowStride == 1): a tile is 32 whole rows of the
+// packed result, i.e. ONE contiguous run of 32 * cols elements in the destination. Lanes read down
+// the source columns as usual and park the (already converted) values in 32-bit slots tile[c][r];
+// then every lane gathers the 16 bytes of its chunk of the run and stores them as one vector, so a
+// warp writes 512 contiguous bytes per instruction instead of one 128-byte row segment. That is
+// what a remote GPU's memory wants to see over NVLink. Needs cols * sizeof(D) to be a multiple of
+// 16 and a 16-byte aligned destination.
+template <typename S, typename D, bool kConvert>
+__device__ __forceinline__ void stridedNarrowTile(const StridedArgs& a, uint32_t localTile, int lane, uint8_t* tileMem) {
+  constexpr int TR = 32, P = TR + 1;
+  constexpr int K = 16 / sizeof(D);  // destination elements per 16-byte chunk
+  uint32_t* tile = reinterpret_cast<uint32_t*>(tileMem);
+  const int64_t rows = a.rows, colStride = a.colStride;
+  const int cols = static_cast<int>(a.cols);
+  const S* src = static_cast<const S*>(a.src);
+  D* dst = static_cast<D*>(a.dst);
+  const int64_t r0 = static_cast<int64_t>(localTile) * TR;
+  const int nr = static_cast<int>(rows - r0 < TR ? rows - r0 : TR);
+  constexpr int kBatch = 16;
+  {
+    const bool act = lane < nr;
+    const S* colPtr = src + (r0 + lane);
+    for (int c = 0; c < cols; c += kBatch) {
+      S v[kBatch];
+#pragma unroll
+      for (int k = 0; k < kBatch; ++k)
+        if (act && c + k < cols && TPB_DBG_SRC(a, colPtr + static_cast<int64_t>(c + k) * colStride, sizeof(S)))
+          v[k] = colPtr[static_cast<int64_t>(c + k) * colStride];
+#pragma unroll
+      for (int k = 0; k < kBatch; ++k) {
+        if (act && c + k < cols) {
+          D out;
+          if constexpr (kConvert) out = fromFloat<D>(toFloat<S>(v[k]));
+          else out = v[k];
+          uint32_t bits = 0;
+          if constexpr (sizeof(D) == 4) bits = *reinterpret_cast<const uint32_t*>(&out);
+          else if constexpr (sizeof(D) == 2) bits = *reinterpret_cast<const uint16_t*>(&out);
+          else bits = *reinterpret_cast<const uint8_t*>(&out);
+          tile[(c + k) * P + lane] = bits;
+        }
+      }
+    }
+  }
+  __syncwarp();
+  {
+    const int chunksPerRow = cols / K;
+    const int chunks = nr * chunksPerRow;
+    uint4* out = reinterpret_cast<uint4*>(dst + r0 * cols);
+    // (r, c) of chunk q, advanced by 32 chunks per step without dividing in the loop.
+    int r = lane / chunksPerRow;
+    int cc = lane - r * chunksPerRow;  // chunk index within its row
+    const int stepRows = 32 / chunksPerRow, stepChunks = 32 - stepRows * chunksPerRow;
+    for (int q = lane; q < chunks; q += 32) {
+      const int c = cc * K;
+      alignas(16) D vals[K];
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const uint32_t bits = tile[(c + k) * P + r];
+        if constexpr (sizeof(D) == 4) vals[k] = *reinterpret_cast<const D*>(&bits);
+        else if constexpr (sizeof(D) == 2) {
+          const uint16_t h = static_cast<uint16_t>(bits);
+          vals[k] = *reinterpret_cast<const D*>(&h);
+        } else {
+          const uint8_t b = static_cast<uint8_t>(bits);
+          vals[k] = *reinterpret_cast<const D*>(&b);
+        }
+      }
+      if (TPB_DBG_DST(a, out + q, 16)) out[q] = *reinterpret_cast<const uint4*>(vals);
+      r += stepRows;
+      cc += stepChunks;
+      if (cc >= chunksPerRow) {
+        cc -= chunksPerRow;
+        ++r;
+      }
+    }
+  }
+  __syncwarp();
+}
+
+template <typename S, typename D, bool kConvert>
+__device__ __noinline__ void stridedNarrowTilesTyped(const PushEntry& e, uint32_t first, uint32_t step, int lane,
+                                                     uint8_t* tileMem) {
+  const StridedArgs a = loadStridedArgs(e);
+#pragma unroll 1
+  for (uint32_t t = first; t < a.numTiles; t += step) stridedNarrowTile<S, D, kConvert>(a, t, lane, tileMem);
+}
+
+__device__ __forceinline__ void stridedNarrowTiles(const PushEntry& e, uint32_t first, uint32_t step, int lane,
+                                                   uint8_t* tileMem) {
+  if (e.srcDtype == e.dstDtype || e.dstDtype == static_cast<uint8_t>(DType::kBytes)) {
+    switch (e.srcElemSize) {
+      case 1: stridedNarrowTilesTyped<uint8_t, uint8_t, false>(e, first, step, lane, tileMem); break;
+      case 2: stridedNarrowTilesTyped<uint16_t, uint16_t, false>(e, first, step, lane, tileMem); break;
+      default: stridedNarrowTilesTyped<uint32_t, uint32_t, false>(e, first, step, lane, tileMem); break;
+    }
+    return;
+  }
+  const uint32_t key = (static_cast<uint32_t>(e.srcDtype) << 8) | e.dstDtype;
+  constexpr uint32_t F32 = static_cast<uint32_t>(DType::kF32), BF = static_cast<uint32_t>(DType::kBF16),
+                     F16 = static_cast<uint32_t>(DType::kF16);
+  switch (key) {
+    case (F32 << 8) | BF: stridedNarrowTilesTyped<float, __nv_bfloat16, true>(e, first, step, lane, tileMem); break;
+    case (F32 << 8) | F16: stridedNarrowTilesTyped<float, __half, true>(e, first, step, lane, tileMem); break;
+    case (BF << 8) | F32: stridedNarrowTilesTyped<__nv_bfloat16, float, true>(e, first, step, lane, tileMem); break;
+    case (F16 << 8) | F32: stridedNarrowTilesTyped<__half, float, true>(e, first, step, lane, tileMem); break;
+    case (BF << 8) | F16: stridedNarrowTilesTyped<__nv_bfloat16, __half, true>(e, first, step, lane, tileMem); break;
+    case (F16 << 8) | BF: stridedNarrowTilesTyped<__half, __nv_bfloat16, true>(e, first, step, lane, tileMem); break;
+    default: break;
+  }
+}
+
 // Transposed matrix of 2-byte elements (rowStride == 1), with the source, the destination, both
 // extents and the column stride all even: a warp moves a 64x64 tile, reading 32-bit words down the
 // source columns (128 B per instruction instead of 64) and writing 32-bit words along the packed
@@ -545,6 +664,7 @@ __device__ __forceinline__ void runPlainWarp(const PushParams<N>& p, uint32_t fi
     } else {
       // One call handles every tile of this entry that falls to this warp.
       if (e->kind == kStridedWide16) stridedWide16Tiles(*e, local, totalWarps, lane, tileMem);
+      else if (e->kind == kStridedNarrow) stridedNarrowTiles(*e, local, totalWarps, lane, tileMem);
       else stridedTiles(*e, local, totalWarps, lane, tileMem);
       t += (e->numTiles - local + totalWarps - 1) / totalWarps * totalWarps;
     }
@@ -762,9 +882,9 @@ void launchOne(const PushEntry* entries, uint32_t n, uint32_t bulkTiles, uint32_
   p.bulkStages = bulkStages;
   p.warpTileBytes = 0;
   for (uint32_t i = 0; i < n; ++i) {
-    const uint32_t need = entries[i].kind == kStridedWide16 ? kWideWarpTileBytes
-        : entries[i].kind == kStrided                        ? kWarpTileBytes
-                                                             : 0;
+    const uint32_t need = entries[i].kind == kStridedWide16 || entries[i].kind == kStridedNarrow ? kWideWarpTileBytes
+        : entries[i].kind == kStrided                                                            ? kWarpTileBytes
+                                                                                                 : 0;
     if (need > p.warpTileBytes) p.warpTileBytes = need;
   }
   int dev = 0;
@@ -849,6 +969,10 @@ void pushEntry(PushPlan& plan, PushEntry e) {
     e.numTiles = static_cast<uint32_t>((e.count + perTile - 1) / perTile);
     e.tileStart = plan.plainTiles;
     plan.plainTiles += e.numTiles;
+  } else if (e.kind == kStridedNarrow) {
+    e.numTiles = static_cast<uint32_t>((e.rows + kStridedTile - 1) / kStridedTile);
+    e.tileStart = plan.plainTiles;
+    plan.plainTiles += e.numTiles;
   } else if (e.kind == kStridedWide16) {
     const uint64_t tr = (e.rows + kWideTile - 1) / kWideTile, tc = (e.cols + kWideTile - 1) / kWideTile;
     e.numTiles = static_cast<uint32_t>(tr * tc);
@@ -904,6 +1028,14 @@ void appendToPlan(PushPlan& plan, const CopyItem& item, bool useBulk) {
           v.cols >= kWideTile && v.rows % 2 == 0 && v.cols % 2 == 0 && v.colStride % 2 == 0 && (both & 3) == 0 &&
           smemWithWide <= kMaxSmemPerCta)
         e.kind = kStridedWide16;
+      // Few columns: whole packed rows per tile, written as one contiguous run (wins over the above).
+      const uint64_t dstRowBytes = static_cast<uint64_t>(v.cols) * e.dstElemSize;
+      const uint32_t narrowRows = getPushTuning().narrowRows;
+      if ((narrowRows == 2 || (narrowRows == 1 && item.remote)) && v.rowStride == 1 && v.colStride != 1 &&
+          v.cols <= kNarrowMaxCols && e.srcElemSize <= 4 && e.dstElemSize <= 4 &&
+          dstRowBytes % 16 == 0 && (reinterpret_cast<uintptr_t>(item.dst) & 15) == 0 && v.rows > 1 &&
+          smemWithWide <= kMaxSmemPerCta)
+        e.kind = kStridedNarrow;
     }
     e.rows = v.rows;
     e.cols = v.cols;

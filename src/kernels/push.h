@@ -30,6 +30,8 @@ enum EntryKind : uint32_t {
   kCastPlain = 2,    // contiguous with dtype conversion
   kStrided = 3,      // 2-D strided source -> packed destination (optional conversion)
   kStridedWide16 = 4,  // transposed 2-byte elements, everything 4-byte aligned: 64x64 tiles moved as 32-bit words
+  kStridedNarrow = 5,  // transposed matrix of at most 64 columns: a tile is 32 whole packed rows, written as one
+                       // contiguous run with 16 bytes per lane (optional conversion)
 };
 
 struct alignas(16) PushEntry {
@@ -49,6 +51,7 @@ constexpr int kMaxEntriesLarge = 96;
 constexpr uint32_t kPlainTileBytes = 8 * 1024;  // one warp's unit of work (destination bytes)
 constexpr int kStridedTile = 32;                // a warp transposes 32x32 elements (16x32 for 8-byte ones)
 constexpr int kWideTile = 64;                   // kStridedWide16: 64x64 two-byte elements per warp tile
+constexpr int kNarrowMaxCols = 64;              // kStridedNarrow: 32 rows x (<= 64) columns per warp tile
 constexpr int kThreads = 512;                   // full kernel: warp 0 drives TMA, warps 1..15 use registers
 constexpr int kLightThreads = 256;              // light kernel (no bulk pipeline, static shared memory only)
 constexpr int kMaxBulkStages = 8;
@@ -59,6 +62,9 @@ struct PushTuning {
   uint32_t bulkTileBytes = 32 * 1024;  // multiple of 1024
   uint32_t bulkStages = 3;             // 2..kMaxBulkStages; stages * tile must fit in shared memory
   uint32_t bulkMinBytes = 512 * 1024;  // entries smaller than this take the plain path
+  // Transposed matrices of at most 64 columns written as whole packed rows (kStridedNarrow):
+  // 0 never, 1 for remote destinations (default), 2 always. TPB_PUSH_NARROW overrides the default.
+  uint32_t narrowRows = 1;
 };
 void setPushTuning(const PushTuning& t);
 PushTuning getPushTuning();
@@ -87,6 +93,9 @@ struct CopyItem {
   DType dstDtype = DType::kBytes;   // == srcDtype (or kBytes) when no conversion
   bool strided = false;
   StridedView view;
+  // The destination is another GPU's memory: prefer the paths whose stores form long contiguous
+  // runs (what NVLink wants) over the ones that are fastest against local HBM.
+  bool remote = false;
 };
 
 // True if (src -> dst) is a conversion the kernels implement.

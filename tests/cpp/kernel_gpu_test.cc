@@ -212,7 +212,7 @@ TPB_GPU_TEST(Kernel, WideTransposeOfTwoByteElements, 1) {
     int64_t rows, cols;
     bool withBulk;
   };
-  for (Case c : {Case{64, 64, false}, Case{130, 198, false}, Case{1024, 258, false}, Case{2050, 514, true},
+  for (Case c : {Case{64, 66, false}, Case{130, 198, false}, Case{1024, 258, false}, Case{2050, 514, true},
                  Case{66, 4096, true}}) {
     std::vector<uint16_t> host(c.rows * c.cols);
     std::mt19937 rng(static_cast<uint32_t>(c.rows * 7 + c.cols));
@@ -270,14 +270,14 @@ TPB_GPU_TEST(Kernel, WideTransposeOfTwoByteElements, 1) {
   // Odd extents, an odd column stride or a misaligned destination fall back to the element-wise tiles.
   {
     PushPlan plan;
-    DeviceBuf src(65 * 64 * 2), dst(65 * 64 * 2 + 64);
+    DeviceBuf src(65 * 66 * 2), dst(65 * 66 * 2 + 64);
     CopyItem it;
     it.src = src.p;
     it.dst = dst.p;
-    it.srcBytes = 65 * 64 * 2;
+    it.srcBytes = 65 * 66 * 2;
     it.srcDtype = it.dstDtype = DType::kBF16;
     it.strided = true;
-    it.view = StridedView{DType::kBF16, 65, 64, 1, 65};
+    it.view = StridedView{DType::kBF16, 65, 66, 1, 65};
     appendToPlan(plan, it, true);
     EXPECT_EQ(int(plan.entries.back().kind), int(kStrided));
     it.srcBytes = 64 * 64 * 2;
@@ -285,6 +285,95 @@ TPB_GPU_TEST(Kernel, WideTransposeOfTwoByteElements, 1) {
     it.dst = dst.p + 2;
     appendToPlan(plan, it, true);
     EXPECT_EQ(int(plan.entries.back().kind), int(kStrided));
+  }
+}
+
+// Transposed matrices of at most 64 columns take the narrow path: 32 whole packed rows per tile,
+// written as one contiguous run; with and without conversion, odd row counts, several widths.
+TPB_GPU_TEST(Kernel, NarrowTransposeWritesWholeRows, 1) {
+  struct Case {
+    int64_t rows, cols;
+    size_t es;     // source element size
+    bool toBf16;   // fp32 -> bf16 on the way (es == 4 only)
+  };
+  for (Case c : {Case{2, 64, 4, false}, Case{33, 64, 4, false}, Case{1000, 64, 4, false}, Case{4097, 32, 4, false},
+                 Case{77, 4, 4, false}, Case{300, 64, 2, false}, Case{129, 8, 2, false}, Case{65, 16, 1, false},
+                 Case{999, 64, 4, true}, Case{64, 8, 4, true}, Case{31, 48, 2, false}}) {
+    const size_t srcBytes = c.rows * c.cols * c.es;
+    const size_t des = c.toBf16 ? 2 : c.es;
+    const size_t packed = c.rows * c.cols * des;
+    std::vector<uint8_t> host(srcBytes);
+    std::mt19937 rng(static_cast<uint32_t>(c.rows * 31 + c.cols + c.es));
+    if (c.toBf16) {
+      auto* f = reinterpret_cast<float*>(host.data());
+      std::normal_distribution<float> dist(0.f, 100.f);
+      for (size_t i = 0; i < srcBytes / 4; ++i) f[i] = dist(rng);
+    } else {
+      for (auto& b : host) b = static_cast<uint8_t>(rng());
+    }
+    DeviceBuf src(srcBytes), dst(packed + 2 * kGuard);
+    CK(cudaMemcpy(src.p, host.data(), srcBytes, cudaMemcpyHostToDevice));
+    CK(cudaMemset(dst.p, 0xCD, dst.n));
+    PushPlan plan;
+    CopyItem it;
+    it.src = src.p;
+    it.dst = dst.p + kGuard;
+    it.srcBytes = srcBytes;
+    const DType dt = c.es == 1 ? DType::kU8 : c.es == 2 ? DType::kF16 : DType::kF32;
+    it.srcDtype = dt;
+    it.dstDtype = c.toBf16 ? DType::kBF16 : dt;
+    it.strided = true;
+    it.view = StridedView{dt, c.rows, c.cols, 1, c.rows};
+    it.remote = true;  // the path is chosen for destinations on another GPU; its result is the same anywhere
+    appendToPlan(plan, it, true);
+    EXPECT_EQ(int(plan.entries.back().kind), int(kStridedNarrow));
+    EXPECT_EQ(plan.entries.back().numTiles, uint32_t((c.rows + 31) / 32));
+    launchPush(plan, nullptr, 148, nullptr, 0, nullptr, nullptr);
+    CK(cudaDeviceSynchronize());
+    auto out = download(dst.p, dst.n);
+    for (int64_t r = 0; r < c.rows; ++r)
+      for (int64_t col = 0; col < c.cols; ++col) {
+        const uint8_t* want = &host[(col * c.rows + r) * c.es];
+        const uint8_t* got = &out[kGuard + (r * c.cols + col) * des];
+        bool same;
+        if (c.toBf16) {
+          float f;
+          std::memcpy(&f, want, 4);
+          uint16_t g;
+          std::memcpy(&g, got, 2);
+          same = g == f32ToBf16(f);
+        } else {
+          same = std::memcmp(want, got, c.es) == 0;
+        }
+        if (!same)
+          throw tpbtest::TestFailure("narrow transpose mismatch at (" + std::to_string(r) + "," + std::to_string(col) +
+                                     ") of " + std::to_string(c.rows) + "x" + std::to_string(c.cols) + " es=" +
+                                     std::to_string(c.es));
+      }
+    EXPECT_EQ(int(out[kGuard - 1]), 0xCD);
+    EXPECT_EQ(int(out[kGuard + packed]), 0xCD);
+  }
+  // Rows that are not whole 16-byte chunks, a misaligned destination or 8-byte elements keep the other paths.
+  {
+    DeviceBuf src(4096), dst(4096 + 64);
+    auto kindOf = [&](int64_t rows, int64_t cols, DType dt, uint8_t* d, bool remote = true) {
+      PushPlan plan;
+      CopyItem it;
+      it.src = src.p;
+      it.dst = d;
+      it.srcBytes = rows * cols * dtypeSize(dt);
+      it.srcDtype = it.dstDtype = dt;
+      it.strided = true;
+      it.view = StridedView{dt, rows, cols, 1, rows};
+      it.remote = remote;
+      appendToPlan(plan, it, true);
+      return int(plan.entries.back().kind);
+    };
+    EXPECT_EQ(kindOf(10, 6, DType::kF32, dst.p), int(kStrided));        // 24-byte rows
+    EXPECT_EQ(kindOf(10, 8, DType::kF32, dst.p + 4), int(kStrided));    // destination off the 16-byte grid
+    EXPECT_EQ(kindOf(10, 8, DType::kI64, dst.p), int(kStrided));        // 8-byte elements
+    EXPECT_EQ(kindOf(10, 8, DType::kF32, dst.p), int(kStridedNarrow));
+    EXPECT_EQ(kindOf(10, 8, DType::kF32, dst.p, false), int(kStrided));  // local destination: the 32x32 tiles are faster
   }
 }
 

@@ -11,15 +11,20 @@
 //     without CTA-wide barriers: ragged heads and tails, relatively misaligned buffers, dtype
 //     conversion (fp32 <-> bf16/fp16), and 2-D strided sources, which a warp transposes through
 //     its private padded shared-memory tile so that both the strided reads and the packed writes
-//     are coalesced.
+//     are coalesced (32x32 elements; 64x64 moved as 32-bit words for 2-byte elements; 32 whole
+//     packed rows written as one contiguous run for matrices of at most 64 columns bound for
+//     another GPU). A warp makes one call per tensor for all of its tiles.
 //   * Tiles are dealt round-robin (bulk tile t to CTA t mod gridDim.x, warp tile t to warp
 //     t mod #warps), so no scheduling state lives in global memory.
 //   * Completion: every CTA makes its writes visible system-wide, then arrives on a counter;
 //     the last CTA resets the counter and publishes the flag with a release store at system
 //     scope. The flag lives in the receiver's memory; its stream waits on it.
 //
-// A "light" instantiation (256 threads, static shared memory only, no bulk pipeline) serves small
-// messages, where launch latency matters more than bandwidth.
+// A "light" instantiation (256 threads, no bulk pipeline, shared memory only when a tensor is
+// staged through it) serves messages without bulk work, where launch latency matters most.
+//
+// Built with -DTPB_DEBUG_KERNELS the copy paths check every address against its table entry,
+// skip what lies outside and count it (boundsViolations()); nothing in here can trap.
 //
 // Every wait in here is bounded: a bulk load that does not complete within the limit makes the
 // CTA record kStatusBarrierTimeout, drain its own outstanding stores and fall through to the

@@ -73,8 +73,13 @@ class LoopCallback {
       auto bound = [subject, fn = std::move(fn), error,
                     tup = std::make_tuple(std::decay_t<decltype(args)>(std::forward<decltype(args)>(args))...)]() mutable {
         if (error) subject->setError(error);
-        std::apply(
-            [&](auto&... a) { fn(*subject, std::move(a)...); }, tup);
+        // Whatever a peer makes this object do, an exception on the loop thread would end the
+        // process: it becomes the object's error instead (every pending callback then fires).
+        try {
+          std::apply([&](auto&... a) { fn(*subject, std::move(a)...); }, tup);
+        } catch (const std::exception& ex) {
+          subject->setError(TPB_CREATE_ERROR(LogicError, std::string("while handling a peer's message: ") + ex.what()));
+        }
       };
       subject->loop().deferToLoop(std::move(bound));
     };

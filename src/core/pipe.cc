@@ -152,12 +152,24 @@ void PipeImpl::initFromLoop() {
     state_ = CLIENT_WAITING_FOR_BROCHURE_ANSWER;
     transport::readNop<BrochureAnswer>(
         *descriptorConnection_, callbackWrapper_([](PipeImpl& impl, BrochureAnswer answer) {
-          if (!impl.error_) impl.onReadWhileClientWaitingForBrochureAnswer(answer);
+          // What the peer says may be well formed and still make no sense (an unknown transport,
+          // a channel map that contradicts ours): that fails this pipe, not the process.
+          if (impl.error_) return;
+          try {
+            impl.onReadWhileClientWaitingForBrochureAnswer(answer);
+          } catch (const std::exception& ex) {
+            impl.setError(TPB_CREATE_ERROR(LogicError, std::string("inconsistent handshake from the peer: ") + ex.what()));
+          }
         }));
   } else if (state_ == SERVER_WAITING_FOR_BROCHURE) {
     transport::readNop<Brochure>(
         *descriptorConnection_, callbackWrapper_([](PipeImpl& impl, Brochure brochure) {
-          if (!impl.error_) impl.onReadWhileServerWaitingForBrochure(brochure);
+          if (impl.error_) return;
+          try {
+            impl.onReadWhileServerWaitingForBrochure(brochure);
+          } catch (const std::exception& ex) {
+            impl.setError(TPB_CREATE_ERROR(LogicError, std::string("inconsistent handshake from the peer: ") + ex.what()));
+          }
         }));
   }
 }
@@ -326,7 +338,13 @@ bool PipeImpl::channelSupportsLayouts(const Device& local, const Device& remote)
 // ---- user operations ------------------------------------------------------------------------
 void PipeImpl::readDescriptor(Pipe::read_descriptor_callback_fn fn) {
   auto self = shared_from_this();
-  context_->deferToLoop([self, fn = std::move(fn)]() mutable { self->readDescriptorFromLoop(std::move(fn)); });
+  context_->deferToLoop([self, fn = std::move(fn)]() mutable {
+    try {
+      self->readDescriptorFromLoop(std::move(fn));
+    } catch (const std::exception& ex) {
+      self->setError(TPB_CREATE_ERROR(LogicError, ex.what()));
+    }
+  });
 }
 
 void PipeImpl::readDescriptorFromLoop(Pipe::read_descriptor_callback_fn fn) {
@@ -365,13 +383,26 @@ void PipeImpl::readFromLoop(Allocation allocation, Pipe::read_callback_fn fn) {
   // Never call back from inside read(): advance from a fresh loop iteration.
   auto self = shared_from_this();
   int64_t seq = op->sequenceNumber;
-  context_->deferToLoop([self, seq]() { self->readOps_.advanceOperation(seq); });
+  context_->deferToLoop([self, seq]() {
+    try {
+      self->readOps_.advanceOperation(seq);
+    } catch (const std::exception& ex) {
+      // E.g. a tensor between devices that no registered channel connects.
+      self->setError(TPB_CREATE_ERROR(LogicError, ex.what()));
+    }
+  });
 }
 
 void PipeImpl::write(Message message, Pipe::write_callback_fn fn) {
   auto self = shared_from_this();
   context_->deferToLoop([self, message = std::move(message), fn = std::move(fn)]() mutable {
-    self->writeFromLoop(std::move(message), std::move(fn));
+    try {
+      self->writeFromLoop(std::move(message), std::move(fn));
+    } catch (const std::exception& ex) {
+      // E.g. a tensor on a device pair no registered channel serves: the pipe fails, the write's
+      // callback (already queued) reports it.
+      self->setError(TPB_CREATE_ERROR(LogicError, ex.what()));
+    }
   });
 }
 

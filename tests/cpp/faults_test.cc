@@ -269,3 +269,83 @@ TPB_TEST(Faults, ScrambledFramesAtAnyPointNeverCrashThePeer) {
     server.reset();
   }
 }
+
+// A peer that speaks the wire format but answers the handshake with nonsense (here: a raw socket
+// playing server and naming a transport nobody registered) fails the pipe with an error; it does
+// not take the process down.
+#include <arpa/inet.h>
+#include <netinet/in.h>
+#include <sys/socket.h>
+#include <unistd.h>
+
+#include "common/nop.h"
+#include "core/nop_types.h"
+
+namespace {
+bool readFully(int fd, void* p, size_t n) {
+  auto* b = static_cast<uint8_t*>(p);
+  while (n > 0) {
+    ssize_t got = ::read(fd, b, n);
+    if (got <= 0) return false;
+    b += got;
+    n -= static_cast<size_t>(got);
+  }
+  return true;
+}
+bool readFrame(int fd, std::vector<uint8_t>& out) {
+  uint64_t len = 0;
+  if (!readFully(fd, &len, sizeof(len)) || len > (1u << 20)) return false;
+  out.resize(len);
+  return len == 0 || readFully(fd, out.data(), len);
+}
+bool writeFrame(int fd, const std::vector<uint8_t>& bytes) {
+  const uint64_t len = bytes.size();
+  return ::write(fd, &len, sizeof(len)) == ssize_t(sizeof(len)) &&
+      ::write(fd, bytes.data(), bytes.size()) == ssize_t(bytes.size());
+}
+}  // namespace
+
+TPB_TEST(Faults, NonsenseHandshakeAnswerFailsThePipeNotTheProcess) {
+  int listenFd = ::socket(AF_INET, SOCK_STREAM, 0);
+  EXPECT_TRUE(listenFd >= 0);
+  sockaddr_in sa{};
+  sa.sin_family = AF_INET;
+  sa.sin_port = 0;
+  ::inet_pton(AF_INET, "127.0.0.1", &sa.sin_addr);
+  EXPECT_EQ(::bind(listenFd, reinterpret_cast<sockaddr*>(&sa), sizeof(sa)), 0);
+  EXPECT_EQ(::listen(listenFd, 4), 0);
+  socklen_t len = sizeof(sa);
+  EXPECT_EQ(::getsockname(listenFd, reinterpret_cast<sockaddr*>(&sa), &len), 0);
+  const int port = ntohs(sa.sin_port);
+
+  std::thread fakeServer([&]() {
+    int fd = ::accept(listenFd, nullptr, nullptr);
+    if (fd < 0) return;
+    std::vector<uint8_t> hello, brochure;
+    if (readFrame(fd, hello) && readFrame(fd, brochure)) {
+      BrochureAnswer answer;
+      answer.transport = "carrier-pigeon";  // nobody registered this
+      answer.address = "127.0.0.1:1";
+      answer.transportRegistrationIds[0] = 1;
+      answer.transportRegistrationIds[1] = 2;
+      writeFrame(fd, nop::encode(answer));
+    }
+    // Hold the connection until the client has reacted, then hang up.
+    std::vector<uint8_t> rest;
+    readFrame(fd, rest);
+    ::close(fd);
+  });
+
+  auto ctx = plain("client");
+  auto pipe = ctx->connect("uv://127.0.0.1:" + std::to_string(port));
+  std::promise<Error> w;
+  pipe->write(Message(), [&](const Error& e) { w.set_value(e); });
+  auto fw = w.get_future();
+  Error e = waitFor(fw);
+  EXPECT_TRUE(bool(e));
+  EXPECT_TRUE(e.what().find("inconsistent handshake") != std::string::npos);
+  pipe->close();
+  ctx->join();
+  fakeServer.join();
+  ::close(listenFd);
+}

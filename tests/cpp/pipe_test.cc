@@ -466,3 +466,40 @@ TPB_TEST(Pipe, DeadlinesFailASilentPeerAndSpareAPromptOne) {
   EXPECT_TRUE(timedOut.load());
   EXPECT_TRUE(laterAlsoFailed.load());
 }
+
+// A tensor between devices that no registered channel connects (a CUDA buffer on contexts that
+// only know CPU channels) fails the pipe on both ends with a logic error; nothing is thrown on
+// the callback thread, where an exception would end the process.
+TPB_TEST(Pipe, TensorWithoutASuitableChannelFailsThePipe) {
+  static uint8_t fakeDeviceMemory[64];
+  std::atomic<bool> writerFailed{false}, readerFailed{false};
+  runPair(
+      [&](Pipe& p) {
+        std::promise<Error> done;
+        p.readDescriptor([&](const Error& e, Descriptor d) {
+          if (e) return done.set_value(e);
+          Allocation a;
+          Allocation::Tensor t;
+          t.buffer = CpuBuffer{fakeDeviceMemory};
+          a.tensors.push_back(t);
+          p.read(std::move(a), [&](const Error& e2) { done.set_value(e2); });
+        });
+        auto f = done.get_future();
+        readerFailed = bool(waitFor(f));
+      },
+      [&](Pipe& p) {
+        Message m;
+        Message::Tensor t;
+        t.buffer = CudaBuffer{fakeDeviceMemory, nullptr, 0};  // never dereferenced: no CUDA channel exists here
+        t.length = sizeof(fakeDeviceMemory);
+        t.targetDevice = Device(kCpuDeviceType, 0);
+        m.tensors.push_back(t);
+        std::promise<Error> done;
+        p.write(std::move(m), [&](const Error& e) { done.set_value(e); });
+        auto f = done.get_future();
+        Error e = waitFor(f);
+        writerFailed = e.isOfType<LogicError>();
+      });
+  EXPECT_TRUE(writerFailed.load());
+  EXPECT_TRUE(readerFailed.load());
+}

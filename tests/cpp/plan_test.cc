@@ -145,3 +145,38 @@ TPB_TEST(Plan, CastTableAndSizes) {
   EXPECT_EQ(int(patternByte(7, 5)), int(patternByte(7, 5)));
   EXPECT_TRUE(patternByte(7, 0) != patternByte(8, 0) || patternByte(7, 1) != patternByte(8, 1));
 }
+
+TPB_TEST(Plan, NarrowMatricesFollowTheDestinationAndTheTuning) {
+  auto kindOf = [](bool remote) {
+    PushPlan plan;
+    CopyItem v = contiguous(0x30000000, 0x40000000, 1000 * 64 * 4);
+    v.srcDtype = v.dstDtype = DType::kF32;
+    v.strided = true;
+    v.view = StridedView{DType::kF32, 1000, 64, 1, 1000};
+    v.remote = remote;
+    appendToPlan(plan, v, true);
+    return int(plan.entries.back().kind);
+  };
+  const PushTuning before = getPushTuning();
+  PushTuning t = before;
+  t.narrowRows = 1;  // the default: whole packed rows only towards another GPU
+  setPushTuning(t);
+  EXPECT_EQ(kindOf(true), int(kStridedNarrow));
+  EXPECT_EQ(kindOf(false), int(kStrided));
+  t.narrowRows = 0;
+  setPushTuning(t);
+  EXPECT_EQ(kindOf(true), int(kStrided));
+  t.narrowRows = 2;
+  setPushTuning(t);
+  EXPECT_EQ(kindOf(false), int(kStridedNarrow));
+  setPushTuning(before);
+  // 1000 rows in tiles of 32 whole rows.
+  PushPlan plan;
+  CopyItem v = contiguous(0x30000000, 0x40000000, 1000 * 64 * 4);
+  v.srcDtype = v.dstDtype = DType::kF32;
+  v.strided = true;
+  v.view = StridedView{DType::kF32, 1000, 64, 1, 1000};
+  v.remote = true;
+  appendToPlan(plan, v, true);
+  EXPECT_EQ(plan.entries.back().numTiles, uint32_t(32));
+}

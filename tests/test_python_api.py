@@ -137,3 +137,26 @@ def test_tensor_metadata_fast_path_agrees_with_json(built):
                     b'[1, 2]', b'{"dtype": 3, "shape": [1]}']:
         got = _parse_tensor_metadata(foreign)
         assert got is None or got == ("x", [1, "a"])
+
+
+def test_trace_from_the_environment_is_written_at_exit(built, tmp_path):
+    import json
+    import os
+    import subprocess
+    import sys
+    pattern = str(tmp_path / "trace.%p.json")
+    code = (
+        "import torch, tensorpipe_b200 as tpb\n"
+        "a = tpb.default_context('a', cuda=False); b = tpb.default_context('b', cuda=False)\n"
+        "l = a.listen(['uv://127.0.0.1']); f = l.accept_future()\n"
+        "o = b.connect(l.url('uv')); i = f.result(30)\n"
+        "s = o.send([torch.ones(4)]); i.recv().result(30); s.result(30)\n"
+        "a.join(); b.join()\n")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = {**os.environ, "TPB_TRACE": pattern, "PYTHONPATH": root}
+    proc = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=120)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    files = [p for p in os.listdir(tmp_path) if p.startswith("trace.") and p.endswith(".json")]
+    assert len(files) == 1 and "%p" not in files[0]  # the process id took the place of %p
+    names = {e["name"] for e in json.load(open(tmp_path / files[0]))}
+    assert {"pipe.write", "pipe.write.done", "pipe.readDescriptor", "pipe.read", "pipe.read.done"} <= names

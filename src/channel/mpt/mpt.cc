@@ -303,6 +303,33 @@ void ChannelImpl::closeFromLoop(const Error& e) {
   for (auto& op : queued) op.cb(error_);
 }
 
+// What the user holds. The implementation is kept alive by the accept callbacks armed on its
+// lanes, so without this its last reference could die on a lane's own I/O thread, whose
+// destructor would then try to join itself. Dropping the shell joins from the caller's thread.
+class ContextShell final : public Context {
+ public:
+  explicit ContextShell(std::shared_ptr<ContextImpl> impl) : impl_(std::move(impl)) {}
+  ~ContextShell() override { impl_->join(); }
+  bool isViable() const override { return impl_->isViable(); }
+  size_t numConnectionsNeeded() const override { return impl_->numConnectionsNeeded(); }
+  const std::unordered_map<Device, std::string>& deviceDescriptors() const override {
+    return impl_->deviceDescriptors();
+  }
+  bool canCommunicateWithRemote(const std::string& local, const std::string& remote) const override {
+    return impl_->canCommunicateWithRemote(local, remote);
+  }
+  std::shared_ptr<Channel> createChannel(std::vector<std::shared_ptr<transport::Connection>> connections,
+                                         Endpoint endpoint) override {
+    return impl_->createChannel(std::move(connections), endpoint);
+  }
+  void setId(std::string id) override { impl_->setId(std::move(id)); }
+  void close() override { impl_->close(); }
+  void join() override { impl_->join(); }
+
+ private:
+  std::shared_ptr<ContextImpl> impl_;
+};
+
 }  // namespace
 
 std::shared_ptr<Context> create(std::vector<std::shared_ptr<transport::Context>> contexts,
@@ -312,7 +339,7 @@ std::shared_ptr<Context> create(std::vector<std::shared_ptr<transport::Context>>
     if (!c->isViable()) return std::make_shared<NonViableContext>();
   auto ctx = std::make_shared<ContextImpl>(std::move(contexts), std::move(listeners));
   ctx->start();
-  return ctx;
+  return std::make_shared<ContextShell>(std::move(ctx));
 }
 
 }  // namespace mpt

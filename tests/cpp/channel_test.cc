@@ -470,3 +470,22 @@ TPB_TEST(Channel, CudaP2pOptionsFollowTheEnvironment) {
   p2p::Options d = p2p::applyEnvironment(p2p::Options());
   EXPECT_EQ(d.eagerThreshold, size_t(64 * 1024));
 }
+
+// Every channel context can be dropped without join(): its destructor closes and joins on its
+// own (reference case: mpt ContextIsNotJoined, tensorpipe/test/channel/mpt/mpt_test.cc:17-109;
+// here for every CPU backend, with and without a channel having existed).
+TPB_TEST(Channel, ContextsCanBeDroppedWithoutJoin) {
+  for (const Backend& b : kBackends) {
+    {
+      auto ctx = b.make();
+      (void)ctx->isViable();
+    }  // never used, never joined
+    {
+      auto ctx = b.make();
+      if (!ctx->isViable()) continue;
+      auto descriptors = ctx->deviceDescriptors();
+      EXPECT_FALSE(descriptors.empty());
+      ctx->close();
+    }  // closed but not joined
+  }
+}

@@ -503,3 +503,62 @@ TPB_TEST(Pipe, TensorWithoutASuitableChannelFailsThePipe) {
   EXPECT_TRUE(writerFailed.load());
   EXPECT_TRUE(readerFailed.load());
 }
+
+// The client pings, the server answers, several times in a row on one pipe: once with the
+// client waiting for each answer before the next ping, once with every step issued from inside
+// the previous step's callback (nothing may run inline, or this recursion would nest).
+// (Reference cases: Context.ClientPingSerial / ClientPingInline, tensorpipe/test/core/context_test.cc.)
+TPB_TEST(Context, ClientPingSerialAndFromInsideCallbacks) {
+  auto ping = makeMessage(21, {32}, {128, 4096});
+  constexpr int kRounds = 5;
+  runPair(
+      [&](Pipe& p) {
+        for (int i = 0; i < 2 * kRounds; ++i) {
+          expectSame(ping, readSync(p));
+          writeSync(p, ping.view(false));
+        }
+      },
+      [&](Pipe& p) {
+        for (int i = 0; i < kRounds; ++i) {
+          writeSync(p, ping.view(false));
+          expectSame(ping, readSync(p));
+        }
+        // Now the same conversation as a chain of callbacks.
+        std::promise<Error> finished;
+        std::atomic<int> depth{0}, maxDepth{0};
+        std::vector<std::vector<uint8_t>> payloadIn(ping.payloads.size()), tensorIn(ping.tensors.size());
+        std::function<void(int)> round = [&](int left) {
+          if (left == 0) return finished.set_value(Error::kSuccess);
+          p.write(ping.view(false), [&, left](const Error& e) {
+            if (e) return finished.set_value(e);
+            int d = ++depth;
+            if (d > maxDepth) maxDepth = d;
+            p.readDescriptor([&, left](const Error& e2, Descriptor desc) {
+              if (e2) return finished.set_value(e2);
+              Allocation a;
+              for (size_t i = 0; i < desc.payloads.size(); ++i) {
+                payloadIn[i].resize(desc.payloads[i].length);
+                a.payloads.push_back({payloadIn[i].data()});
+              }
+              for (size_t i = 0; i < desc.tensors.size(); ++i) {
+                tensorIn[i].resize(desc.tensors[i].length);
+                Allocation::Tensor t;
+                t.buffer = CpuBuffer{tensorIn[i].data()};
+                a.tensors.push_back(t);
+              }
+              p.read(std::move(a), [&, left](const Error& e3) {
+                if (e3) return finished.set_value(e3);
+                round(left - 1);
+              });
+            });
+            --depth;
+          });
+        };
+        round(kRounds);
+        auto f = finished.get_future();
+        Error e = waitFor(f);
+        EXPECT_FALSE(bool(e));
+        EXPECT_EQ(maxDepth.load(), 1);  // callbacks never nested
+        EXPECT_TRUE(tensorIn.back() == ping.tensors.back());
+      });
+}

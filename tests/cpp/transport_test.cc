@@ -399,3 +399,33 @@ TPB_TEST(TransportUv, AbsurdFrameLengthFailsTheConnectionNotTheProcess) {
   ::close(fd);
   ctx->join();
 }
+
+// Transport contexts can be dropped without join() in every state: unused, listening, with a
+// connection up and operations pending. The destructor joins from the caller's thread.
+TPB_TEST(Transport, ContextsCanBeDroppedWithoutJoin) {
+  for (bool shm : {false, true}) {
+    auto make = [&]() { return shm ? transport::shm::create() : transport::uv::create(); };
+    const std::string listenAddr = shm ? std::string("tpb-drop-test-") + std::to_string(::getpid()) : "127.0.0.1";
+    { auto ctx = make(); }
+    {
+      auto ctx = make();
+      if (!ctx->isViable()) continue;
+      auto l = ctx->listen(listenAddr);
+      l->accept([](const Error&, std::shared_ptr<transport::Connection>) {});
+    }
+    {
+      auto ctx = make();
+      auto l = ctx->listen(listenAddr);
+      auto c = ctx->connect(l->addr());
+      auto s = acceptSync(*l);
+      std::atomic<int> called{0};
+      s->read([&](const Error&, const void*, size_t) { ++called; });
+      c->write("abc", 3, [&](const Error&) { ++called; });
+      c.reset();
+      s.reset();
+      l.reset();
+      ctx.reset();  // joins: both callbacks have fired by now, with data or with an error
+      EXPECT_EQ(called.load(), 2);
+    }
+  }
+}

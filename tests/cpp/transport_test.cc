@@ -429,3 +429,33 @@ TPB_TEST(Transport, ContextsCanBeDroppedWithoutJoin) {
     }
   }
 }
+
+// A listener still knows its address after it was closed, and one created on a context that was
+// already closed can still be asked for it (reference cases Listener_CreateThenCloseAndThenGetAddress
+// and Listener_CreateAfterClosingContextAndThenGetAddress, tensorpipe/test/transport/listener_test.cc).
+TPB_TEST(Transport, ListenerAddressSurvivesClose) {
+  {
+    auto ctx = transport::uv::create();
+    auto l = ctx->listen("127.0.0.1");
+    const std::string before = l->addr();
+    l->close();
+    EXPECT_EQ(l->addr(), before);
+    EXPECT_TRUE(before.rfind("127.0.0.1:", 0) == 0);
+    ctx->join();
+    EXPECT_EQ(l->addr(), before);
+  }
+  {
+    auto ctx = transport::uv::create();
+    ctx->close();
+    bool threw = false;
+    std::string addr;
+    try {
+      auto l = ctx->listen("127.0.0.1");
+      addr = l->addr();
+    } catch (const std::exception&) {
+      threw = true;  // refusing to listen on a closed context is as good an answer
+    }
+    EXPECT_TRUE(threw || !addr.empty());
+    ctx->join();
+  }
+}

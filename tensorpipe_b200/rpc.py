@@ -66,6 +66,30 @@ def _loads(data: bytes, tensors: List[torch.Tensor]) -> Any:
     return _TensorUnpickler(io.BytesIO(data), tensors).load()
 
 
+def send_object(pipe: Pipe, obj: Any, target_device: Optional[str] = None) -> Future:
+    """Send any picklable object over a pipe. Tensors inside it (at any depth) travel as message
+    tensors over the best channel instead of through pickle; `target_device` ("cuda:1", "cpu")
+    names where the receiver wants them, otherwise the receiver decides."""
+    payload, tensors = _dumps(obj)
+    targets = [target_device] * len(tensors) if target_device else None
+    return pipe.send(tensors, [payload], b"O", target_devices=targets)
+
+
+def recv_object(pipe: Pipe, device: Optional[str] = None) -> Future:
+    """The counterpart of send_object: a future of the object, tensors rebuilt in place."""
+    out: Future = Future()
+
+    def done(fut: Future) -> None:
+        try:
+            msg = fut.result()
+            out.set_result(_loads(bytes(msg.payloads[0]), msg.tensors))
+        except Exception as exc:  # noqa: BLE001
+            out.set_exception(exc)
+
+    pipe.recv(device=device).add_done_callback(done)
+    return out
+
+
 class RRef:
     """Handle on a value that lives on its owner (what `remote` returns)."""
 

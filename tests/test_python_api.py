@@ -160,3 +160,18 @@ def test_trace_from_the_environment_is_written_at_exit(built, tmp_path):
     assert len(files) == 1 and "%p" not in files[0]  # the process id took the place of %p
     names = {e["name"] for e in json.load(open(tmp_path / files[0]))}
     assert {"pipe.write", "pipe.write.done", "pipe.readDescriptor", "pipe.read", "pipe.read.done"} <= names
+
+
+def test_objects_with_tensors_inside(built):
+    from tensorpipe_b200 import rpc
+    a, b, listener, out_pipe, in_pipe = connected_pair(cuda=False)
+    obj = {"step": 7, "weights": [torch.arange(6.0).reshape(2, 3), torch.ones(4, dtype=torch.int64)],
+           "nested": ("text", {"t": torch.full((3,), 2.5)})}
+    sent = rpc.send_object(out_pipe, obj)
+    got = rpc.recv_object(in_pipe).result(30)
+    sent.result(30)
+    assert got["step"] == 7 and got["nested"][0] == "text"
+    assert torch.equal(got["weights"][0], obj["weights"][0]) and torch.equal(got["weights"][1], obj["weights"][1])
+    assert torch.equal(got["nested"][1]["t"], torch.full((3,), 2.5))
+    a.join()
+    b.join()

@@ -15,7 +15,9 @@
 
 namespace tpb {
 
-class ContextImpl;
+namespace core {
+class ContextCore;
+}
 
 class ContextOptions {
  public:
@@ -68,7 +70,7 @@ class Context final {
   ~Context();
 
  private:
-  std::shared_ptr<ContextImpl> impl_;
+  std::shared_ptr<core::ContextCore> impl_;
 };
 
 }  // namespace tpb

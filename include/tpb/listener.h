@@ -13,15 +13,17 @@
 
 namespace tpb {
 
-class ContextImpl;
-class ListenerImpl;
+namespace core {
+class ContextCore;
+class ListenerCore;
+}  // namespace core
 
 class Listener final {
   enum ConstructorToken { kToken };
 
  public:
-  Listener(ConstructorToken, std::shared_ptr<ContextImpl> context, std::string id,
-           const std::vector<std::string>& urls);
+  // Only a context creates listeners.
+  Listener(ConstructorToken, std::shared_ptr<core::ListenerCore> impl);
 
   using accept_callback_fn = std::function<void(const Error&, std::shared_ptr<Pipe>)>;
   // One-shot: re-arm to accept the next pipe. Unclaimed pipes queue up.
@@ -37,8 +39,8 @@ class Listener final {
   ~Listener();
 
  private:
-  std::shared_ptr<ListenerImpl> impl_;
-  friend class ContextImpl;
+  std::shared_ptr<core::ListenerCore> impl_;
+  friend class core::ContextCore;
 };
 
 }  // namespace tpb

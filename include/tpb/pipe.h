@@ -14,9 +14,11 @@
 
 namespace tpb {
 
-class ContextImpl;
-class ListenerImpl;
-class PipeImpl;
+namespace core {
+class ContextCore;
+class ListenerCore;
+class PipeCore;
+}  // namespace core
 
 // Optional deadlines (not in the reference, where a silent peer hangs an operation forever).
 // Zero means "wait forever". When a deadline passes the pipe fails with TimeoutError: the late
@@ -32,9 +34,7 @@ class Pipe final {
   enum ConstructorToken { kToken };
 
  public:
-  Pipe(ConstructorToken, std::shared_ptr<ContextImpl> context, std::string id,
-       std::string remoteName, const std::string& url);
-  Pipe(ConstructorToken, std::shared_ptr<PipeImpl> impl);
+  Pipe(ConstructorToken, std::shared_ptr<core::PipeCore> impl);
 
   using read_descriptor_callback_fn = std::function<void(const Error&, Descriptor)>;
   using read_callback_fn = std::function<void(const Error&)>;
@@ -63,9 +63,9 @@ class Pipe final {
   ~Pipe();
 
  private:
-  std::shared_ptr<PipeImpl> impl_;
-  friend class ContextImpl;
-  friend class ListenerImpl;
+  std::shared_ptr<core::PipeCore> impl_;
+  friend class core::ContextCore;
+  friend class core::ListenerCore;
 };
 
 }  // namespace tpb

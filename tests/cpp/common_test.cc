@@ -1,14 +1,14 @@
 // Unit tests of the common runtime: byte ring (wrap-around, partial reads and writes, a forked
-// producer), ordered operation queue, rearmable callbacks, the on-demand loop, the completion
+// producer), the backend registry, the on-demand loop, the completion
 // poller, system probes. (Reference counterparts: tensorpipe/test/common/ringbuffer_test.cc,
 // shm_ringbuffer_test.cc, epoll_loop_test.cc.)
 #include <atomic>
 #include <random>
 
-#include "common/callback.h"
 #include "common/epoll_loop.h"
 #include "common/loop.h"
-#include "common/ops.h"
+#include "common/url.h"
+#include "core/backends.h"
 #include "common/poller.h"
 #include "common/ringbuffer.h"
 #include "common/shm_segment.h"
@@ -90,55 +90,44 @@ TPB_TEST(Common, ShmSegmentIsSharedThroughItsFd) {
 }
 
 namespace {
-struct TestOp {
-  enum State { UNINITIALIZED, STARTED, FINISHED };
-  int64_t sequenceNumber = -1;
-  State state = UNINITIALIZED;
-  bool ready = false;
+struct FakeBackend {
+  explicit FakeBackend(bool viable) : viable(viable) {}
+  bool isViable() const { return viable; }
+  bool viable;
 };
 }  // namespace
 
-TPB_TEST(Common, OpQueueFinishesInOrderEvenWhenLaterOpsAreReadyFirst) {
-  std::vector<int64_t> finished;
-  OpQueue<TestOp>* qp = nullptr;
-  OpQueue<TestOp> q([&](TestOp& op, TestOp::State prev) {
-    OpQueue<TestOp>::attemptTransition(op, TestOp::UNINITIALIZED, TestOp::STARTED, prev >= TestOp::STARTED);
-    OpQueue<TestOp>::attemptTransition(op, TestOp::STARTED, TestOp::FINISHED, op.ready && prev == TestOp::FINISHED,
-                                       [&]() { finished.push_back(op.sequenceNumber); });
-  });
-  qp = &q;
-  (void)qp;
-  for (int i = 0; i < 4; ++i) q.advanceOperation(q.emplaceBack());
-  EXPECT_EQ(q.size(), size_t(4));
-  // Later operations become ready first: nothing may finish before operation 0.
-  for (int64_t seq : {3, 1, 2}) {
-    q.findOperation(seq)->ready = true;
-    q.advanceOperation(seq);
-  }
-  EXPECT_TRUE(finished.empty());
-  q.findOperation(0)->ready = true;
-  q.advanceOperation(0);
-  EXPECT_EQ(finished.size(), size_t(4));
-  for (int i = 0; i < 4; ++i) EXPECT_EQ(finished[i], int64_t(i));
-  EXPECT_TRUE(q.empty());
-  EXPECT_TRUE(q.findOperation(2) == nullptr);
+TPB_TEST(Common, BackendsAreKeptBestFirstAndRefuseDuplicates) {
+  core::Backends<FakeBackend> reg("backend");
+  EXPECT_TRUE(reg.add(10, "mid", std::make_shared<FakeBackend>(true)));
+  EXPECT_TRUE(reg.add(-5, "low", std::make_shared<FakeBackend>(true)));
+  EXPECT_TRUE(reg.add(400, "top", std::make_shared<FakeBackend>(true)));
+  // not viable: skipped without an error, and its name and priority stay free
+  EXPECT_FALSE(reg.add(50, "broken", std::make_shared<FakeBackend>(false)));
+  EXPECT_TRUE(reg.find("broken") == nullptr);
+  EXPECT_TRUE(reg.add(50, "fine", std::make_shared<FakeBackend>(true)));
+  std::vector<std::string> order;
+  for (const auto& slot : reg.bestFirst()) order.push_back(slot.name);
+  EXPECT_EQ(order.size(), size_t(4));
+  EXPECT_EQ(order[0], std::string("top"));
+  EXPECT_EQ(order[1], std::string("fine"));
+  EXPECT_EQ(order[2], std::string("mid"));
+  EXPECT_EQ(order[3], std::string("low"));
+  EXPECT_THROWS(reg.add(7, "mid", std::make_shared<FakeBackend>(true)));    // name taken
+  EXPECT_THROWS(reg.add(10, "other", std::make_shared<FakeBackend>(true))); // priority taken
+  EXPECT_THROWS(reg.add(1, "", std::make_shared<FakeBackend>(true)));
+  EXPECT_THROWS(reg.require("nobody"));
+  EXPECT_TRUE(reg.require("low") != nullptr);
 }
 
-TPB_TEST(Common, RearmableCallbackPairsEitherOrder) {
-  RearmableCallback<int, std::string> cb;
-  std::vector<std::pair<int, std::string>> seen;
-  cb.trigger(1, "early");  // result first: stored
-  EXPECT_EQ(cb.numStored(), size_t(1));
-  cb.arm([&](int a, std::string s) { seen.emplace_back(a, s); });
-  EXPECT_EQ(seen.size(), size_t(1));
-  cb.arm([&](int a, std::string s) { seen.emplace_back(a, s); });  // callback first: stored
-  EXPECT_EQ(cb.numArmed(), size_t(1));
-  cb.trigger(2, "late");
-  EXPECT_EQ(seen.size(), size_t(2));
-  EXPECT_EQ(seen[1].second, std::string("late"));
-  cb.arm([&](int a, std::string s) { seen.emplace_back(a, s); });
-  cb.triggerAll([] { return std::make_tuple(-1, std::string("closed")); });
-  EXPECT_EQ(seen.back().first, -1);
+TPB_TEST(Common, UrlSplitsAtTheScheme) {
+  auto [scheme, rest] = splitSchemeOfURL("shm://some/name");
+  EXPECT_EQ(scheme, std::string("shm"));
+  EXPECT_EQ(rest, std::string("some/name"));
+  auto [s2, r2] = splitSchemeOfURL("uv://[::1]:80");
+  EXPECT_EQ(s2, std::string("uv"));
+  EXPECT_EQ(r2, std::string("[::1]:80"));
+  EXPECT_THROWS(splitSchemeOfURL("no-scheme-here"));
 }
 
 TPB_TEST(Common, OnDemandLoopRunsOneTaskAtATimeAndNeverNests) {

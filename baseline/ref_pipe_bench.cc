@@ -111,8 +111,10 @@ struct Bench {
   }
 
   // The sizes of the 64-tensor mixed message as delivered: dtype cycles fp32, bf16, int64; sizes
-  // log-uniform in [1 KiB, 16 MiB] rounded to rows of 64 elements; every other fp32 tensor arrives
-  // as bf16. Same generator and seed as the native benchmark, so both sides move the same bytes.
+  // log-uniform in [1 KiB, 16 MiB] rounded to whole rows (64 columns, or for every fourth tensor a
+  // column count log-uniform in [8, 4096], the transposed views of the native message); every other
+  // fp32 tensor arrives as bf16. Same generator and seed as the native benchmark, so both sides
+  // move the same bytes.
   static std::vector<Segment> mixedSegments(uint64_t seed, size_t* delivered) {
     std::vector<Segment> segs;
     std::mt19937_64 rng(seed);
@@ -124,8 +126,13 @@ struct Bench {
       const double lg = std::log(1024.0) + (std::log(16.0 * 1024 * 1024) - std::log(1024.0)) *
                                                 (static_cast<double>(rng() % 100000) / 100000.0);
       const uint64_t bytes = static_cast<uint64_t>(std::exp(lg));
-      const uint64_t rows = std::max<uint64_t>(1, bytes / es / 64);
-      const uint64_t elems = rows * 64;
+      uint64_t cols = 64;
+      if (i % 4 == 3) {
+        const double lc = std::log(8.0) + (std::log(4096.0) - std::log(8.0)) * (static_cast<double>(rng() % 100000) / 100000.0);
+        cols = static_cast<uint64_t>(std::exp(lc));
+      }
+      const uint64_t rows = std::max<uint64_t>(1, bytes / es / cols);
+      const uint64_t elems = rows * cols;
       bool cast = false;
       if (es == 4) cast = (fp32Count++ % 2) == 0;
       const size_t out = cast ? elems * 2 : elems * es;

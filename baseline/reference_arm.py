@@ -119,7 +119,7 @@ def main(args, metric):
     import torch
     import torch.distributed as dist
     sys.path.insert(0, REPO)
-    from bench import ClockSampler, percentile
+    from bench import ClockSampler, bench_config, messages_per_step, percentile
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
@@ -163,17 +163,18 @@ def main(args, metric):
         sys.exit(0)
 
     try:
-        h.command(f"stream {args.bytes} {max(args.warmup, 3)} {args.depth}")
+        burst = messages_per_step(args.bytes, args.steps)
+        h.command(f"stream {args.bytes} {max(args.warmup, 3) * burst} {args.depth}", timeout=900)
         barrier()
         sampler = ClockSampler(local_rank)
         if rank == 0:
             sampler.start()
-        ms = float(h.command(f"stream {args.bytes} {args.steps} {args.depth}")[0])
+        ms = float(h.command(f"stream {args.bytes} {args.steps * burst} {args.depth}", timeout=1800)[0])
         barrier()
         clocks = sampler.stop() if rank == 0 else None
         ms = max_over_ranks(ms)
         ms_per_step = ms / args.steps
-        value = world * args.bytes / (ms_per_step * 1e-3) / 1e9
+        value = world * burst * args.bytes / (ms_per_step * 1e-3) / 1e9
 
         sweep = []
         if not args.no_sweep:
@@ -245,11 +246,9 @@ def main(args, metric):
             "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 5), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "reference",
             "reference_build": "TensorPipe as bundled in PyTorch (torch/include/tensorpipe, libtorch_cpu/cuda)",
-            "config": {"model": "pipe ring: 1 bf16 tensor per message", "global_batch": world,
-                       "seq_len": args.bytes // 2, "bytes_per_message": args.bytes,
-                       "parallelism": f"ring{world}" if world > 1 else "loopback (two pipes, one process, one GPU)",
-                       "l2": "inputs larger than L2 (no flush)", "writes_in_flight": args.depth,
-                       "channels": "cuda_xth (same process) / cuda_ipc (other process) / cuda_basic"},
+            "config": bench_config(args, world, burst),
+            "data_path": "cuda_xth (same process) / cuda_ipc (other process) / cuda_basic: cudaMemcpyAsync",
+            "timed_region_s": round(ms * 1e-3, 4),
             "clocks": clocks, "gpu_launches": 0, "e2e": e2e, "sweep": sweep, "latency": latency,
             "mixed_64_tensor_message": mixed,
         }

@@ -1,11 +1,13 @@
 #!/usr/bin/env python
 """Headline benchmark: pipe GPU->GPU throughput and small-message latency.
 
-One step = every rank sends one bf16 tensor of `--bytes` (default 256 MiB, larger than L2, so no
-L2 flush is needed) through a Pipe to the next rank of a ring and receives one from the previous
-rank; with one GPU the two pipe ends live in one process on the same device. The value is the
-whole-job aggregate GB/s (N x bytes / step time), timed on the device with CUDA events, max over
-ranks. Also reported: a size sweep from 4 KiB to 1 GiB, p50/p99 small-message latency, the
+One message = every rank sends one bf16 tensor of `--bytes` (default 256 MiB, larger than L2, so
+no L2 flush is needed) through a Pipe to the next rank of a ring and receives one from the previous
+rank; with one GPU the two pipe ends live in one process on the same device. One step is a burst
+of M such messages back to back (M depends only on the message size and on --steps, is the same
+for both arms and is printed in `config`), so that the timed region lasts a quarter of a second
+or more whatever --steps is. The value is the whole-job aggregate GB/s (N x M x bytes / step
+time), timed on the device with CUDA events, max over ranks. Also reported: a size sweep from 4 KiB to 1 GiB, p50/p99 small-message latency, the
 64-tensor mixed-dtype message, and an end-to-end number through the Python API that includes a
 host->device copy of every step's input from pinned memory and a device->host read of a checksum.
 
@@ -162,6 +164,22 @@ class ClockSampler:
         }
 
 
+def messages_per_step(nbytes, steps):
+    """Messages in one step: enough that `steps` steps last at least a quarter of a second at the
+    fastest rate any arm reaches (a loopback copy at 3.3 TB/s plus 5 us per message)."""
+    import math
+    fastest = 5e-6 + nbytes / 3.3e12
+    return max(1, min(4096, math.ceil(0.25 / (max(steps, 1) * fastest))))
+
+
+def bench_config(args, world, burst):
+    """The `config` object of the JSON line; identical for both arms."""
+    return {"model": "pipe ring: 1 bf16 tensor per message", "global_batch": world,
+            "seq_len": args.bytes // 2, "bytes_per_message": args.bytes, "messages_per_step": burst,
+            "parallelism": f"ring{world}" if world > 1 else "loopback (two pipes, one process, one GPU)",
+            "l2": "inputs larger than L2 (no flush)", "writes_in_flight": args.depth}
+
+
 def percentile(samples, q):
     if not samples:
         return None
@@ -257,20 +275,21 @@ def run_native(args):
             raise SystemExit(f"verification failed at {size} bytes: {res.mismatches} bytes differ")
     barrier()
 
-    # Headline: W warm-up steps, then exactly K timed steps.
-    rb.run_stream(args.bytes, max(args.warmup, 3), args.depth, False)
+    # Headline: W warm-up steps, then exactly K timed steps of `burst` messages each.
+    burst = messages_per_step(args.bytes, args.steps)
+    rb.run_stream(args.bytes, max(args.warmup, 3) * burst, args.depth, False)
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     launches_before = _C.kernel_launch_count()
-    res = rb.run_stream(args.bytes, args.steps, args.depth, False)
+    res = rb.run_stream(args.bytes, args.steps * burst, args.depth, False)
     launches = _C.kernel_launch_count() - launches_before
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     ms = max_over_ranks(res.device_ms)
     ms_per_step = ms / args.steps
-    value = world * args.bytes / (ms_per_step * 1e-3) / 1e9
+    value = world * burst * args.bytes / (ms_per_step * 1e-3) / 1e9
 
     # End to end right after the headline, on contexts of its own.
     e2e = None
@@ -324,6 +343,12 @@ def run_native(args):
 
     def run_mixed():
         # 64-tensor mixed-dtype message (strided views + receiver-requested casts), one fused launch.
+        # First one message from a seeded source, every delivered element checked against a CPU
+        # restatement of the gather and of the conversion.
+        barrier()
+        check, _ = rb.run_mixed(1, 1, True)
+        if check.mismatches:
+            raise RuntimeError(f"mixed message: {check.mismatches} delivered elements differ from the CPU restatement")
         barrier()
         rb.run_mixed(3, 1)
         barrier()
@@ -332,7 +357,8 @@ def run_native(args):
         mixed_ms = max_over_ranks(mres.device_ms) / 10
         return {"tensors": 64, "bytes_per_msg": mixed_bytes, "ms_per_msg": round(mixed_ms, 4),
                 "GBps": round(world * mixed_bytes / (mixed_ms * 1e-3) / 1e9, 2),
-                "kernel_launches_per_msg": mres.kernel_launches / 10}
+                "kernel_launches_per_msg": mres.kernel_launches / 10,
+                "verified": "one message element by element against a CPU restatement, before timing"}
 
     sweep = [] if args.no_sweep else auxiliary("sweep", run_sweep)
     latency = auxiliary("latency", run_latency)
@@ -346,11 +372,10 @@ def run_native(args):
             "metric": METRIC, "value": round(value, 3), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 5), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "native",
-            "config": {"model": "pipe ring: 1 bf16 tensor per message", "global_batch": world,
-                       "seq_len": args.bytes // 2, "bytes_per_message": args.bytes,
-                       "parallelism": f"ring{world}" if world > 1 else "loopback (two pipes, one process, one GPU)",
-                       "l2": "inputs larger than L2 (no flush)", "writes_in_flight": args.depth,
-                       "path": "plain ld/st" if args.no_bulk else "TMA bulk"},
+            "config": bench_config(args, world, burst),
+            "data_path": "cuda_p2p push kernel, " + ("plain ld/st" if args.no_bulk else "TMA bulk loads and stores"),
+            "timed_region_s": round(ms * 1e-3, 4),
+            "roofline": roofline(world, value),
             "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e, "sweep": sweep, "latency": latency,
             "mixed_64_tensor_message": mixed,
         }
@@ -359,9 +384,34 @@ def run_native(args):
         dist.destroy_process_group()
 
 
+def roofline(world, value_gbs):
+    """Achieved fraction of the roofline for the headline: across GPUs the bytes cross NVLink once
+    (900 GB/s per direction per GPU nominal; 770 GB/s is what a copy-engine peer copy measured on
+    this pool); on one GPU they are read and written once in HBM (MEASURED_PEAKS.json)."""
+    per_gpu = value_gbs / world
+    if world > 1:
+        return {"per_gpu_per_direction_GBps": round(per_gpu, 1), "of_nvlink_900_nominal": round(per_gpu / 900.0, 3),
+                "of_measured_peer_copy_770": round(per_gpu / 770.0, 3)}
+    hbm = None
+    try:
+        with open(os.path.join(REPO, "MEASURED_PEAKS.json")) as f:
+            hbm = float(json.load(f)["hbm_gbs"])
+    except (OSError, ValueError, KeyError):
+        pass
+    out = {"hbm_read_plus_write_GBps": round(2 * per_gpu, 1)}
+    if hbm:
+        out["of_measured_hbm_copy"] = round(2 * per_gpu / hbm, 3)
+    else:
+        out["of_fallback_hbm_6650"] = round(2 * per_gpu / 6650.0, 3)
+    return out
+
+
 def run_e2e(args, tpb, torch, dist, rank, world, local_rank, barrier, max_over_ranks, gather):
-    """The same ring through the public Python API. Every step copies its input from pinned host
-    memory to the device, sends it, receives the neighbour's tensor and reads a checksum back."""
+    """The same ring through the public Python API, end to end: every step's input starts in pinned
+    host memory and the step ends with a checksum of the received tensor read back to the host.
+    The pinned tensor itself is what is sent: the push kernel of this rank's GPU reads it over
+    PCIe and stores it into the next rank's GPU, so the host->device copy of the step IS the pipe
+    transfer (one pass over PCIe instead of a staging copy followed by a send)."""
     dev = torch.device("cuda", local_rank)
     nbytes = args.bytes
     steps = max(5, min(args.steps, 20))
@@ -377,13 +427,11 @@ def run_e2e(args, tpb, torch, dist, rank, world, local_rank, barrier, max_over_r
 
     host_in = torch.empty(nbytes // 2, dtype=torch.bfloat16).pin_memory()
     host_in.normal_()
-    x = torch.empty(nbytes // 2, dtype=torch.bfloat16, device=dev)
     bufs = [torch.empty(nbytes // 2, dtype=torch.bfloat16, device=dev) for _ in range(2)]
     result = torch.empty(1, dtype=torch.float32).pin_memory()
 
     def step(i):
-        x.copy_(host_in, non_blocking=True)                       # H2D, nbytes
-        sent = out_pipe.send([x], target_devices=[target])
+        sent = out_pipe.send([host_in], target_devices=[target])  # H2D (nbytes) fused into the transfer
         msg = in_pipe.recv(out=[bufs[i & 1]]).result(120)
         sent.result(120)
         checksum = msg.tensors[0][:4096].float().sum()
@@ -401,13 +449,22 @@ def run_e2e(args, tpb, torch, dist, rank, world, local_rank, barrier, max_over_r
     dt = time.perf_counter() - t0
     barrier()
     dt = max_over_ranks(dt)
+    # What arrived is what the previous rank holds in host memory? Every rank filled its own random
+    # tensor, so compare checksums over the whole tensor through a gather.
+    mine = float(host_in.float().sum())
+    got = float(bufs[(steps - 1) & 1].float().sum())
+    sums = gather((mine, got))
+    expected = sums[(rank - 1) % world][0]
+    if abs(got - expected) > 1e-3 * max(1.0, abs(expected)):
+        raise RuntimeError(f"end-to-end: received checksum {got} differs from the sender's {expected}")
     out_pipe.close()
     in_pipe.close()
     send_ctx.join()
     recv_ctx.join()
     return {"value": round(world * nbytes * steps / dt / 1e9, 3), "unit": "GB/s", "steps": steps,
             "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": 4,
-            "api": "tensorpipe_b200.Pipe.send / Pipe.recv (torch tensors)"}
+            "api": "tensorpipe_b200.Pipe.send / Pipe.recv (torch tensors); the pinned host tensor is sent as it is",
+            "verified": "full-tensor checksum against the sender's"}
 
 
 def main():

@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """All-pairs multi-tensor messages: every rank concurrently sends every other rank a message of 64
 tensors with mixed dtypes (fp32, bf16, int64), sizes log-uniform from 1 KiB to 16 MiB, a quarter of
-them non-contiguous transposed 2-D views, and the receiver asks for an fp32 -> bf16 conversion on
+them non-contiguous transposed 2-D views (8 to 4096 columns, log-uniform), and the receiver asks for an fp32 -> bf16 conversion on
 half of the fp32 tensors. Each message is moved by one fused kernel launch on its sender.
 Reports aggregate and per-GPU GB/s (bytes delivered), timed on the device, max over ranks.
 
@@ -24,7 +24,7 @@ def make_message(seed, device):
         dtype = (torch.float32, torch.bfloat16, torch.int64)[i % 3]
         nbytes = int(math.exp(rng.uniform(math.log(1024), math.log(16 << 20))))
         elems = max(64, nbytes // torch.empty((), dtype=dtype).element_size())
-        cols = 64
+        cols = int(math.exp(rng.uniform(math.log(8), math.log(4096)))) if i % 4 == 3 else 64
         rows = max(1, elems // cols)
         if dtype == torch.int64:
             t = torch.randint(-1000, 1000, (cols, rows) if i % 4 == 3 else (rows, cols), dtype=dtype, device=device)

@@ -120,14 +120,21 @@ std::shared_ptr<Context> create(std::shared_ptr<Context> cpuContext);
 }
 namespace cuda_p2p {
 // Every field can be overridden from the environment when the channel is created:
-// TPB_CUDA_P2P_EAGER_THRESHOLD, _INBOX_BYTES, _MAX_CTAS, _WAIT_KERNEL (0/1), _WAIT_TIMEOUT_MS, _BULK (0/1).
+// TPB_CUDA_P2P_EAGER_THRESHOLD, _INBOX_BYTES, _MAX_CTAS, _WAIT_KERNEL (0/1), _FUSED_WAIT (0/1),
+// _WAIT_TIMEOUT_MS, _BULK (0/1), _CLOSE_TIMEOUT_MS.
 struct Options {
-  size_t eagerThreshold = 64 * 1024;     // batches up to this many bytes go through the inbox
-  size_t inboxBytes = 8u << 20;          // per-peer inbox ring in device memory
-  int maxCtas = 0;                        // 0 = one persistent CTA per SM
+  size_t eagerThreshold = 1u << 20;      // batches up to this many bytes go through the inbox
+  size_t inboxBytes = 32u << 20;         // per-peer inbox ring in device memory
+  int maxCtas = 0;                        // 0 = one persistent CTA per SM, shared between the
+                                          // channels that are sending from that GPU at the moment
   bool waitWithKernel = false;            // true: bounded wait kernel; false: stream memory op
-  uint64_t waitTimeoutNs = 2'000'000'000ull;  // bound of the wait kernel
+  bool fuseWaitIntoUnpack = true;         // small messages from ANOTHER GPU: the unpack kernel waits itself
+  uint64_t waitTimeoutNs = 2'000'000'000ull;  // bound of every device-side wait
   bool useBulkCopy = true;                // TMA bulk pipeline for aligned contiguous data
+  uint64_t closeTimeoutMs = 3000;         // how long a closing end waits for the peer's goodbye
+  // Host-side fault injection for tests: the N-th push of a channel (counting from 0) is announced
+  // to the receiver but not launched, so that the receiver's bounded wait runs out. -1: never.
+  int faultSkipLaunch = -1;
 };
 // The device-to-device channel: a persistent sm_100a kernel on the sender pushes straight into
 // the receiver's memory (same process: raw pointers; other process: IPC-mapped) and publishes a

@@ -96,6 +96,8 @@ struct FaultPlan {
   int delayMs = 0;           // delay every write by this long
   int corruptFromWrite = -1; // >=0: from the N-th write on, frames are sent with their bytes scrambled
   unsigned corruptSeed = 1;  //      (same length, seeded noise XOR-ed over the content)
+  int swallowFromWrite = -1; // >=0: from the N-th write of a connection on, frames vanish: the writer is told
+                             //      they went out, the peer never sees them (a peer that has gone silent)
 };
 std::shared_ptr<Context> wrapWithFaults(std::shared_ptr<Context> inner, FaultPlan plan);
 

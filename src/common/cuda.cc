@@ -173,6 +173,18 @@ int cudaDeviceForPointer(const void* ptr) {
   return ordinal;
 }
 
+bool cudaIsLocalDeviceMemory(const void* ptr, int device) {
+  const CudaLib& lib = CudaLib::get();
+  if (!lib.ok) return false;
+  unsigned type = 0;
+  int ordinal = -1;
+  const CUdeviceptr_t p = reinterpret_cast<CUdeviceptr_t>(ptr);
+  if (lib.cuPointerGetAttribute(&type, CudaLib::kAttrMemoryType, p) != 0) return false;
+  if (type != 2 /* CU_MEMORYTYPE_DEVICE */) return false;
+  if (lib.cuPointerGetAttribute(&ordinal, CudaLib::kAttrDeviceOrdinal, p) != 0) return false;
+  return ordinal == device;
+}
+
 bool cudaAllocationInfo(const void* ptr, void** base, size_t* size, unsigned long long* bufferId) {
   const CudaLib& lib = CudaLib::get();
   if (!lib.ok) return false;

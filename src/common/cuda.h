@@ -149,6 +149,10 @@ int cudaDeviceCountNoThrow();
 std::string cudaDeviceUuid(int device);
 // Device index that owns a device pointer, or -1.
 int cudaDeviceForPointer(const void* ptr);
+// True when `ptr` is ordinary device memory of `device`: the only kind of source the bulk-copy
+// (TMA) path of the push kernel is given. Pinned host memory and another GPU's memory are read
+// with plain loads instead.
+bool cudaIsLocalDeviceMemory(const void* ptr, int device);
 // Base address, size and driver buffer id of the allocation containing ptr.
 bool cudaAllocationInfo(const void* ptr, void** base, size_t* size, unsigned long long* bufferId);
 // Enable peer access from `device` to `peer` once (idempotent). Returns false if impossible.

@@ -16,6 +16,9 @@ namespace tpb {
 struct alignas(64) RingHeader {
   uint64_t size;  // data bytes, power of two
   uint64_t magic;
+  // Set by a producer that found the ring too full to go on; a consumer that frees space while
+  // it is set owes the producer a wake-up (how it delivers it is the transport's business).
+  std::atomic<uint32_t> producerStalled;
   alignas(64) std::atomic<uint64_t> head;  // consumer cursor
   alignas(64) std::atomic<uint64_t> tail;  // producer cursor
 };
@@ -23,13 +26,14 @@ static_assert(sizeof(RingHeader) == 192, "ring header layout is part of the shm 
 
 class Ring {
  public:
-  static constexpr uint64_t kMagic = 0x7470625f72696e67ull;  // "tpb_ring"
+  static constexpr uint64_t kMagic = 0x7470625f72696e32ull;  // "tpb_rin2"
   Ring() = default;
   Ring(void* mem, uint64_t dataBytes, bool init) : h_(static_cast<RingHeader*>(mem)) {
     data_ = reinterpret_cast<uint8_t*>(h_ + 1);
     if (init) {
       h_->size = dataBytes;
       h_->magic = kMagic;
+      h_->producerStalled.store(0, std::memory_order_relaxed);
       h_->head.store(0, std::memory_order_relaxed);
       h_->tail.store(0, std::memory_order_release);
     }
@@ -58,6 +62,18 @@ class Ring {
     h_->tail.store(tail + n, std::memory_order_release);
     return n;
   }
+  // Producer: announce (or withdraw) that it waits for space. After announcing, look at
+  // freeBytes() once more before going idle: the consumer may have freed space in between.
+  void setProducerStalled(bool stalled) {
+    h_->producerStalled.store(stalled ? 1 : 0, std::memory_order_seq_cst);
+    std::atomic_thread_fence(std::memory_order_seq_cst);
+  }
+  // Consumer: call after read() freed space; true means the producer must be woken.
+  bool producerStalled() const {
+    std::atomic_thread_fence(std::memory_order_seq_cst);
+    return h_->producerStalled.load(std::memory_order_seq_cst) != 0;
+  }
+
   // Consumer side.
   uint64_t usedBytes() const {
     return h_->tail.load(std::memory_order_acquire) - h_->head.load(std::memory_order_relaxed);

@@ -163,7 +163,31 @@ struct PushParams {
   uint32_t bulkTileBytes;
   uint32_t bulkStages;
   uint32_t warpTileBytes;  // shared memory per register-path warp (0 when no entry needs staging)
+  // Optional: nothing is read before *waitFlag has reached waitValue (cyclic comparison) or the
+  // time limit has passed; used by a receiver that unpacks what another GPU is still delivering.
+  const uint32_t* waitFlag;
+  uint32_t waitValue;
+  uint64_t waitTimeoutNs;
+  // Optional: a word (mapped host memory) that receives doneValue once every CTA of the launch
+  // has finished, whether the launch succeeded or gave up: the host's cheap way to learn that a
+  // launch is over without an event.
+  uint32_t* doneSlot;
+  uint32_t doneValue;
 };
+
+// The arrive counter of a launch doubles as its failure latch: the low half counts CTAs that
+// have reported in, every CTA that gave up adds one to the high half.
+constexpr uint32_t kArriveMask = 0xffffu;
+constexpr uint32_t kArriveFailed = 0x10000u;
+
+__device__ __forceinline__ void reportStatus(uint32_t* status, uint32_t code) {
+  // The word may live in mapped host memory, where only a plain store is certain to be seen
+  // by the CPU; codes are never cleared by a kernel, so the order of racing writers is moot.
+  if (status) {
+    *reinterpret_cast<volatile uint32_t*>(status) = code;
+    __threadfence_system();
+  }
+}
 
 template <int N>
 __device__ __forceinline__ const PushEntry* findEntry(const PushParams<N>& p, uint32_t tile, bool bulk) {
@@ -676,23 +700,57 @@ __device__ __forceinline__ void runPlainWarp(const PushParams<N>& p, uint32_t fi
   }
 }
 
+// One lane polls, the CTA learns the outcome. Bounded by the timer and by an iteration cap.
 template <int N>
-__device__ __forceinline__ void publish(const PushParams<N>& p) {
-  if (p.flag == nullptr) return;
+__device__ __forceinline__ bool waitForProducer(const PushParams<N>& p) {
+  if (p.waitFlag == nullptr) return true;
+  bool arrived = true;
+  if (threadIdx.x == 0) {
+    arrived = false;
+    const uint64_t start = globalTimerNs();
+    uint32_t backoff = 32;
+    for (uint64_t i = 0; i < (1ull << 32); ++i) {
+      if (static_cast<int32_t>(loadAcquireSys(p.waitFlag) - p.waitValue) >= 0) {
+        arrived = true;
+        break;
+      }
+      if (globalTimerNs() - start > p.waitTimeoutNs) break;
+      __nanosleep(backoff);
+      if (backoff < 1024) backoff <<= 1;
+    }
+    if (!arrived) reportStatus(p.status, kStatusWaitTimeout);
+  }
+  return __syncthreads_and(arrived) != 0;
+}
+
+// Last step of every launch. A launch that gave up anywhere (a bulk load that never completed,
+// a producer that never arrived) does NOT publish its flag: whoever waits for it runs into its
+// own time limit instead of reading half-written data.
+template <int N>
+__device__ __forceinline__ void publish(const PushParams<N>& p, bool failedHere) {
+  if (p.flag == nullptr && p.doneSlot == nullptr) return;
   // Make this thread's writes visible system-wide before the CTA reports in.
   __threadfence_system();
-  __syncthreads();
+  const bool ctaFailed = __syncthreads_or(failedHere) != 0;
   if (threadIdx.x == 0) {
-    if (gridDim.x == 1) {
-      // Only one CTA: the barrier above already ordered every write of the launch before this.
-      storeReleaseSys(p.flag, p.flagValue);
-      return;
+    bool last = true, anyFailed = ctaFailed;
+    if (gridDim.x > 1) {
+      const uint32_t mine = 1u + (ctaFailed ? kArriveFailed : 0u);
+      const uint32_t before = atomicAdd(p.counter, mine);
+      last = (before & kArriveMask) == gridDim.x - 1;
+      anyFailed = ((before + mine) & ~kArriveMask) != 0;
+      if (last) {
+        *p.counter = 0;  // ready for the next launch that is given this counter
+        __threadfence_system();
+      }
     }
-    const uint32_t arrived = atomicAdd(p.counter, 1u);
-    if (arrived == gridDim.x - 1) {
-      *p.counter = 0;  // ready for the next launch on this stream
-      __threadfence_system();
-      storeReleaseSys(p.flag, p.flagValue);
+    // With one CTA the barrier above already ordered every write of the launch before this.
+    if (last) {
+      if (p.flag != nullptr && !anyFailed) storeReleaseSys(p.flag, p.flagValue);
+      if (p.doneSlot != nullptr) {
+        *reinterpret_cast<volatile uint32_t*>(p.doneSlot) = p.doneValue;
+        __threadfence_system();
+      }
     }
   }
 }
@@ -711,12 +769,17 @@ __global__ void __launch_bounds__(kThreads, 1) tpb_push_pack(const __grid_consta
   const int tid = threadIdx.x;
   const int S = static_cast<int>(p.bulkStages);
   const bool haveBulk = p.bulkTiles > blockIdx.x;
+  bool failed = false;
 
   if (tid == 0 && haveBulk) {
     for (int s = 0; s < S; ++s) mbarInit(&full[s], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  if (!waitForProducer(p)) {
+    publish(p, true);
+    return;
+  }
 
   if (tid < 32) {
     // ---- warp 0: the bulk copy pipeline, driven by one elected lane ----
@@ -724,7 +787,6 @@ __global__ void __launch_bounds__(kThreads, 1) tpb_push_pack(const __grid_consta
       const uint32_t first = blockIdx.x, step = gridDim.x;
       const uint32_t mine = (p.bulkTiles - first + step - 1) / step;  // tiles this CTA owns
       const uint32_t tileBytes = p.bulkTileBytes;
-      bool failed = false;
 #ifdef TPB_DEBUG_KERNELS
       // A bulk copy off the 16-byte grid is an illegal instruction: check the whole table first
       // and leave the pipeline alone if any entry is wrong.
@@ -781,7 +843,7 @@ __global__ void __launch_bounds__(kThreads, 1) tpb_push_pack(const __grid_consta
         }
       }
       bulkWaitAll();  // stores are complete (not merely read out of shared memory)
-      if (failed && p.status) atomicMax(p.status, static_cast<uint32_t>(kStatusBarrierTimeout));
+      if (failed) reportStatus(p.status, kStatusBarrierTimeout);
     }
   } else {
     // ---- warps 1..: everything that needs registers ----
@@ -790,7 +852,7 @@ __global__ void __launch_bounds__(kThreads, 1) tpb_push_pack(const __grid_consta
     runPlainWarp(p, blockIdx.x * kPlainWarps + warp, gridDim.x * kPlainWarps, tid & 31,
                  warpTiles + warp * p.warpTileBytes);
   }
-  publish(p);
+  publish(p, failed);
 }
 
 template <int N>
@@ -798,27 +860,29 @@ __global__ void __launch_bounds__(kLightThreads, 2) tpb_push_pack_light(const __
   extern __shared__ __align__(16) uint8_t lightTiles[];  // kWarps * p.warpTileBytes, none for plain copies
   constexpr uint32_t kWarps = kLightThreads / 32;
   const uint32_t warp = threadIdx.x / 32;
+  if (!waitForProducer(p)) {
+    publish(p, true);
+    return;
+  }
   runPlainWarp(p, blockIdx.x * kWarps + warp, gridDim.x * kWarps, threadIdx.x & 31, lightTiles + warp * p.warpTileBytes);
-  publish(p);
+  publish(p, false);
 }
 
 __global__ void tpb_wait_flag(const uint32_t* flag, uint32_t value, uint64_t timeoutNs, uint32_t* status) {
   if (threadIdx.x != 0) return;
   const uint64_t start = globalTimerNs();
   uint32_t backoff = 32;
-  uint32_t result = kStatusWaitTimeout;
   // Both limits bound the loop: the timer deadline and an iteration cap.
   for (uint64_t i = 0; i < (1ull << 32); ++i) {
     const uint32_t v = loadAcquireSys(flag);
-    if (static_cast<int32_t>(v - value) >= 0) {
-      result = kStatusOk;
-      break;
-    }
+    if (static_cast<int32_t>(v - value) >= 0) return;
     if (globalTimerNs() - start > timeoutNs) break;
     __nanosleep(backoff);
     if (backoff < 1024) backoff <<= 1;
   }
-  if (status) *status = result;
+  // Only a failure is written: the word is shared with other waits and an earlier failure must
+  // not be wiped out by a later success.
+  reportStatus(status, kStatusWaitTimeout);
 }
 
 __global__ void tpb_delay(uint32_t* buf, size_t words, uint64_t ns) {
@@ -873,7 +937,7 @@ void check(cudaError_t e, const char* what) {
 template <int N>
 void launchOne(const PushEntry* entries, uint32_t n, uint32_t bulkTiles, uint32_t plainTiles, uint32_t bulkTileBytes,
                uint32_t bulkStages, cudaStream_t stream, int maxCtas, uint32_t* flag, uint32_t flagValue,
-               uint32_t* counter, uint32_t* status) {
+               uint32_t* counter, uint32_t* status, const WaitBefore& wait, const DoneSlot& done) {
   PushParams<N> p;
   for (uint32_t i = 0; i < n; ++i) p.entries[i] = entries[i];
   p.numEntries = n;
@@ -883,6 +947,11 @@ void launchOne(const PushEntry* entries, uint32_t n, uint32_t bulkTiles, uint32_
   p.flag = flag;
   p.counter = counter;
   p.status = status;
+  p.waitFlag = wait.flag;
+  p.waitValue = wait.value;
+  p.waitTimeoutNs = wait.timeoutNs;
+  p.doneSlot = done.slot;
+  p.doneValue = done.value;
   p.bulkTileBytes = bulkTileBytes;
   p.bulkStages = bulkStages;
   p.warpTileBytes = 0;
@@ -994,6 +1063,20 @@ void pushEntry(PushPlan& plan, PushEntry e) {
 }
 }  // namespace
 
+void chooseBulkTile(PushPlan& plan, uint64_t bulkBytes, int ctas) {
+  const PushTuning t = getPushTuning();
+  plan.bulkStages = t.bulkStages;
+  plan.bulkTileBytes = t.bulkTileBytes;
+  if (!plan.entries.empty() || bulkBytes == 0 || ctas <= 0) return;
+  const uint64_t perWave = static_cast<uint64_t>(ctas) * t.bulkTileBytes;
+  const uint64_t waves = (bulkBytes + perWave - 1) / perWave;
+  uint64_t tile = (bulkBytes + waves * ctas - 1) / (waves * ctas);
+  tile = (tile + 1023) / 1024 * 1024;
+  if (tile < 4096) tile = 4096;
+  if (tile > t.bulkTileBytes) tile = t.bulkTileBytes;
+  plan.bulkTileBytes = static_cast<uint32_t>(tile);
+}
+
 void appendToPlan(PushPlan& plan, const CopyItem& item, bool useBulk) {
   if (plan.bulkTileBytes == 0) {
     const PushTuning t = getPushTuning();
@@ -1102,7 +1185,9 @@ void appendToPlan(PushPlan& plan, const CopyItem& item, bool useBulk) {
 }
 
 int launchPush(const PushPlan& plan, cudaStream_t stream, int maxCtas, uint32_t* flag, uint32_t flagValue,
-               uint32_t* counter, uint32_t* status) {
+               uint32_t* counter, uint32_t* status, WaitBefore wait, DoneSlot done) {
+  if ((flag != nullptr || done.slot != nullptr) && counter == nullptr && maxCtas > 1)
+    throw std::runtime_error("a launch that publishes a flag or a completion word from several CTAs needs an arrive counter");
   const size_t n = plan.entries.size();
   trace::Scope traced("tpb_push_pack launch", plan.totalBytesOut);
   if (maxCtas <= 0) maxCtas = 1;
@@ -1111,10 +1196,10 @@ int launchPush(const PushPlan& plan, cudaStream_t stream, int maxCtas, uint32_t*
   if (n <= static_cast<size_t>(kMaxEntriesLarge)) {
     if (n <= static_cast<size_t>(kMaxEntriesSmall))
       launchOne<kMaxEntriesSmall>(plan.entries.data(), static_cast<uint32_t>(n), plan.bulkTiles, plan.plainTiles,
-                                  tileBytes, stages, stream, maxCtas, flag, flagValue, counter, status);
+                                  tileBytes, stages, stream, maxCtas, flag, flagValue, counter, status, wait, done);
     else
       launchOne<kMaxEntriesLarge>(plan.entries.data(), static_cast<uint32_t>(n), plan.bulkTiles, plan.plainTiles,
-                                  tileBytes, stages, stream, maxCtas, flag, flagValue, counter, status);
+                                  tileBytes, stages, stream, maxCtas, flag, flagValue, counter, status, wait, done);
     return 1;
   }
   // More entries than one parameter block holds: several launches on the same stream, each with
@@ -1134,8 +1219,10 @@ int launchPush(const PushPlan& plan, cudaStream_t stream, int maxCtas, uint32_t*
       }
     }
     const bool last = first + cnt == n;
+    // Only the first launch waits for the producer; stream order covers the rest.
     launchOne<kMaxEntriesLarge>(part.data(), static_cast<uint32_t>(cnt), bulk, plain, tileBytes, stages, stream,
-                                maxCtas, last ? flag : nullptr, flagValue, counter, status);
+                                maxCtas, last ? flag : nullptr, flagValue, counter, status,
+                                first == 0 ? wait : WaitBefore(), last ? done : DoneSlot());
     ++launches;
   }
   return launches;

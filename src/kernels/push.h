@@ -102,19 +102,46 @@ struct CopyItem {
 bool castSupported(DType src, DType dst);
 uint64_t convertedBytes(uint64_t srcBytes, DType src, DType dst);
 
+// Chooses the bulk tile of a plan that is still empty, for `bulkBytes` of bulk-path data spread
+// over `ctas` CTAs: the largest tile not above the tuned one that leaves every CTA about the same
+// number of tiles. A 1 MiB message then becomes 148 tiles of 7 KiB that move at once instead of 32
+// tiles of 32 KiB on 32 SMs, and an 8 MiB message two full waves instead of one and three
+// quarters. Without this call a plan uses the tuned tile size.
+void chooseBulkTile(PushPlan& plan, uint64_t bulkBytes, int ctas);
+
 // Splits items into kernel entries (aligned body for the bulk path, ragged head/tail for the
 // plain path) and numbers their tiles. `useBulk=false` routes everything through the plain path.
 void appendToPlan(PushPlan& plan, const CopyItem& item, bool useBulk);
 
+// A launch may be told to hold back until a flag that another GPU writes has reached a value
+// (cyclic comparison, as tpb_wait_flag does), for at most timeoutNs; on a timeout it copies
+// nothing, reports kStatusWaitTimeout and does not publish its own flag. Only for producers on
+// ANOTHER GPU: a kernel must not spin on something a different launch on its own GPU produces.
+struct WaitBefore {
+  const uint32_t* flag = nullptr;
+  uint32_t value = 0;
+  uint64_t timeoutNs = 0;
+};
+
+// A word in mapped host memory that the launch sets to `value` when all of its CTAs are through
+// (also when the launch gave up): lets the host follow launches without events.
+struct DoneSlot {
+  uint32_t* slot = nullptr;
+  uint32_t value = 0;
+};
+
 // Launches the plan on `stream` of the current device. `flag` may be null; when set, `counter`
 // must point to a zeroed 32-bit word in this device's memory that is private to launches
-// serialised on one stream (the kernel leaves it zeroed again). `status` may be null.
-// Returns the number of kernel launches made (plans with many entries take several).
+// that cannot overlap on the GPU (the kernel leaves it zeroed again). `status` (device or mapped
+// host memory) may be null; a launch that gives up writes a KernelStatus there and leaves the
+// flag unpublished. Returns the number of kernel launches made (plans with many entries take
+// several).
 int launchPush(const PushPlan& plan, cudaStream_t stream, int maxCtas, uint32_t* flag,
-               uint32_t flagValue, uint32_t* counter, uint32_t* status);
+               uint32_t flagValue, uint32_t* counter, uint32_t* status, WaitBefore wait = WaitBefore(),
+               DoneSlot done = DoneSlot());
 
-// Waits until *flag - value >= 0 (cyclic) or until timeoutNs elapsed; writes kStatusOk or
-// kStatusWaitTimeout to *status (device or mapped host memory).
+// Waits until *flag - value >= 0 (cyclic) or until timeoutNs elapsed; on a timeout writes
+// kStatusWaitTimeout to *status (device or mapped host memory) and otherwise leaves it alone.
 void launchWaitFlag(cudaStream_t stream, const uint32_t* flag, uint32_t value, uint64_t timeoutNs,
                     uint32_t* status);
 

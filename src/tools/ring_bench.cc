@@ -52,6 +52,7 @@ struct RingBench::Impl {
                          const std::vector<cudaStream_t>& sendStreams,
                          const std::vector<std::shared_ptr<Pipe>>& recvPipes, int steps, uint64_t seed,
                          uint64_t* bytesPerMessage);
+  uint64_t verifyMixed(uint64_t seed);
 
   std::shared_ptr<Context> makeContext(const std::string& name) {
     auto ctx = std::make_shared<Context>(ContextOptions().name(name));
@@ -382,7 +383,8 @@ std::vector<double> RingBench::runLatency(size_t bytes, int laps, int rank, int 
 
 namespace {
 // 64 tensors: dtype cycles fp32, bf16, int64; sizes log-uniform in [1 KiB, 16 MiB]; every 4th is a
-// transposed 2-D view; every other fp32 tensor is cast to bf16 by the receiver.
+// transposed 2-D view whose column count is drawn log-uniformly from [8, 4096] (so that no single
+// code path of the kernel is favoured); every other fp32 tensor is cast to bf16 by the receiver.
 struct MixedSpec {
   DType dtype;
   bool transposed;
@@ -407,6 +409,10 @@ MixedLayout makeMixedLayout(uint64_t seed) {
     const uint64_t es = dtypeSize(s.dtype);
     s.transposed = i % 4 == 3;
     s.cols = 64;
+    if (s.transposed) {
+      const double lc = std::log(8.0) + (std::log(4096.0) - std::log(8.0)) * (static_cast<double>(rng() % 100000) / 100000.0);
+      s.cols = static_cast<int64_t>(std::exp(lc));
+    }
     s.rows = static_cast<int64_t>(std::max<uint64_t>(1, bytes / es / s.cols));
     const uint64_t elems = static_cast<uint64_t>(s.rows) * s.cols;
     s.srcBytes = elems * es;
@@ -475,9 +481,73 @@ PhaseResult RingBench::runMixedMesh(int steps, uint64_t seed, uint64_t* bytesPer
   return m.runMixedOn(m.meshSend, m.meshSendDevice, m.meshSendStream, m.meshRecv, steps, seed, bytesPerMessage);
 }
 
+namespace {
+uint16_t toBf16(uint32_t bits) {
+  if ((bits & 0x7f800000u) == 0x7f800000u && (bits & 0x007fffffu)) return 0x7fff;  // NaN (compared loosely)
+  const uint32_t lsb = (bits >> 16) & 1;
+  return static_cast<uint16_t>((bits + 0x7fffu + lsb) >> 16);
+}
+bool isNanBf16(uint16_t v) { return (v & 0x7f80) == 0x7f80 && (v & 0x7f); }
+}  // namespace
+
+// One message from a source filled with the seeded pattern, then every delivered tensor against
+// a CPU restatement of what the sender's kernel must have done with it: gather of the transposed
+// views, round-to-nearest-even conversion of the fp32 tensors the receiver wanted as bf16, plain
+// bytes for the rest. Returns the number of elements that differ.
+uint64_t RingBench::Impl::verifyMixed(uint64_t seed) {
+  Impl& m = *this;
+  TPB_CUDA_CHECK(cudaSetDevice(m.opts.device));
+  const MixedLayout layout = makeMixedLayout(seed);
+  const uint64_t fillSeed = 0xfeed0000 + seed;
+  kernels::launchFill(m.sendStream, m.src, layout.srcTotal, fillSeed);
+  TPB_CUDA_CHECK(cudaStreamSynchronize(m.sendStream));
+  TPB_CUDA_CHECK(cudaMemsetAsync(m.dst[0], 0xA5, layout.dstTotal, m.recvStream));
+  TPB_CUDA_CHECK(cudaStreamSynchronize(m.recvStream));
+  uint64_t bytes = 0;
+  runMixedOn({m.sendPipe}, {m.nextDevice}, {m.sendStream}, {m.recvPipe}, 1, seed, &bytes);
+  TPB_CUDA_CHECK(cudaStreamSynchronize(m.recvStream));
+  std::vector<uint8_t> got(layout.dstTotal);
+  TPB_CUDA_CHECK(cudaMemcpy(got.data(), m.dst[0], got.size(), cudaMemcpyDeviceToHost));
+  // The source as the sender saw it (every rank fills the same pattern).
+  std::vector<uint32_t> src((layout.srcTotal + 3) / 4);
+  for (size_t w = 0; w < src.size(); ++w) {
+    uint32_t v = 0;
+    for (int b = 0; b < 4; ++b) v |= static_cast<uint32_t>(kernels::patternByte(fillSeed, w * 4 + b)) << (8 * b);
+    src[w] = v;
+  }
+  const uint8_t* srcBytes = reinterpret_cast<const uint8_t*>(src.data());
+  uint64_t bad = 0;
+  for (const MixedSpec& s : layout.specs) {
+    const size_t es = dtypeSize(s.dtype);
+    const uint8_t* in = srcBytes + s.srcOff;
+    const uint8_t* out = got.data() + s.dstOff;
+    const uint64_t elems = static_cast<uint64_t>(s.rows) * s.cols;
+    for (uint64_t i = 0; i < elems; ++i) {
+      // element i of the delivered (packed, row-major [rows, cols]) tensor
+      uint64_t from = i;
+      if (s.transposed) from = (i % s.cols) * static_cast<uint64_t>(s.rows) + i / s.cols;
+      if (s.cast) {
+        uint32_t bits;
+        std::memcpy(&bits, in + from * 4, 4);
+        uint16_t want = toBf16(bits), have;
+        std::memcpy(&have, out + i * 2, 2);
+        if (want != have && !(isNanBf16(want) && isNanBf16(have))) ++bad;
+      } else if (std::memcmp(in + from * es, out + i * es, es) != 0) {
+        ++bad;
+      }
+    }
+  }
+  return bad;
+}
+
 PhaseResult RingBench::runMixed(int steps, uint64_t seed, uint64_t* bytesPerStep, bool verify) {
-  (void)verify;
   Impl& m = *impl_;
+  if (verify) {
+    PhaseResult r;
+    r.mismatches = m.verifyMixed(seed);
+    if (bytesPerStep) *bytesPerStep = makeMixedLayout(seed).delivered;
+    return r;
+  }
   return m.runMixedOn({m.sendPipe}, {m.nextDevice}, {m.sendStream}, {m.recvPipe}, steps, seed, bytesPerStep);
 }
 

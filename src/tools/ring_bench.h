@@ -19,7 +19,7 @@ struct RingBenchOptions {
   bool useShm = true;         // register the shm transport (control traffic) next to TCP
   bool useBulkCopy = true;
   bool waitWithKernel = false;
-  size_t eagerThreshold = 64 * 1024;
+  size_t eagerThreshold = 1u << 20;
   int maxCtas = 0;
   size_t maxBytes = 1ull << 30;  // largest tensor that will be sent (buffers are sized for it)
   std::string channel = "cuda_p2p";  // or "cuda_basic"
@@ -52,8 +52,10 @@ class RingBench {
   // write -> data visible on the device), one sample per lap. Rank 0 starts the token.
   std::vector<double> runLatency(size_t bytes, int laps, int rank, int world);
 
-  // 64-tensor mixed message (fp32/bf16/int64, a quarter transposed views, half of the fp32
-  // tensors cast to bf16 by the receiver), `steps` times. Returns the bytes delivered per step.
+  // 64-tensor mixed message (fp32/bf16/int64, a quarter transposed views of 8 to 4096 columns,
+  // half of the fp32 tensors cast to bf16 by the receiver), `steps` times. Returns the bytes
+  // delivered per step. With `verify` one message is sent from a seeded source and every delivered
+  // element is compared with a CPU restatement (result in PhaseResult::mismatches; nothing is timed).
   PhaseResult runMixed(int steps, uint64_t seed, uint64_t* bytesPerStep, bool verify);
 
   // All-pairs mode: dial every other rank's listener ("url|device" per rank, own entry ignored) and

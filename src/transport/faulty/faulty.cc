@@ -33,6 +33,13 @@ class FaultyConnection final : public Connection {
       });
       return;
     }
+    if (plan_.swallowFromWrite >= 0 && n >= plan_.swallowFromWrite) {
+      // Nothing reaches the wire; the completion is reported from a short-lived thread so that it
+      // never runs on the caller's stack.
+      auto keep = inner_;
+      std::thread([keep, fn = std::move(fn)]() mutable { fn(Error::kSuccess); }).detach();
+      return;
+    }
     if (n < plan_.dropWrites) {
       // Pretend success without sending anything; a zero-length read on our own side keeps the
       // callback off the caller's stack.

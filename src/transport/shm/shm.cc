@@ -405,8 +405,26 @@ class ConnectionImpl final : public FdHandler, public std::enable_shared_from_th
   }
   void write(WriteOp op) {
     auto self = shared_from_this();
+    {
+      // Short cut: when nothing is queued ahead and the whole frame fits, the caller's own thread
+      // copies it into the peer's inbox and pokes the peer; only the completion goes through the
+      // reactor thread. This takes one thread hand-off out of every control message.
+      std::unique_lock<std::mutex> lock(outboxMutex_);
+      if (directWrites_ && queuedWrites_ == 0 && outbox_.freeBytes() >= sizeof(uint32_t) + op.length) {
+        outbox_.write(&op.length, sizeof(uint32_t));
+        if (op.length) outbox_.write(op.ptr, op.length);
+        pokePeer(peerInboxToken_);
+        lock.unlock();
+        ctx_->reactor().deferToLoop([self, fn = std::move(op.fn)]() mutable { fn(Error::kSuccess); });
+        return;
+      }
+      ++queuedWrites_;
+    }
     ctx_->reactor().deferToLoop([self, op = std::move(op)]() mutable {
-      if (self->error_) return op.fn(self->error_);
+      if (self->error_) {
+        self->forgetQueuedWrite();
+        return op.fn(self->error_);
+      }
       self->writes_.push_back(std::move(op));
       if (self->peerGone_) return self->closeFromLoop(TPB_CREATE_ERROR(EOFError));
       if (self->state_ == kEstablished) self->processWrites();
@@ -424,6 +442,18 @@ class ConnectionImpl final : public FdHandler, public std::enable_shared_from_th
   void onPeerBootstrap(const Bootstrap& b, int fds[3]);
   void processReads();
   void processWrites();
+  // The outbox is too full to go on: say so in the ring header, so that the reader pokes our
+  // outbox token once it has made room, and look once more (it may just have done so). Returns
+  // true if there is room after all. Call with outboxMutex_ held.
+  bool waitForSpace(uint64_t needed) {
+    outbox_.setProducerStalled(true);
+    stalled_ = true;
+    return outbox_.freeBytes() >= needed;
+  }
+  void forgetQueuedWrite() {
+    std::unique_lock<std::mutex> lock(outboxMutex_);
+    --queuedWrites_;
+  }
   void pokePeer(uint32_t token) {
     if (peerQueue_.push(token)) {
       uint64_t one = 1;
@@ -449,6 +479,12 @@ class ConnectionImpl final : public FdHandler, public std::enable_shared_from_th
   bool peerGone_ = false;
   std::deque<ReadOp> reads_;
   std::deque<WriteOp> writes_;
+  // The outbox has one producer at a time: whoever holds this mutex, the reactor thread working
+  // through writes_ or a caller taking the short cut in write().
+  std::mutex outboxMutex_;
+  bool directWrites_ = false;  // established, peer alive: callers may write the outbox themselves
+  size_t queuedWrites_ = 0;    // writes handed to the reactor thread and not completed yet
+  bool stalled_ = false;       // the ring header says we wait for space
 };
 
 void ConnectionImpl::initFromLoop() {
@@ -513,6 +549,10 @@ void ConnectionImpl::handleFdEvents(int events) {
     // a TCP socket buffer would); the connection fails once a read cannot be satisfied.
     if (state_ != kEstablished) return closeFromLoop(TPB_CREATE_ERROR(EOFError));
     peerGone_ = true;
+    {
+      std::unique_lock<std::mutex> lock(outboxMutex_);
+      directWrites_ = false;
+    }
     if (watching_) ctx_->reactor().unwatchFd(sock_);
     watching_ = false;
     if (!writes_.empty()) return closeFromLoop(TPB_CREATE_ERROR(EOFError));
@@ -534,6 +574,10 @@ void ConnectionImpl::onPeerBootstrap(const Bootstrap& b, int fds[3]) {
   if (!peerQueue_.valid(peerReactorSeg_.size()) || !outbox_.valid(outboxSeg_.size()))
     return closeFromLoop(TPB_CREATE_ERROR(ShortReadError, 0, 0));
   state_ = kEstablished;
+  {
+    std::unique_lock<std::mutex> lock(outboxMutex_);
+    directWrites_ = true;
+  }
   processWrites();
   if (state_ == kEstablished) processReads();
 }
@@ -574,7 +618,7 @@ void ConnectionImpl::processReads() {
       op.bodyRead += n;
       if (op.bodyRead < op.frameLen) {
         // Let the writer refill while we wait for the rest.
-        if (n > 0 && !peerGone_) { pokePeer(peerOutboxToken_); consumed = false; }
+        if (n > 0 && !peerGone_ && inbox_.producerStalled()) { pokePeer(peerOutboxToken_); consumed = false; }
         break;
       }
     }
@@ -586,38 +630,46 @@ void ConnectionImpl::processReads() {
     if (state_ == kEstablished && !reads_.empty()) closeFromLoop(TPB_CREATE_ERROR(EOFError));
     return;
   }
-  if (consumed && state_ == kEstablished) pokePeer(peerOutboxToken_);
+  // A writer that ran out of ring space waits for exactly this.
+  if (consumed && state_ == kEstablished && inbox_.producerStalled()) pokePeer(peerOutboxToken_);
 }
 
 void ConnectionImpl::processWrites() {
   if (state_ != kEstablished) return;
   auto self = shared_from_this();
-  bool produced = false;
-  while (state_ == kEstablished && !writes_.empty()) {
-    WriteOp& op = writes_.front();
-    if (!op.headerWritten) {
-      if (outbox_.freeBytes() < sizeof(uint32_t)) break;
-      outbox_.write(&op.length, sizeof(uint32_t));
-      op.headerWritten = true;
-      produced = true;
-    }
-    if (op.bodyWritten < op.length) {
-      uint64_t n = outbox_.write(op.ptr + op.bodyWritten, op.length - op.bodyWritten);
-      if (n > 0) produced = true;
-      op.bodyWritten += n;
-      if (op.bodyWritten < op.length) {
-        if (n > 0) { pokePeer(peerInboxToken_); produced = false; }
-        break;
+  std::vector<Connection::write_callback_fn> completed;
+  {
+    std::unique_lock<std::mutex> lock(outboxMutex_);
+    bool produced = false;
+    while (!writes_.empty()) {
+      WriteOp& op = writes_.front();
+      if (!op.headerWritten) {
+        if (outbox_.freeBytes() < sizeof(uint32_t) && !waitForSpace(sizeof(uint32_t))) break;
+        outbox_.write(&op.length, sizeof(uint32_t));
+        op.headerWritten = true;
+        produced = true;
       }
+      if (op.bodyWritten < op.length) {
+        uint64_t n = outbox_.write(op.ptr + op.bodyWritten, op.length - op.bodyWritten);
+        if (n > 0) produced = true;
+        op.bodyWritten += n;
+        if (op.bodyWritten < op.length) {
+          if (waitForSpace(1)) continue;
+          break;
+        }
+      }
+      completed.push_back(std::move(op.fn));
+      writes_.pop_front();
+      --queuedWrites_;
     }
-    WriteOp done = std::move(writes_.front());
-    writes_.pop_front();
-    // Poke before the callback so the reader starts while we run user code.
-    pokePeer(peerInboxToken_);
-    produced = false;
-    done.fn(Error::kSuccess);
+    if (writes_.empty() && stalled_) {
+      outbox_.setProducerStalled(false);
+      stalled_ = false;
+    }
+    // Poke before the callbacks so the reader starts while we run user code.
+    if (produced) pokePeer(peerInboxToken_);
   }
-  if (produced && state_ == kEstablished) pokePeer(peerInboxToken_);
+  for (auto& fn : completed) fn(Error::kSuccess);
 }
 
 void ConnectionImpl::closeFromLoop(const Error& e) {
@@ -625,6 +677,13 @@ void ConnectionImpl::closeFromLoop(const Error& e) {
   error_ = e;
   auto self = shared_from_this();
   state_ = kClosed;
+  {
+    // No caller may be half way through the short cut of write() when the eventfd goes away.
+    std::unique_lock<std::mutex> lock(outboxMutex_);
+    directWrites_ = false;
+    if (peerEventFd_ >= 0) ::close(peerEventFd_);
+    peerEventFd_ = -1;
+  }
   if (watching_) ctx_->reactor().unwatchFd(sock_);
   watching_ = false;
   if (sock_ >= 0) ::close(sock_);
@@ -634,13 +693,15 @@ void ConnectionImpl::closeFromLoop(const Error& e) {
     ctx_->reactor().removeToken(myOutboxToken_);
     tokensRegistered_ = false;
   }
-  if (peerEventFd_ >= 0) ::close(peerEventFd_);
-  peerEventFd_ = -1;
   ctx_->unenroll(self);
   auto reads = std::move(reads_);
   auto writes = std::move(writes_);
   reads_.clear();
   writes_.clear();
+  {
+    std::unique_lock<std::mutex> lock(outboxMutex_);
+    queuedWrites_ -= writes.size();
+  }
   for (auto& r : reads) r.fn(error_, nullptr, 0);
   for (auto& w : writes) w.fn(error_);
 }

@@ -133,18 +133,29 @@ class Pipe:
         self._p.write(out, callback)
 
     def _supports_layouts(self, local: str, target: str) -> bool:
-        # Fixed once the pipe is established: asked once per device pair, not per tensor.
+        # Fixed once the pipe is established: a yes is remembered per device pair. A no is asked
+        # again next time, because a pipe that is still being set up answers no for every pair.
         key = (local, target)
-        known = self._layouts.get(key)
-        if known is None:
-            known = self._layouts[key] = bool(self._p.channel_supports_layouts(local, target))
+        if self._layouts.get(key):
+            return True
+        known = bool(self._p.channel_supports_layouts(local, target))
+        if known:
+            self._layouts[key] = True
         return known
 
     def _add_tensor(self, out, t: torch.Tensor, target: Optional[str], metadata: Optional[bytes] = None,
                     streams: Optional[Dict[torch.device, int]] = None) -> None:
         local = _device_str(t.device)
+        if (t.device.type == "cpu" and target is not None and target.startswith("cuda") and t.is_contiguous()
+                and t.numel() > 0 and torch.cuda.is_available() and t.is_pinned()):
+            # Pinned host memory bound for a GPU: with unified addressing the device can read it in
+            # place, so the push kernel of the current GPU takes it straight from host memory into
+            # the receiving GPU (one pass over PCIe, no staging copy on this side). The message then
+            # says the tensor comes from that GPU.
+            gpu = torch.device("cuda", torch.cuda.current_device())
+            if self._supports_layouts(_device_str(gpu), target):
+                return self._add_raw(out, t, t.data_ptr(), gpu, target, metadata, streams, None)
         view = None
-        code = DTYPE_CODES.get(t.dtype, 0)
         if not t.is_contiguous():
             packable = (
                 t.dim() == 2
@@ -157,24 +168,29 @@ class Pipe:
                 view = (t.shape[0], t.shape[1], t.stride(0), t.stride(1))
             else:
                 t = t.contiguous()
+        self._add_raw(out, t, t.data_ptr(), t.device, target, metadata, streams, view)
+
+    def _add_raw(self, out, t: torch.Tensor, ptr: int, device: torch.device, target: Optional[str],
+                 metadata: Optional[bytes], streams: Optional[Dict[torch.device, int]], view) -> None:
+        """Adds `t` as a tensor that the library reads at `ptr` on behalf of `device`."""
         meta = metadata if metadata is not None else (
             '{"dtype": "%s", "shape": %s}' % (_DTYPE_NAMES.get(t.dtype) or str(t.dtype).replace("torch.", ""),
                                               list(t.shape))).encode()
-        dev_type, dev_index = local.split(":")
+        dev_type, dev_index = _device_str(device).split(":")
         if streams is None:
-            stream = _stream_handle(t.device)
+            stream = _stream_handle(device)
         else:
-            stream = streams.get(t.device)
+            stream = streams.get(device)
             if stream is None:
-                stream = streams[t.device] = _stream_handle(t.device)
+                stream = streams[device] = _stream_handle(device)
         out.add_tensor(
-            t.data_ptr(),
+            ptr,
             t.numel() * t.element_size(),
             dev_type,
             int(dev_index),
             stream,
             meta,
-            code,
+            DTYPE_CODES.get(t.dtype, 0),
             view,
             target,
             t,
@@ -209,6 +225,21 @@ class Pipe:
         `cast` maps a tensor index to the dtype this side wants it converted to on the way."""
         fut: Future = Future()
         cast = cast or {}
+        # The descriptor arrives on a library thread, whose notion of "current device" and "current
+        # stream" is not the caller's: both are taken here, on the caller's thread, and the
+        # allocation below happens under them. The received tensors are then ordered on the stream
+        # the caller was working on, and belong to it as far as torch's allocator is concerned.
+        if torch.cuda.is_available() and torch.cuda.is_initialized():
+            caller_device = torch.cuda.current_device()
+            caller_streams = {i: torch.cuda.current_stream(i) for i in range(torch.cuda.device_count())}
+        else:
+            caller_device, caller_streams = None, {}
+
+        def stream_of(dev: torch.device):
+            if dev.type != "cuda":
+                return None
+            index = dev.index if dev.index is not None else caller_device
+            return caller_streams.get(index) or torch.cuda.current_stream(dev)
 
         def on_descriptor(err: str, desc: dict) -> None:
             if err:
@@ -231,12 +262,20 @@ class Pipe:
                     shape = meta[1] if meta else [td["length"]]
                     want = cast.get(i)
                     dst_dtype = want if want is not None else src_dtype
+                    here = caller_device if caller_device is not None else 0
                     where = td["target_device"] or device or (
-                        f"cuda:{torch.cuda.current_device()}" if td["source_device"].startswith("cuda") else "cpu")
+                        f"cuda:{here}" if td["source_device"].startswith("cuda") else "cpu")
                     if out is not None:
                         t = out[i]
+                        stream = stream_of(t.device)
                     else:
-                        t = torch.empty(shape, dtype=dst_dtype, device=where.replace("cpu:0", "cpu"))
+                        where_dev = torch.device(where.replace("cpu:0", "cpu"))
+                        stream = stream_of(where_dev)
+                        if stream is not None:
+                            with torch.cuda.stream(stream):
+                                t = torch.empty(shape, dtype=dst_dtype, device=where_dev)
+                        else:
+                            t = torch.empty(shape, dtype=dst_dtype, device=where_dev)
                     msg.tensors.append(t)
                     dev_type, _, dev_index = _device_str(t.device).partition(":")
                     cast_code = None
@@ -244,7 +283,8 @@ class Pipe:
                         if want not in _CASTABLE or src_dtype not in _CASTABLE:
                             raise ValueError(f"cannot convert {src_dtype} to {want} in flight")
                         cast_code = DTYPE_CODES[want]
-                    alloc.add_tensor(t.data_ptr(), dev_type, int(dev_index), _stream_handle(t.device), cast_code,
+                    alloc.add_tensor(t.data_ptr(), dev_type, int(dev_index),
+                                     stream.cuda_stream if stream is not None else 0, cast_code,
                                      DTYPE_CODES.get(src_dtype, 0), t)
 
                 def on_read(err2: str) -> None:

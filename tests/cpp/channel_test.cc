@@ -6,6 +6,7 @@
 
 #include <random>
 
+#include "channel_wiring.h"
 #include "test_util.h"
 
 using namespace tpb;
@@ -35,50 +36,6 @@ const Backend kBackends[] = {
     {"xth", [] { return channel::xth::create(); }, false},
     {"mpt", [] { return makeMpt(); }, false},
     {"cma", [] { return channel::cma::create(); }, true},
-};
-
-// Opens `n` tagged connections between two transport contexts. The server side sorts them by tag.
-struct Wiring {
-  std::shared_ptr<transport::Context> tctx = transport::uv::create();
-  std::shared_ptr<transport::Listener> listener;
-  std::string listen() {
-    listener = tctx->listen("127.0.0.1");
-    return listener->addr();
-  }
-  std::vector<std::shared_ptr<transport::Connection>> acceptAll(size_t n) {
-    std::vector<std::shared_ptr<transport::Connection>> out(n);
-    for (size_t i = 0; i < n; ++i) {
-      std::promise<std::shared_ptr<transport::Connection>> pc;
-      listener->accept([&](const Error& e, std::shared_ptr<transport::Connection> c) { pc.set_value(e ? nullptr : c); });
-      auto fc = pc.get_future();
-      auto c = waitFor(fc);
-      if (!c) throw TestFailure("accept failed");
-      std::promise<uint64_t> tag;
-      c->read([&](const Error& e, const void* p, size_t len) {
-        uint64_t v = UINT64_MAX;
-        if (!e && len == 8) std::memcpy(&v, p, 8);
-        tag.set_value(v);
-      });
-      auto ft = tag.get_future();
-      uint64_t idx = waitFor(ft);
-      if (idx >= n) throw TestFailure("bad connection tag");
-      out[idx] = c;
-    }
-    return out;
-  }
-  std::vector<std::shared_ptr<transport::Connection>> connectAll(const std::string& addr, size_t n) {
-    std::vector<std::shared_ptr<transport::Connection>> out;
-    for (size_t i = 0; i < n; ++i) {
-      auto c = tctx->connect(addr);
-      auto tag = std::make_shared<uint64_t>(i);
-      std::promise<Error> pw;
-      c->write(tag.get(), 8, [&, tag](const Error& e) { pw.set_value(e); });
-      auto fw = pw.get_future();
-      if (waitFor(fw)) throw TestFailure("tag write failed");
-      out.push_back(std::move(c));
-    }
-    return out;
-  }
 };
 
 void sendSync(channel::Channel& ch, void* p, size_t n) {
@@ -468,7 +425,7 @@ TPB_TEST(Channel, CudaP2pOptionsFollowTheEnvironment) {
                         "TPB_CUDA_P2P_WAIT_KERNEL", "TPB_CUDA_P2P_WAIT_TIMEOUT_MS", "TPB_CUDA_P2P_BULK"})
     ::unsetenv(n);
   p2p::Options d = p2p::applyEnvironment(p2p::Options());
-  EXPECT_EQ(d.eagerThreshold, size_t(64 * 1024));
+  EXPECT_EQ(d.eagerThreshold, size_t(1u << 20));
 }
 
 // Every channel context can be dropped without join(): its destructor closes and joins on its

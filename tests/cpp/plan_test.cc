@@ -180,3 +180,51 @@ TPB_TEST(Plan, NarrowMatricesFollowTheDestinationAndTheTuning) {
   appendToPlan(plan, v, true);
   EXPECT_EQ(plan.entries.back().numTiles, uint32_t(32));
 }
+
+// ---- the cache of opened IPC mappings (bookkeeping only: the two driver calls are counters) ----
+#include "channel/cuda_p2p/mapping_cache.h"
+
+TPB_TEST(Plan, MappingsAreKeyedByHandleAndAccessingDeviceAndIdleOnesAreClosed) {
+  using tpb::channel::cuda_p2p::MappingCache;
+  MappingCache cache;
+  std::vector<std::pair<uintptr_t, int>> opened, closed;
+  uintptr_t next = 0x1000;
+  cache.setBackendForTesting(
+      [&](const MappingCache::Handle&, int device, size_t* size) {
+        *size = 4096;
+        opened.emplace_back(next, device);
+        void* p = reinterpret_cast<void*>(next);
+        next += 0x1000;
+        return p;
+      },
+      [&](void* base, int device) { closed.emplace_back(reinterpret_cast<uintptr_t>(base), device); });
+  cache.setLimits(4, 0);  // at most four mappings; anything not in use this instant counts as idle
+  MappingCache::Handle a{}, b{};
+  a[0] = 1;
+  b[0] = 2;
+  size_t size = 0;
+  std::string why;
+  // The same allocation seen from two GPUs is two mappings: peer access is enabled per accessing
+  // device when a mapping is opened.
+  void* a0 = cache.open(a, 0, &size, &why);
+  void* a1 = cache.open(a, 1, &size, &why);
+  EXPECT_TRUE(a0 != nullptr && a1 != nullptr && a0 != a1);
+  EXPECT_EQ(size, size_t(4096));
+  EXPECT_EQ(opened.size(), size_t(2));
+  EXPECT_TRUE(cache.open(a, 0, &size, &why) == a0);  // a hit: nothing is opened again
+  EXPECT_EQ(opened.size(), size_t(2));
+  // A pinned mapping (a channel's arena) survives any eviction.
+  void* pinned = cache.open(b, 0, nullptr, &why, /*pin=*/true);
+  const uint64_t before = cache.generation();
+  MappingCache::Handle more{};
+  for (int i = 0; i < 6; ++i) {
+    more[1] = static_cast<uint8_t>(10 + i);
+    EXPECT_TRUE(cache.open(more, 0, nullptr, &why) != nullptr);
+  }
+  EXPECT_TRUE(cache.size() <= 5);
+  EXPECT_TRUE(!closed.empty());
+  EXPECT_TRUE(cache.generation() != before);  // holders of old addresses must look them up again
+  for (auto& c : closed) EXPECT_TRUE(c.first != reinterpret_cast<uintptr_t>(pinned));
+  EXPECT_TRUE(cache.open(b, 0, nullptr, &why) == pinned);
+  EXPECT_EQ(cache.closedCount(), uint64_t(closed.size()));
+}

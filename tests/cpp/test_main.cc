@@ -50,7 +50,7 @@ int main(int argc, char** argv) {
       while (std::getline(ss, item, ',')) filters.push_back(item);
     }
   }
-  int failed = 0, passed = 0, skipped = 0;
+  int failed = 0, passed = 0, skipped = 0, matched = 0;
   for (auto& t : tpbtest::registry()) {
     if (t.needsGpu != gpu) continue;
     if (!filters.empty()) {
@@ -58,6 +58,7 @@ int main(int argc, char** argv) {
       for (auto& f : filters) match = match || t.name.find(f) != std::string::npos;
       if (!match) continue;
     }
+    ++matched;
     if (list) {
       std::cout << t.name << "\n";
       continue;
@@ -115,5 +116,10 @@ int main(int argc, char** argv) {
     }
   }
   if (!list) std::cout << passed << " passed, " << failed << " failed, " << skipped << " skipped" << std::endl;
+  if (!filters.empty() && matched == 0) {
+    // A filter that selects nothing is a typo in whoever runs the suites, not a pass.
+    std::cout << "no " << (gpu ? "GPU" : "CPU") << " test matches the filter" << std::endl;
+    return 2;
+  }
   return failed ? 1 : 0;
 }

@@ -3,8 +3,11 @@
 // the reference's uv transport and basic channel. The test suite runs this library's pipes against
 // it in both directions to prove that the handshake and the descriptor wire format are compatible.
 //
-//   ref_interop server <port>            listen on 127.0.0.1:<port>, echo every message, forever
-//   ref_interop client <address> <n>     connect to uv://<address>, send n messages, check echoes
+//   ref_interop server <port> [full]          listen on 127.0.0.1:<port>, echo every message, forever
+//   ref_interop client <address> <n> [full]   connect to uv://<address>, send n messages, check echoes
+// With "full" the context carries every CPU backend the way PyTorch's RPC agent registers them
+// (transports uv and shm; channels basic, cma, mpt_uv over three lanes), so that the other side's negotiation has to
+// steer clear of everything the two libraries do not really share.
 #include <cstring>
 #include <future>
 #include <iostream>
@@ -16,10 +19,23 @@
 
 namespace tp = tensorpipe;
 
+bool gFull = false;
+
 std::shared_ptr<tp::Context> makeContext(const std::string& name) {
   auto ctx = std::make_shared<tp::Context>(tp::ContextOptions().name(name));
   ctx->registerTransport(0, "uv", tp::transport::uv::create());
   ctx->registerChannel(0, "basic", tp::channel::basic::create());
+  if (gFull) {
+    ctx->registerTransport(10, "shm", tp::transport::shm::create());
+    ctx->registerChannel(10, "cma", tp::channel::cma::create());
+    std::vector<std::shared_ptr<tp::transport::Context>> lanes;
+    std::vector<std::shared_ptr<tp::transport::Listener>> laneListeners;
+    for (int i = 0; i < 3; ++i) {
+      lanes.push_back(tp::transport::uv::create());
+      laneListeners.push_back(lanes.back()->listen("127.0.0.1"));
+    }
+    ctx->registerChannel(5, "mpt_uv", tp::channel::mpt::create(std::move(lanes), std::move(laneListeners)));
+  }
   return ctx;
 }
 
@@ -71,9 +87,12 @@ void echoLoop(std::shared_ptr<tp::Pipe> pipe) {
 int main(int argc, char** argv) {
   if (argc < 3) return 2;
   std::string mode = argv[1];
+  gFull = std::string(argv[argc - 1]) == "full";
   if (mode == "server") {
     auto ctx = makeContext("ref-server");
-    auto listener = ctx->listen({std::string("uv://127.0.0.1:") + argv[2]});
+    std::vector<std::string> urls = {std::string("uv://127.0.0.1:") + argv[2]};
+    if (gFull) urls.push_back("shm://");
+    auto listener = ctx->listen(urls);
     std::function<void()> arm = [&]() {
       listener->accept([&](const tp::Error& e, std::shared_ptr<tp::Pipe> pipe) {
         if (e) return;

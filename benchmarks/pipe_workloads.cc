@@ -16,6 +16,18 @@
 //       rank 0 serves, ranks 1..N-1 (one forked process each, GPU r mod #GPUs) issue requests of a
 //       256 B payload + one 4 KiB fp32 CUDA tensor and wait for a same-shaped reply; prints
 //       p50 / p99 round-trip latency over all clients and messages per second.
+//   --workload all_pairs  --ranks N  [--iters 10]
+//       N forked processes, one per GPU; every rank sends every other rank a message of 64 CUDA
+//       tensors (fp32 / bf16 / int64, 1 KiB - 16 MiB log-uniform), two messages in flight per
+//       pipe, all pipes at once. Against this library a quarter of the tensors are transposed 2-D
+//       views and half of the fp32 tensors are converted to bf16 on the way; the reference has
+//       neither, so it moves contiguous tensors of the delivered sizes (its layout work is left
+//       out, in its favour). Prints aggregate and per-GPU GB/s of delivered bytes, device-timed.
+//   --workload pp_1f1b  --ranks S  [--iters 5] [--micro-batches 32] [--fwd-us 600] [--bwd-us 1200]
+//       S pipeline stages, one process and GPU each; 16 MiB activations forward and 16 MiB
+//       gradients backward between neighbours through pipes, 1F1B schedule, `micro-batches` per
+//       step; the stage's compute is a device memset calibrated to last fwd-us / bwd-us, the same
+//       for both libraries. Prints steps per second.
 #include <cuda_runtime.h>
 #include <sys/mman.h>
 #include <sys/wait.h>
@@ -23,6 +35,8 @@
 
 #include <algorithm>
 #include <atomic>
+#include <cmath>
+#include <mutex>
 #include <chrono>
 #include <cstring>
 #include <functional>
@@ -53,6 +67,7 @@ struct Options {
   std::string workload = "cpu_pingpong", transport = "uv", channel = "basic";
   int iters = 1000, ranks = 2, warmup = 20;
   size_t bytes = 64;
+  int microBatches = 32, fwdUs = 600, bwdUs = 1200;
 };
 
 static void die(const std::string& what) {
@@ -67,7 +82,29 @@ struct Shared {
   std::atomic<int> clientsDone;
   double p50[64], p99[64], mean[64], seconds[64];
   std::atomic<int> failed;
+  // multi-rank workloads: every rank's listener URL, a reusable barrier, per-rank results
+  char urls[64][128];
+  std::atomic<int> urlsReady;
+  std::atomic<int> barrierCount;
+  std::atomic<int> barrierPhase;
+  double deviceMs[64], hostMs[64];
+  uint64_t delivered;
 };
+
+// All `n` ranks meet here; a rank that failed elsewhere makes the others give up instead of hanging.
+static void rankBarrier(Shared* sh, int n) {
+  const int phase = sh->barrierPhase.load();
+  if (sh->barrierCount.fetch_add(1) + 1 == n) {
+    sh->barrierCount = 0;
+    sh->barrierPhase.fetch_add(1);
+    return;
+  }
+  auto t0 = Clock::now();
+  while (sh->barrierPhase.load() == phase) {
+    if (sh->failed.load() || std::chrono::duration<double>(Clock::now() - t0).count() > 300) die("a peer rank failed");
+    std::this_thread::yield();
+  }
+}
 
 static double percentile(std::vector<double> v, double q) {
   std::sort(v.begin(), v.end());
@@ -518,6 +555,415 @@ static int rpcFanIn(const Options& o, Shared* sh) {
   return 0;
 }
 
+
+// ---- workload 3: all pairs ----------------------------------------------------------------------
+namespace mesh {
+
+struct Spec {
+  int dtype;  // 0 fp32, 1 bf16, 2 int64
+  bool transposed, cast;
+  int64_t rows, cols;
+  uint64_t srcOff, dstOff, srcBytes, dstBytes;
+};
+struct Layout {
+  std::vector<Spec> specs;
+  uint64_t srcTotal = 0, dstTotal = 0, delivered = 0;
+};
+// Same generator as the library's own ring benchmark: 64 tensors, dtype cycling fp32 / bf16 / int64,
+// sizes log-uniform in [1 KiB, 16 MiB], every fourth a transposed view of 8 - 4096 columns, every
+// other fp32 tensor delivered as bf16.
+static Layout makeLayout(uint64_t seed) {
+  Layout L;
+  std::mt19937_64 rng(seed);
+  int fp32Count = 0;
+  for (int i = 0; i < 64; ++i) {
+    Spec s{};
+    s.dtype = i % 3;
+    const uint64_t es = s.dtype == 0 ? 4 : (s.dtype == 1 ? 2 : 8);
+    const double lg = std::log(1024.0) + (std::log(16.0 * 1024 * 1024) - std::log(1024.0)) *
+                                              (static_cast<double>(rng() % 100000) / 100000.0);
+    const uint64_t bytes = static_cast<uint64_t>(std::exp(lg));
+    s.transposed = i % 4 == 3;
+    s.cols = 64;
+    if (s.transposed) {
+      const double lc = std::log(8.0) + (std::log(4096.0) - std::log(8.0)) * (static_cast<double>(rng() % 100000) / 100000.0);
+      s.cols = static_cast<int64_t>(std::exp(lc));
+    }
+    s.rows = static_cast<int64_t>(std::max<uint64_t>(1, bytes / es / s.cols));
+    const uint64_t elems = static_cast<uint64_t>(s.rows) * s.cols;
+    s.srcBytes = elems * es;
+    if (s.dtype == 0) s.cast = (fp32Count++ % 2) == 0;
+    s.dstBytes = s.cast ? elems * 2 : s.srcBytes;
+    s.srcOff = L.srcTotal;
+    s.dstOff = L.dstTotal;
+    L.srcTotal += (s.srcBytes + 255) / 256 * 256;
+    L.dstTotal += (s.dstBytes + 255) / 256 * 256;
+    L.delivered += s.dstBytes;
+    L.specs.push_back(s);
+  }
+  return L;
+}
+
+}  // namespace mesh
+
+static int allPairs(const Options& o, Shared* sh) {
+  const int world = o.ranks;
+  if (world < 2 || world > 64) die("--ranks must be 2..64");
+  const mesh::Layout layout = mesh::makeLayout(1234);
+  sh->delivered = layout.delivered;
+  std::vector<pid_t> pids;
+  for (int rank = 0; rank < world; ++rank) {
+    pid_t pid = fork();
+    if (pid != 0) {
+      pids.push_back(pid);
+      continue;
+    }
+    int numGpus = 0;
+    cudaGetDeviceCount(&numGpus);
+    if (numGpus == 0) die("no GPU");
+    const int dev = rank % numGpus;
+    cudaSetDevice(dev);
+    cudaStream_t recvStream;
+    cudaStreamCreateWithFlags(&recvStream, cudaStreamNonBlocking);
+    std::vector<cudaStream_t> sendStreams(world, nullptr);
+    for (int j = 0; j < world; ++j)
+      if (j != rank) cudaStreamCreateWithFlags(&sendStreams[j], cudaStreamNonBlocking);
+    uint8_t* src = nullptr;
+    uint8_t* dst[2] = {nullptr, nullptr};
+    // Against the reference the source holds contiguous tensors of the delivered sizes.
+#ifdef USE_REFERENCE
+    const uint64_t srcTotal = layout.dstTotal;
+#else
+    const uint64_t srcTotal = layout.srcTotal;
+#endif
+    if (cudaMalloc(&src, srcTotal) != cudaSuccess) die("cudaMalloc");
+    cudaMemset(src, 0x3c, srcTotal);
+    for (auto& d : dst)
+      if (cudaMalloc(&d, layout.dstTotal * (world - 1)) != cudaSuccess) die("cudaMalloc");
+    cudaDeviceSynchronize();
+    cudaEvent_t evStart, evEnd;
+    cudaEventCreate(&evStart);
+    cudaEventCreate(&evEnd);
+
+    auto ctx = makeCudaContext("rank" + std::to_string(rank));
+    auto listener = ctx->listen({"uv://127.0.0.1", "shm://"});
+    std::strncpy(sh->urls[rank], listener->url("uv").c_str(), sizeof(sh->urls[rank]) - 1);
+    sh->urlsReady.fetch_add(1);
+    while (sh->urlsReady.load() < world) std::this_thread::sleep_for(std::chrono::milliseconds(1));
+
+    // Pipes: one outgoing per peer (rotation order, so that the ranks do not all start with the
+    // same receiver), one incoming per peer.
+    std::mutex mu;
+    std::vector<std::shared_ptr<lib::Pipe>> incoming;
+    std::promise<void> allIn;
+    std::function<void()> arm = [&]() {
+      listener->accept([&](const lib::Error& e, std::shared_ptr<lib::Pipe> p) {
+        if (e) return;
+        bool done;
+        {
+          std::unique_lock<std::mutex> l(mu);
+          incoming.push_back(std::move(p));
+          done = static_cast<int>(incoming.size()) == world - 1;
+        }
+        if (done) allIn.set_value();
+        else arm();
+      });
+    };
+    arm();
+    std::vector<std::shared_ptr<lib::Pipe>> outgoing;
+    std::vector<int> outRank;
+    for (int d = 1; d < world; ++d) {
+      const int j = (rank + d) % world;
+      outgoing.push_back(ctx->connect(sh->urls[j]));
+      outRank.push_back(j);
+    }
+    if (allIn.get_future().wait_for(std::chrono::seconds(120)) != std::future_status::ready) die("mesh did not come up");
+
+    auto runRound = [&](int iters, double* deviceMs, double* hostMs) {
+      const int totalRecv = iters * (world - 1), totalSend = iters * (world - 1);
+      std::atomic<int> received{0}, sent{0};
+      std::promise<void> recvDone, sendDone;
+      std::vector<int> readsIssued(world, 0);
+      std::function<void(size_t, int)> armRead = [&](size_t k, int remaining) {
+        if (remaining == 0) return;
+        auto pipe = incoming[k];
+        pipe->readDescriptor([&, k, remaining, pipe](const lib::Error& e, lib::Descriptor d) {
+          if (e) die("readDescriptor: " + e.what());
+          if (d.tensors.size() != layout.specs.size()) die("unexpected message shape");
+          uint8_t* base = dst[readsIssued[k]++ & 1] + k * layout.dstTotal;
+          lib::Allocation a;
+          for (const auto& s : layout.specs) {
+            lib::Allocation::Tensor t;
+            t.buffer = cudaBuffer(base + s.dstOff, recvStream, dev);
+#ifndef USE_REFERENCE
+            if (s.cast) {
+              t.castTo = lib::DType::kBF16;
+              t.sourceDtype = lib::DType::kF32;
+            }
+#endif
+            a.tensors.push_back(t);
+          }
+          pipe->read(std::move(a), [&, k, remaining](const lib::Error& e2) {
+            if (e2) die("read: " + e2.what());
+            if (received.fetch_add(1) + 1 == totalRecv) {
+              cudaSetDevice(dev);
+              cudaEventRecord(evEnd, recvStream);
+              recvDone.set_value();
+            } else {
+              armRead(k, remaining - 1);
+            }
+          });
+        });
+      };
+      std::function<void(size_t, int)> sendOne = [&](size_t k, int remaining) {
+        if (remaining == 0) return;
+        int targetDev = outRank[k] % numGpus;
+        lib::Message msg;
+        for (const auto& s : layout.specs) {
+          lib::Message::Tensor t;
+#ifdef USE_REFERENCE
+          t.buffer = cudaBuffer(src + s.dstOff, sendStreams[outRank[k]], dev);
+          t.length = s.dstBytes;
+#else
+          t.buffer = cudaBuffer(src + s.srcOff, sendStreams[outRank[k]], dev);
+          t.length = s.srcBytes;
+          t.dtype = s.dtype == 0 ? lib::DType::kF32 : (s.dtype == 1 ? lib::DType::kBF16 : lib::DType::kI64);
+          if (s.transposed) {
+            lib::StridedView v;
+            v.dtype = t.dtype;
+            v.rows = s.rows;
+            v.cols = s.cols;
+            v.rowStride = 1;
+            v.colStride = s.rows;
+            t.view = v;
+          }
+#endif
+          t.targetDevice = lib::Device(lib::kCudaDeviceType, targetDev);
+          msg.tensors.push_back(t);
+        }
+        outgoing[k]->write(std::move(msg), [&, k, remaining](const lib::Error& e) {
+          if (e) die("write: " + e.what());
+          if (sent.fetch_add(1) + 1 == totalSend) sendDone.set_value();
+          sendOne(k, remaining - 1);
+        });
+      };
+      rankBarrier(sh, world);
+      auto t0 = Clock::now();
+      cudaEventRecord(evStart, recvStream);
+      for (int chain = 0; chain < 2; ++chain) {
+        const int share = chain == 0 ? (iters + 1) / 2 : iters / 2;
+        for (size_t k = 0; k < incoming.size(); ++k) armRead(k, share);
+      }
+      for (int chain = 0; chain < 2; ++chain) {
+        const int share = chain == 0 ? (iters + 1) / 2 : iters / 2;
+        for (size_t k = 0; k < outgoing.size(); ++k) sendOne(k, share);
+      }
+      if (recvDone.get_future().wait_for(std::chrono::seconds(300)) != std::future_status::ready) die("receiving timed out");
+      if (sendDone.get_future().wait_for(std::chrono::seconds(300)) != std::future_status::ready) die("sending timed out");
+      cudaEventSynchronize(evEnd);
+      float ms = 0;
+      cudaEventElapsedTime(&ms, evStart, evEnd);
+      *deviceMs = ms;
+      *hostMs = std::chrono::duration<double, std::milli>(Clock::now() - t0).count();
+      for (int j = 0; j < world; ++j)
+        if (sendStreams[j]) cudaStreamSynchronize(sendStreams[j]);
+    };
+    double dms = 0, hms = 0;
+    runRound(std::max(2, o.warmup > 10 ? 3 : o.warmup), &dms, &hms);
+    runRound(o.iters, &dms, &hms);
+    sh->deviceMs[rank] = dms;
+    sh->hostMs[rank] = hms;
+    rankBarrier(sh, world);
+    outgoing.clear();
+    incoming.clear();
+    ctx->join();
+    _exit(0);
+  }
+  bool ok = true;
+  for (pid_t pid : pids) {
+    int st = 0;
+    waitpid(pid, &st, 0);
+    if (!WIFEXITED(st) || WEXITSTATUS(st)) {
+      ok = false;
+      sh->failed = 1;
+    }
+  }
+  if (!ok) {
+    std::cout << "{\"impl\": \"" << kImpl << "\", \"workload\": \"all_pairs\", \"error\": \"a rank failed\"}" << std::endl;
+    return 1;
+  }
+  double ms = 0;
+  for (int r = 0; r < world; ++r) ms = std::max(ms, sh->deviceMs[r]);
+  ms /= o.iters;
+  const double perGpu = static_cast<double>(sh->delivered) * (world - 1) / (ms * 1e-3) / 1e9;
+  std::cout << "{\"impl\": \"" << kImpl << "\", \"workload\": \"all_pairs\", \"ranks\": " << world
+            << ", \"tensors_per_message\": 64, \"bytes_per_message\": " << sh->delivered
+            << ", \"ms_per_round\": " << ms << ", \"per_gpu_egress_GBps\": " << perGpu
+            << ", \"aggregate_GBps\": " << perGpu * world << ", \"per_gpu_fraction_of_900\": " << perGpu / 900.0
+            << ", \"layout_work\": \""
+#ifdef USE_REFERENCE
+            << "none: contiguous tensors of the delivered sizes"
+#else
+            << "16 transposed views of 8-4096 columns, 11 fp32->bf16 conversions"
+#endif
+            << "\"}" << std::endl;
+  return 0;
+}
+
+// ---- workload 4: 1F1B pipeline --------------------------------------------------------------------
+static int pipeline1F1B(const Options& o, Shared* sh) {
+  const int stages = o.ranks;
+  if (stages < 2 || stages > 64) die("--ranks must be 2..64");
+  constexpr size_t kActivation = 16u << 20;  // 8 x 1024 tokens x 1024 features, bf16
+  const int M = o.microBatches;
+  std::vector<pid_t> pids;
+  for (int s = 0; s < stages; ++s) {
+    pid_t pid = fork();
+    if (pid != 0) {
+      pids.push_back(pid);
+      continue;
+    }
+    int numGpus = 0;
+    cudaGetDeviceCount(&numGpus);
+    if (numGpus == 0) die("no GPU");
+    const int dev = s % numGpus;
+    cudaSetDevice(dev);
+    cudaStream_t stream;
+    cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking);
+    // Activation / gradient buffers: one per micro-batch in flight (at most `stages` of them).
+    const int slots = stages + 1;
+    std::vector<uint8_t*> actIn(slots), actOut(slots), gradIn(slots), gradOut(slots);
+    for (int i = 0; i < slots; ++i) {
+      cudaMalloc(&actIn[i], kActivation);
+      cudaMalloc(&actOut[i], kActivation);
+      cudaMalloc(&gradIn[i], kActivation);
+      cudaMalloc(&gradOut[i], kActivation);
+    }
+    // "Compute": a memset sized so that it lasts the requested time on this GPU.
+    uint8_t* scratch = nullptr;
+    const size_t scratchBytes = 1ull << 30;
+    if (cudaMalloc(&scratch, scratchBytes) != cudaSuccess) die("cudaMalloc scratch");
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    for (int i = 0; i < 3; ++i) cudaMemsetAsync(scratch, i, scratchBytes, stream);
+    cudaEventRecord(e0, stream);
+    cudaMemsetAsync(scratch, 7, scratchBytes, stream);
+    cudaEventRecord(e1, stream);
+    cudaEventSynchronize(e1);
+    float msPerGiB = 0;
+    cudaEventElapsedTime(&msPerGiB, e0, e1);
+    auto compute = [&](int us) {
+      size_t bytes = static_cast<size_t>(static_cast<double>(us) * 1e-3 / msPerGiB * scratchBytes);
+      while (bytes > 0) {
+        const size_t n = std::min(bytes, scratchBytes);
+        cudaMemsetAsync(scratch, 1, n, stream);
+        bytes -= n;
+      }
+    };
+
+    auto ctx = makeCudaContext("stage" + std::to_string(s));
+    auto listener = ctx->listen({"uv://127.0.0.1", "shm://"});
+    std::strncpy(sh->urls[s], listener->url("uv").c_str(), sizeof(sh->urls[s]) - 1);
+    sh->urlsReady.fetch_add(1);
+    while (sh->urlsReady.load() < stages) std::this_thread::sleep_for(std::chrono::milliseconds(1));
+    // One pipe per neighbour pair: stage s dials stage s+1; activations go down it, gradients come back up.
+    std::shared_ptr<lib::Pipe> next, prev;
+    std::promise<std::shared_ptr<lib::Pipe>> accepted;
+    if (s > 0)
+      listener->accept([&](const lib::Error& e, std::shared_ptr<lib::Pipe> p) {
+        if (e) die("accept: " + e.what());
+        accepted.set_value(std::move(p));
+      });
+    if (s < stages - 1) next = ctx->connect(sh->urls[s + 1]);
+    if (s > 0) prev = accepted.get_future().get();
+    const int nextDev = (s + 1) % numGpus, prevDev = (s + stages - 1) % numGpus;
+
+    auto sendTensor = [&](lib::Pipe& pipe, uint8_t* p, int targetDev) {
+      lib::Message m;
+      lib::Message::Tensor t;
+      t.buffer = cudaBuffer(p, stream, dev);
+      t.length = kActivation;
+      t.targetDevice = lib::Device(lib::kCudaDeviceType, targetDev);
+      m.tensors.push_back(t);
+      pipe.write(std::move(m), [](const lib::Error& e) {
+        if (e) die("write: " + e.what());
+      });
+    };
+    auto recvTensor = [&](lib::Pipe& pipe, uint8_t* p) {
+      std::promise<void> got;
+      pipe.readDescriptor([&](const lib::Error& e, lib::Descriptor) {
+        if (e) die("readDescriptor: " + e.what());
+        lib::Allocation a;
+        lib::Allocation::Tensor t;
+        t.buffer = cudaBuffer(p, stream, dev);
+        a.tensors.push_back(t);
+        pipe.read(std::move(a), [&](const lib::Error& e2) {
+          if (e2) die("read: " + e2.what());
+          got.set_value();
+        });
+      });
+      if (got.get_future().wait_for(std::chrono::seconds(120)) != std::future_status::ready) die("a stage stopped answering");
+    };
+    auto forward = [&](int mb) {
+      if (s > 0) recvTensor(*prev, actIn[mb % slots]);
+      compute(o.fwdUs);
+      if (s < stages - 1) sendTensor(*next, actOut[mb % slots], nextDev);
+    };
+    auto backward = [&](int mb) {
+      if (s < stages - 1) recvTensor(*next, gradIn[mb % slots]);
+      compute(o.bwdUs);
+      if (s > 0) sendTensor(*prev, gradOut[mb % slots], prevDev);
+    };
+    auto step = [&]() {
+      // 1F1B: warm up with as many forwards as there are stages behind this one, then alternate,
+      // then drain the backwards.
+      const int warm = std::min(M, stages - 1 - s);
+      int f = 0, b = 0;
+      for (; f < warm; ++f) forward(f);
+      while (f < M) {
+        forward(f++);
+        backward(b++);
+      }
+      while (b < M) backward(b++);
+      cudaStreamSynchronize(stream);
+    };
+    for (int i = 0; i < std::max(1, std::min(o.warmup, 2)); ++i) step();
+    rankBarrier(sh, stages);
+    auto t0 = Clock::now();
+    for (int i = 0; i < o.iters; ++i) step();
+    sh->seconds[s] = std::chrono::duration<double>(Clock::now() - t0).count();
+    rankBarrier(sh, stages);
+    next.reset();
+    prev.reset();
+    ctx->join();
+    _exit(0);
+  }
+  bool ok = true;
+  for (pid_t pid : pids) {
+    int st = 0;
+    waitpid(pid, &st, 0);
+    if (!WIFEXITED(st) || WEXITSTATUS(st)) {
+      ok = false;
+      sh->failed = 1;
+    }
+  }
+  if (!ok) {
+    std::cout << "{\"impl\": \"" << kImpl << "\", \"workload\": \"pp_1f1b\", \"error\": \"a stage failed\"}" << std::endl;
+    return 1;
+  }
+  double seconds = 0;
+  for (int s = 0; s < stages; ++s) seconds = std::max(seconds, sh->seconds[s]);
+  // What the schedule costs with free communication: (M + stages - 1) slots of (fwd + bwd).
+  const double ideal = (o.microBatches + stages - 1) * (o.fwdUs + o.bwdUs) * 1e-6;
+  std::cout << "{\"impl\": \"" << kImpl << "\", \"workload\": \"pp_1f1b\", \"stages\": " << stages
+            << ", \"micro_batches\": " << o.microBatches << ", \"activation_bytes\": " << kActivation
+            << ", \"fwd_us\": " << o.fwdUs << ", \"bwd_us\": " << o.bwdUs << ", \"steps\": " << o.iters
+            << ", \"steps_per_second\": " << o.iters / seconds << ", \"seconds_per_step\": " << seconds / o.iters
+            << ", \"compute_only_seconds_per_step\": " << ideal << "}" << std::endl;
+  return 0;
+}
+
 int main(int argc, char** argv) {
   Options o;
   for (int i = 1; i + 1 < argc; i += 2) {
@@ -529,12 +975,17 @@ int main(int argc, char** argv) {
     else if (k == "--ranks") o.ranks = std::stoi(v);
     else if (k == "--warmup") o.warmup = std::stoi(v);
     else if (k == "--bytes") o.bytes = std::stoull(v);
+    else if (k == "--micro-batches") o.microBatches = std::stoi(v);
+    else if (k == "--fwd-us") o.fwdUs = std::stoi(v);
+    else if (k == "--bwd-us") o.bwdUs = std::stoi(v);
   }
   auto* sh = static_cast<Shared*>(mmap(nullptr, sizeof(Shared), PROT_READ | PROT_WRITE, MAP_SHARED | MAP_ANONYMOUS, -1, 0));
   std::memset(static_cast<void*>(sh), 0, sizeof(Shared));
   if (o.workload == "cpu_pingpong") return cpuPingPong(o, sh);
   if (o.workload == "rpc_fanin") return rpcFanIn(o, sh);
   if (o.workload == "transport_pingpong") return transportPingPong(o, sh);
+  if (o.workload == "all_pairs") return allPairs(o, sh);
+  if (o.workload == "pp_1f1b") return pipeline1F1B(o, sh);
   std::cerr << "unknown workload" << std::endl;
   return 2;
 }

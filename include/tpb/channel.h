@@ -123,8 +123,10 @@ namespace cuda_p2p {
 // TPB_CUDA_P2P_EAGER_THRESHOLD, _INBOX_BYTES, _MAX_CTAS, _WAIT_KERNEL (0/1), _FUSED_WAIT (0/1),
 // _WAIT_TIMEOUT_MS, _BULK (0/1), _CLOSE_TIMEOUT_MS.
 struct Options {
-  size_t eagerThreshold = 1u << 20;      // batches up to this many bytes go through the inbox
-  size_t inboxBytes = 32u << 20;         // per-peer inbox ring in device memory
+  size_t eagerThreshold = 64 * 1024;     // batches up to this many bytes go through the inbox: one
+                                          // control hop less (lower latency), one small kernel more on
+                                          // the receiver (which is why larger batches do not)
+  size_t inboxBytes = 16u << 20;         // per-peer inbox ring in device memory
   int maxCtas = 0;                        // 0 = one persistent CTA per SM, shared between the
                                           // channels that are sending from that GPU at the moment
   bool waitWithKernel = false;            // true: bounded wait kernel; false: stream memory op

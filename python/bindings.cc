@@ -124,7 +124,7 @@ PYBIND11_MODULE(_C, m) {
         o.useBulkCopy = useBulkCopy;
         return channel::cuda_p2p::create(o);
       },
-      py::arg("eager_threshold") = 1u << 20, py::arg("inbox_bytes") = 32u << 20, py::arg("max_ctas") = 0,
+      py::arg("eager_threshold") = 64 * 1024, py::arg("inbox_bytes") = 16u << 20, py::arg("max_ctas") = 0,
       py::arg("wait_with_kernel") = false, py::arg("use_bulk_copy") = true);
   m.def(
       "create_mpt_channel",
@@ -373,7 +373,7 @@ PYBIND11_MODULE(_C, m) {
              return std::make_unique<tools::RingBench>(o);
            }),
            py::arg("device") = 0, py::arg("use_shm") = true, py::arg("use_bulk_copy") = true,
-           py::arg("wait_with_kernel") = false, py::arg("eager_threshold") = 1u << 20, py::arg("max_ctas") = 0,
+           py::arg("wait_with_kernel") = false, py::arg("eager_threshold") = 64 * 1024, py::arg("max_ctas") = 0,
            py::arg("max_bytes") = 1ull << 30, py::arg("channel") = "cuda_p2p")
       .def("listen_url", &tools::RingBench::listenUrl)
       .def("connect", &tools::RingBench::connect, py::call_guard<py::gil_scoped_release>())

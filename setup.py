@@ -23,7 +23,7 @@ setup(
     name="tensorpipe_b200",
     version="0.1.0",
     description="A Blackwell-native tensor pipe: point-to-point messages of CPU and CUDA tensors",
-    packages=["tensorpipe_b200", "tensorpipe_b200.utils"],
+    packages=["tensorpipe_b200"],
     py_modules=["pytensorpipe"],
     package_data={"tensorpipe_b200": ["_C*.so"]},
     python_requires=">=3.9",

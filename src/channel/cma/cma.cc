@@ -61,8 +61,11 @@ std::shared_ptr<Context> create() {
   // A process that made itself non-dumpable cannot be read by its peers.
   if (::prctl(PR_GET_DUMPABLE, 0, 0, 0, 0) != 1) return std::make_shared<NonViableContext>();
 
+  // The prefix differs from the reference's ("cma:", tensorpipe/channel/cma/context_impl.cc:236-243)
+  // on purpose: this channel speaks its own protocol on one connection, the reference's speaks
+  // another on two, so the two must never select each other.
   std::ostringstream d;
-  d << "cma:" << *boot << "_" << *pidns << "_" << *userns << "_" << ::geteuid() << "_" << ::getegid();
+  d << "tpbcma1:" << *boot << "_" << *pidns << "_" << *userns << "_" << ::geteuid() << "_" << ::getegid();
 
   if (auto lsms = getLinuxSecurityModules()) {
     for (const auto& lsm : *lsms) {

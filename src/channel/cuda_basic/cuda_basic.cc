@@ -211,9 +211,12 @@ class ContextImpl final : public Context, public std::enable_shared_from_this<Co
     const int n = cudaDeviceCountNoThrow();
     if (n == 0) return;
     auto add = [&](const Device& d) {
+      // Same structure as the reference's descriptor (tensorpipe/channel/cuda_basic/context_impl.cc:
+      // 27-31,64-80) but with a prefixed inner descriptor, so that a reference peer's cuda_basic
+      // never matches: the chunking and the control traffic of the two differ.
       DeviceDescriptor dd;
       dd.deviceType = d.type;
-      dd.cpuDescriptor = it->second;
+      dd.cpuDescriptor = "tpbcb1:" + it->second;
       auto bytes = nop::encode(dd);
       descriptors_[d] = std::string(bytes.begin(), bytes.end());
     };
@@ -228,7 +231,10 @@ class ContextImpl final : public Context, public std::enable_shared_from_this<Co
     DeviceDescriptor l, r;
     if (!nop::decode(local.data(), local.size(), l) || !nop::decode(remote.data(), remote.size(), r)) return false;
     if (l.deviceType == kCpuDeviceType && r.deviceType == kCpuDeviceType) return false;  // not our job
-    return cpu_->canCommunicateWithRemote(l.cpuDescriptor, r.cpuDescriptor);
+    const std::string prefix = "tpbcb1:";
+    if (l.cpuDescriptor.compare(0, prefix.size(), prefix) != 0 || r.cpuDescriptor.compare(0, prefix.size(), prefix) != 0)
+      return false;
+    return cpu_->canCommunicateWithRemote(l.cpuDescriptor.substr(prefix.size()), r.cpuDescriptor.substr(prefix.size()));
   }
   std::shared_ptr<Channel> createChannel(std::vector<std::shared_ptr<transport::Connection>> conns, Endpoint ep) override {
     auto inner = cpu_->createChannel(std::move(conns), ep);

@@ -6,8 +6,8 @@
 // the context is built from N transport contexts and N listeners; the listening endpoint of a
 // channel sends ServerHello{(address, registration id) per lane} on the connection the pipe
 // provided; the connecting endpoint dials every lane and identifies itself with
-// ClientHello{registration id}; a tensor of L bytes is cut into N contiguous chunks of L/N bytes
-// (the last takes the remainder), chunk i travelling on lane i. The device descriptor is
+// ClientHello{registration id}; a tensor of L bytes is cut into N contiguous chunks at the byte offsets L*i/N
+// (rounded down), chunk i travelling on lane i. The device descriptor is
 // "N:<dd1>:<dd2>..." so both ends must have the same lane transports.
 #include <deque>
 #include <map>
@@ -241,7 +241,9 @@ void ChannelImpl::issue(Op op) {
     return;
   }
   const size_t n = lanes_.size();
-  const size_t per = op.length / n;
+  // Cut points at length * i / n, rounded down: what a reference peer's lanes expect
+  // (tensorpipe/channel/mpt/channel_impl.cc:203-215), so the two libraries can share the channel.
+  auto cut = [&](size_t i) { return static_cast<size_t>(static_cast<unsigned __int128>(op.length) * i / n); };
   struct Join {
     size_t remaining;
     Error error;
@@ -252,8 +254,8 @@ void ChannelImpl::issue(Op op) {
   join->cb = std::move(op.cb);
   auto self = shared_from_this();
   for (size_t i = 0; i < n; ++i) {
-    const size_t off = i * per;
-    const size_t len = i + 1 == n ? op.length - off : per;
+    const size_t off = cut(i);
+    const size_t len = cut(i + 1) - off;
     auto done = [self, join](const Error& e) {
       self->ctx_->loop_.deferToLoop([self, join, e]() {
         if (e && !join->error) join->error = e;

@@ -24,7 +24,9 @@ std::shared_ptr<Context> create() {
   auto boot = getBootID();
   auto pidns = getLinuxNamespaceId(LinuxNamespace::kPid);
   if (!boot || !pidns) return std::make_shared<NonViableContext>();
-  std::string d = *boot + "_" + *pidns + "_" + std::to_string(::getpid());
+  // Prefixed so that it never equals a reference peer's xth descriptor (the bare triple,
+  // tensorpipe/channel/xth/context_impl.cc:29-45): the two speak different protocols.
+  std::string d = "tpbxth1:" + *boot + "_" + *pidns + "_" + std::to_string(::getpid());
   return std::make_shared<copy::ContextImpl>(std::move(d), &copyInProcess, "TP_XTH_loop");
 }
 

@@ -83,10 +83,12 @@ __global__ void __launch_bounds__(kThreads) tpb_noalloc_push_kernel(unsigned cha
 
 thread_local std::string t_lastCudaError;
 
-// Device address of g_scratch for the current device; resolved once per device.
-int lookupScratch(unsigned char** out) {
+// Device address of g_scratch for the current device and that device's SM count; both resolved
+// once per device.
+int lookupScratch(unsigned char** out, int* smCount) {
   static std::mutex mu;
   static unsigned char* perDevice[kMaxDevices] = {};
+  static int smsOf[kMaxDevices] = {};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
@@ -102,9 +104,16 @@ int lookupScratch(unsigned char** out) {
       cudaGetLastError();
       return TPB_NOALLOC_CUDA_ERROR;
     }
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) {
+      cudaGetLastError();
+      sms = 1;
+    }
+    smsOf[dev] = sms;
     perDevice[dev] = static_cast<unsigned char*>(p);
   }
   *out = perDevice[dev];
+  *smCount = smsOf[dev];
   return TPB_NOALLOC_OK;
 }
 
@@ -122,6 +131,7 @@ extern "C" int tpb_noalloc_push(const tpb_noalloc_item* items, size_t count, uin
   for (size_t i = 0; i < count; ++i) {
     if (items[i].bytes == 0) continue;
     if (items[i].src == nullptr || items[i].dst == nullptr) return TPB_NOALLOC_BAD_ARGUMENT;
+    if (items[i].bytes > UINT64_MAX - kTileBytes) return TPB_NOALLOC_BAD_ARGUMENT;  // rounding up would wrap
     const uint64_t t = (items[i].bytes + kTileBytes - 1) / kTileBytes;
     if (t > 0xffffffffull - tiles) return TPB_NOALLOC_BAD_ARGUMENT;
     table[n].src = items[i].src;
@@ -134,7 +144,8 @@ extern "C" int tpb_noalloc_push(const tpb_noalloc_item* items, size_t count, uin
   }
 
   unsigned char* scratch = nullptr;
-  int rc = lookupScratch(&scratch);
+  int sms = 1;
+  int rc = lookupScratch(&scratch, &sms);
   if (rc != TPB_NOALLOC_OK) return rc;
 
   cudaError_t e = cudaSuccess;
@@ -145,10 +156,6 @@ extern "C" int tpb_noalloc_push(const tpb_noalloc_item* items, size_t count, uin
     e = cudaMemcpyAsync(scratch + kCounterBytes, table, n * sizeof(TableEntry), cudaMemcpyHostToDevice, stream);
   }
   if (e == cudaSuccess) {
-    int sms = 0, dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (sms <= 0) sms = 1;
     const uint32_t warpsPerCta = kThreads / 32;
     uint32_t grid = (tiles + warpsPerCta - 1) / warpsPerCta;
     if (grid > static_cast<uint32_t>(sms) * 4) grid = static_cast<uint32_t>(sms) * 4;

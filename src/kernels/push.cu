@@ -55,6 +55,23 @@ PushTuning initialTuning() {
   if (const char* e = std::getenv("TPB_PUSH_NARROW")) {
     if (e[0] >= '0' && e[0] <= '2' && e[1] == 0) t.narrowRows = static_cast<uint32_t>(e[0] - '0');
   }
+  // The shape of the bulk pipeline can be tried out without rebuilding; values that setPushTuning
+  // would refuse are ignored.
+  auto number = [](const char* name, uint32_t fallback) {
+    const char* e = std::getenv(name);
+    if (!e || !*e) return fallback;
+    char* end = nullptr;
+    const unsigned long v = std::strtoul(e, &end, 0);
+    return end && *end == 0 ? static_cast<uint32_t>(v) : fallback;
+  };
+  const uint32_t tile = number("TPB_PUSH_TILE_BYTES", t.bulkTileBytes);
+  const uint32_t stages = number("TPB_PUSH_STAGES", t.bulkStages);
+  if (tile % 1024 == 0 && tile > 0 && stages >= 2 && stages <= static_cast<uint32_t>(kMaxBulkStages) &&
+      static_cast<size_t>(tile) * stages <= 160 * 1024) {
+    t.bulkTileBytes = tile;
+    t.bulkStages = stages;
+  }
+  t.bulkMinBytes = number("TPB_PUSH_BULK_MIN_BYTES", t.bulkMinBytes);
   return t;
 }
 PushTuning gTuning = initialTuning();

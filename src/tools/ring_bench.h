@@ -19,7 +19,7 @@ struct RingBenchOptions {
   bool useShm = true;         // register the shm transport (control traffic) next to TCP
   bool useBulkCopy = true;
   bool waitWithKernel = false;
-  size_t eagerThreshold = 1u << 20;
+  size_t eagerThreshold = 64 * 1024;
   int maxCtas = 0;
   size_t maxBytes = 1ull << 30;  // largest tensor that will be sent (buffers are sized for it)
   std::string channel = "cuda_p2p";  // or "cuda_basic"

@@ -425,7 +425,7 @@ TPB_TEST(Channel, CudaP2pOptionsFollowTheEnvironment) {
                         "TPB_CUDA_P2P_WAIT_KERNEL", "TPB_CUDA_P2P_WAIT_TIMEOUT_MS", "TPB_CUDA_P2P_BULK"})
     ::unsetenv(n);
   p2p::Options d = p2p::applyEnvironment(p2p::Options());
-  EXPECT_EQ(d.eagerThreshold, size_t(1u << 20));
+  EXPECT_EQ(d.eagerThreshold, size_t(64 * 1024));
 }
 
 // Every channel context can be dropped without join(): its destructor closes and joins on its

@@ -88,6 +88,9 @@ struct DeviceTensor {
     CK(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
     CK(cudaMalloc(&p, bytes + 512));
     CK(cudaMemset(p, 0xCD, bytes + 512));
+    // The fill runs on the default stream, which the tensor's own (non-blocking) stream is not
+    // ordered with, and a peer may start writing the moment it learns the address.
+    CK(cudaDeviceSynchronize());
   }
   ~DeviceTensor() {
     cudaSetDevice(device);

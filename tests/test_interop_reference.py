@@ -1,6 +1,7 @@
 """Wire-compatibility with the reference library, live: this library's pipes against an echo peer
 built only from the TensorPipe that PyTorch ships (baseline/ref_interop.cc), in both directions,
-over the uv transport and the basic channel. This is what validates the from-scratch libnop codec
+over the uv transport and the basic channel, also with every other CPU backend registered on both
+sides (which the two must then agree not to use). This is what validates the from-scratch libnop codec
 and the handshake (Packet, Brochure, BrochureAnswer, Descriptor, DescriptorReply) end to end.
 Skipped when torch does not ship the TensorPipe headers or the peer cannot be compiled."""
 import os
@@ -48,14 +49,23 @@ def plain_context(name):
     return ctx
 
 
-def test_our_client_against_reference_server(built):
+def full_context(name):
+    """Everything default_context() registers for CPU tensors (shm and uv; basic, cma, xth, mpt_uv):
+    only uv and basic are really shared with the reference peer (which registers uv, shm, basic, cma,
+    mpt_uv), and the negotiation has to find that out."""
+    return tpb.default_context(name, cuda=False, mpt_lanes=3)
+
+
+@pytest.mark.parametrize("full", [False, True], ids=["uv+basic", "every backend registered"])
+def test_our_client_against_reference_server(built, full):
     peer = build_peer()
     port = free_port()
-    server = subprocess.Popen([peer, "server", str(port)], stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True)
+    server = subprocess.Popen([peer, "server", str(port)] + (["full"] if full else []), stdin=subprocess.PIPE,
+                              stdout=subprocess.PIPE, text=True)
     try:
         line = server.stdout.readline()
         assert line.startswith("listening"), line
-        ctx = plain_context("ours")
+        ctx = full_context("ours") if full else plain_context("ours")
         pipe = ctx.connect(f"uv://127.0.0.1:{port}", remote_name="ref-server")
         for i in range(5):
             tensors = [torch.randn(1000 * (i + 1)), torch.arange(17 + i, dtype=torch.int64)]
@@ -74,10 +84,11 @@ def test_our_client_against_reference_server(built):
         server.wait(timeout=20)
 
 
-def test_reference_client_against_our_server(built):
+@pytest.mark.parametrize("full", [False, True], ids=["uv+basic", "every backend registered"])
+def test_reference_client_against_our_server(built, full):
     peer = build_peer()
-    ctx = plain_context("ours")
-    listener = ctx.listen(["uv://127.0.0.1"])
+    ctx = full_context("ours") if full else plain_context("ours")
+    listener = ctx.listen(["uv://127.0.0.1", "shm://"] if full else ["uv://127.0.0.1"])
     stop = threading.Event()
 
     def serve(pipe):
@@ -93,7 +104,8 @@ def test_reference_client_against_our_server(built):
 
     listener.accept(lambda err, pipe: serve(pipe) if not err else None)
     addr = listener.url("uv").split("://")[1]
-    out = subprocess.run([peer, "client", addr, "6"], capture_output=True, text=True, timeout=120)
+    out = subprocess.run([peer, "client", addr, "6"] + (["full"] if full else []), capture_output=True, text=True,
+                         timeout=120)
     stop.set()
     assert out.returncode == 0 and out.stdout.strip() == "ok 6", out.stdout + out.stderr
     ctx.join()

@@ -2,7 +2,7 @@
 results, remote errors, remote references. CPU here; with CUDA tensors under -m gpu."""
 import pytest
 
-from tensorpipe_b200.utils import rpc_selftest
+import rpc_selftest
 
 
 def test_rpc_three_processes_cpu(built):

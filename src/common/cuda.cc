@@ -5,46 +5,33 @@
 
 #include <tpb/buffer.h>
 
-namespace tpb {
+#include "common/dl.h"
 
-namespace {
-template <typename F>
-bool loadSym(void* h, F& fn, std::initializer_list<const char*> names) {
-  for (const char* n : names) {
-    void* p = ::dlsym(h, n);
-    if (p) {
-      fn = reinterpret_cast<F>(p);
-      return true;
-    }
-  }
-  return false;
-}
-}  // namespace
+namespace tpb {
 
 const CudaLib& CudaLib::get() {
   static CudaLib lib = [] {
     CudaLib l;
-    l.handle = ::dlopen("libcuda.so.1", RTLD_LOCAL | RTLD_LAZY);
-    if (!l.handle) {
-      const char* e = ::dlerror();
-      l.why = e ? e : "dlopen(libcuda.so.1) failed";
+    DynamicLibraryHandle dl("libcuda.so.1");
+    if (!dl.loaded()) {
+      l.why = dl.error();
       TPB_VLOG(9) << "CUDA driver not loaded: " << l.why;
       return l;
     }
-    bool all = loadSym(l.handle, l.cuInit, {"cuInit"}) &&
-        loadSym(l.handle, l.cuDeviceGetCount, {"cuDeviceGetCount"}) &&
-        loadSym(l.handle, l.cuPointerGetAttribute, {"cuPointerGetAttribute"}) &&
-        loadSym(l.handle, l.cuMemGetAddressRange, {"cuMemGetAddressRange_v2"}) &&
-        loadSym(l.handle, l.cuGetErrorString, {"cuGetErrorString"}) &&
-        loadSym(l.handle, l.cuCtxGetCurrent, {"cuCtxGetCurrent"});
-    loadSym(l.handle, l.cuDeviceGet, {"cuDeviceGet"});
-    loadSym(l.handle, l.cuDevicePrimaryCtxRetain, {"cuDevicePrimaryCtxRetain"});
-    loadSym(l.handle, l.cuCtxPushCurrent, {"cuCtxPushCurrent_v2", "cuCtxPushCurrent"});
-    loadSym(l.handle, l.cuCtxPopCurrent, {"cuCtxPopCurrent_v2", "cuCtxPopCurrent"});
-    loadSym(l.handle, l.cuDevicePrimaryCtxGetState, {"cuDevicePrimaryCtxGetState"});
+    bool all = dl.load(l.cuInit, {"cuInit"}) && dl.load(l.cuDeviceGetCount, {"cuDeviceGetCount"}) &&
+        dl.load(l.cuPointerGetAttribute, {"cuPointerGetAttribute"}) &&
+        dl.load(l.cuMemGetAddressRange, {"cuMemGetAddressRange_v2"}) &&
+        dl.load(l.cuGetErrorString, {"cuGetErrorString"}) && dl.load(l.cuCtxGetCurrent, {"cuCtxGetCurrent"});
+    dl.load(l.cuDeviceGet, {"cuDeviceGet"});
+    dl.load(l.cuDevicePrimaryCtxRetain, {"cuDevicePrimaryCtxRetain"});
+    dl.load(l.cuCtxPushCurrent, {"cuCtxPushCurrent_v2", "cuCtxPushCurrent"});
+    dl.load(l.cuCtxPopCurrent, {"cuCtxPopCurrent_v2", "cuCtxPopCurrent"});
+    dl.load(l.cuDevicePrimaryCtxGetState, {"cuDevicePrimaryCtxGetState"});
     // Stream memory operations are optional (the wait kernel is the fallback).
-    loadSym(l.handle, l.cuStreamWaitValue32, {"cuStreamWaitValue32_v2", "cuStreamWaitValue32"});
-    loadSym(l.handle, l.cuStreamWriteValue32, {"cuStreamWriteValue32_v2", "cuStreamWriteValue32"});
+    dl.load(l.cuStreamWaitValue32, {"cuStreamWaitValue32_v2", "cuStreamWaitValue32"});
+    dl.load(l.cuStreamWriteValue32, {"cuStreamWriteValue32_v2", "cuStreamWriteValue32"});
+    // The driver stays mapped for the life of the process: the entry points above are kept.
+    l.handle = dl.release();
     if (!all) {
       l.why = "libcuda.so.1 lacks required symbols";
       return l;
@@ -68,13 +55,13 @@ const CudaLib& CudaLib::get() {
 const NvmlLib& NvmlLib::get() {
   static NvmlLib lib = [] {
     NvmlLib l;
-    l.handle = ::dlopen("libnvidia-ml.so.1", RTLD_LOCAL | RTLD_LAZY);
-    if (!l.handle) return l;
+    DynamicLibraryHandle dl("libnvidia-ml.so.1");
+    if (!dl.loaded()) return l;
     int (*init)() = nullptr;
-    if (!loadSym(l.handle, init, {"nvmlInit_v2"}) ||
-        !loadSym(l.handle, l.deviceGetHandleByUUID, {"nvmlDeviceGetHandleByUUID"}) ||
-        !loadSym(l.handle, l.deviceGetP2PStatus, {"nvmlDeviceGetP2PStatus"}))
-      return l;
+    const bool all = dl.load(init, {"nvmlInit_v2"}) && dl.load(l.deviceGetHandleByUUID, {"nvmlDeviceGetHandleByUUID"}) &&
+        dl.load(l.deviceGetP2PStatus, {"nvmlDeviceGetP2PStatus"});
+    l.handle = dl.release();
+    if (!all) return l;
     if (init() != 0) return l;
     l.ok = true;
     return l;

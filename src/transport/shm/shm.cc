@@ -27,10 +27,12 @@
 
 #include <tpb/transport.h>
 
+#include "common/busy_polling_loop.h"
 #include "common/defs.h"
 #include "common/loop.h"
 #include "common/ringbuffer.h"
 #include "common/shm_segment.h"
+#include "common/socket.h"
 #include "common/system.h"
 
 namespace tpb {
@@ -99,68 +101,12 @@ class ReactorQueue {
   uint64_t head_ = 0;  // consumer-private
 };
 
-// ---- fd passing -----------------------------------------------------------------------------
+// What the two ends tell each other over the bootstrap socket, next to three descriptors
+// (reactor segment, reactor eventfd, inbox segment) carried as SCM_RIGHTS.
 struct Bootstrap {
   uint32_t inboxToken = 0;
   uint32_t outboxToken = 0;
 };
-
-Error sendBootstrap(int sock, const Bootstrap& b, const int fds[3]) {
-  msghdr msg{};
-  iovec iov{const_cast<Bootstrap*>(&b), sizeof(b)};
-  msg.msg_iov = &iov;
-  msg.msg_iovlen = 1;
-  alignas(cmsghdr) char ctrl[CMSG_SPACE(sizeof(int) * 3)] = {};
-  msg.msg_control = ctrl;
-  msg.msg_controllen = sizeof(ctrl);
-  cmsghdr* c = CMSG_FIRSTHDR(&msg);
-  c->cmsg_level = SOL_SOCKET;
-  c->cmsg_type = SCM_RIGHTS;
-  c->cmsg_len = CMSG_LEN(sizeof(int) * 3);
-  std::memcpy(CMSG_DATA(c), fds, sizeof(int) * 3);
-  for (;;) {
-    ssize_t n = ::sendmsg(sock, &msg, MSG_NOSIGNAL);
-    if (n < 0 && errno == EINTR) continue;
-    if (n < 0) return TPB_CREATE_ERROR(SystemError, "sendmsg", errno);
-    if (n != sizeof(b)) return TPB_CREATE_ERROR(ShortWriteError, sizeof(b), n);
-    return Error::kSuccess;
-  }
-}
-
-// Returns EAGAIN-as-success with got=false when nothing is there yet.
-Error recvBootstrap(int sock, Bootstrap& b, int fds[3], bool& got) {
-  got = false;
-  msghdr msg{};
-  iovec iov{&b, sizeof(b)};
-  msg.msg_iov = &iov;
-  msg.msg_iovlen = 1;
-  alignas(cmsghdr) char ctrl[CMSG_SPACE(sizeof(int) * 3)] = {};
-  msg.msg_control = ctrl;
-  msg.msg_controllen = sizeof(ctrl);
-  ssize_t n = ::recvmsg(sock, &msg, MSG_CMSG_CLOEXEC);
-  if (n < 0) {
-    if (errno == EAGAIN || errno == EWOULDBLOCK || errno == EINTR) return Error::kSuccess;
-    return TPB_CREATE_ERROR(SystemError, "recvmsg", errno);
-  }
-  if (n == 0) return TPB_CREATE_ERROR(EOFError);
-  if (n != sizeof(b)) return TPB_CREATE_ERROR(ShortReadError, sizeof(b), n);
-  cmsghdr* c = CMSG_FIRSTHDR(&msg);
-  if (!c || c->cmsg_level != SOL_SOCKET || c->cmsg_type != SCM_RIGHTS ||
-      c->cmsg_len != CMSG_LEN(sizeof(int) * 3))
-    return TPB_CREATE_ERROR(ShortReadError, 3, 0);
-  std::memcpy(fds, CMSG_DATA(c), sizeof(int) * 3);
-  got = true;
-  return Error::kSuccess;
-}
-
-sockaddr_un abstractAddr(const std::string& name, socklen_t& len) {
-  sockaddr_un sa{};
-  sa.sun_family = AF_UNIX;
-  size_t n = std::min(name.size(), sizeof(sa.sun_path) - 1);
-  std::memcpy(sa.sun_path + 1, name.data(), n);  // leading NUL = abstract namespace
-  len = static_cast<socklen_t>(offsetof(sockaddr_un, sun_path) + 1 + n);
-  return sa;
-}
 
 class ContextImpl;
 
@@ -189,7 +135,7 @@ class FdHandler {
 };
 
 // ---- the reactor thread ---------------------------------------------------------------------
-class Reactor final : public ThreadLoop {
+class Reactor final : public BusyPollingLoop {
  public:
   Reactor() {
     auto [e, seg] = ShmSegment::create(ReactorQueue::bytesNeeded());
@@ -251,66 +197,47 @@ class Reactor final : public ThreadLoop {
     fdRecords_.erase(it);
   }
 
-  void close() {
-    if (!closed_.exchange(true)) wakeupEventLoop();
+ protected:
+  // Tokens that peers pushed into the shared queue since the last pass.
+  bool pollOnce() override {
+    bool worked = false;
+    uint32_t token;
+    int budget = 256;
+    while (budget-- > 0 && queue_.pop(token)) {
+      worked = true;
+      runToken(token);
+    }
+    return worked;
   }
-  void join() {
-    close();
-    joinThread();
+  bool readyToClose() override { return handlers_.empty(); }
+  void onWork() override { lastWork_ = Clock::now(); }
+  // Spin for a while after the last piece of work (looking at the descriptors now and then),
+  // then sleep until a peer or a deferred function pokes the eventfd.
+  void onIdle(uint64_t idlePasses) override {
+    if ((idlePasses & 0x3f) != 0) return pause();
+    pollFds(0);
+    if (std::chrono::duration_cast<std::chrono::microseconds>(Clock::now() - lastWork_).count() <= spinUs_) return;
+    // Go to sleep: announce it, look once more, then block until poked.
+    queue_.setSleeping(true);
+    sleeping_.store(true, std::memory_order_seq_cst);
+    uint32_t t = UINT32_MAX;
+    const bool popped = queue_.pop(t);
+    if (popped || hasDeferred()) {
+      queue_.setSleeping(false);
+      sleeping_.store(false);
+      if (popped) runToken(t);
+    } else {
+      pollFds(closing() ? 10 : -1);
+      queue_.setSleeping(false);
+      sleeping_.store(false);
+    }
+    lastWork_ = Clock::now();
   }
 
- protected:
-  void eventLoop() override {
-    using clock = std::chrono::steady_clock;
-    auto lastWork = clock::now();
-    uint32_t idle = 0;
-    for (;;) {
-      bool worked = runDeferredFunctions() > 0;
-      uint32_t token;
-      int budget = 256;
-      while (budget-- > 0 && queue_.pop(token)) {
-        worked = true;
-        if (token < functions_.size() && functions_[token]) {
-          auto fn = functions_[token];  // copy: the function may unregister itself
-          fn();
-        }
-      }
-      if (worked) {
-        idle = 0;
-        lastWork = clock::now();
-        continue;
-      }
-      if (closed_.load() && handlers_.empty() && !hasDeferred()) break;
-      ++idle;
-      if ((idle & 0x3f) == 0) {
-        pollFds(0);
-        auto now = clock::now();
-        if (std::chrono::duration_cast<std::chrono::microseconds>(now - lastWork).count() > spinUs_) {
-          // Go to sleep: announce it, look once more, then block until poked.
-          queue_.setSleeping(true);
-          sleeping_.store(true, std::memory_order_seq_cst);
-          uint32_t t = UINT32_MAX;
-          bool popped = queue_.pop(t);
-          if (popped || hasDeferred()) {
-            queue_.setSleeping(false);
-            sleeping_.store(false);
-            if (popped && t < functions_.size() && functions_[t]) {
-              auto fn = functions_[t];
-              fn();
-            }
-          } else {
-            pollFds(closed_.load() ? 10 : -1);
-            queue_.setSleeping(false);
-            sleeping_.store(false);
-          }
-          lastWork = clock::now();
-          idle = 0;
-        }
-      } else {
-#if defined(__x86_64__)
-        __builtin_ia32_pause();
-#endif
-      }
+  void runToken(uint32_t token) {
+    if (token < functions_.size() && functions_[token]) {
+      auto fn = functions_[token];  // copy: the function may unregister itself
+      fn();
     }
   }
 
@@ -344,8 +271,9 @@ class Reactor final : public ThreadLoop {
   ReactorQueue queue_;
   int eventFd_ = -1;
   int epollFd_ = -1;
+  using Clock = std::chrono::steady_clock;
   long spinUs_ = 2000;
-  std::atomic<bool> closed_{false};
+  Clock::time_point lastWork_ = Clock::now();
   std::atomic<bool> sleeping_{false};
   std::vector<std::function<void()>> functions_;
   std::vector<uint32_t> freeTokens_;
@@ -387,7 +315,7 @@ class ConnectionImpl final : public FdHandler, public std::enable_shared_from_th
  public:
   enum State { kInitializing, kWaitingForPeer, kEstablished, kClosed };
 
-  ConnectionImpl(std::shared_ptr<ContextImpl> ctx, int sock) : ctx_(std::move(ctx)), sock_(sock) {}
+  ConnectionImpl(std::shared_ptr<ContextImpl> ctx, Socket sock) : ctx_(std::move(ctx)), sock_(std::move(sock)) {}
   ConnectionImpl(std::shared_ptr<ContextImpl> ctx, std::string addr)
       : ctx_(std::move(ctx)), connectAddr_(std::move(addr)), isClient_(true) {}
 
@@ -463,7 +391,7 @@ class ConnectionImpl final : public FdHandler, public std::enable_shared_from_th
   }
 
   std::shared_ptr<ContextImpl> ctx_;
-  int sock_ = -1;
+  Socket sock_;
   std::string connectAddr_;
   bool isClient_ = false;
   State state_ = kInitializing;
@@ -490,23 +418,19 @@ class ConnectionImpl final : public FdHandler, public std::enable_shared_from_th
 void ConnectionImpl::initFromLoop() {
   auto self = shared_from_this();
   if (ctx_->closed()) {
-    if (sock_ >= 0) ::close(sock_);
-    sock_ = -1;
+    sock_.reset();
     error_ = TPB_CREATE_ERROR(ContextClosedError);
     state_ = kClosed;
     return;
   }
   ctx_->enroll(self);
   if (isClient_) {
-    sock_ = ::socket(AF_UNIX, SOCK_STREAM | SOCK_CLOEXEC, 0);
-    if (sock_ < 0) return closeFromLoop(TPB_CREATE_ERROR(SystemError, "socket", errno));
-    socklen_t len;
-    sockaddr_un sa = abstractAddr(connectAddr_, len);
-    if (::connect(sock_, reinterpret_cast<sockaddr*>(&sa), len) < 0)
-      return closeFromLoop(TPB_CREATE_ERROR(SystemError, "connect", errno));
+    auto [created, sock] = Socket::createForFamily(AF_UNIX);
+    if (created) return closeFromLoop(created);
+    sock_ = std::move(sock);
+    if (Error connected = sock_.connectAbstract(connectAddr_)) return closeFromLoop(connected);
   }
-  int flags = ::fcntl(sock_, F_GETFL, 0);
-  ::fcntl(sock_, F_SETFL, flags | O_NONBLOCK);
+  if (Error e = sock_.setNonBlocking()) return closeFromLoop(e);
 
   auto [e, seg] = ShmSegment::create(Ring::bytesNeeded(kRingBytes));
   if (e) return closeFromLoop(e);
@@ -524,10 +448,10 @@ void ConnectionImpl::initFromLoop() {
 
   Bootstrap b{myInboxToken_, myOutboxToken_};
   int fds[3] = {ctx_->reactor().segmentFd(), ctx_->reactor().eventFd(), inboxSeg_.fd()};
-  Error se = sendBootstrap(sock_, b, fds);
+  Error se = sock_.sendWithFds(b, fds);
   if (se) return closeFromLoop(se);
   state_ = kWaitingForPeer;
-  ctx_->reactor().watchFd(sock_, EPOLLIN | EPOLLRDHUP, self);
+  ctx_->reactor().watchFd(sock_.fd(), EPOLLIN | EPOLLRDHUP, self);
   watching_ = true;
 }
 
@@ -538,7 +462,7 @@ void ConnectionImpl::handleFdEvents(int events) {
     Bootstrap b;
     int fds[3] = {-1, -1, -1};
     bool got = false;
-    Error e = recvBootstrap(sock_, b, fds, got);
+    Error e = sock_.recvWithFds(b, fds, got);
     if (e) return closeFromLoop(e);
     if (got) onPeerBootstrap(b, fds);
     return;
@@ -553,7 +477,7 @@ void ConnectionImpl::handleFdEvents(int events) {
       std::unique_lock<std::mutex> lock(outboxMutex_);
       directWrites_ = false;
     }
-    if (watching_) ctx_->reactor().unwatchFd(sock_);
+    if (watching_) ctx_->reactor().unwatchFd(sock_.fd());
     watching_ = false;
     if (!writes_.empty()) return closeFromLoop(TPB_CREATE_ERROR(EOFError));
     processReads();
@@ -684,10 +608,9 @@ void ConnectionImpl::closeFromLoop(const Error& e) {
     if (peerEventFd_ >= 0) ::close(peerEventFd_);
     peerEventFd_ = -1;
   }
-  if (watching_) ctx_->reactor().unwatchFd(sock_);
+  if (watching_) ctx_->reactor().unwatchFd(sock_.fd());
   watching_ = false;
-  if (sock_ >= 0) ::close(sock_);
-  sock_ = -1;
+  sock_.reset();
   if (tokensRegistered_) {
     ctx_->reactor().removeToken(myInboxToken_);
     ctx_->reactor().removeToken(myOutboxToken_);
@@ -746,24 +669,13 @@ class ConnectionShell final : public Connection {
 class ListenerImpl final : public FdHandler, public std::enable_shared_from_this<ListenerImpl> {
  public:
   ListenerImpl(std::shared_ptr<ContextImpl> ctx, const std::string& addr) : ctx_(std::move(ctx)) {
-    fd_ = ::socket(AF_UNIX, SOCK_STREAM | SOCK_NONBLOCK | SOCK_CLOEXEC, 0);
-    TPB_THROW_SYSTEM_IF(fd_ < 0, errno, "socket");
-    if (addr.empty()) {
-      // Autobind: the kernel picks a unique abstract name.
-      sockaddr_un sa{};
-      sa.sun_family = AF_UNIX;
-      TPB_THROW_SYSTEM_IF(::bind(fd_, reinterpret_cast<sockaddr*>(&sa), sizeof(sa_family_t)) < 0, errno, "bind");
-    } else {
-      socklen_t len;
-      sockaddr_un sa = abstractAddr(addr, len);
-      TPB_THROW_SYSTEM_IF(::bind(fd_, reinterpret_cast<sockaddr*>(&sa), len) < 0, errno, "bind");
-    }
-    TPB_THROW_SYSTEM_IF(::listen(fd_, 128) < 0, errno, "listen");
-    sockaddr_un bound{};
-    socklen_t blen = sizeof(bound);
-    ::getsockname(fd_, reinterpret_cast<sockaddr*>(&bound), &blen);
-    size_t n = blen - offsetof(sockaddr_un, sun_path);
-    addr_ = n > 1 ? std::string(bound.sun_path + 1, n - 1) : std::string();
+    auto [created, sock] = Socket::createForFamily(AF_UNIX, SOCK_NONBLOCK);
+    TPB_THROW_SYSTEM_IF(bool(created), errno, "socket");
+    sock_ = std::move(sock);
+    // An empty address autobinds: the kernel picks a unique abstract name.
+    TPB_THROW_SYSTEM_IF(bool(sock_.bindAbstract(addr)), errno, "bind");
+    TPB_THROW_SYSTEM_IF(bool(sock_.listen(128)), errno, "listen");
+    addr_ = sock_.boundAbstractName();
   }
   void init() {
     auto self = shared_from_this();
@@ -779,7 +691,7 @@ class ListenerImpl final : public FdHandler, public std::enable_shared_from_this
       self->armed_.push_back(std::move(fn));
       // Accept-side backpressure: the listening socket is only watched while someone waits.
       if (!self->watching_) {
-        self->ctx_->reactor().watchFd(self->fd_, EPOLLIN, self);
+        self->ctx_->reactor().watchFd(self->sock_.fd(), EPOLLIN, self);
         self->watching_ = true;
       }
     });
@@ -793,10 +705,9 @@ class ListenerImpl final : public FdHandler, public std::enable_shared_from_this
     if (error_) return;
     error_ = e;
     auto self = shared_from_this();
-    if (watching_) ctx_->reactor().unwatchFd(fd_);
+    if (watching_) ctx_->reactor().unwatchFd(sock_.fd());
     watching_ = false;
-    if (fd_ >= 0) ::close(fd_);
-    fd_ = -1;
+    sock_.reset();
     ctx_->unenroll(self);
     auto armed = std::move(armed_);
     armed_.clear();
@@ -805,28 +716,25 @@ class ListenerImpl final : public FdHandler, public std::enable_shared_from_this
   void handleFdEvents(int events) override {
     auto self = shared_from_this();
     (void)events;
-    while (!armed_.empty() && fd_ >= 0) {
-      int cfd = ::accept4(fd_, nullptr, nullptr, SOCK_CLOEXEC);
-      if (cfd < 0) {
-        if (errno == EAGAIN || errno == EWOULDBLOCK) break;
-        if (errno == EINTR || errno == ECONNABORTED) continue;
-        return closeFromLoop(TPB_CREATE_ERROR(SystemError, "accept", errno));
-      }
-      auto impl = std::make_shared<ConnectionImpl>(ctx_, cfd);
+    while (!armed_.empty() && sock_.hasValue()) {
+      auto [failed, incoming] = sock_.accept();
+      if (failed) return closeFromLoop(failed);
+      if (!incoming.hasValue()) break;  // nobody waiting in the backlog
+      auto impl = std::make_shared<ConnectionImpl>(ctx_, std::move(incoming));
       impl->init();
       auto fn = std::move(armed_.front());
       armed_.pop_front();
       fn(Error::kSuccess, std::make_shared<ConnectionShell>(std::move(impl)));
     }
-    if (armed_.empty() && watching_ && fd_ >= 0) {
-      ctx_->reactor().unwatchFd(fd_);
+    if (armed_.empty() && watching_ && sock_.hasValue()) {
+      ctx_->reactor().unwatchFd(sock_.fd());
       watching_ = false;
     }
   }
 
  private:
   std::shared_ptr<ContextImpl> ctx_;
-  int fd_ = -1;
+  Socket sock_;
   std::string addr_;
   Error error_;
   bool watching_ = false;

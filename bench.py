@@ -409,9 +409,9 @@ def roofline(world, value_gbs):
 def run_e2e(args, tpb, torch, dist, rank, world, local_rank, barrier, max_over_ranks, gather):
     """The same ring through the public Python API, end to end: every step's input starts in pinned
     host memory and the step ends with a checksum of the received tensor read back to the host.
-    The pinned tensor itself is what is sent: the push kernel of this rank's GPU reads it over
-    PCIe and stores it into the next rank's GPU, so the host->device copy of the step IS the pipe
-    transfer (one pass over PCIe instead of a staging copy followed by a send)."""
+    The pinned tensor itself is what is sent: the channel brings it into this rank's GPU with the
+    copy engine piece by piece while its push kernel forwards the piece before to the next rank's
+    GPU, so the host->device copy of the step overlaps the pipe transfer."""
     dev = torch.device("cuda", local_rank)
     nbytes = args.bytes
     steps = max(5, min(args.steps, 20))
@@ -431,8 +431,9 @@ def run_e2e(args, tpb, torch, dist, rank, world, local_rank, barrier, max_over_r
     result = torch.empty(1, dtype=torch.float32).pin_memory()
 
     def step(i):
-        sent = out_pipe.send([host_in], target_devices=[target])  # H2D (nbytes) fused into the transfer
-        msg = in_pipe.recv(out=[bufs[i & 1]]).result(120)
+        incoming = in_pipe.recv(out=[bufs[i & 1]])
+        sent = out_pipe.send([host_in], target_devices=[target])  # H2D (nbytes) overlapped with the transfer
+        msg = incoming.result(120)
         sent.result(120)
         checksum = msg.tensors[0][:4096].float().sum()
         result.copy_(checksum.reshape(1), non_blocking=True)      # D2H, 4 bytes

@@ -75,6 +75,9 @@ std::shared_ptr<Context> create();
 // Address helpers (tensorpipe/transport/uv/utility.cc:20-215 counterparts).
 std::pair<Error, std::string> lookupAddrForIface(const std::string& iface);
 std::pair<Error, std::string> lookupAddrForHostname();
+// The address NCCL's bootstrap would choose (interfaces named ib* first, docker* and lo* last);
+// `family` is AF_INET, AF_INET6 or 0 for either.
+std::pair<Error, std::string> lookupAddrLikeNccl(int family = 0);
 }  // namespace tcp
 namespace uv {
 inline std::shared_ptr<Context> create() { return tcp::create(); }

@@ -10,7 +10,6 @@
 // Done arrives. Sends and receives are matched in order, so no sequence numbers travel.
 #pragma once
 
-#include <condition_variable>
 #include <deque>
 #include <mutex>
 #include <set>
@@ -21,6 +20,7 @@
 
 #include "common/defs.h"
 #include "common/loop.h"
+#include "common/queue.h"
 #include "common/nop.h"
 #include "transport/nop_io.h"
 
@@ -80,15 +80,11 @@ class ContextImpl final : public Context, public std::enable_shared_from_this<Co
     descriptors_[Device(kCpuDeviceType, 0)] = std::move(descriptor);
     thread_ = std::thread([this, threadName]() {
       setThreadName(threadName);
+      // The copy thread sleeps in pop(); an empty function is the request to stop, queued behind
+      // whatever copies were requested before it.
       for (;;) {
-        std::function<void()> job;
-        {
-          std::unique_lock<std::mutex> l(mu_);
-          cv_.wait(l, [&] { return stop_ || !jobs_.empty(); });
-          if (jobs_.empty()) return;
-          job = std::move(jobs_.front());
-          jobs_.pop_front();
-        }
+        std::function<void()> job = jobs_.pop();
+        if (!job) return;
         job();
       }
     });
@@ -121,24 +117,16 @@ class ContextImpl final : public Context, public std::enable_shared_from_this<Co
     loop_.runInLoop([]() {});
   }
   void stopThread() {
-    {
-      std::unique_lock<std::mutex> l(mu_);
-      stop_ = true;
-    }
-    cv_.notify_all();
+    if (!stopRequested_.exchange(true)) jobs_.push(nullptr);
     if (thread_.joinable()) thread_.join();
   }
   // The copy runs on the copy thread; `done` is then deferred to the loop.
   void requestCopy(uint64_t pid, const void* remote, void* local, size_t len, std::function<void(const Error&)> done) {
     auto self = shared_from_this();
-    {
-      std::unique_lock<std::mutex> l(mu_);
-      jobs_.push_back([self, pid, remote, local, len, done = std::move(done)]() {
-        Error e = self->copyFn_(pid, remote, local, len);
-        self->loop_.deferToLoop([done, e]() { done(e); });
-      });
-    }
-    cv_.notify_one();
+    jobs_.push([self, pid, remote, local, len, done = std::move(done)]() {
+      Error e = self->copyFn_(pid, remote, local, len);
+      self->loop_.deferToLoop([done, e]() { done(e); });
+    });
   }
   OnDemandLoop loop_;
   bool closed_ = false;
@@ -148,10 +136,10 @@ class ContextImpl final : public Context, public std::enable_shared_from_this<Co
   CopyFn copyFn_;
   std::unordered_map<Device, std::string> descriptors_;
   std::thread thread_;
-  std::mutex mu_;
-  std::condition_variable cv_;
-  std::deque<std::function<void()>> jobs_;
-  bool stop_ = false;
+  // Copies wait here for the copy thread. The bound only matters to a caller that queues
+  // thousands of tensors without waiting for any: it then blocks until the thread catches up.
+  Queue<std::function<void()>> jobs_{4096};
+  std::atomic<bool> stopRequested_{false};
   std::atomic<bool> joined_{false};
 };
 

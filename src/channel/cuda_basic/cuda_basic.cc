@@ -3,32 +3,40 @@
 //
 // Same role and negotiation as the reference's channel (tensorpipe/channel/cuda_basic/
 // context_impl.cc:27-128: wraps a CPU channel, never serves cpu->cpu, descriptor = {device type,
-// inner descriptor}) with a different data path: instead of cudaMemcpyAsync plus
-// cudaStreamAddCallback per 1 MiB chunk (channel_impl.cc:58-71), a pack kernel on the user's
-// stream writes each chunk into a mapped pinned slot and publishes a host-visible flag with a
-// system-scope release store; a poller thread notices the flag and hands the slot to the CPU
-// channel. On the receiving side the CPU channel fills a pinned slot and an unpack kernel on the
-// user's stream moves it into the tensor; the slot returns to the pool when an event recorded
-// after the kernel has fired.
+// inner descriptor}) with a different data path. The reference issues one cudaMemcpyAsync plus
+// one cudaStreamAddCallback per 1 MiB chunk (channel_impl.cc:58-71,117-229). Here:
 //
-// Ordering: both ends cut every tensor into the same chunks and feed the inner channel strictly
-// in chunk order (one ordered queue per direction), because the inner channel matches its k-th
-// send with the peer's k-th recv.
+//   stage out  one kernel launch packs as many 2 MiB pieces as there are free pinned slots, of
+//              as many tensors of the message as that covers, straight into mapped pinned memory:
+//              contiguous bytes, or the packed form of a 2-D strided view (any element range of
+//              it), and publishes one host-visible flag with a system-scope release store; a
+//              poller thread notices the flag and hands the slots to the CPU channel in order.
+//   stage in   the CPU channel fills pinned slots; one kernel launch moves every slot that has
+//              arrived since the last launch into its tensor, converting the element type on the
+//              way when the receiver asked for that; the slots return to the pool when an event
+//              recorded behind the kernel has fired.
+//
+// Both ends cut every tensor into the same pieces (2 MiB of packed source bytes) and feed the
+// inner channel strictly in piece order, because the inner channel matches its k-th send with
+// the peer's k-th recv. Views and conversions never change the pieces: a view is packed by the
+// sender, a conversion is applied by the receiver, so neither end needs to know what the other
+// does and nothing but tensor bytes crosses the inner channel.
 #include <atomic>
-#include <condition_variable>
+#include <cstring>
 #include <deque>
-#include <list>
 #include <map>
 #include <set>
-#include <thread>
 
 #include <tpb/channel.h>
 
 #include "channel/nonviable.h"
+#include "common/allocator.h"
 #include "common/cuda.h"
 #include "common/defs.h"
 #include "common/loop.h"
 #include "common/nop.h"
+#include "common/poller.h"
+#include "common/trace.h"
 #include "kernels/push.h"
 
 namespace tpb {
@@ -37,8 +45,9 @@ namespace cuda_basic {
 
 namespace {
 
-constexpr size_t kChunkBytes = 4u << 20;
-constexpr int kSlotsPerDirection = 8;
+constexpr size_t kPieceBytes = 2u << 20;
+constexpr size_t kSlotsPerDirection = 16;
+constexpr const char* kInnerPrefix = "tpbcb1:";
 
 struct DeviceDescriptor {
   std::string deviceType;
@@ -46,160 +55,184 @@ struct DeviceDescriptor {
   TPB_NOP_STRUCTURE(DeviceDescriptor, deviceType, cpuDescriptor)
 };
 
-// Polls conditions (host flags written by kernels, CUDA events) off the loop thread and fires a
-// one-shot callback when one turns true. Sleeps when there is nothing to watch.
-class Poller {
- public:
-  Poller() {
-    thread_ = std::thread([this]() {
-      setThreadName("TP_CUDA_poller");
-      run();
-    });
-  }
-  ~Poller() { stop(); }
-  void watch(std::function<bool()> ready, std::function<void()> fire) {
-    {
-      std::unique_lock<std::mutex> l(mu_);
-      items_.push_back({std::move(ready), std::move(fire)});
-    }
-    cv_.notify_one();
-  }
-  void stop() {
-    {
-      std::unique_lock<std::mutex> l(mu_);
-      if (stop_) return;
-      stop_ = true;
-    }
-    cv_.notify_all();
-    if (thread_.joinable()) thread_.join();
-  }
-
- private:
-  struct Item {
-    std::function<bool()> ready;
-    std::function<void()> fire;
-  };
-  void run() {
-    std::unique_lock<std::mutex> l(mu_);
-    for (;;) {
-      cv_.wait(l, [&] { return stop_ || !items_.empty(); });
-      if (stop_) {
-        // Fire what is left so that nobody waits forever; the channels are closing anyway.
-        auto rest = std::move(items_);
-        items_.clear();
-        l.unlock();
-        for (auto& it : rest) it.fire();
-        return;
-      }
-      std::vector<std::function<void()>> fired;
-      for (auto it = items_.begin(); it != items_.end();) {
-        bool ok = false;
-        try {
-          ok = it->ready();
-        } catch (...) {
-          ok = true;  // a failing query must not wedge the queue; the fire path re-checks
-        }
-        if (ok) {
-          fired.push_back(std::move(it->fire));
-          it = items_.erase(it);
-        } else {
-          ++it;
-        }
-      }
-      l.unlock();
-      for (auto& f : fired) f();
-      if (fired.empty()) std::this_thread::yield();
-      l.lock();
-    }
-  }
-  std::mutex mu_;
-  std::condition_variable cv_;
-  std::list<Item> items_;
-  bool stop_ = false;
-  std::thread thread_;
-};
-
-// Pinned, mapped staging slots of one direction, allocated on first use.
-struct SlotPool {
+// Pinned, mapped staging slots of one direction, allocated on first use and handed out in
+// request order by the chunk pool.
+struct Slots {
   uint8_t* base = nullptr;
   volatile uint32_t* flags = nullptr;  // one host-visible word per slot
-  std::deque<int> free;
+  std::unique_ptr<Allocator> pool;
   bool ensure() {
     if (base) return true;
     void* p = nullptr;
-    if (cudaHostAlloc(&p, kChunkBytes * kSlotsPerDirection + 4096, cudaHostAllocPortable | cudaHostAllocMapped) !=
+    if (cudaHostAlloc(&p, kPieceBytes * kSlotsPerDirection + 4096, cudaHostAllocPortable | cudaHostAllocMapped) !=
         cudaSuccess) {
       cudaGetLastError();
       return false;
     }
     base = static_cast<uint8_t*>(p);
-    flags = reinterpret_cast<volatile uint32_t*>(base + kChunkBytes * kSlotsPerDirection);
-    for (int i = 0; i < kSlotsPerDirection; ++i) {
-      flags[i] = 0;
-      free.push_back(i);
-    }
+    flags = reinterpret_cast<volatile uint32_t*>(base + kPieceBytes * kSlotsPerDirection);
+    for (size_t i = 0; i < kSlotsPerDirection; ++i) flags[i] = 0;
+    pool = std::make_unique<Allocator>(base, kSlotsPerDirection, kPieceBytes);
     return true;
   }
-  uint8_t* slot(int i) const { return base + static_cast<size_t>(i) * kChunkBytes; }
-  ~SlotPool() {
+  size_t indexOf(const uint8_t* slot) const { return static_cast<size_t>(slot - base) / kPieceBytes; }
+  ~Slots() {
+    pool.reset();
     if (base) cudaFreeHost(base);
   }
 };
+
+// ---- host-side restatements for the rare CPU ends of a layout --------------------------------
+uint16_t floatToBf16(float f) {
+  uint32_t x;
+  std::memcpy(&x, &f, 4);
+  if ((x & 0x7f800000u) == 0x7f800000u && (x & 0x007fffffu)) return static_cast<uint16_t>((x >> 16) | 0x40);
+  return static_cast<uint16_t>((x + 0x7fffu + ((x >> 16) & 1)) >> 16);
+}
+float bf16ToFloat(uint16_t h) {
+  uint32_t x = static_cast<uint32_t>(h) << 16;
+  float f;
+  std::memcpy(&f, &x, 4);
+  return f;
+}
+bool hostCastSupported(DType s, DType d) {
+  return (s == DType::kF32 && d == DType::kBF16) || (s == DType::kBF16 && d == DType::kF32);
+}
+void hostCast(const uint8_t* src, DType s, uint8_t* dst, size_t elems) {
+  if (s == DType::kF32) {
+    for (size_t i = 0; i < elems; ++i) {
+      float f;
+      std::memcpy(&f, src + i * 4, 4);
+      const uint16_t h = floatToBf16(f);
+      std::memcpy(dst + i * 2, &h, 2);
+    }
+  } else {
+    for (size_t i = 0; i < elems; ++i) {
+      uint16_t h;
+      std::memcpy(&h, src + i * 2, 2);
+      const float f = bf16ToFloat(h);
+      std::memcpy(dst + i * 4, &f, 4);
+    }
+  }
+}
+// Packed elements [first, first + count) of a 2-D view over host memory.
+void hostGather(const uint8_t* base, const StridedView& v, size_t es, uint64_t first, uint64_t count, uint8_t* out) {
+  for (uint64_t i = 0; i < count; ++i) {
+    const uint64_t e = first + i;
+    const int64_t r = static_cast<int64_t>(e / v.cols), c = static_cast<int64_t>(e % v.cols);
+    std::memcpy(out + i * es, base + (r * v.rowStride + c * v.colStride) * static_cast<int64_t>(es), es);
+  }
+}
+
+// Packed elements [first, first + count) of a 2-D view over device memory, as kernel entries: a
+// ragged end of the first row, whole rows, a ragged start of the last row.
+void appendViewRange(kernels::PushPlan& plan, const uint8_t* base, const StridedView& v, uint64_t first,
+                     uint64_t count, uint8_t* out) {
+  const int64_t es = static_cast<int64_t>(dtypeSize(v.dtype));
+  auto add = [&](int64_t row, int64_t col, int64_t rows, int64_t cols) {
+    kernels::CopyItem c;
+    c.src = base + (row * v.rowStride + col * v.colStride) * es;
+    c.dst = out;
+    c.srcBytes = static_cast<uint64_t>(rows * cols * es);
+    c.srcDtype = c.dstDtype = v.dtype;
+    c.strided = true;
+    c.view = StridedView{v.dtype, rows, cols, v.rowStride, v.colStride};
+    kernels::appendToPlan(plan, c, false);
+    out += rows * cols * es;
+  };
+  uint64_t cur = first, end = first + count;
+  const uint64_t cols = static_cast<uint64_t>(v.cols);
+  if (cur % cols != 0) {
+    const uint64_t n = std::min<uint64_t>(cols - cur % cols, end - cur);
+    add(static_cast<int64_t>(cur / cols), static_cast<int64_t>(cur % cols), 1, static_cast<int64_t>(n));
+    cur += n;
+  }
+  if (end - cur >= cols) {
+    const uint64_t rows = (end - cur) / cols;
+    add(static_cast<int64_t>(cur / cols), 0, static_cast<int64_t>(rows), v.cols);
+    cur += rows * cols;
+  }
+  if (cur < end) add(static_cast<int64_t>(cur / cols), 0, 1, static_cast<int64_t>(end - cur));
+}
 
 class ContextImpl;
 
 class ChannelImpl final : public Channel, public std::enable_shared_from_this<ChannelImpl> {
  public:
   ChannelImpl(std::shared_ptr<ContextImpl> ctx, std::shared_ptr<Channel> inner) : ctx_(std::move(ctx)), inner_(std::move(inner)) {}
+  ~ChannelImpl() override;
   void init();
-  void send(Buffer buffer, size_t length, TSendCallback cb) override;
-  void recv(Buffer buffer, size_t length, TRecvCallback cb) override;
+  void send(Buffer buffer, size_t length, TSendCallback cb) override {
+    SendItem it;
+    it.buffer = buffer;
+    it.length = length;
+    it.callback = std::move(cb);
+    std::vector<SendItem> v;
+    v.push_back(std::move(it));
+    sendBatch(std::move(v));
+  }
+  void recv(Buffer buffer, size_t length, TRecvCallback cb) override {
+    RecvItem it;
+    it.buffer = buffer;
+    it.length = length;
+    it.callback = std::move(cb);
+    std::vector<RecvItem> v;
+    v.push_back(std::move(it));
+    recvBatch(std::move(v));
+  }
+  void sendBatch(std::vector<SendItem> items) override;
+  void recvBatch(std::vector<RecvItem> items) override;
+  bool supportsLayouts() const override { return true; }
   void setId(std::string id) override { inner_->setId(id + ".cpu"); }
   void close() override;
   void closeFromLoop(const Error& e);
 
  private:
+  // One tensor of a batch.
   struct Op {
-    size_t remaining = 0;   // chunks not yet accounted for
+    size_t remaining = 0;  // pieces not yet accounted for
     Error error;
     std::function<void(const Error&)> cb;
-  };
-  struct Chunk {
-    std::shared_ptr<Op> op;
     bool cuda = false;
-    uint8_t* ptr = nullptr;  // CPU pointer, or device pointer
-    size_t len = 0;
+    uint8_t* ptr = nullptr;  // host or device address of the tensor
     int device = -1;
     cudaStream_t stream = nullptr;
-    int slot = -1;
-    uint32_t flagValue = 0;
-    bool staged = false;    // send: pack kernel launched / recv: inner recv issued
-    bool ready = false;     // send: pack finished
+    // send side
+    std::optional<StridedView> view;
+    // recv side
+    std::optional<DType> castTo;
+    DType srcDtype = DType::kBytes;
   };
+  // 2 MiB (or less) of one tensor's packed source bytes.
+  struct Piece {
+    std::shared_ptr<Op> op;
+    uint64_t off = 0;  // in packed source bytes
+    size_t len = 0;
+    Allocator::TChunk slot;
+    bool slotRequested = false;
+    bool launched = false;                  // send: the pack kernel has been launched
+    uint32_t flagIndex = 0, flagValue = 0;  // send: the flag of the launch that packs this piece
+  };
+  void sendBatchFromLoop(std::vector<SendItem> items);
+  void recvBatchFromLoop(std::vector<RecvItem> items);
   void pumpSend();
+  void packReady();
   void pumpRecv();
-  void chunkDone(const std::shared_ptr<Op>& op, const Error& e);
+  void unpackArrived();
+  void pieceDone(const std::shared_ptr<Op>& op, const Error& e);
   uint32_t* counterFor(int device, cudaStream_t stream);
 
   std::shared_ptr<ContextImpl> ctx_;
   std::shared_ptr<Channel> inner_;
   Error error_;
-  std::deque<Chunk> sendQueue_;  // in chunk order; front = next to hand to the inner channel
-  std::deque<Chunk> recvQueue_;  // chunks whose inner recv has not been issued yet
-  SlotPool sendSlots_, recvSlots_;
+  std::deque<Piece> sendQueue_;   // in piece order; front = next to hand to the inner channel
+  std::deque<Piece*> toPack_;     // pieces that got a slot and wait for the next pack launch
+  std::deque<Piece> recvQueue_;   // pieces whose inner recv has not been issued yet
+  std::deque<Piece> arrived_;     // device-bound pieces that sit in their slot, in order
+  bool unpackScheduled_ = false;
+  Slots sendSlots_, recvSlots_;
   uint32_t nextFlagValue_ = 1;
   std::map<std::pair<int, cudaStream_t>, uint32_t*> counters_;  // one arrive counter per launching stream
-
- public:
-  ~ChannelImpl() override {
-    for (auto& c : counters_) {
-      try {
-        CudaDeviceGuard g(c.first.first);
-        cudaFree(c.second);
-      } catch (...) {
-      }
-    }
-  }
 };
 
 class ContextImpl final : public Context, public std::enable_shared_from_this<ContextImpl> {
@@ -213,10 +246,10 @@ class ContextImpl final : public Context, public std::enable_shared_from_this<Co
     auto add = [&](const Device& d) {
       // Same structure as the reference's descriptor (tensorpipe/channel/cuda_basic/context_impl.cc:
       // 27-31,64-80) but with a prefixed inner descriptor, so that a reference peer's cuda_basic
-      // never matches: the chunking and the control traffic of the two differ.
+      // never matches: the pieces and the control traffic of the two differ.
       DeviceDescriptor dd;
       dd.deviceType = d.type;
-      dd.cpuDescriptor = "tpbcb1:" + it->second;
+      dd.cpuDescriptor = kInnerPrefix + it->second;
       auto bytes = nop::encode(dd);
       descriptors_[d] = std::string(bytes.begin(), bytes.end());
     };
@@ -231,7 +264,7 @@ class ContextImpl final : public Context, public std::enable_shared_from_this<Co
     DeviceDescriptor l, r;
     if (!nop::decode(local.data(), local.size(), l) || !nop::decode(remote.data(), remote.size(), r)) return false;
     if (l.deviceType == kCpuDeviceType && r.deviceType == kCpuDeviceType) return false;  // not our job
-    const std::string prefix = "tpbcb1:";
+    const std::string prefix = kInnerPrefix;
     if (l.cpuDescriptor.compare(0, prefix.size(), prefix) != 0 || r.cpuDescriptor.compare(0, prefix.size(), prefix) != 0)
       return false;
     return cpu_->canCommunicateWithRemote(l.cpuDescriptor.substr(prefix.size()), r.cpuDescriptor.substr(prefix.size()));
@@ -262,7 +295,7 @@ class ContextImpl final : public Context, public std::enable_shared_from_this<Co
     loop_.runInLoop([]() {});
   }
   OnDemandLoop loop_;
-  Poller poller_;
+  Poller poller_;  // the completion poller every device channel uses (common/poller.h)
   bool closed_ = false;
   std::set<std::weak_ptr<ChannelImpl>, std::owner_less<std::weak_ptr<ChannelImpl>>> channels_;
 
@@ -271,6 +304,16 @@ class ContextImpl final : public Context, public std::enable_shared_from_this<Co
   bool viable_ = false;
   std::unordered_map<Device, std::string> descriptors_;
 };
+
+ChannelImpl::~ChannelImpl() {
+  for (auto& c : counters_) {
+    try {
+      CudaDeviceGuard g(c.first.first);
+      cudaFree(c.second);
+    } catch (...) {
+    }
+  }
+}
 
 void ChannelImpl::init() {
   auto self = shared_from_this();
@@ -293,7 +336,7 @@ uint32_t* ChannelImpl::counterFor(int device, cudaStream_t stream) {
   return static_cast<uint32_t*>(p);
 }
 
-void ChannelImpl::chunkDone(const std::shared_ptr<Op>& op, const Error& e) {
+void ChannelImpl::pieceDone(const std::shared_ptr<Op>& op, const Error& e) {
   if (e && !op->error) op->error = e;
   if (--op->remaining == 0) {
     auto cb = std::move(op->cb);
@@ -301,188 +344,327 @@ void ChannelImpl::chunkDone(const std::shared_ptr<Op>& op, const Error& e) {
   }
 }
 
-void ChannelImpl::send(Buffer buffer, size_t length, TSendCallback cb) {
+void ChannelImpl::sendBatch(std::vector<SendItem> items) {
   auto self = shared_from_this();
-  ctx_->loop_.deferToLoop([self, buffer, length, cb = std::move(cb)]() mutable {
-    if (self->error_) return cb(self->error_);
-    if (length == 0) return cb(Error::kSuccess);
-    auto op = std::make_shared<Op>();
-    op->cb = std::move(cb);
-    op->remaining = (length + kChunkBytes - 1) / kChunkBytes;
-    for (size_t off = 0; off < length; off += kChunkBytes) {
-      Chunk c;
-      c.op = op;
-      c.len = std::min(kChunkBytes, length - off);
-      if (buffer.isCuda()) {
-        const CudaBuffer& b = buffer.unwrap<CudaBuffer>();
-        c.cuda = true;
-        c.ptr = static_cast<uint8_t*>(b.ptr) + off;
-        c.device = cudaDeviceForPointerOrHint(b);
-        c.stream = static_cast<cudaStream_t>(b.stream);
-      } else {
-        c.ptr = static_cast<uint8_t*>(buffer.unwrap<CpuBuffer>().ptr) + off;
-      }
-      self->sendQueue_.push_back(std::move(c));
+  auto shared = std::make_shared<std::vector<SendItem>>(std::move(items));
+  ctx_->loop_.deferToLoop([self, shared]() { self->sendBatchFromLoop(std::move(*shared)); });
+}
+
+void ChannelImpl::recvBatch(std::vector<RecvItem> items) {
+  auto self = shared_from_this();
+  auto shared = std::make_shared<std::vector<RecvItem>>(std::move(items));
+  ctx_->loop_.deferToLoop([self, shared]() { self->recvBatchFromLoop(std::move(*shared)); });
+}
+
+void ChannelImpl::sendBatchFromLoop(std::vector<SendItem> items) {
+  for (auto& it : items) {
+    if (error_) {
+      it.callback(error_);
+      continue;
     }
-    self->pumpSend();
-  });
+    if (it.length == 0) {
+      it.callback(Error::kSuccess);
+      continue;
+    }
+    if (it.view && static_cast<uint64_t>(it.view->rows) * it.view->cols * dtypeSize(it.view->dtype) != it.length) {
+      it.callback(TPB_CREATE_ERROR(LogicError, "strided view does not match the tensor length"));
+      continue;
+    }
+    auto op = std::make_shared<Op>();
+    op->cb = std::move(it.callback);
+    op->remaining = (it.length + kPieceBytes - 1) / kPieceBytes;
+    op->view = it.view;
+    if (it.buffer.isCuda()) {
+      const CudaBuffer& b = it.buffer.unwrap<CudaBuffer>();
+      op->cuda = true;
+      op->ptr = static_cast<uint8_t*>(b.ptr);
+      op->device = cudaDeviceForPointerOrHint(b);
+      op->stream = static_cast<cudaStream_t>(b.stream);
+    } else {
+      op->ptr = static_cast<uint8_t*>(it.buffer.unwrap<CpuBuffer>().ptr);
+    }
+    for (uint64_t off = 0; off < it.length; off += kPieceBytes) {
+      Piece p;
+      p.op = op;
+      p.off = off;
+      p.len = std::min<uint64_t>(kPieceBytes, it.length - off);
+      sendQueue_.push_back(std::move(p));
+    }
+  }
+  pumpSend();
 }
 
 void ChannelImpl::pumpSend() {
   if (error_) return;
   auto self = shared_from_this();
   try {
-    // Stage: start the pack kernel of every CUDA chunk for which a slot is free, in order.
-    for (auto& c : sendQueue_) {
-      if (c.staged) continue;
-      if (!c.cuda) {
-        c.staged = c.ready = true;
-        continue;
-      }
+    // Slots: every device piece asks for one, in order; the pool answers in that order. A piece
+    // that has its slot joins the next pack launch.
+    for (auto& p : sendQueue_) {
+      if (p.slotRequested || !p.op->cuda) continue;
       if (!sendSlots_.ensure()) throw std::runtime_error("cannot allocate pinned staging memory");
-      if (sendSlots_.free.empty()) break;
-      c.slot = sendSlots_.free.front();
-      sendSlots_.free.pop_front();
-      c.flagValue = nextFlagValue_++;
-      CudaDeviceGuard g(c.device);
-      kernels::PushPlan plan;
-      kernels::CopyItem item;
-      item.src = c.ptr;
-      item.dst = sendSlots_.slot(c.slot);
-      item.srcBytes = c.len;
-      kernels::appendToPlan(plan, item, false);
-      uint32_t* flag = const_cast<uint32_t*>(sendSlots_.flags + c.slot);
-      kernels::launchPush(plan, c.stream, cudaSmCount(c.device), flag, c.flagValue, counterFor(c.device, c.stream), nullptr);
-      c.staged = true;
-      volatile uint32_t* hostFlag = sendSlots_.flags + c.slot;
-      const uint32_t want = c.flagValue;
-      ctx_->poller_.watch([hostFlag, want]() { return static_cast<int32_t>(*hostFlag - want) >= 0; },
-                          [self]() { self->ctx_->loop_.deferToLoop([self]() { self->pumpSend(); }); });
+      if (sendSlots_.pool->numAvailable() == 0) break;  // the rest ask when slots come back
+      p.slotRequested = true;
+      Piece* piece = &p;  // a deque keeps element addresses across push_back and pop_front
+      sendSlots_.pool->alloc(p.len, [this, piece](const Error& e, Allocator::TChunk chunk) {
+        if (e) return;  // the pool only fails when the channel is going away
+        piece->slot = std::move(chunk);
+        toPack_.push_back(piece);
+      });
     }
-    // Hand over: the front chunk goes to the CPU channel once its bytes are in the slot.
+    if (!toPack_.empty()) packReady();
+    // Hand over: the front piece goes to the CPU channel once its bytes are where they must be.
     while (!sendQueue_.empty()) {
-      Chunk& c = sendQueue_.front();
-      if (!c.staged) break;
-      if (c.cuda && !c.ready) {
-        if (static_cast<int32_t>(sendSlots_.flags[c.slot] - c.flagValue) < 0) break;
+      Piece& front = sendQueue_.front();
+      if (front.op->cuda) {
+        if (!front.launched) break;
+        if (static_cast<int32_t>(sendSlots_.flags[front.flagIndex] - front.flagValue) < 0) break;
         std::atomic_thread_fence(std::memory_order_acquire);
-        c.ready = true;
-      }
-      Chunk chunk = std::move(c);
-      sendQueue_.pop_front();
-      if (chunk.cuda) {
-        // The source is reusable once packed; the op completes when all its chunks are packed
-        // (stream order) — the slot lives on until the CPU channel is done with it.
-        const int slot = chunk.slot;
-        inner_->send(CpuBuffer{sendSlots_.slot(slot)}, chunk.len, [self, slot](const Error& e) {
-          self->ctx_->loop_.deferToLoop([self, slot, e]() {
-            self->sendSlots_.free.push_back(slot);
+        Piece piece = std::move(front);
+        sendQueue_.pop_front();
+        // The source is reusable once packed: the tensor completes when all its pieces are
+        // packed (stream order). The slot lives on until the CPU channel is done with it.
+        Allocator::TChunk slot = piece.slot;
+        inner_->send(CpuBuffer{slot.get()}, piece.len, [self, slot](const Error& e) mutable {
+          self->ctx_->loop_.deferToLoop([self, slot = std::move(slot), e]() mutable {
+            slot.reset();  // back to the pool, on the loop
             if (e) return self->closeFromLoop(e);
             self->pumpSend();
           });
         });
-        chunkDone(chunk.op, Error::kSuccess);
-      } else {
-        auto op = chunk.op;
-        inner_->send(CpuBuffer{chunk.ptr}, chunk.len, [self, op](const Error& e) {
-          self->ctx_->loop_.deferToLoop([self, op, e]() {
-            self->chunkDone(op, e);
-            if (e) self->closeFromLoop(e);
-          });
-        });
+        pieceDone(piece.op, Error::kSuccess);
+        continue;
       }
+      // A host tensor goes as it lies; a view over host memory is packed here first.
+      Piece piece = std::move(front);
+      sendQueue_.pop_front();
+      const uint8_t* from = piece.op->ptr + piece.off;
+      auto keep = std::make_shared<std::vector<uint8_t>>();
+      if (piece.op->view) {
+        const size_t es = dtypeSize(piece.op->view->dtype);
+        keep->resize(piece.len);
+        hostGather(piece.op->ptr, *piece.op->view, es, piece.off / es, piece.len / es, keep->data());
+        from = keep->data();
+      }
+      auto op = piece.op;
+      inner_->send(CpuBuffer{const_cast<uint8_t*>(from)}, piece.len, [self, op, keep](const Error& e) {
+        self->ctx_->loop_.deferToLoop([self, op, e]() {
+          self->pieceDone(op, e);
+          if (e) self->closeFromLoop(e);
+        });
+      });
     }
   } catch (const std::exception& ex) {
     closeFromLoop(TPB_CREATE_ERROR(CudaError, ex.what()));
   }
 }
 
-void ChannelImpl::recv(Buffer buffer, size_t length, TRecvCallback cb) {
+// One launch for every piece that has a slot by now (of one device and stream at a time): the
+// pieces of a large tensor, or many small tensors, or both.
+void ChannelImpl::packReady() {
   auto self = shared_from_this();
-  ctx_->loop_.deferToLoop([self, buffer, length, cb = std::move(cb)]() mutable {
-    if (self->error_) return cb(self->error_);
-    if (length == 0) return cb(Error::kSuccess);
-    auto op = std::make_shared<Op>();
-    op->cb = std::move(cb);
-    op->remaining = (length + kChunkBytes - 1) / kChunkBytes;
-    for (size_t off = 0; off < length; off += kChunkBytes) {
-      Chunk c;
-      c.op = op;
-      c.len = std::min(kChunkBytes, length - off);
-      if (buffer.isCuda()) {
-        const CudaBuffer& b = buffer.unwrap<CudaBuffer>();
-        c.cuda = true;
-        c.ptr = static_cast<uint8_t*>(b.ptr) + off;
-        c.device = cudaDeviceForPointerOrHint(b);
-        c.stream = static_cast<cudaStream_t>(b.stream);
+  while (!toPack_.empty()) {
+    const int device = toPack_.front()->op->device;
+    cudaStream_t stream = toPack_.front()->op->stream;
+    trace::Scope traced("cuda_basic.pack", toPack_.size());
+    CudaDeviceGuard g(device);
+    kernels::PushPlan plan;
+    std::vector<Piece*> group;
+    while (!toPack_.empty() && toPack_.front()->op->device == device && toPack_.front()->op->stream == stream) {
+      Piece* p = toPack_.front();
+      toPack_.pop_front();
+      uint8_t* out = p->slot.get();
+      if (p->op->view) {
+        const size_t es = dtypeSize(p->op->view->dtype);
+        appendViewRange(plan, p->op->ptr, *p->op->view, p->off / es, p->len / es, out);
       } else {
-        c.ptr = static_cast<uint8_t*>(buffer.unwrap<CpuBuffer>().ptr) + off;
+        kernels::CopyItem item;
+        item.src = p->op->ptr + p->off;
+        item.dst = out;
+        item.srcBytes = p->len;
+        kernels::appendToPlan(plan, item, false);
       }
-      self->recvQueue_.push_back(std::move(c));
+      group.push_back(p);
     }
-    self->pumpRecv();
-  });
+    const uint32_t flagIndex = static_cast<uint32_t>(sendSlots_.indexOf(group.front()->slot.get()));
+    const uint32_t flagValue = nextFlagValue_++;
+    uint32_t* flag = const_cast<uint32_t*>(sendSlots_.flags + flagIndex);
+    kernels::launchPush(plan, stream, cudaSmCount(device), flag, flagValue, counterFor(device, stream), nullptr);
+    for (Piece* p : group) {
+      p->launched = true;
+      p->flagIndex = flagIndex;
+      p->flagValue = flagValue;
+    }
+    volatile uint32_t* hostFlag = sendSlots_.flags + flagIndex;
+    ctx_->poller_.watch([hostFlag, flagValue]() { return static_cast<int32_t>(*hostFlag - flagValue) >= 0; },
+                        [self]() { self->ctx_->loop_.deferToLoop([self]() { self->pumpSend(); }); });
+  }
+}
+
+void ChannelImpl::recvBatchFromLoop(std::vector<RecvItem> items) {
+  for (auto& it : items) {
+    if (error_) {
+      it.callback(error_);
+      continue;
+    }
+    if (it.length == 0) {
+      it.callback(Error::kSuccess);
+      continue;
+    }
+    auto op = std::make_shared<Op>();
+    op->cb = std::move(it.callback);
+    op->remaining = (it.length + kPieceBytes - 1) / kPieceBytes;
+    op->castTo = it.castTo;
+    op->srcDtype = it.srcDtype;
+    if (it.castTo && *it.castTo == it.srcDtype) op->castTo.reset();
+    const char* refused = nullptr;
+    if (it.buffer.isCuda()) {
+      const CudaBuffer& b = it.buffer.unwrap<CudaBuffer>();
+      op->cuda = true;
+      op->ptr = static_cast<uint8_t*>(b.ptr);
+      op->device = cudaDeviceForPointerOrHint(b);
+      op->stream = static_cast<cudaStream_t>(b.stream);
+      if (op->castTo && !kernels::castSupported(op->srcDtype, *op->castTo))
+        refused = "unsupported dtype conversion requested by the receiver";
+    } else {
+      op->ptr = static_cast<uint8_t*>(it.buffer.unwrap<CpuBuffer>().ptr);
+      if (op->castTo && !hostCastSupported(op->srcDtype, *op->castTo))
+        refused = "this conversion is not available for a tensor received on the host";
+    }
+    if (refused) {
+      // The peer is sending this tensor already: without a place for it the channel is over.
+      const Error why = TPB_CREATE_ERROR(LogicError, refused);
+      op->cb(why);
+      closeFromLoop(why);
+      continue;
+    }
+    for (uint64_t off = 0; off < it.length; off += kPieceBytes) {
+      Piece p;
+      p.op = op;
+      p.off = off;
+      p.len = std::min<uint64_t>(kPieceBytes, it.length - off);
+      recvQueue_.push_back(std::move(p));
+    }
+  }
+  pumpRecv();
 }
 
 void ChannelImpl::pumpRecv() {
   if (error_) return;
   auto self = shared_from_this();
   try {
+    // Strictly in piece order: the inner channel pairs its k-th recv with the peer's k-th send.
     while (!recvQueue_.empty()) {
-      Chunk& front = recvQueue_.front();
-      if (front.cuda) {
+      Piece& front = recvQueue_.front();
+      if (front.op->cuda && !front.slot) {
+        if (front.slotRequested) break;  // the pool will call back
         if (!recvSlots_.ensure()) throw std::runtime_error("cannot allocate pinned staging memory");
-        if (recvSlots_.free.empty()) break;
-        front.slot = recvSlots_.free.front();
-        recvSlots_.free.pop_front();
+        front.slotRequested = true;
+        Piece* piece = &front;
+        auto answeredInline = std::make_shared<bool>(true);
+        recvSlots_.pool->alloc(front.len, [this, self, piece, answeredInline](const Error& e, Allocator::TChunk chunk) {
+          if (e || error_) return;  // after a close the piece it was meant for is gone
+          piece->slot = std::move(chunk);
+          if (!*answeredInline) pumpRecv();  // a slot came back later: carry on from here
+        });
+        *answeredInline = false;
+        if (!front.slot) break;
       }
-      Chunk c = std::move(front);
+      Piece piece = std::move(front);
       recvQueue_.pop_front();
-      if (!c.cuda) {
-        auto op = c.op;
-        inner_->recv(CpuBuffer{c.ptr}, c.len, [self, op](const Error& e) {
+      auto op = piece.op;
+      if (!op->cuda && !op->castTo) {
+        inner_->recv(CpuBuffer{op->ptr + piece.off}, piece.len, [self, op](const Error& e) {
           self->ctx_->loop_.deferToLoop([self, op, e]() {
-            self->chunkDone(op, e);
+            self->pieceDone(op, e);
             if (e) self->closeFromLoop(e);
           });
         });
         continue;
       }
-      inner_->recv(CpuBuffer{recvSlots_.slot(c.slot)}, c.len, [self, c](const Error& e) {
-        self->ctx_->loop_.deferToLoop([self, c, e]() {
+      if (!op->cuda) {
+        // Host tensor with a conversion: receive into a temporary, convert on arrival.
+        auto temp = std::make_shared<std::vector<uint8_t>>(piece.len);
+        const uint64_t off = piece.off;
+        const size_t len = piece.len;
+        inner_->recv(CpuBuffer{temp->data()}, len, [self, op, temp, off, len](const Error& e) {
+          self->ctx_->loop_.deferToLoop([self, op, temp, off, len, e]() {
+            if (!e) {
+              const size_t ses = dtypeSize(op->srcDtype), des = dtypeSize(*op->castTo);
+              hostCast(temp->data(), op->srcDtype, op->ptr + off / ses * des, len / ses);
+            }
+            self->pieceDone(op, e);
+            if (e) self->closeFromLoop(e);
+          });
+        });
+        continue;
+      }
+      auto shared = std::make_shared<Piece>(std::move(piece));
+      inner_->recv(CpuBuffer{shared->slot.get()}, shared->len, [self, shared](const Error& e) {
+        self->ctx_->loop_.deferToLoop([self, shared, e]() {
           if (e || self->error_) {
-            self->recvSlots_.free.push_back(c.slot);
-            self->chunkDone(c.op, e ? e : self->error_);
+            shared->slot.reset();
+            self->pieceDone(shared->op, e ? e : self->error_);
             if (e) self->closeFromLoop(e);
             return;
           }
-          try {
-            // Unpack on the user's stream; the slot is reusable once the kernel has run.
-            CudaDeviceGuard g(c.device);
-            kernels::PushPlan plan;
-            kernels::CopyItem item;
-            item.src = self->recvSlots_.slot(c.slot);
-            item.dst = c.ptr;
-            item.srcBytes = c.len;
-            kernels::appendToPlan(plan, item, false);
-            kernels::launchPush(plan, c.stream, cudaSmCount(c.device), nullptr, 0, nullptr, nullptr);
-            auto ev = std::make_shared<CudaEvent>(c.device);
-            ev->record(c.stream);
-            const int slot = c.slot;
-            self->ctx_->poller_.watch([ev]() { return ev->query(); },
-                                      [self, slot, ev]() {
-                                        self->ctx_->loop_.deferToLoop([self, slot]() {
-                                          self->recvSlots_.free.push_back(slot);
-                                          self->pumpRecv();
-                                        });
-                                      });
-            self->chunkDone(c.op, Error::kSuccess);  // enqueued on the stream = received
-          } catch (const std::exception& ex) {
-            self->chunkDone(c.op, TPB_CREATE_ERROR(CudaError, ex.what()));
-            self->closeFromLoop(TPB_CREATE_ERROR(CudaError, ex.what()));
+          self->arrived_.push_back(std::move(*shared));
+          // Everything that arrives in this turn of the loop shares one unpack launch.
+          if (!self->unpackScheduled_) {
+            self->unpackScheduled_ = true;
+            self->ctx_->loop_.deferToLoop([self]() {
+              self->unpackScheduled_ = false;
+              self->unpackArrived();
+            });
           }
         });
       });
+    }
+  } catch (const std::exception& ex) {
+    closeFromLoop(TPB_CREATE_ERROR(CudaError, ex.what()));
+  }
+}
+
+void ChannelImpl::unpackArrived() {
+  if (error_) return;
+  auto self = shared_from_this();
+  try {
+    while (!arrived_.empty()) {
+      const int device = arrived_.front().op->device;
+      cudaStream_t stream = arrived_.front().op->stream;
+      trace::Scope traced("cuda_basic.unpack", arrived_.size());
+      CudaDeviceGuard g(device);
+      kernels::PushPlan plan;
+      auto group = std::make_shared<std::vector<Piece>>();
+      while (!arrived_.empty() && arrived_.front().op->device == device && arrived_.front().op->stream == stream) {
+        Piece p = std::move(arrived_.front());
+        arrived_.pop_front();
+        kernels::CopyItem item;
+        item.src = p.slot.get();
+        item.srcBytes = p.len;
+        if (p.op->castTo) {
+          const size_t ses = dtypeSize(p.op->srcDtype), des = dtypeSize(*p.op->castTo);
+          item.dst = p.op->ptr + p.off / ses * des;
+          item.srcDtype = p.op->srcDtype;
+          item.dstDtype = *p.op->castTo;
+        } else {
+          item.dst = p.op->ptr + p.off;
+        }
+        kernels::appendToPlan(plan, item, false);
+        group->push_back(std::move(p));
+      }
+      kernels::launchPush(plan, stream, cudaSmCount(device), nullptr, 0, nullptr, nullptr);
+      // The slots are free again once the kernel has read them.
+      auto ev = std::make_shared<CudaEvent>(device);
+      ev->record(stream);
+      ctx_->poller_.watch([ev]() { return ev->query(); },
+                          [self, group, ev]() {
+                            self->ctx_->loop_.deferToLoop([self, group]() {
+                              for (auto& p : *group) p.slot.reset();
+                              self->pumpRecv();
+                            });
+                          });
+      for (auto& p : *group) pieceDone(p.op, Error::kSuccess);  // enqueued on the stream = received
     }
   } catch (const std::exception& ex) {
     closeFromLoop(TPB_CREATE_ERROR(CudaError, ex.what()));
@@ -499,12 +681,16 @@ void ChannelImpl::closeFromLoop(const Error& e) {
   error_ = e;
   inner_->close();
   ctx_->channels_.erase(weak_from_this());
+  toPack_.clear();
   auto sends = std::move(sendQueue_);
   auto recvs = std::move(recvQueue_);
+  auto arrived = std::move(arrived_);
   sendQueue_.clear();
   recvQueue_.clear();
-  for (auto& c : sends) chunkDone(c.op, error_);
-  for (auto& c : recvs) chunkDone(c.op, error_);
+  arrived_.clear();
+  for (auto& p : sends) pieceDone(p.op, error_);
+  for (auto& p : recvs) pieceDone(p.op, error_);
+  for (auto& p : arrived) pieceDone(p.op, error_);
 }
 
 }  // namespace

@@ -6,8 +6,10 @@
 // memcpys through staging slots with a control round trip per 8 MiB chunk, the SENDER runs one
 // persistent kernel (kernels/push.cu) that reads its own tensors and stores straight into the
 // receiver's memory, for all tensors of the message at once, then publishes a flag in the
-// receiver's memory. Raw pointers when both ends live in one process, CUDA IPC mappings otherwise;
-// everything else is the same code.
+// receiver's memory. When both ends live in one process the targets are raw pointers, completion
+// is a CUDA event the receiver's stream waits for (no flag, no fence at the end of the kernel) and
+// everything goes by rendezvous; between processes the targets are CUDA IPC mappings, completion is
+// a flag, and small batches go eagerly.
 //
 // Control protocol on the channel's single connection (one nop-encoded Packet per frame). Both
 // endpoints number their non-empty batches independently per direction; the k-th batch sent
@@ -149,8 +151,9 @@ struct Launched {
   uint8_t eager = 0;
   uint64_t inboxOffset = 0;
   uint64_t creditValue = 0;
+  uint64_t event = 0;  // same process: the cudaEvent_t recorded behind the push
   std::string error;
-  TPB_NOP_STRUCTURE(Launched, seq, eager, inboxOffset, creditValue, error)
+  TPB_NOP_STRUCTURE(Launched, seq, eager, inboxOffset, creditValue, event, error)
 };
 
 struct Credit {
@@ -374,6 +377,34 @@ class ExportCache {
   std::map<uintptr_t, Entry> byBase_;
 };
 
+// Large tensors in pinned host memory travel in pieces: the copy engine brings a piece into a slot
+// of device memory while the push kernel sends the piece before it on to the peer, so the PCIe
+// copy runs at the copy engine's rate and the NVLink hop hides behind it. One per context and
+// sending device, shared by its channels (all of them work from the context's one loop thread;
+// the slots are handed from use to use by events).
+constexpr uint64_t kHostFeedMinBytes = 4u << 20;   // smaller host tensors are read by the kernel in place
+constexpr uint64_t kHostFeedTailBytes = 2u << 20;  // the piece that travels with the publishing launch
+struct HostFeed {
+  static constexpr size_t kSlots = 2;
+  int device = -1;
+  size_t pieceBytes = 0;
+  cudaStream_t copyStream = nullptr;
+  uint8_t* slots = nullptr;
+  std::unique_ptr<CudaEvent> begin;
+  std::unique_ptr<CudaEvent> copied[kSlots], sent[kSlots];
+  bool everSent[kSlots] = {};
+  uint64_t next = 0;
+  ~HostFeed() {
+    if (device < 0) return;
+    try {
+      CudaDeviceGuard g(device);
+      if (copyStream) cudaStreamSynchronize(copyStream), cudaStreamDestroy(copyStream);
+      if (slots) cudaFree(slots);
+    } catch (...) {
+    }
+  }
+};
+
 class ContextImpl;
 
 // This end's arena on one of its devices: flags and arrive counters, then the inbox ring.
@@ -538,14 +569,14 @@ class ChannelImpl final : public Channel, public std::enable_shared_from_this<Ch
   void sendByeWhenIdle();
   int allCtas(int device) const { return opts_.maxCtas > 0 ? opts_.maxCtas : cudaSmCount(device); }
   int ctasFor(int device);
-  // Whether a source may go through the bulk-copy (TMA) pipeline: only plain device memory of
-  // the launching GPU does. Pinned host memory that a user hands over as a tensor of this GPU,
-  // or memory of another GPU, is read with ordinary loads. (Asked only for tensors large enough
-  // to take the bulk path at all.)
+  // Whether a source may go through the bulk-copy (TMA) pipeline: memory of the launching GPU
+  // does, and so does pinned host memory that a user hands over as a tensor of this GPU (the
+  // deep queue of bulk loads is what keeps PCIe busy); memory of another GPU is read with
+  // ordinary loads. (Asked only for tensors large enough to take the bulk path at all.)
   bool bulkFor(const void* src, size_t bytes, int device) const {
     if (!opts_.useBulkCopy) return false;
     if (bytes < kernels::getPushTuning().bulkMinBytes) return true;
-    return cudaIsLocalDeviceMemory(src, device);
+    return cudaIsLocalMemory(src, device);
   }
   bool sourceIsOtherGpu(const RecvOp& op) const;
   template <typename It>
@@ -579,6 +610,23 @@ class ChannelImpl final : public Channel, public std::enable_shared_from_this<Ch
   uint64_t launchedUpTo_ = 0;   // one past the newest launched sequence number
   bool waitingForRoom_ = false;
   int launchesMade_ = 0;
+  // Same process: events recorded behind the pushes, reused round-robin. The receiver makes its
+  // stream wait for an event as soon as the Launched frame naming it arrives, long before the
+  // sender comes round to that event again.
+  static constexpr size_t kEventRing = 512;
+  std::map<int, std::vector<std::unique_ptr<CudaEvent>>> eventRings_;
+  CudaEvent* lastPushEvent_ = nullptr;
+  CudaEvent& eventFor(int device, uint64_t seq);
+  struct HostFedItem {
+    const uint8_t* src;
+    uint8_t* dst;
+    uint64_t bytes;
+    bool remote;
+  };
+  // Queues all pieces of `items` but the last on `stream`; the last one is added to `plan`, so
+  // that the launch which publishes the batch carries it. Returns the slot that launch frees.
+  int feedFromHost(HostFeed& feed, const std::vector<HostFedItem>& items, cudaStream_t stream, int ctas,
+                   kernels::PushPlan& plan);
   // Closing.
   bool byeSent_ = false, byeReceived_ = false, finished_ = false;
   bool peerLeft_ = false;  // the peer said goodbye while this end was open: only early arrivals can still be received
@@ -588,6 +636,8 @@ class ChannelImpl final : public Channel, public std::enable_shared_from_this<Ch
 
 class ContextImpl final : public Context, public std::enable_shared_from_this<ContextImpl> {
  public:
+  HostFeed* hostFeedFor(int device);
+  std::map<int, std::unique_ptr<HostFeed>> hostFeeds_;
   explicit ContextImpl(Options opts) : opts_(opts) {
     const int n = cudaDeviceCountNoThrow();
     if (n == 0) return;
@@ -992,7 +1042,16 @@ void ChannelImpl::advanceConfirmed() {
   while (confirmed_ < launchedUpTo_ && done[confirmed_ % kFlagSlots] == static_cast<uint32_t>(confirmed_ + 1)) ++confirmed_;
 }
 
+CudaEvent& ChannelImpl::eventFor(int device, uint64_t seq) {
+  auto& ring = eventRings_[device];
+  if (ring.empty()) ring.resize(kEventRing);
+  auto& slot = ring[seq % kEventRing];
+  if (!slot) slot = std::make_unique<CudaEvent>(device);
+  return *slot;
+}
+
 bool ChannelImpl::roomFor(uint64_t seq) {
+  if (sameProcess_) return true;  // no flag slots, no counters: nothing to run out of
   if (seq - confirmed_ < kMaxUnfinished) return true;
   advanceConfirmed();
   if (seq - confirmed_ < kMaxUnfinished) return true;
@@ -1027,6 +1086,7 @@ int ChannelImpl::ctasFor(int device) {
 }
 
 ChannelImpl::Eager ChannelImpl::tryEager(SendOp& op) {
+  if (sameProcess_) return Eager::kNotEligible;
   auto pa = peerArenas_.find(op.targetDevice.index);
   if (pa == peerArenas_.end()) return Eager::kNotEligible;
   PeerArena& peer = pa->second;
@@ -1128,13 +1188,76 @@ ChannelImpl::Eager ChannelImpl::tryEager(SendOp& op) {
   return Eager::kLaunched;
 }
 
+HostFeed* ContextImpl::hostFeedFor(int device) {
+  auto& feed = hostFeeds_[device];
+  if (feed) return feed.get();
+  auto f = std::make_unique<HostFeed>();
+  f->pieceBytes = (std::max<size_t>(opts_.hostPieceBytes, 1u << 20) + 255) / 256 * 256;
+  CudaDeviceGuard g(device);
+  if (cudaStreamCreateWithFlags(&f->copyStream, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaMalloc(reinterpret_cast<void**>(&f->slots), HostFeed::kSlots * f->pieceBytes) != cudaSuccess) {
+    cudaGetLastError();
+    if (f->copyStream) cudaStreamDestroy(f->copyStream);
+    return nullptr;
+  }
+  f->device = device;
+  f->begin = std::make_unique<CudaEvent>(device);
+  for (size_t i = 0; i < HostFeed::kSlots; ++i) {
+    f->copied[i] = std::make_unique<CudaEvent>(device);
+    f->sent[i] = std::make_unique<CudaEvent>(device);
+  }
+  feed = std::move(f);
+  return feed.get();
+}
+
+int ChannelImpl::feedFromHost(HostFeed& feed, const std::vector<HostFedItem>& items, cudaStream_t stream, int ctas,
+                              kernels::PushPlan& plan) {
+  // The host memory is read after whatever the user queued on the stream before the send.
+  feed.begin->record(stream);
+  feed.begin->wait(feed.copyStream, feed.device);
+  int lastSlot = -1;
+  for (size_t i = 0; i < items.size(); ++i) {
+    const HostFedItem& it = items[i];
+    const bool lastItem = i + 1 == items.size();
+    for (uint64_t off = 0; off < it.bytes;) {
+      uint64_t len = std::min<uint64_t>(feed.pieceBytes, it.bytes - off);
+      // Nothing hides the push of the very last piece: keep it small.
+      if (lastItem && off + len >= it.bytes && len > 2 * kHostFeedTailBytes) len = (len - kHostFeedTailBytes) & ~uint64_t(255);
+      const size_t slot = feed.next++ % HostFeed::kSlots;
+      uint8_t* piece = feed.slots + slot * feed.pieceBytes;
+      if (feed.everSent[slot]) feed.sent[slot]->wait(feed.copyStream, feed.device);
+      TPB_CUDA_CHECK(cudaMemcpyAsync(piece, it.src + off, len, cudaMemcpyHostToDevice, feed.copyStream));
+      feed.copied[slot]->record(feed.copyStream);
+      feed.copied[slot]->wait(stream, feed.device);
+      kernels::CopyItem c;
+      c.src = piece;
+      c.dst = it.dst + off;
+      c.srcBytes = len;
+      c.remote = it.remote;
+      off += len;
+      if (lastItem && off >= it.bytes) {
+        kernels::appendToPlan(plan, c, opts_.useBulkCopy);
+        lastSlot = static_cast<int>(slot);
+      } else {
+        kernels::PushPlan piecePlan;
+        kernels::chooseBulkTile(piecePlan, len, ctas);
+        kernels::appendToPlan(piecePlan, c, opts_.useBulkCopy);
+        kernels::launchPush(piecePlan, stream, ctas, nullptr, 0, nullptr, statusWord());
+        feed.sent[slot]->record(stream);
+        feed.everSent[slot] = true;
+      }
+    }
+  }
+  return lastSlot;
+}
+
 void ChannelImpl::launchRendezvous(SendOp& op) {
   trace::Scope traced("p2p.send.rendezvous", op.seq);
   const RecvReady& ready = *op.ready;
   if (ready.targets.size() != op.items.size())
     return closeFromLoop(TPB_CREATE_ERROR(LogicError, "peer announced a different number of tensors"));
   CudaDeviceGuard g(op.srcDevice);
-  if (ready.arena) {
+  if (ready.arena && !sameProcess_) {
     PeerArena pa;
     pa.handle = ready.arena->handle;
     pa.address = ready.arena->address;
@@ -1143,12 +1266,15 @@ void ChannelImpl::launchRendezvous(SendOp& op) {
     pa.announcedSeq = static_cast<int64_t>(ready.seq);
     peerArenas_[ready.deviceIdx] = pa;
   }
-  auto arena = peerArenas_.find(ready.deviceIdx);
-  if (arena == peerArenas_.end())
-    return closeFromLoop(TPB_CREATE_ERROR(LogicError, "peer never announced its arena for that device"));
   std::string why;
-  uint8_t* arenaBase = peerArenaBase(arena->second, op.srcDevice, &why);
-  if (!arenaBase) return closeFromLoop(TPB_CREATE_ERROR(CudaError, why));
+  uint8_t* arenaBase = nullptr;
+  if (!sameProcess_) {
+    auto arena = peerArenas_.find(ready.deviceIdx);
+    if (arena == peerArenas_.end())
+      return closeFromLoop(TPB_CREATE_ERROR(LogicError, "peer never announced its arena for that device"));
+    arenaBase = peerArenaBase(arena->second, op.srcDevice, &why);
+    if (!arenaBase) return closeFromLoop(TPB_CREATE_ERROR(CudaError, why));
+  }
   if (sameProcess_ && ready.deviceIdx != op.srcDevice && !cudaEnablePeerAccessOnce(op.srcDevice, ready.deviceIdx))
     return closeFromLoop(TPB_CREATE_ERROR(CudaError, "peer access between the two GPUs cannot be enabled"));
   for (const RegionWire& r : ready.newRegions) {
@@ -1165,12 +1291,18 @@ void ChannelImpl::launchRendezvous(SendOp& op) {
   {
     uint64_t bulkBytes = 0;
     const uint64_t bulkMin = kernels::getPushTuning().bulkMinBytes;
-    for (auto& it : op.items)
-      if (!it.view && it.length >= bulkMin) bulkBytes += it.length;
+    for (auto& it : op.items) {
+      if (it.view || it.length < bulkMin) continue;
+      // Of a tensor fed from host memory only the last piece is part of this plan.
+      const bool fed = opts_.hostPieceBytes != 0 && it.length >= kHostFeedMinBytes &&
+          cudaIsPinnedHostMemory(it.buffer.unwrap<CudaBuffer>().ptr);
+      bulkBytes += fed ? kHostFeedTailBytes : it.length;
+    }
     kernels::chooseBulkTile(plan, bulkBytes, ctas);
   }
   const uint64_t generation = MappingCache::get().generation();
   const uint64_t now = nowNs();
+  std::vector<HostFedItem> fromHost;
   for (size_t i = 0; i < op.items.size(); ++i) {
     SendItem& it = op.items[i];
     const TargetWire& t = ready.targets[i];
@@ -1213,6 +1345,11 @@ void ChannelImpl::launchRendezvous(SendOp& op) {
       return closeFromLoop(TPB_CREATE_ERROR(LogicError, "unsupported dtype conversion requested by the receiver"));
     if (kernels::convertedBytes(it.length, c.srcDtype, c.dstDtype) != t.bytes)
       return closeFromLoop(TPB_CREATE_ERROR(LogicError, "receiver's buffer size does not match the tensor"));
+    if (opts_.hostPieceBytes != 0 && !c.strided && c.dstDtype == c.srcDtype && it.length >= kHostFeedMinBytes &&
+        cudaIsPinnedHostMemory(c.src)) {
+      fromHost.push_back({static_cast<const uint8_t*>(c.src), static_cast<uint8_t*>(c.dst), it.length, c.remote});
+      continue;
+    }
     kernels::appendToPlan(plan, c, bulkFor(c.src, it.length, op.srcDevice));
   }
 
@@ -1228,24 +1365,50 @@ void ChannelImpl::launchRendezvous(SendOp& op) {
     ev.record(s);
     ev.wait(stream, op.srcDevice);
   }
-  Error err;
-  Arena* mine = arenaFor(op.srcDevice, err);
-  if (!mine) return closeFromLoop(err);
-  uint32_t* flag = reinterpret_cast<uint32_t*>(arenaBase) + (op.seq % kFlagSlots);
-  const bool launch = launchesMade_++ != opts_.faultSkipLaunch;
-  if (launch)
-    kernels::launchPush(plan, stream, ctas, flag, flagValueFor(op.seq), mine->pushCounter(op.seq), statusWord(),
-                        kernels::WaitBefore(), doneSlotFor(op.seq));
-  if (!others.empty()) {
-    CudaEvent ev(op.srcDevice);
-    ev.record(stream);
-    for (cudaStream_t s : others) ev.wait(s, op.srcDevice);
+  HostFeed* feed = nullptr;
+  int feedSlot = -1;
+  if (!fromHost.empty()) {
+    feed = ctx_->hostFeedFor(op.srcDevice);
+    if (!feed) return closeFromLoop(TPB_CREATE_ERROR(CudaError, "no device memory for the pieces of a host tensor"));
+    try {
+      feedSlot = feedFromHost(*feed, fromHost, stream, ctas, plan);
+    } catch (const std::exception& ex) {
+      return closeFromLoop(TPB_CREATE_ERROR(CudaError, ex.what()));
+    }
   }
-  noteLaunch(op.seq, launch);
-  TPB_VLOG(6) << "Channel " << id_ << " launched the push of batch #" << op.seq << " (" << plan.entries.size()
-              << " entries, " << plan.totalBytesOut << " bytes)";
   Launched l;
   l.seq = op.seq;
+  const bool launch = launchesMade_++ != opts_.faultSkipLaunch;
+  if (sameProcess_) {
+    // Nothing to publish: the receiver's stream waits for an event recorded behind the kernel.
+    if (launch) kernels::launchPush(plan, stream, ctas, nullptr, 0, nullptr, statusWord());
+    CudaEvent& done = eventFor(op.srcDevice, op.seq);
+    done.record(stream);
+    l.event = reinterpret_cast<uint64_t>(done.raw());
+    lastPushEvent_ = &done;
+    for (cudaStream_t s : others) done.wait(s, op.srcDevice);
+    launchedUpTo_ = op.seq + 1;
+  } else {
+    Error err;
+    Arena* mine = arenaFor(op.srcDevice, err);
+    if (!mine) return closeFromLoop(err);
+    uint32_t* flag = reinterpret_cast<uint32_t*>(arenaBase) + (op.seq % kFlagSlots);
+    if (launch)
+      kernels::launchPush(plan, stream, ctas, flag, flagValueFor(op.seq), mine->pushCounter(op.seq), statusWord(),
+                          kernels::WaitBefore(), doneSlotFor(op.seq));
+    if (!others.empty()) {
+      CudaEvent ev(op.srcDevice);
+      ev.record(stream);
+      for (cudaStream_t s : others) ev.wait(s, op.srcDevice);
+    }
+    noteLaunch(op.seq, launch);
+  }
+  if (feedSlot >= 0) {
+    feed->sent[feedSlot]->record(stream);
+    feed->everSent[feedSlot] = true;
+  }
+  TPB_VLOG(6) << "Channel " << id_ << " launched the push of batch #" << op.seq << " (" << plan.entries.size()
+              << " entries, " << plan.totalBytesOut << " bytes)";
   writePacket(l);
   finishSend(op, Error::kSuccess);
 }
@@ -1285,7 +1448,7 @@ void ChannelImpl::recvBatchFromLoop(std::vector<RecvItem> items) {
     uint64_t total = 0;
     for (auto& it : op.items) total += alignUp(it.length);
     const uint64_t threshold = std::min<uint64_t>(opts_.eagerThreshold, opts_.inboxBytes / 2);
-    op.expectEager = op.sourceDevice >= 0 && a != arenas_.end() && a->second.announcedSeq >= 0 &&
+    op.expectEager = !sameProcess_ && op.sourceDevice >= 0 && a != arenas_.end() && a->second.announcedSeq >= 0 &&
         static_cast<int64_t>(op.seq) > a->second.announcedSeq && total <= threshold;
     if (peerLeft_ && !op.notice) {
       // Nothing announces this batch any more.
@@ -1310,9 +1473,9 @@ void ChannelImpl::sendReady(RecvOp& op) {
   r.deviceIdx = op.device;
   try {
     Error err;
-    Arena* a = arenaFor(op.device, err);
-    if (!a) return closeFromLoop(err);
-    if (a->announcedSeq < 0) {
+    Arena* a = sameProcess_ ? nullptr : arenaFor(op.device, err);
+    if (!sameProcess_ && !a) return closeFromLoop(err);
+    if (a && a->announcedSeq < 0) {
       ArenaWire w;
       w.handle = a->handle;
       w.address = reinterpret_cast<uint64_t>(a->base);
@@ -1402,16 +1565,23 @@ void ChannelImpl::completeRecv(RecvOp& op) {
       if (s != stream && std::find(others.begin(), others.end(), s) == others.end()) others.push_back(s);
     }
     Error err;
-    Arena* a = arenaFor(op.device, err);
-    if (!a) return closeFromLoop(err);
-    uint32_t* flag = a->flag(op.seq);
+    Arena* a = sameProcess_ ? nullptr : arenaFor(op.device, err);
+    if (!sameProcess_ && !a) return closeFromLoop(err);
+    if (sameProcess_) {
+      if (n.eager || !n.event)
+        return closeFromLoop(TPB_CREATE_ERROR(LogicError, "a push within one process must come with its event"));
+      TPB_CUDA_CHECK(cudaStreamWaitEvent(stream, reinterpret_cast<cudaEvent_t>(n.event), 0));
+    }
+    uint32_t* flag = a ? a->flag(op.seq) : nullptr;
     const uint32_t value = flagValueFor(op.seq);
-    a->awaited[op.seq % kFlagSlots] = value;
-    a->anyWait = true;
+    if (a) {
+      a->awaited[op.seq % kFlagSlots] = value;
+      a->anyWait = true;
+    }
     const CudaLib& lib = CudaLib::get();
     const bool fuse = n.eager && opts_.fuseWaitIntoUnpack && op.staged.empty() && sourceIsOtherGpu(op);
     bool watchStatus = false;
-    if (!fuse) {
+    if (!fuse && !sameProcess_) {
       if (!opts_.waitWithKernel && lib.cuStreamWaitValue32) {
         trace::Scope w("p2p.recv.waitvalue", op.seq);
         int rc = lib.cuStreamWaitValue32(stream, reinterpret_cast<CUdeviceptr_t>(flag), value, CudaLib::kWaitGeq);
@@ -1733,9 +1903,17 @@ void ChannelImpl::closeFromLoop(const Error& e, bool connectionBroken) {
 
 void ChannelImpl::sendByeWhenIdle() {
   if (byeSent_ || finished_) return;
+  auto self = shared_from_this();
+  if (sameProcess_) {
+    // The newest event stands for every push before it: they ran on streams the user ordered.
+    if (!lastPushEvent_ || cudaEventQuery(lastPushEvent_->raw()) != cudaErrorNotReady) return sendBye();
+    cudaEvent_t raw = lastPushEvent_->raw();
+    ctx_->poller_.watch([raw]() { return cudaEventQuery(raw) != cudaErrorNotReady; },
+                        [self]() { self->ctx_->loop_.deferToLoop([self]() { self->sendBye(); }); });
+    return;
+  }
   advanceConfirmed();
   if (confirmed_ == launchedUpTo_) return sendBye();
-  auto self = shared_from_this();
   whenPushFinishes(confirmed_, [self]() { self->sendByeWhenIdle(); });
 }
 
@@ -1780,6 +1958,7 @@ Options applyEnvironment(Options o) {
   num("TPB_CUDA_P2P_FUSED_WAIT", o.fuseWaitIntoUnpack);
   num("TPB_CUDA_P2P_BULK", o.useBulkCopy);
   num("TPB_CUDA_P2P_CLOSE_TIMEOUT_MS", o.closeTimeoutMs);
+  num("TPB_CUDA_P2P_HOST_PIECE_BYTES", o.hostPieceBytes);
   unsigned long long ms = o.waitTimeoutNs / 1'000'000ull;
   num("TPB_CUDA_P2P_WAIT_TIMEOUT_MS", ms);
   o.waitTimeoutNs = ms * 1'000'000ull;

@@ -160,7 +160,7 @@ int cudaDeviceForPointer(const void* ptr) {
   return ordinal;
 }
 
-bool cudaIsLocalDeviceMemory(const void* ptr, int device) {
+bool cudaIsLocalMemory(const void* ptr, int device) {
   const CudaLib& lib = CudaLib::get();
   if (!lib.ok) return false;
   unsigned type = 0;
@@ -170,6 +170,14 @@ bool cudaIsLocalDeviceMemory(const void* ptr, int device) {
   if (type != 2 /* CU_MEMORYTYPE_DEVICE */) return false;
   if (lib.cuPointerGetAttribute(&ordinal, CudaLib::kAttrDeviceOrdinal, p) != 0) return false;
   return ordinal == device;
+}
+
+bool cudaIsPinnedHostMemory(const void* ptr) {
+  const CudaLib& lib = CudaLib::get();
+  if (!lib.ok || ptr == nullptr) return false;
+  unsigned type = 0;
+  if (lib.cuPointerGetAttribute(&type, CudaLib::kAttrMemoryType, reinterpret_cast<CUdeviceptr_t>(ptr)) != 0) return false;
+  return type == 1 /* CU_MEMORYTYPE_HOST */;
 }
 
 bool cudaAllocationInfo(const void* ptr, void** base, size_t* size, unsigned long long* bufferId) {

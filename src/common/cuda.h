@@ -149,10 +149,11 @@ int cudaDeviceCountNoThrow();
 std::string cudaDeviceUuid(int device);
 // Device index that owns a device pointer, or -1.
 int cudaDeviceForPointer(const void* ptr);
-// True when `ptr` is ordinary device memory of `device`: the only kind of source the bulk-copy
-// (TMA) path of the push kernel is given. Pinned host memory and another GPU's memory are read
-// with plain loads instead.
-bool cudaIsLocalDeviceMemory(const void* ptr, int device);
+// True when `ptr` is memory of `device` itself: the only source the bulk-copy (TMA) path of the
+// push kernel is given. Another GPU's memory and pinned host memory are read with plain loads.
+bool cudaIsLocalMemory(const void* ptr, int device);
+// True when `ptr` is page-locked host memory that CUDA knows about.
+bool cudaIsPinnedHostMemory(const void* ptr);
 // Base address, size and driver buffer id of the allocation containing ptr.
 bool cudaAllocationInfo(const void* ptr, void** base, size_t* size, unsigned long long* bufferId);
 // Enable peer access from `device` to `peer` once (idempotent). Returns false if impossible.

@@ -674,6 +674,32 @@ std::pair<Error, std::string> lookupAddrForHostname() {
   return {Error::kSuccess, found};
 }
 
+// The address NCCL would pick for its sockets, so that both libraries of one job end up on the
+// same network: the first interface that is up, not a loopback over IPv6 and (optionally) of the
+// wanted family, ranked by name — "ib*" first (IP over InfiniBand), then anything else, then
+// "docker*", then "lo*". Same ranking as tensorpipe/transport/uv/utility.cc:138-215.
+std::pair<Error, std::string> lookupAddrLikeNccl(int family) {
+  ifaddrs* list = nullptr;
+  if (::getifaddrs(&list) < 0) return {TPB_CREATE_ERROR(SystemError, "getifaddrs", errno), ""};
+  // rank 0: ib*, 1: unremarkable, 2: docker*, 3: lo*
+  std::string best[4];
+  for (ifaddrs* p = list; p; p = p->ifa_next) {
+    if (!p->ifa_addr || !p->ifa_name) continue;
+    const int fam = p->ifa_addr->sa_family;
+    if (fam != AF_INET && fam != AF_INET6) continue;
+    if (!(p->ifa_flags & IFF_UP) || !(p->ifa_flags & IFF_RUNNING)) continue;
+    if (fam == AF_INET6 && (p->ifa_flags & IFF_LOOPBACK)) continue;
+    if (family != AF_UNSPEC && fam != family) continue;
+    const std::string name = p->ifa_name;
+    const int rank = name.rfind("ib", 0) == 0 ? 0 : name.rfind("docker", 0) == 0 ? 2 : name.rfind("lo", 0) == 0 ? 3 : 1;
+    if (best[rank].empty()) best[rank] = formatAddr(p->ifa_addr, false);
+  }
+  ::freeifaddrs(list);
+  for (const std::string& addr : best)
+    if (!addr.empty()) return {Error::kSuccess, addr};
+  return {TPB_CREATE_ERROR(NoAddrFoundError), ""};
+}
+
 }  // namespace tcp
 }  // namespace transport
 }  // namespace tpb

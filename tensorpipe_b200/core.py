@@ -148,10 +148,11 @@ class Pipe:
         local = _device_str(t.device)
         if (t.device.type == "cpu" and target is not None and target.startswith("cuda") and t.is_contiguous()
                 and t.numel() > 0 and torch.cuda.is_available() and t.is_pinned()):
-            # Pinned host memory bound for a GPU: with unified addressing the device can read it in
-            # place, so the push kernel of the current GPU takes it straight from host memory into
-            # the receiving GPU (one pass over PCIe, no staging copy on this side). The message then
-            # says the tensor comes from that GPU.
+            # Pinned host memory bound for a GPU: handed to the device-to-device channel as a tensor
+            # of the current GPU. The channel brings a large one in through the copy engine piece
+            # by piece while its kernel forwards the piece before (the host->device copy overlaps
+            # the transfer); a small one its kernel reads in place. The message then says the
+            # tensor comes from that GPU.
             gpu = torch.device("cuda", torch.cuda.current_device())
             if self._supports_layouts(_device_str(gpu), target):
                 return self._add_raw(out, t, t.data_ptr(), gpu, target, metadata, streams, None)

@@ -297,6 +297,79 @@ static void manyInFlight(int serverDevice, int clientDevice) {
 TPB_GPU_TEST(CudaChannel, P2pManyBatchesInFlightOneDevice, 1) { manyInFlight(0, 0); }
 TPB_GPU_TEST(CudaChannel, P2pManyBatchesInFlightTwoDevices, 2) { manyInFlight(0, 1); }
 
+// A large tensor in pinned host memory, handed over as a tensor of the sending GPU, is brought in
+// by the copy engine piece by piece while the push kernel forwards the pieces; a device tensor in
+// the same batch travels with the last piece. Sizes that are not a multiple of the piece size,
+// twice in a row so that the slots are reused.
+static void hostFed(bool processes, int serverDevice, int clientDevice) {
+  constexpr size_t kHostBytes = (21u << 20) + 40;
+  constexpr size_t kDeviceBytes = (1u << 20) + 8;
+  channel::cuda_p2p::Options o;
+  o.hostPieceBytes = 4u << 20;  // six pieces per tensor: both slots are reused
+  runPair(
+      processes, p2p(o), p2p(o),
+      [=](channel::Channel& ch) {
+        for (int round = 0; round < 2; ++round) {
+          DeviceTensor big(serverDevice, kHostBytes), small(serverDevice, kDeviceBytes);
+          std::promise<Error> pr;
+          std::atomic<int> left{2}, failed{0};
+          std::vector<channel::RecvItem> v;
+          for (DeviceTensor* t : {&big, &small}) {
+            channel::RecvItem it;
+            it.buffer = CudaBuffer{t->data(), big.stream, serverDevice};
+            it.length = t->bytes;
+            it.sourceDevice = Device(kCudaDeviceType, clientDevice);
+            it.callback = [&](const Error& e) {
+              if (e) ++failed;
+              if (--left == 0) pr.set_value(e);
+            };
+            v.push_back(std::move(it));
+          }
+          ch.recvBatch(std::move(v));
+          auto f = pr.get_future();
+          expectOk(waitFor(f), "recvBatch");
+          EXPECT_EQ(failed.load(), 0);
+          CK(cudaStreamSynchronize(big.stream));
+          EXPECT_EQ(big.mismatches(8100 + round), uint64_t(0));
+          EXPECT_EQ(small.mismatches(8200 + round), uint64_t(0));
+        }
+      },
+      [=](channel::Channel& ch) {
+        CK(cudaSetDevice(clientDevice));
+        uint8_t* host = nullptr;
+        CK(cudaHostAlloc(reinterpret_cast<void**>(&host), kHostBytes, cudaHostAllocPortable));
+        DeviceTensor small(clientDevice, kDeviceBytes);
+        for (int round = 0; round < 2; ++round) {
+          kernels::launchFill(small.stream, host, kHostBytes, 8100 + round);
+          small.fill(8200 + round);
+          std::promise<Error> pr;
+          std::atomic<int> left{2}, failed{0};
+          std::vector<channel::SendItem> v;
+          for (int i = 0; i < 2; ++i) {
+            channel::SendItem it;
+            it.buffer = i == 0 ? CudaBuffer{host, small.stream, clientDevice} : small.buffer();
+            it.length = i == 0 ? kHostBytes : kDeviceBytes;
+            it.targetDevice = Device(kCudaDeviceType, serverDevice);
+            it.callback = [&](const Error& e) {
+              if (e) ++failed;
+              if (--left == 0) pr.set_value(e);
+            };
+            v.push_back(std::move(it));
+          }
+          ch.sendBatch(std::move(v));
+          auto f = pr.get_future();
+          expectOk(waitFor(f), "sendBatch");
+          EXPECT_EQ(failed.load(), 0);
+          // the next fill of the host buffer is ordered behind the copies by the stream
+        }
+        CK(cudaStreamSynchronize(small.stream));
+        CK(cudaFreeHost(host));
+      });
+}
+TPB_GPU_TEST(CudaChannel, P2pPinnedHostTensorSameProcess, 1) { hostFed(false, 0, 0); }
+TPB_GPU_TEST(CudaChannel, P2pPinnedHostTensorTwoProcesses, 1) { hostFed(true, 0, 0); }
+TPB_GPU_TEST(CudaChannel, P2pPinnedHostTensorAcrossDevices, 2) { hostFed(true, 0, 1); }
+
 // The sender announces a push that it never launches (host-side fault injection). The receiver's
 // bounded wait runs out: its stream drains instead of hanging, the kernel reports the time-out,
 // and the channel fails, so that whatever is received next says so instead of delivering data

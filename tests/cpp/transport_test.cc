@@ -7,6 +7,8 @@
 
 #include "transport/nop_io.h"
 #include "core/nop_types.h"
+#include <sys/socket.h>
+
 #include "test_util.h"
 
 using namespace tpb;
@@ -350,6 +352,20 @@ TPB_TEST(TransportUv, AddressHelpers) {
   EXPECT_EQ(addr, std::string("127.0.0.1"));
   auto [e2, addr2] = transport::tcp::lookupAddrForIface("no-such-iface0");
   EXPECT_TRUE(e2.isOfType<transport::NoAddrFoundError>());
+  // The NCCL-like choice: some address a listener can bind to; with only a loopback interface
+  // up it is the loopback address, and a family filter is honoured.
+  auto [e3, nccl] = transport::tcp::lookupAddrLikeNccl();
+  EXPECT_FALSE(bool(e3));
+  EXPECT_FALSE(nccl.empty());
+  {
+    auto probe = transport::uv::create();
+    auto l = probe->listen(nccl.find(':') != std::string::npos ? "[" + nccl + "]" : nccl);
+    EXPECT_FALSE(l->addr().empty());
+    probe->join();
+  }
+  auto [e4, v4] = transport::tcp::lookupAddrLikeNccl(AF_INET);
+  EXPECT_FALSE(bool(e4));
+  EXPECT_TRUE(v4.find(':') == std::string::npos && v4.find('.') != std::string::npos);
   // IPv6 loopback listen + connect.
   auto ctx = transport::uv::create();
   try {

@@ -50,16 +50,19 @@ using Clock = std::chrono::steady_clock;
 struct Args {
   int rank = 0, world = 1, device = 0, nextDevice = 0, basePort = 29700;
   size_t maxBytes = 1ull << 30;
+  std::string channels = "all";  // or "cuda_basic": only the staged CUDA channel (and basic)
 };
 
-std::shared_ptr<tp::Context> makeContext(const std::string& name) {
+std::shared_ptr<tp::Context> makeContext(const std::string& name, const std::string& channels) {
   auto ctx = std::make_shared<tp::Context>(tp::ContextOptions().name(name));
   ctx->registerTransport(0, "uv", tp::transport::uv::create());
   ctx->registerTransport(10, "shm", tp::transport::shm::create());
   ctx->registerChannel(0, "basic", tp::channel::basic::create());
   ctx->registerChannel(101, "cuda_basic", tp::channel::cuda_basic::create(tp::channel::basic::create()));
-  ctx->registerChannel(300, "cuda_ipc", tp::channel::cuda_ipc::create());
-  ctx->registerChannel(400, "cuda_xth", tp::channel::cuda_xth::create());
+  if (channels != "cuda_basic") {
+    ctx->registerChannel(300, "cuda_ipc", tp::channel::cuda_ipc::create());
+    ctx->registerChannel(400, "cuda_xth", tp::channel::cuda_xth::create());
+  }
   return ctx;
 }
 
@@ -83,8 +86,8 @@ struct Bench {
     CK(cudaMemset(src, 1, args.maxBytes));
     CK(cudaEventCreate(&evStart));
     CK(cudaEventCreate(&evEnd));
-    sendCtx = makeContext("send" + std::to_string(args.rank));
-    recvCtx = makeContext("recv" + std::to_string(args.rank));
+    sendCtx = makeContext("send" + std::to_string(args.rank), args.channels);
+    recvCtx = makeContext("recv" + std::to_string(args.rank), args.channels);
     const std::string myAddr = "uv://127.0.0.1:" + std::to_string(args.basePort + args.rank);
     listener = recvCtx->listen({myAddr, "shm://tpref-" + std::to_string(args.basePort + args.rank)});
     std::promise<std::shared_ptr<tp::Pipe>> accepted;
@@ -350,6 +353,7 @@ int main(int argc, char** argv) {
     else if (k == "--next-device") args.nextDevice = std::stoi(v);
     else if (k == "--base-port") args.basePort = std::stoi(v);
     else if (k == "--max-bytes") args.maxBytes = std::stoull(v);
+    else if (k == "--channels") args.channels = v;
   }
   Bench b;
   b.args = args;

@@ -69,10 +69,11 @@ def _compile(src):
 
 
 class Harness:
-    def __init__(self, rank, world, device, next_device, base_port, max_bytes):
+    def __init__(self, rank, world, device, next_device, base_port, max_bytes, channels="all"):
         self.proc = subprocess.Popen(
             [BIN, "--rank", str(rank), "--world", str(world), "--device", str(device), "--next-device",
-             str(next_device), "--base-port", str(base_port), "--max-bytes", str(max_bytes)],
+             str(next_device), "--base-port", str(base_port), "--max-bytes", str(max_bytes),
+             "--channels", channels],
             stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, bufsize=1)
 
     def readline(self, timeout):

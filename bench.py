@@ -409,9 +409,10 @@ def roofline(world, value_gbs):
 def run_e2e(args, tpb, torch, dist, rank, world, local_rank, barrier, max_over_ranks, gather):
     """The same ring through the public Python API, end to end: every step's input starts in pinned
     host memory and the step ends with a checksum of the received tensor read back to the host.
-    The pinned tensor itself is what is sent: the channel brings it into this rank's GPU with the
-    copy engine piece by piece while its push kernel forwards the piece before to the next rank's
-    GPU, so the host->device copy of the step overlaps the pipe transfer."""
+    The pinned tensor itself is what is sent: the channel brings it in through the copy engine,
+    straight into the receiving buffer when that is on this rank's GPU, else in 32 MiB pieces that
+    its push kernel forwards to the next rank's GPU while the next piece is being copied, so the
+    host->device copy of the step overlaps the pipe transfer."""
     dev = torch.device("cuda", local_rank)
     nbytes = args.bytes
     steps = max(5, min(args.steps, 20))
@@ -432,7 +433,7 @@ def run_e2e(args, tpb, torch, dist, rank, world, local_rank, barrier, max_over_r
 
     def step(i):
         incoming = in_pipe.recv(out=[bufs[i & 1]])
-        sent = out_pipe.send([host_in], target_devices=[target])  # H2D (nbytes) overlapped with the transfer
+        sent = out_pipe.send([host_in], target_devices=[target])  # the H2D copy (nbytes) overlaps the transfer
         msg = incoming.result(120)
         sent.result(120)
         checksum = msg.tensors[0][:4096].float().sum()

@@ -121,7 +121,7 @@ std::shared_ptr<Context> create(std::shared_ptr<Context> cpuContext);
 namespace cuda_p2p {
 // Every field can be overridden from the environment when the channel is created:
 // TPB_CUDA_P2P_EAGER_THRESHOLD, _INBOX_BYTES, _MAX_CTAS, _WAIT_KERNEL (0/1), _FUSED_WAIT (0/1),
-// _WAIT_TIMEOUT_MS, _BULK (0/1), _CLOSE_TIMEOUT_MS, _HOST_PIECE_BYTES.
+// _WAIT_TIMEOUT_MS, _BULK (0/1), _CLOSE_TIMEOUT_MS, _HOST_COPY_MIN_BYTES, _HOST_PIECE_BYTES.
 struct Options {
   size_t eagerThreshold = 64 * 1024;     // batches up to this many bytes go through the inbox: one
                                           // control hop less (lower latency), one small kernel more on
@@ -134,11 +134,13 @@ struct Options {
   uint64_t waitTimeoutNs = 2'000'000'000ull;  // bound of every device-side wait
   bool useBulkCopy = true;                // TMA bulk pipeline for aligned contiguous data
   uint64_t closeTimeoutMs = 3000;         // how long a closing end waits for the peer's goodbye
-  size_t hostPieceBytes = 32u << 20;     // a large tensor in pinned host memory comes in through the
-                                          // copy engine in pieces of this size (two slots of device
-                                          // memory per sending GPU, allocated on first use) while
-                                          // the kernel forwards the piece before; 0: the kernel
-                                          // reads host memory in place
+  size_t hostCopyMinBytes = 8u << 20;    // a tensor in pinned host memory of at least this size is
+                                          // brought in by the copy engine (straight into a receiver
+                                          // on the same GPU; in pieces forwarded by the kernel to
+                                          // another GPU); smaller ones the kernel reads in place;
+                                          // 0: always the kernel
+  size_t hostPieceBytes = 32u << 20;     // size of those pieces (two slots of device memory per
+                                          // sending GPU, allocated on first use)
   // Host-side fault injection for tests: the N-th push of a channel (counting from 0) is announced
   // to the receiver but not launched, so that the receiver's bounded wait runs out. -1: never.
   int faultSkipLaunch = -1;

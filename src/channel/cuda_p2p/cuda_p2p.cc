@@ -377,13 +377,17 @@ class ExportCache {
   std::map<uintptr_t, Entry> byBase_;
 };
 
-// Large tensors in pinned host memory travel in pieces: the copy engine brings a piece into a slot
-// of device memory while the push kernel sends the piece before it on to the peer, so the PCIe
-// copy runs at the copy engine's rate and the NVLink hop hides behind it. One per context and
-// sending device, shared by its channels (all of them work from the context's one loop thread;
-// the slots are handed from use to use by events).
-constexpr uint64_t kHostFeedMinBytes = 4u << 20;   // smaller host tensors are read by the kernel in place
-constexpr uint64_t kHostFeedTailBytes = 2u << 20;  // the piece that travels with the publishing launch
+// A large tensor in pinned host memory never goes through the kernel's own loads (SM-issued reads
+// over PCIe reach 40 GB/s, the copy engine 55). Bound for this GPU's memory, the copy engine puts
+// it straight into the receiver's buffer. Bound for another GPU, it travels in pieces: the copy
+// engine brings a piece into a slot of device memory while the push kernel sends the piece before
+// it over NVLink, so the NVLink hop hides behind the PCIe copy. (One copy-engine copy from host
+// memory into the peer GPU also runs at 55 GB/s alone, but measured well below the pieces when
+// both GPUs of a pair do it at once.) In both cases a short tail travels with the launch that
+// publishes the batch. One feed per context and sending device, shared by its channels (all of
+// them work from the context's one loop thread; the slots pass from use to use by events).
+constexpr uint64_t kHostTailBytes = 64u << 10;      // read by the kernel from host memory in place
+constexpr uint64_t kHostLastPieceBytes = 2u << 20;  // nothing hides the push of the last piece: it is short
 struct HostFeed {
   static constexpr size_t kSlots = 2;
   int device = -1;
@@ -617,16 +621,12 @@ class ChannelImpl final : public Channel, public std::enable_shared_from_this<Ch
   std::map<int, std::vector<std::unique_ptr<CudaEvent>>> eventRings_;
   CudaEvent* lastPushEvent_ = nullptr;
   CudaEvent& eventFor(int device, uint64_t seq);
-  struct HostFedItem {
+  struct HostItem {
     const uint8_t* src;
     uint8_t* dst;
-    uint64_t bytes;
-    bool remote;
+    uint64_t bytes;  // without the tail
   };
-  // Queues all pieces of `items` but the last on `stream`; the last one is added to `plan`, so
-  // that the launch which publishes the batch carries it. Returns the slot that launch frees.
-  int feedFromHost(HostFeed& feed, const std::vector<HostFedItem>& items, cudaStream_t stream, int ctas,
-                   kernels::PushPlan& plan);
+  void feedFromHost(HostFeed& feed, const HostItem& item, cudaStream_t stream, int ctas);
   // Closing.
   bool byeSent_ = false, byeReceived_ = false, finished_ = false;
   bool peerLeft_ = false;  // the peer said goodbye while this end was open: only early arrivals can still be received
@@ -1210,45 +1210,34 @@ HostFeed* ContextImpl::hostFeedFor(int device) {
   return feed.get();
 }
 
-int ChannelImpl::feedFromHost(HostFeed& feed, const std::vector<HostFedItem>& items, cudaStream_t stream, int ctas,
-                              kernels::PushPlan& plan) {
+// Queues the pieces of one host tensor bound for another GPU: copies on the feed's stream, pushes
+// on the user's. May throw (CUDA errors).
+void ChannelImpl::feedFromHost(HostFeed& feed, const HostItem& item, cudaStream_t stream, int ctas) {
   // The host memory is read after whatever the user queued on the stream before the send.
   feed.begin->record(stream);
   feed.begin->wait(feed.copyStream, feed.device);
-  int lastSlot = -1;
-  for (size_t i = 0; i < items.size(); ++i) {
-    const HostFedItem& it = items[i];
-    const bool lastItem = i + 1 == items.size();
-    for (uint64_t off = 0; off < it.bytes;) {
-      uint64_t len = std::min<uint64_t>(feed.pieceBytes, it.bytes - off);
-      // Nothing hides the push of the very last piece: keep it small.
-      if (lastItem && off + len >= it.bytes && len > 2 * kHostFeedTailBytes) len = (len - kHostFeedTailBytes) & ~uint64_t(255);
-      const size_t slot = feed.next++ % HostFeed::kSlots;
-      uint8_t* piece = feed.slots + slot * feed.pieceBytes;
-      if (feed.everSent[slot]) feed.sent[slot]->wait(feed.copyStream, feed.device);
-      TPB_CUDA_CHECK(cudaMemcpyAsync(piece, it.src + off, len, cudaMemcpyHostToDevice, feed.copyStream));
-      feed.copied[slot]->record(feed.copyStream);
-      feed.copied[slot]->wait(stream, feed.device);
-      kernels::CopyItem c;
-      c.src = piece;
-      c.dst = it.dst + off;
-      c.srcBytes = len;
-      c.remote = it.remote;
-      off += len;
-      if (lastItem && off >= it.bytes) {
-        kernels::appendToPlan(plan, c, opts_.useBulkCopy);
-        lastSlot = static_cast<int>(slot);
-      } else {
-        kernels::PushPlan piecePlan;
-        kernels::chooseBulkTile(piecePlan, len, ctas);
-        kernels::appendToPlan(piecePlan, c, opts_.useBulkCopy);
-        kernels::launchPush(piecePlan, stream, ctas, nullptr, 0, nullptr, statusWord());
-        feed.sent[slot]->record(stream);
-        feed.everSent[slot] = true;
-      }
-    }
+  for (uint64_t off = 0; off < item.bytes;) {
+    uint64_t len = std::min<uint64_t>(feed.pieceBytes, item.bytes - off);
+    if (off + len >= item.bytes && len > 2 * kHostLastPieceBytes) len = (len - kHostLastPieceBytes) & ~uint64_t(255);
+    const size_t slot = feed.next++ % HostFeed::kSlots;
+    uint8_t* piece = feed.slots + slot * feed.pieceBytes;
+    if (feed.everSent[slot]) feed.sent[slot]->wait(feed.copyStream, feed.device);
+    TPB_CUDA_CHECK(cudaMemcpyAsync(piece, item.src + off, len, cudaMemcpyHostToDevice, feed.copyStream));
+    feed.copied[slot]->record(feed.copyStream);
+    feed.copied[slot]->wait(stream, feed.device);
+    kernels::CopyItem c;
+    c.src = piece;
+    c.dst = item.dst + off;
+    c.srcBytes = len;
+    c.remote = true;
+    kernels::PushPlan piecePlan;
+    kernels::chooseBulkTile(piecePlan, len, ctas);
+    kernels::appendToPlan(piecePlan, c, opts_.useBulkCopy);
+    kernels::launchPush(piecePlan, stream, ctas, nullptr, 0, nullptr, statusWord());
+    feed.sent[slot]->record(stream);
+    feed.everSent[slot] = true;
+    off += len;
   }
-  return lastSlot;
 }
 
 void ChannelImpl::launchRendezvous(SendOp& op) {
@@ -1293,16 +1282,15 @@ void ChannelImpl::launchRendezvous(SendOp& op) {
     const uint64_t bulkMin = kernels::getPushTuning().bulkMinBytes;
     for (auto& it : op.items) {
       if (it.view || it.length < bulkMin) continue;
-      // Of a tensor fed from host memory only the last piece is part of this plan.
-      const bool fed = opts_.hostPieceBytes != 0 && it.length >= kHostFeedMinBytes &&
-          cudaIsPinnedHostMemory(it.buffer.unwrap<CudaBuffer>().ptr);
-      bulkBytes += fed ? kHostFeedTailBytes : it.length;
+      // Host memory never takes the bulk path (and of a large host tensor only the tail is here).
+      if (cudaIsPinnedHostMemory(it.buffer.unwrap<CudaBuffer>().ptr)) continue;
+      bulkBytes += it.length;
     }
     kernels::chooseBulkTile(plan, bulkBytes, ctas);
   }
   const uint64_t generation = MappingCache::get().generation();
   const uint64_t now = nowNs();
-  std::vector<HostFedItem> fromHost;
+  std::vector<HostItem> hostLocal, hostRemote;
   for (size_t i = 0; i < op.items.size(); ++i) {
     SendItem& it = op.items[i];
     const TargetWire& t = ready.targets[i];
@@ -1345,9 +1333,16 @@ void ChannelImpl::launchRendezvous(SendOp& op) {
       return closeFromLoop(TPB_CREATE_ERROR(LogicError, "unsupported dtype conversion requested by the receiver"));
     if (kernels::convertedBytes(it.length, c.srcDtype, c.dstDtype) != t.bytes)
       return closeFromLoop(TPB_CREATE_ERROR(LogicError, "receiver's buffer size does not match the tensor"));
-    if (opts_.hostPieceBytes != 0 && !c.strided && c.dstDtype == c.srcDtype && it.length >= kHostFeedMinBytes &&
-        cudaIsPinnedHostMemory(c.src)) {
-      fromHost.push_back({static_cast<const uint8_t*>(c.src), static_cast<uint8_t*>(c.dst), it.length, c.remote});
+    if (opts_.hostCopyMinBytes != 0 && !c.strided && c.dstDtype == c.srcDtype && it.length >= opts_.hostCopyMinBytes &&
+        it.length > 2 * kHostTailBytes && cudaIsPinnedHostMemory(c.src)) {
+      const uint64_t head = (it.length - kHostTailBytes) & ~uint64_t(255);
+      const bool otherGpu = ready.deviceIdx >= 0 && static_cast<size_t>(ready.deviceIdx) < peerUuids_.size() &&
+          peerUuids_[ready.deviceIdx] != myUuids_[op.srcDevice];
+      (otherGpu ? hostRemote : hostLocal).push_back({static_cast<const uint8_t*>(c.src), static_cast<uint8_t*>(c.dst), head});
+      c.src = static_cast<const uint8_t*>(c.src) + head;
+      c.dst = static_cast<uint8_t*>(c.dst) + head;
+      c.srcBytes = it.length - head;
+      kernels::appendToPlan(plan, c, false);
       continue;
     }
     kernels::appendToPlan(plan, c, bulkFor(c.src, it.length, op.srcDevice));
@@ -1365,16 +1360,19 @@ void ChannelImpl::launchRendezvous(SendOp& op) {
     ev.record(s);
     ev.wait(stream, op.srcDevice);
   }
-  HostFeed* feed = nullptr;
-  int feedSlot = -1;
-  if (!fromHost.empty()) {
-    feed = ctx_->hostFeedFor(op.srcDevice);
-    if (!feed) return closeFromLoop(TPB_CREATE_ERROR(CudaError, "no device memory for the pieces of a host tensor"));
-    try {
-      feedSlot = feedFromHost(*feed, fromHost, stream, ctas, plan);
-    } catch (const std::exception& ex) {
-      return closeFromLoop(TPB_CREATE_ERROR(CudaError, ex.what()));
+  try {
+    for (const HostItem& h : hostLocal) {
+      trace::Scope copyTraced("p2p.send.hostcopy", op.seq);
+      TPB_CUDA_CHECK(cudaMemcpyAsync(h.dst, h.src, h.bytes, cudaMemcpyDefault, stream));
     }
+    if (!hostRemote.empty()) {
+      trace::Scope feedTraced("p2p.send.hostfeed", op.seq);
+      HostFeed* feed = ctx_->hostFeedFor(op.srcDevice);
+      if (!feed) return closeFromLoop(TPB_CREATE_ERROR(CudaError, "no device memory for the pieces of a host tensor"));
+      for (const HostItem& h : hostRemote) feedFromHost(*feed, h, stream, ctas);
+    }
+  } catch (const std::exception& ex) {
+    return closeFromLoop(TPB_CREATE_ERROR(CudaError, ex.what()));
   }
   Launched l;
   l.seq = op.seq;
@@ -1402,10 +1400,6 @@ void ChannelImpl::launchRendezvous(SendOp& op) {
       for (cudaStream_t s : others) ev.wait(s, op.srcDevice);
     }
     noteLaunch(op.seq, launch);
-  }
-  if (feedSlot >= 0) {
-    feed->sent[feedSlot]->record(stream);
-    feed->everSent[feedSlot] = true;
   }
   TPB_VLOG(6) << "Channel " << id_ << " launched the push of batch #" << op.seq << " (" << plan.entries.size()
               << " entries, " << plan.totalBytesOut << " bytes)";
@@ -1958,6 +1952,7 @@ Options applyEnvironment(Options o) {
   num("TPB_CUDA_P2P_FUSED_WAIT", o.fuseWaitIntoUnpack);
   num("TPB_CUDA_P2P_BULK", o.useBulkCopy);
   num("TPB_CUDA_P2P_CLOSE_TIMEOUT_MS", o.closeTimeoutMs);
+  num("TPB_CUDA_P2P_HOST_COPY_MIN_BYTES", o.hostCopyMinBytes);
   num("TPB_CUDA_P2P_HOST_PIECE_BYTES", o.hostPieceBytes);
   unsigned long long ms = o.waitTimeoutNs / 1'000'000ull;
   num("TPB_CUDA_P2P_WAIT_TIMEOUT_MS", ms);

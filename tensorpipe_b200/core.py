@@ -149,10 +149,11 @@ class Pipe:
         if (t.device.type == "cpu" and target is not None and target.startswith("cuda") and t.is_contiguous()
                 and t.numel() > 0 and torch.cuda.is_available() and t.is_pinned()):
             # Pinned host memory bound for a GPU: handed to the device-to-device channel as a tensor
-            # of the current GPU. The channel brings a large one in through the copy engine piece
-            # by piece while its kernel forwards the piece before (the host->device copy overlaps
-            # the transfer); a small one its kernel reads in place. The message then says the
-            # tensor comes from that GPU.
+            # of the current GPU. A large one comes in through the copy engine: straight into a
+            # receiver on the same GPU, in pieces that the channel's kernel forwards to another
+            # GPU while the next piece is being copied (the host->device copy overlaps the
+            # transfer). A small one the kernel reads in place. The message then says the tensor
+            # comes from that GPU.
             gpu = torch.device("cuda", torch.cuda.current_device())
             if self._supports_layouts(_device_str(gpu), target):
                 return self._add_raw(out, t, t.data_ptr(), gpu, target, metadata, streams, None)

@@ -297,15 +297,16 @@ static void manyInFlight(int serverDevice, int clientDevice) {
 TPB_GPU_TEST(CudaChannel, P2pManyBatchesInFlightOneDevice, 1) { manyInFlight(0, 0); }
 TPB_GPU_TEST(CudaChannel, P2pManyBatchesInFlightTwoDevices, 2) { manyInFlight(0, 1); }
 
-// A large tensor in pinned host memory, handed over as a tensor of the sending GPU, is brought in
-// by the copy engine piece by piece while the push kernel forwards the pieces; a device tensor in
-// the same batch travels with the last piece. Sizes that are not a multiple of the piece size,
-// twice in a row so that the slots are reused.
+// A large tensor in pinned host memory, handed over as a tensor of the sending GPU, comes in
+// through the copy engine (straight into a receiver on the same GPU, in pieces forwarded by the
+// kernel to another GPU) except for a short tail, which travels with the kernel launch that also
+// carries the device tensor of the same batch. A ragged size, twice in a row, with pieces small
+// enough that both slots are reused.
 static void hostFed(bool processes, int serverDevice, int clientDevice) {
   constexpr size_t kHostBytes = (21u << 20) + 40;
   constexpr size_t kDeviceBytes = (1u << 20) + 8;
   channel::cuda_p2p::Options o;
-  o.hostPieceBytes = 4u << 20;  // six pieces per tensor: both slots are reused
+  o.hostPieceBytes = 4u << 20;
   runPair(
       processes, p2p(o), p2p(o),
       [=](channel::Channel& ch) {

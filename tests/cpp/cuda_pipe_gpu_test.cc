@@ -391,8 +391,19 @@ TPB_GPU_TEST(CudaPipe, SameProcessTwoDevices, 2) {
 
 namespace {
 // Strided view + cast, checked element by element against a host gather and host rounding.
-void layoutsCase(bool crossProc, int recvDevice, int sendDevice) {
+// With `staged` the contexts have no device-to-device channel: the same message goes through
+// pinned host memory (cuda_basic), which packs views on the sender and converts on the receiver.
+void layoutsCase(bool crossProc, int recvDevice, int sendDevice, bool staged = false) {
   constexpr int64_t kRows = 300, kCols = 129;
+  auto makeContext = [staged](const std::string& name) {
+    if (!staged) return ::makeContext(name);
+    auto ctx = std::make_shared<Context>(ContextOptions().name(name));
+    ctx->registerTransport(0, "uv", transport::uv::create());
+    ctx->registerTransport(1, "shm", transport::shm::create());
+    ctx->registerChannel(0, "basic", channel::basic::create());
+    ctx->registerChannel(5, "cuda_basic", channel::cuda_basic::create(channel::basic::create()));
+    return ctx;
+  };
   auto server = [=](std::function<void(std::string)> tell, std::function<std::string()> hear) {
     auto ctx = makeContext("server");
     auto listener = ctx->listen({"uv://127.0.0.1", "shm://"});
@@ -500,3 +511,6 @@ void layoutsCase(bool crossProc, int recvDevice, int sendDevice) {
 TPB_GPU_TEST(CudaPipe, StridedViewAndCastSameProcess, 1) { layoutsCase(false, 0, 0); }
 TPB_GPU_TEST(CudaPipe, StridedViewAndCastTwoProcesses, 1) { layoutsCase(true, 0, 0); }
 TPB_GPU_TEST(CudaPipe, StridedViewAndCastTwoDevices, 2) { layoutsCase(true, 0, 1); }
+TPB_GPU_TEST(CudaBasic, StridedViewAndCastSameProcess, 1) { layoutsCase(false, 0, 0, true); }
+TPB_GPU_TEST(CudaBasic, StridedViewAndCastTwoProcesses, 1) { layoutsCase(true, 0, 0, true); }
+TPB_GPU_TEST(CudaBasic, StridedViewAndCastTwoDevices, 2) { layoutsCase(true, 0, 1, true); }

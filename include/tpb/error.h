@@ -124,6 +124,16 @@ class CudaError final : public BaseError {
   std::string m_;
 };
 
+// A failed RDMA work request or verbs call, with the provider's text (ibv transport, cuda_gdr).
+class IbvError final : public BaseError {
+ public:
+  explicit IbvError(std::string m) : m_(std::move(m)) {}
+  std::string what() const override { return "ibv: " + m_; }
+
+ private:
+  std::string m_;
+};
+
 class DlError final : public BaseError {
  public:
   explicit DlError(std::string m) : m_(std::move(m)) {}

@@ -55,6 +55,10 @@ class Pipe final {
   // Name the peer gave to its context (or the name passed to connect()).
   const std::string& getRemoteName();
 
+  // Name of the transport the two ends settled on for descriptors and payloads ("uv", "shm",
+  // ...), once the pipe is established; before that, the one the handshake travels over.
+  std::string transportName();
+
   // True when the channel selected for (localDevice -> remoteDevice) tensors understands
   // strided views and receiver-requested casts. Valid once the pipe is established.
   bool channelSupportsLayouts(const Device& local, const Device& remote);

@@ -249,6 +249,7 @@ PYBIND11_MODULE(_C, m) {
            },
            py::arg("write_ms") = 0, py::arg("read_ms") = 0, py::arg("descriptor_ms") = 0,
            "Deadlines for operations issued from now on (0 = wait forever); a missed one fails the pipe with 'timeout'.")
+      .def("transport_name", &Pipe::transportName, py::call_guard<py::gil_scoped_release>())
       .def("channel_supports_layouts",
            [](Pipe& self, const std::string& local, const std::string& remote) {
              Device l = parseDevice(local), r = parseDevice(remote);

@@ -184,6 +184,7 @@ class PipeCore final : public std::enable_shared_from_this<PipeCore> {
   void write(Message message, Pipe::write_callback_fn fn);
   void setTimeouts(PipeTimeouts timeouts);
   bool routeSupportsLayouts(const Device& local, const Device& remote);
+  std::string transportName();
   const std::string& remoteName() const { return remoteName_; }
   void close();
 

@@ -307,6 +307,12 @@ bool PipeCore::routeSupportsLayouts(const Device& local, const Device& remote) {
   return yes;
 }
 
+std::string PipeCore::transportName() {
+  std::string name;
+  context_->runSync([&]() { name = wireTransport_; });
+  return name;
+}
+
 void PipeCore::close() {
   auto self = shared_from_this();
   context_->defer([self]() { self->fail(TPB_CREATE_ERROR(PipeClosedError)); });
@@ -344,6 +350,7 @@ void Pipe::read(Allocation allocation, read_callback_fn fn) { impl_->read(std::m
 void Pipe::write(Message message, write_callback_fn fn) { impl_->write(std::move(message), std::move(fn)); }
 void Pipe::setTimeouts(PipeTimeouts timeouts) { impl_->setTimeouts(timeouts); }
 const std::string& Pipe::getRemoteName() { return impl_->remoteName(); }
+std::string Pipe::transportName() { return impl_->transportName(); }
 bool Pipe::channelSupportsLayouts(const Device& local, const Device& remote) {
   return impl_->routeSupportsLayouts(local, remote);
 }

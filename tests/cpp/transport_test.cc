@@ -5,6 +5,7 @@
 
 #include <random>
 
+#include "transport/ibv/ibv.h"
 #include "transport/nop_io.h"
 #include "core/nop_types.h"
 #include <sys/socket.h>
@@ -24,6 +25,13 @@ struct Backend {
 const Backend kBackends[] = {
     {"uv", [] { return transport::uv::create(); }, "127.0.0.1"},
     {"shm", [] { return transport::shm::create(); }, ""},
+    // The RDMA transport over a software fabric (one per process: its contexts must share it).
+    {"ibv",
+     [] {
+       static auto fabric = verbs::loopbackProvider();
+       return transport::ibv::createWithProvider(fabric);
+     },
+     "127.0.0.1"},
 };
 
 std::shared_ptr<transport::Connection> acceptSync(transport::Listener& l) {

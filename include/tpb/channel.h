@@ -162,8 +162,9 @@ namespace cuda_ipc {
 inline std::shared_ptr<Context> create() { return cuda_p2p::create(); }
 }
 namespace cuda_gdr {
-// GPUDirect RDMA across hosts needs InfiniBand NICs, which a single NVSwitch box does not have:
-// the factory probes and reports a non-viable context.
+// GPU memory to GPU memory across hosts through the NICs (GPUDirect RDMA writes into the
+// receiver's registered buffer). Needs libibverbs, a NIC and the GPU peer-memory kernel module;
+// reports a non-viable context where any of them is missing.
 std::shared_ptr<Context> create();
 }
 

@@ -86,8 +86,8 @@ namespace shm {
 std::shared_ptr<Context> create();
 }
 namespace ibv {
-// InfiniBand is not present on a single NVSwitch box: the factory probes for libibverbs and a
-// device and returns a non-viable context when there is none.
+// Framed connections over RDMA writes into registered rings (libibverbs loaded at run time, TCP
+// for the bootstrap). A machine without the library or without a NIC gets a non-viable context.
 std::shared_ptr<Context> create();
 }
 

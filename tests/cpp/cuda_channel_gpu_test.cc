@@ -11,6 +11,7 @@
 
 #include <tpb/tpb.h>
 
+#include "channel/cuda_gdr/cuda_gdr.h"
 #include "channel_wiring.h"
 #include "common/cuda.h"
 #include "kernels/push.h"
@@ -73,6 +74,24 @@ void runPair(bool processes, PeerSetup serverSetup, PeerSetup clientSetup, Body 
 
 PeerSetup p2p(channel::cuda_p2p::Options o = {}) {
   return {[o] { return channel::cuda_p2p::create(o); }, {}, false};
+}
+// cuda_gdr over the software fabric: two "NICs" whose wire is cudaMemcpy between device pointers
+// and which take at most 1 MiB per work request, so that tensors travel in several pieces. The
+// fabric lives in this process: its two ends must too.
+PeerSetup gdr() {
+  static auto fabric = verbs::loopbackProvider(
+      2,
+      [](void* dst, const void* src, size_t n) {
+        // A NIC reports a write done when the bytes are placed: cudaMemcpy between device pointers
+        // may return earlier, so wait for the copy.
+        cudaMemcpyAsync(dst, src, n, cudaMemcpyDefault, cudaStreamPerThread);
+        cudaStreamSynchronize(cudaStreamPerThread);
+      },
+      1u << 20);
+  channel::cuda_gdr::Options o;
+  o.requirePeerMemoryModule = false;
+  o.maxPostedBytes = 2u << 20;
+  return {[o] { return channel::cuda_gdr::createWithProvider(fabric, o); }, {}, false};
 }
 PeerSetup cudaBasic() {
   return {[] { return channel::cuda_basic::create(channel::basic::create()); }, {}, false};
@@ -216,6 +235,8 @@ TPB_GPU_TEST(CudaChannel, P2pTwoProcesses, 1) { basicCases(true, p2p(), 0, 0); }
 TPB_GPU_TEST(CudaChannel, P2pAcrossDevices, 2) { basicCases(true, p2p(), 0, 1); }
 TPB_GPU_TEST(CudaChannel, P2pReverseAcrossDevices, 2) { basicCases(true, p2p(), 1, 0); }
 TPB_GPU_TEST(CudaChannel, P2pSameProcessAcrossDevices, 2) { basicCases(false, p2p(), 0, 1); }
+TPB_GPU_TEST(CudaChannel, GdrOverASoftwareFabric, 1) { basicCases(false, gdr(), 0, 0); }
+TPB_GPU_TEST(CudaChannel, GdrOverASoftwareFabricAcrossDevices, 2) { basicCases(false, gdr(), 0, 1); }
 TPB_GPU_TEST(CudaChannel, BasicSameProcess, 1) { basicCases(false, cudaBasic(), 0, 0); }
 TPB_GPU_TEST(CudaChannel, BasicTwoProcesses, 1) { basicCases(true, cudaBasic(), 0, 0); }
 TPB_GPU_TEST(CudaChannel, BasicAcrossDevices, 2) { basicCases(true, cudaBasic(), 0, 1); }

@@ -7,6 +7,7 @@
 
 #include <tpb/tpb.h>
 
+#include "channel/cuda_gdr/cuda_gdr.h"
 #include "common/role_ring.h"
 #include "common/verbs.h"
 #include "test_util.h"
@@ -293,6 +294,43 @@ TPB_TEST(VerbsSystem, AMachineWithoutInfiniBandHasNoDevicesAndTheTransportSaysSo
     EXPECT_FALSE(l->url("uv").empty());
     pctx->join();
   }
+  ctx->join();
+}
+
+TPB_TEST(CudaGdr, GpusAreMatchedToTheNicBehindTheSameSwitch) {
+  using channel::cuda_gdr::matchGpusToNics;
+  // Two PCIe switches with a NIC and two GPUs each, as sysfs shows them.
+  const std::vector<std::string> nics = {
+      "/sys/devices/pci0000:15/0000:15:01.0/0000:16:00.0/0000:17:04.0/0000:1a:00.0",
+      "/sys/devices/pci0000:97/0000:97:01.0/0000:98:00.0/0000:99:04.0/0000:9c:00.0",
+  };
+  const std::vector<std::string> gpus = {
+      "/sys/devices/pci0000:15/0000:15:01.0/0000:16:00.0/0000:17:00.0/0000:18:00.0",
+      "/sys/devices/pci0000:15/0000:15:01.0/0000:16:00.0/0000:17:08.0/0000:1b:00.0",
+      "/sys/devices/pci0000:97/0000:97:01.0/0000:98:00.0/0000:99:00.0/0000:9a:00.0",
+      "/sys/devices/pci0000:97/0000:97:01.0/0000:98:00.0/0000:99:08.0/0000:9d:00.0",
+      "/sys/devices/pci0000:c0/0000:c0:01.0/0000:c1:00.0",  // shares no root with a NIC
+      "",                                                     // unknown
+  };
+  auto m = matchGpusToNics(gpus, nics);
+  EXPECT_EQ(m.size(), gpus.size());
+  EXPECT_EQ(m[0], 0);
+  EXPECT_EQ(m[1], 0);
+  EXPECT_EQ(m[2], 1);
+  EXPECT_EQ(m[3], 1);
+  // the two without a relative are spread over the NICs
+  EXPECT_EQ(m[4], 0);
+  EXPECT_EQ(m[5], 1);
+  // a deeper match wins over a shallower one
+  const std::vector<std::string> nested = {"/sys/devices/pci0000:15/0000:15:01.0/0000:16:00.0",
+                                           "/sys/devices/pci0000:15/0000:15:01.0/0000:16:00.0/0000:17:00.0/0000:19:00.0"};
+  const auto deeper = matchGpusToNics({gpus[0]}, nested);
+  EXPECT_EQ(deeper[0], 1);
+  const auto none = matchGpusToNics(gpus, {});
+  EXPECT_TRUE(none.size() == gpus.size() && none[0] == -1);
+  // Without InfiniBand (or without a GPU) the channel says it is not viable instead of failing.
+  auto ctx = channel::cuda_gdr::create();
+  if (verbs::systemProvider()->deviceNames().empty()) EXPECT_FALSE(ctx->isViable());
   ctx->join();
 }
 

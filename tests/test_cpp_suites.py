@@ -7,7 +7,8 @@ import subprocess
 import pytest
 
 CPU_SUITES = ["Nop.", "Transport.", "TransportShm.", "TransportUv.", "Pipe.", "Context.", "Listener.",
-              "Channel.", "Common.", "Faults.", "Plan."]
+              "Channel.", "Common.", "Faults.", "Plan.", "RoleRing.", "VerbsLoopback.", "VerbsSystem.",
+              "TransportIbv.", "CudaGdr."]
 GPU_SUITES = ["Kernel.", "CudaPipe.", "CudaBasic.", "CudaChannel."]
 
 

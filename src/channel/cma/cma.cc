@@ -13,6 +13,7 @@
 #include <cstring>
 #include <sstream>
 
+#include "channel/cma/environment.h"
 #include "channel/copy_channel.h"
 #include "channel/nonviable.h"
 #include "common/system.h"
@@ -22,17 +23,6 @@ namespace channel {
 namespace cma {
 
 namespace {
-
-class BadReadError final : public BaseError {
- public:
-  BadReadError(uint64_t expected, uint64_t actual) : expected_(expected), actual_(actual) {}
-  std::string what() const override {
-    return "Expected to read " + std::to_string(expected_) + ", got " + std::to_string(actual_);
-  }
-
- private:
-  uint64_t expected_, actual_;
-};
 
 Error copyFromProcess(uint64_t pid, const void* remote, void* local, size_t len) {
   // One call moves at most 0x7ffff000 bytes; loop for larger tensors and short reads.
@@ -52,49 +42,67 @@ Error copyFromProcess(uint64_t pid, const void* remote, void* local, size_t len)
 
 }  // namespace
 
-std::shared_ptr<Context> create() {
-  auto boot = getBootID();
-  auto pidns = getLinuxNamespaceId(LinuxNamespace::kPid);
-  auto userns = getLinuxNamespaceId(LinuxNamespace::kUser);
-  if (!boot || !pidns || !userns) return std::make_shared<NonViableContext>();
+Environment probeEnvironment(bool declareTracer) {
+  Environment env;
+  env.bootId = getBootID();
+  env.pidNamespace = getLinuxNamespaceId(LinuxNamespace::kPid);
+  env.userNamespace = getLinuxNamespaceId(LinuxNamespace::kUser);
+  env.effectiveUid = ::geteuid();
+  env.effectiveGid = ::getegid();
+  env.dumpable = ::prctl(PR_GET_DUMPABLE, 0, 0, 0, 0) == 1;
+  env.securityModules = getLinuxSecurityModules();
+  env.permittedCapabilities = getPermittedCapabilitiesID();
+  env.yamaScope = getYamaPtraceScope();
+  if (declareTracer && env.yamaScope && *env.yamaScope == 1)
+    env.canDeclareAnyTracer = ::prctl(PR_SET_PTRACER, PR_SET_PTRACER_ANY, 0, 0, 0) == 0;
+  // Self-probe: the call may be filtered (seccomp) or missing.
+  uint64_t probeSrc = 0x0123456789abcdefull, probeDst = 0;
+  Error e = copyFromProcess(static_cast<uint64_t>(::getpid()), &probeSrc, &probeDst, sizeof(probeSrc));
+  env.selfProbeWorks = !e && probeDst == probeSrc;
+  return env;
+}
 
+std::optional<std::string> describe(const Environment& env, std::string* why) {
+  auto no = [&](const char* reason) -> std::optional<std::string> {
+    if (why) *why = reason;
+    return std::nullopt;
+  };
+  if (!env.bootId || !env.pidNamespace || !env.userNamespace) return no("boot id or namespaces cannot be read");
   // A process that made itself non-dumpable cannot be read by its peers.
-  if (::prctl(PR_GET_DUMPABLE, 0, 0, 0, 0) != 1) return std::make_shared<NonViableContext>();
-
+  if (!env.dumpable) return no("the process is not dumpable");
   // The prefix differs from the reference's ("cma:", tensorpipe/channel/cma/context_impl.cc:236-243)
   // on purpose: this channel speaks its own protocol on one connection, the reference's speaks
   // another on two, so the two must never select each other.
   std::ostringstream d;
-  d << "tpbcma1:" << *boot << "_" << *pidns << "_" << *userns << "_" << ::geteuid() << "_" << ::getegid();
-
-  if (auto lsms = getLinuxSecurityModules()) {
-    for (const auto& lsm : *lsms) {
-      if (lsm == "capability") {
-        // Reading needs the target's permitted capabilities to be a subset of ours: require equality.
-        auto caps = getPermittedCapabilitiesID();
-        if (!caps) return std::make_shared<NonViableContext>();
-        d << "_" << *caps;
-      } else if (lsm == "yama") {
-        auto scope = getYamaPtraceScope();
-        if (!scope) return std::make_shared<NonViableContext>();
-        if (*scope == 1) {
-          // "restricted": only declared tracers may attach. Declare everyone.
-          if (::prctl(PR_SET_PTRACER, PR_SET_PTRACER_ANY, 0, 0, 0) != 0) return std::make_shared<NonViableContext>();
-        } else if (*scope >= 2) {
-          return std::make_shared<NonViableContext>();
-        }
-      }
-    }
+  d << "tpbcma1:" << *env.bootId << "_" << *env.pidNamespace << "_" << *env.userNamespace << "_" << env.effectiveUid
+    << "_" << env.effectiveGid;
+  // Reading needs the target's permitted capabilities to be a subset of the reader's, and either
+  // end may be the reader: require equality. The kernel makes this check whether or not the list
+  // of security modules can be read (inside a container it often cannot), so the capabilities are
+  // always part of the descriptor.
+  if (!env.permittedCapabilities) return no("the permitted capabilities cannot be read");
+  d << "_" << *env.permittedCapabilities;
+  bool yamaListed = false;
+  if (env.securityModules)
+    for (const auto& lsm : *env.securityModules) yamaListed = yamaListed || lsm == "yama";
+  if (yamaListed && !env.yamaScope) return no("the YAMA ptrace scope cannot be read");
+  if (env.yamaScope) {
+    // 1 = "restricted": only declared tracers may attach, so everyone is declared one.
+    if (*env.yamaScope == 1 && !env.canDeclareAnyTracer) return no("YAMA restricts ptrace and no tracer can be declared");
+    if (*env.yamaScope >= 2) return no("YAMA allows ptrace to administrators only, or to nobody");
   }
+  if (!env.selfProbeWorks) return no("process_vm_readv is missing or filtered");
+  return d.str();
+}
 
-  // Self-probe: the call may be filtered (seccomp) or missing.
-  uint64_t probeSrc = 0x0123456789abcdefull, probeDst = 0;
-  Error e = copyFromProcess(static_cast<uint64_t>(::getpid()), &probeSrc, &probeDst, sizeof(probeSrc));
-  if (e || probeDst != probeSrc) {
-    TPB_VLOG(4) << "cma not viable: " << (e ? e.what() : BadReadError(probeSrc, probeDst).what());
+std::shared_ptr<Context> create() {
+  std::string why;
+  auto descriptor = describe(probeEnvironment(true), &why);
+  if (!descriptor) {
+    TPB_VLOG(4) << "cma is not viable: " << why;
     return std::make_shared<NonViableContext>();
   }
-  return std::make_shared<copy::ContextImpl>(d.str(), &copyFromProcess, "TP_CMA_loop");
+  return std::make_shared<copy::ContextImpl>(*descriptor, &copyFromProcess, "TP_CMA_loop");
 }
 
 }  // namespace cma

@@ -8,7 +8,7 @@ import pytest
 
 CPU_SUITES = ["Nop.", "Transport.", "TransportShm.", "TransportUv.", "Pipe.", "Context.", "Listener.",
               "Channel.", "Common.", "Faults.", "Plan.", "RoleRing.", "VerbsLoopback.", "VerbsSystem.",
-              "TransportIbv.", "CudaGdr."]
+              "TransportIbv.", "CudaGdr.", "CmaMatrix."]
 GPU_SUITES = ["Kernel.", "CudaPipe.", "CudaBasic.", "CudaChannel."]
 
 

@@ -121,6 +121,44 @@ def test_cuda_tensors_views_and_casts(built):
 
 
 @pytest.mark.gpu
+def test_recv_is_ordered_on_the_callers_stream_and_device(built):
+    """recv() allocates on the device and orders on the stream that are current on the CALLER's
+    thread, not on the library thread that sees the descriptor: work queued on that side stream
+    right after the future resolves must see the data, with no synchronisation in between."""
+    last = torch.cuda.device_count() - 1  # the second GPU where there is one
+    a, b, listener, out_pipe, in_pipe = connected_pair()
+    side = torch.cuda.Stream(device=last)
+    n = 8 << 20
+    for round_ in range(3):
+        x = torch.full((n,), float(round_ + 1), device="cuda:0")
+        torch.cuda.synchronize(0)
+        with torch.cuda.device(last), torch.cuda.stream(side):
+            incoming = in_pipe.recv()
+            sent = out_pipe.send([x], target_devices=[f"cuda:{last}"])
+            msg = incoming.result(30)
+            sent.result(30)
+            t = msg.tensors[0]
+            assert t.device.index == last
+            total = t.sum()  # queued on `side`, behind the wait the library put there
+        side.synchronize()
+        assert float(total) == float(n * (round_ + 1))
+    # explicit output tensors on the side stream work the same way
+    out = torch.zeros(n, device=f"cuda:{last}")
+    x = torch.full((n,), 7.0, device="cuda:0")
+    torch.cuda.synchronize()
+    with torch.cuda.device(last), torch.cuda.stream(side):
+        incoming = in_pipe.recv(out=[out])
+        sent = out_pipe.send([x], target_devices=[f"cuda:{last}"])
+        incoming.result(30)
+        sent.result(30)
+        total = out.sum()
+    side.synchronize()
+    assert float(total) == float(n * 7)
+    a.join()
+    b.join()
+
+
+@pytest.mark.gpu
 def test_smoke_entry_point(built):
     import __graft_entry__
     __graft_entry__.smoke()

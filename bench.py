@@ -256,17 +256,29 @@ def run_native(args):
         dist.all_gather_object(out, obj)
         return out
 
-    if args.e2e_only:
-        e2e = run_e2e(args, tpb, torch, dist, rank, world, local_rank, barrier, max_over_ranks, gather)
-        if rank == 0:
-            print(json.dumps({"impl": "native", "n_gpus": world, "e2e": e2e}), flush=True)
-        if world > 1:
-            dist.destroy_process_group()
-        return
-    max_bytes = max(args.bytes, 0 if args.no_sweep else args.max_sweep_bytes)
+    max_bytes = max(args.bytes, 0 if (args.no_sweep or args.e2e_only) else args.max_sweep_bytes)
     rb = _C.RingBench(device=local_rank, use_bulk_copy=not args.no_bulk, max_bytes=max_bytes)
     urls = gather(f"{rb.listen_url()}|{local_rank}")
     rb.connect(urls[(rank + 1) % world])
+
+    def end_to_end():
+        """The C++ API is the library's primary one (as it is the reference's, whose arm makes the
+        same three calls per step); the same step through the Python layer is reported beside it."""
+        e2e = run_e2e_native_api(args, rb, world, barrier, max_over_ranks)
+        try:
+            e2e["python_api"] = run_e2e(args, tpb, torch, dist, rank, world, local_rank, barrier, max_over_ranks, gather)
+        except Exception as exc:  # noqa: BLE001
+            e2e["python_api"] = {"error": str(exc)}
+        return e2e
+
+    if args.e2e_only:
+        e2e = end_to_end()
+        if rank == 0:
+            print(json.dumps({"impl": "native", "n_gpus": world, "e2e": e2e}), flush=True)
+        del rb
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # Correctness first: byte-exact on-device verification at a few sizes.
     for size in (4096, 1 << 20, (8 << 20) + 16):
@@ -294,7 +306,7 @@ def run_native(args):
     # End to end right after the headline, on contexts of its own.
     e2e = None
     if not args.no_e2e:
-        e2e = run_e2e(args, tpb, torch, dist, rank, world, local_rank, barrier, max_over_ranks, gather)
+        e2e = end_to_end()
 
     # The remaining phases explain the headline; a failure in one of them is reported in its place
     # and ends the auxiliary phases on every rank, but never costs the headline line.
@@ -404,6 +416,26 @@ def roofline(world, value_gbs):
     else:
         out["of_fallback_hbm_6650"] = round(2 * per_gpu / 6650.0, 3)
     return out
+
+
+def run_e2e_native_api(args, rb, world, barrier, max_over_ranks):
+    """The ring end to end through tpb::Pipe::write / readDescriptor / read (RingBench::runEndToEnd,
+    src/tools/ring_bench.cc): every step hands the pinned host tensor itself to Pipe::write (the
+    channel brings it in through the copy engine while the pipe's handshake is still under way and
+    forwards it to the next rank's GPU piece by piece), and ends when four bytes of the received
+    tensor are back in pinned host memory and both streams are idle. Wall clock, max over ranks."""
+    steps = max(5, min(args.steps, 20))
+    rb.run_end_to_end(args.bytes, 3, False)
+    barrier()
+    res = rb.run_end_to_end(args.bytes, steps, True)
+    barrier()
+    if res.mismatches:
+        raise RuntimeError(f"end-to-end: {res.mismatches} bytes of the received tensor differ from the source")
+    dt = max_over_ranks(res.host_ms) * 1e-3
+    return {"value": round(world * args.bytes * steps / dt / 1e9, 3), "unit": "GB/s", "steps": steps,
+            "h2d_bytes_per_step": args.bytes, "d2h_bytes_per_step": 4,
+            "api": "tpb::Pipe::write / readDescriptor / read (C++ API); the pinned host tensor is written as it is",
+            "verified": "every byte of the last received tensor against the source pattern, on the device"}
 
 
 def run_e2e(args, tpb, torch, dist, rank, world, local_rank, barrier, max_over_ranks, gather):

@@ -382,6 +382,8 @@ PYBIND11_MODULE(_C, m) {
            py::arg("verify") = false, py::call_guard<py::gil_scoped_release>())
       .def("run_latency", &tools::RingBench::runLatency, py::arg("bytes"), py::arg("laps"), py::arg("rank") = 0,
            py::arg("world") = 1, py::call_guard<py::gil_scoped_release>())
+      .def("run_end_to_end", &tools::RingBench::runEndToEnd, py::arg("bytes"), py::arg("steps"), py::arg("verify") = false,
+           py::call_guard<py::gil_scoped_release>())
       .def("connect_mesh", &tools::RingBench::connectMesh, py::call_guard<py::gil_scoped_release>())
       .def(
           "run_mixed_mesh",

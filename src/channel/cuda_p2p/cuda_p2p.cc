@@ -398,12 +398,19 @@ struct HostFeed {
   std::unique_ptr<CudaEvent> copied[kSlots], sent[kSlots];
   bool everSent[kSlots] = {};
   uint64_t next = 0;
+  // A third slot for the head start: the first piece of a host tensor is copied in as soon as the
+  // batch is handed over, while the descriptor and the receiver's answer are still travelling, so
+  // the PCIe copy does not wait for the handshake. One batch owns it at a time (host-side flag:
+  // taken at the head start, given back when the push that reads the slot has been launched).
+  uint8_t* early = nullptr;
+  std::unique_ptr<CudaEvent> earlyCopied, earlySent;
+  bool earlyTaken = false, earlyEverSent = false;
   ~HostFeed() {
     if (device < 0) return;
     try {
       CudaDeviceGuard g(device);
       if (copyStream) cudaStreamSynchronize(copyStream), cudaStreamDestroy(copyStream);
-      if (slots) cudaFree(slots);
+      if (slots) cudaFree(slots);  // the early slot is part of the same allocation
     } catch (...) {
     }
   }
@@ -476,6 +483,10 @@ struct SendOp {
   std::vector<SendItem> items;
   bool launched = false;
   std::optional<RecvReady> ready;
+  // The head of one large host tensor of this batch that the copy engine started on when the
+  // batch was handed over, before the receiver answered (see HostFeed::early).
+  int earlyItem = -1;
+  uint64_t earlyBytes = 0;
 };
 
 // A receive buffer that CUDA IPC cannot export (memory from a stream-ordered pool, a virtual-memory
@@ -627,6 +638,8 @@ class ChannelImpl final : public Channel, public std::enable_shared_from_this<Ch
     uint64_t bytes;  // without the tail
   };
   void feedFromHost(HostFeed& feed, const HostItem& item, cudaStream_t stream, int ctas);
+  void startEarly(SendOp& op);
+  void releaseEarly(SendOp& op);
   // Closing.
   bool byeSent_ = false, byeReceived_ = false, finished_ = false;
   bool peerLeft_ = false;  // the peer said goodbye while this end was open: only early arrivals can still be received
@@ -991,6 +1004,7 @@ void ChannelImpl::sendBatchFromLoop(std::vector<SendItem> items) {
     }
     TPB_VLOG(6) << "Channel " << id_ << " send batch #" << op.seq << " (" << op.items.size() << " tensors)"
                 << (op.ready ? ", receiver already announced its buffers" : "");
+    if (!op.ready) startEarly(op);
     sendOps_.push_back(std::move(op));
   }
   pumpSends();
@@ -1195,12 +1209,15 @@ HostFeed* ContextImpl::hostFeedFor(int device) {
   f->pieceBytes = (std::max<size_t>(opts_.hostPieceBytes, 1u << 20) + 255) / 256 * 256;
   CudaDeviceGuard g(device);
   if (cudaStreamCreateWithFlags(&f->copyStream, cudaStreamNonBlocking) != cudaSuccess ||
-      cudaMalloc(reinterpret_cast<void**>(&f->slots), HostFeed::kSlots * f->pieceBytes) != cudaSuccess) {
+      cudaMalloc(reinterpret_cast<void**>(&f->slots), (HostFeed::kSlots + 1) * f->pieceBytes) != cudaSuccess) {
     cudaGetLastError();
     if (f->copyStream) cudaStreamDestroy(f->copyStream);
     return nullptr;
   }
   f->device = device;
+  f->early = f->slots + HostFeed::kSlots * f->pieceBytes;
+  f->earlyCopied = std::make_unique<CudaEvent>(device);
+  f->earlySent = std::make_unique<CudaEvent>(device);
   f->begin = std::make_unique<CudaEvent>(device);
   for (size_t i = 0; i < HostFeed::kSlots; ++i) {
     f->copied[i] = std::make_unique<CudaEvent>(device);
@@ -1208,6 +1225,46 @@ HostFeed* ContextImpl::hostFeedFor(int device) {
   }
   feed = std::move(f);
   return feed.get();
+}
+
+// Head start for a batch whose receiver has not answered yet: the first piece of its first large
+// pinned host tensor goes into the feed's early slot now.
+void ChannelImpl::startEarly(SendOp& op) {
+  if (opts_.hostCopyMinBytes == 0 || op.srcDevice < 0) return;
+  for (size_t i = 0; i < op.items.size(); ++i) {
+    SendItem& it = op.items[i];
+    const void* src = it.buffer.unwrap<CudaBuffer>().ptr;
+    if (it.view || it.length < opts_.hostCopyMinBytes || it.length <= 2 * kHostTailBytes || !cudaIsPinnedHostMemory(src)) continue;
+    try {
+      CudaDeviceGuard g(op.srcDevice);
+      HostFeed* feed = ctx_->hostFeedFor(op.srcDevice);
+      if (!feed || feed->earlyTaken) return;
+      const uint64_t head = (it.length - kHostTailBytes) & ~uint64_t(255);
+      const uint64_t n = std::min<uint64_t>(feed->pieceBytes, head);
+      cudaStream_t stream = static_cast<cudaStream_t>(it.buffer.unwrap<CudaBuffer>().stream);
+      trace::Scope traced("p2p.send.hostearly", op.seq);
+      feed->begin->record(stream);
+      feed->begin->wait(feed->copyStream, feed->device);
+      if (feed->earlyEverSent) feed->earlySent->wait(feed->copyStream, feed->device);
+      TPB_CUDA_CHECK(cudaMemcpyAsync(feed->early, src, n, cudaMemcpyHostToDevice, feed->copyStream));
+      feed->earlyCopied->record(feed->copyStream);
+      feed->earlyTaken = true;
+      op.earlyItem = static_cast<int>(i);
+      op.earlyBytes = n;
+    } catch (const std::exception& ex) {
+      TPB_VLOG(4) << "Channel " << id_ << " gives the head start of batch #" << op.seq << " a miss: " << ex.what();
+    }
+    return;
+  }
+}
+
+// The early slot goes back to the feed: either the push that reads it has been launched (and
+// earlySent recorded behind it) or the batch will not use it after all.
+void ChannelImpl::releaseEarly(SendOp& op) {
+  if (op.earlyItem < 0) return;
+  op.earlyItem = -1;
+  auto it = ctx_->hostFeeds_.find(op.srcDevice);
+  if (it != ctx_->hostFeeds_.end() && it->second) it->second->earlyTaken = false;
 }
 
 // Queues the pieces of one host tensor bound for another GPU: copies on the feed's stream, pushes
@@ -1291,6 +1348,8 @@ void ChannelImpl::launchRendezvous(SendOp& op) {
   const uint64_t generation = MappingCache::get().generation();
   const uint64_t now = nowNs();
   std::vector<HostItem> hostLocal, hostRemote;
+  std::optional<HostItem> early;
+  bool earlyRemote = false;
   for (size_t i = 0; i < op.items.size(); ++i) {
     SendItem& it = op.items[i];
     const TargetWire& t = ready.targets[i];
@@ -1338,7 +1397,16 @@ void ChannelImpl::launchRendezvous(SendOp& op) {
       const uint64_t head = (it.length - kHostTailBytes) & ~uint64_t(255);
       const bool otherGpu = ready.deviceIdx >= 0 && static_cast<size_t>(ready.deviceIdx) < peerUuids_.size() &&
           peerUuids_[ready.deviceIdx] != myUuids_[op.srcDevice];
-      (otherGpu ? hostRemote : hostLocal).push_back({static_cast<const uint8_t*>(c.src), static_cast<uint8_t*>(c.dst), head});
+      // What the head start already brought into the early slot is pushed from there.
+      uint64_t skip = 0;
+      if (op.earlyItem == static_cast<int>(i) && op.earlyBytes <= head) {
+        skip = op.earlyBytes;
+        early = HostItem{nullptr, static_cast<uint8_t*>(c.dst), skip};
+        earlyRemote = c.remote;
+      }
+      if (head > skip)
+        (otherGpu ? hostRemote : hostLocal)
+            .push_back({static_cast<const uint8_t*>(c.src) + skip, static_cast<uint8_t*>(c.dst) + skip, head - skip});
       c.src = static_cast<const uint8_t*>(c.src) + head;
       c.dst = static_cast<uint8_t*>(c.dst) + head;
       c.srcBytes = it.length - head;
@@ -1365,6 +1433,22 @@ void ChannelImpl::launchRendezvous(SendOp& op) {
       trace::Scope copyTraced("p2p.send.hostcopy", op.seq);
       TPB_CUDA_CHECK(cudaMemcpyAsync(h.dst, h.src, h.bytes, cudaMemcpyDefault, stream));
     }
+    if (early) {
+      HostFeed* feed = ctx_->hostFeedFor(op.srcDevice);
+      feed->earlyCopied->wait(stream, feed->device);
+      kernels::CopyItem c;
+      c.src = feed->early;
+      c.dst = early->dst;
+      c.srcBytes = early->bytes;
+      c.remote = earlyRemote;
+      kernels::PushPlan piecePlan;
+      kernels::chooseBulkTile(piecePlan, early->bytes, ctas);
+      kernels::appendToPlan(piecePlan, c, opts_.useBulkCopy);
+      kernels::launchPush(piecePlan, stream, ctas, nullptr, 0, nullptr, statusWord());
+      feed->earlySent->record(stream);
+      feed->earlyEverSent = true;
+    }
+    releaseEarly(op);  // used or not: the slot is free for the next batch from here on
     if (!hostRemote.empty()) {
       trace::Scope feedTraced("p2p.send.hostfeed", op.seq);
       HostFeed* feed = ctx_->hostFeedFor(op.srcDevice);
@@ -1864,8 +1948,10 @@ void ChannelImpl::closeFromLoop(const Error& e, bool connectionBroken) {
   auto recvs = std::move(recvOps_);
   sendOps_.clear();
   recvOps_.clear();
-  for (auto& op : sends)
+  for (auto& op : sends) {
+    releaseEarly(op);
     for (auto& it : op.items) it.callback(error_);
+  }
   for (auto& op : recvs) {
     if (op.items.empty()) continue;
     // Buffers the peer has been told about and whose push has not been announced: a kernel of

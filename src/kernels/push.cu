@@ -52,6 +52,9 @@ std::atomic<uint64_t> gLaunches{0};
 std::mutex gTuningMutex;
 PushTuning initialTuning() {
   PushTuning t;
+  if (const char* e = std::getenv("TPB_PUSH_BAND")) {
+    if (e[0] >= '0' && e[0] <= '2' && e[1] == 0) t.bandRows = static_cast<uint32_t>(e[0] - '0');
+  }
   if (const char* e = std::getenv("TPB_PUSH_NARROW")) {
     if (e[0] >= '0' && e[0] <= '2' && e[1] == 0) t.narrowRows = static_cast<uint32_t>(e[0] - '0');
   }
@@ -608,6 +611,111 @@ __device__ __forceinline__ void stridedNarrowTiles(const PushEntry& e, uint32_t 
   }
 }
 
+// Transposed matrix (rowStride == 1) whose packed rows are at most 8 KiB, for destinations that
+// want long contiguous writes (another GPU's memory over NVLink, where a 64-byte or misaligned
+// 128-byte row segment costs a whole packet): a tile is a band of whole rows, as many as fit in
+// 8 KiB. The band's elements are gathered down the source columns (consecutive rows of one column
+// are adjacent in the source: coalesced, the more so the more rows a band has), converted, and laid
+// out in shared memory exactly as the destination wants them, at the destination's own alignment
+// modulo 16; the band then leaves as ONE contiguous run: bytes up to the first 16-byte boundary,
+// 16-byte vectors, bytes after the last one. No alignment or divisibility is asked of anything.
+template <typename S, typename D, bool kConvert>
+__device__ __forceinline__ void stridedBandTile(const StridedArgs& a, uint32_t band, uint32_t bandRowsCount, int lane,
+                                                uint8_t* tileMem) {
+  const int64_t rows = a.rows, colStride = a.colStride;
+  const uint32_t cols = static_cast<uint32_t>(a.cols);
+  const S* src = static_cast<const S*>(a.src);
+  const int64_t r0 = static_cast<int64_t>(band) * bandRowsCount;
+  const uint32_t nr = static_cast<uint32_t>(rows - r0 < bandRowsCount ? rows - r0 : bandRowsCount);
+  uint8_t* out = static_cast<uint8_t*>(a.dst) + static_cast<uint64_t>(r0) * cols * sizeof(D);
+  const uint32_t skew = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(out) & 15);  // a multiple of sizeof(D)
+  D* stage = reinterpret_cast<D*>(tileMem + skew);
+  const uint32_t n = nr * cols;  // elements of this band
+  // Gather: element q of the (c-major, r-minor) enumeration is (c, r) = (q / nr, q % nr); lanes take
+  // q = lane, lane + 32, ... and keep (c, r) up to date without dividing in the loop.
+  {
+    constexpr int kBatch = 8;
+    uint32_t c = lane / nr, r = lane - c * nr;
+    const uint32_t stepC = 32 / nr, stepR = 32 - stepC * nr;
+    for (uint32_t q = lane; q < n; q += 32 * kBatch) {
+      S v[kBatch];
+      uint32_t cs[kBatch], rs[kBatch];
+#pragma unroll
+      for (int k = 0; k < kBatch; ++k) {
+        cs[k] = c;
+        rs[k] = r;
+        if (q + 32 * k < n && TPB_DBG_SRC(a, src + static_cast<int64_t>(c) * colStride + r0 + r, sizeof(S)))
+          v[k] = src[static_cast<int64_t>(c) * colStride + r0 + r];
+        c += stepC;
+        r += stepR;
+        if (r >= nr) {
+          r -= nr;
+          ++c;
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < kBatch; ++k) {
+        if (q + 32 * k < n) {
+          D o;
+          if constexpr (kConvert) o = fromFloat<D>(toFloat<S>(v[k]));
+          else o = v[k];
+          stage[rs[k] * cols + cs[k]] = o;
+        }
+      }
+    }
+  }
+  __syncwarp();
+  {
+    const uint32_t bytes = n * static_cast<uint32_t>(sizeof(D));
+    const uint8_t* from = tileMem + skew;
+    // head: up to the first 16-byte boundary of the destination (and of the staging area: same skew)
+    const uint32_t head = skew == 0 ? 0 : (16 - skew < bytes ? 16 - skew : bytes);
+    if (static_cast<uint32_t>(lane) < head && TPB_DBG_DST(a, out + lane, 1)) out[lane] = from[lane];
+    const uint32_t vectors = (bytes - head) / 16;
+    const uint4* vfrom = reinterpret_cast<const uint4*>(from + head);
+    uint4* vout = reinterpret_cast<uint4*>(out + head);
+    for (uint32_t i = lane; i < vectors; i += 32)
+      if (TPB_DBG_DST(a, vout + i, 16)) vout[i] = vfrom[i];
+    const uint32_t done = head + vectors * 16;
+    if (done + lane < bytes && TPB_DBG_DST(a, out + done + lane, 1)) out[done + lane] = from[done + lane];
+  }
+  __syncwarp();  // the staging area is reused by this warp's next band
+}
+
+template <typename S, typename D, bool kConvert>
+__device__ __noinline__ void stridedBandTilesTyped(const PushEntry& e, uint32_t first, uint32_t step, int lane,
+                                                   uint8_t* tileMem) {
+  const StridedArgs a = loadStridedArgs(e);
+  const uint32_t rowsPerBand = bandRows(static_cast<uint64_t>(e.cols), sizeof(D));
+#pragma unroll 1
+  for (uint32_t t = first; t < a.numTiles; t += step) stridedBandTile<S, D, kConvert>(a, t, rowsPerBand, lane, tileMem);
+}
+
+__device__ __forceinline__ void stridedBandTiles(const PushEntry& e, uint32_t first, uint32_t step, int lane,
+                                                 uint8_t* tileMem) {
+  if (e.srcDtype == e.dstDtype || e.dstDtype == static_cast<uint8_t>(DType::kBytes)) {
+    switch (e.srcElemSize) {
+      case 1: stridedBandTilesTyped<uint8_t, uint8_t, false>(e, first, step, lane, tileMem); break;
+      case 2: stridedBandTilesTyped<uint16_t, uint16_t, false>(e, first, step, lane, tileMem); break;
+      case 4: stridedBandTilesTyped<uint32_t, uint32_t, false>(e, first, step, lane, tileMem); break;
+      default: stridedBandTilesTyped<uint64_t, uint64_t, false>(e, first, step, lane, tileMem); break;
+    }
+    return;
+  }
+  const uint32_t key = (static_cast<uint32_t>(e.srcDtype) << 8) | e.dstDtype;
+  constexpr uint32_t F32 = static_cast<uint32_t>(DType::kF32), BF = static_cast<uint32_t>(DType::kBF16),
+                     F16 = static_cast<uint32_t>(DType::kF16);
+  switch (key) {
+    case (F32 << 8) | BF: stridedBandTilesTyped<float, __nv_bfloat16, true>(e, first, step, lane, tileMem); break;
+    case (F32 << 8) | F16: stridedBandTilesTyped<float, __half, true>(e, first, step, lane, tileMem); break;
+    case (BF << 8) | F32: stridedBandTilesTyped<__nv_bfloat16, float, true>(e, first, step, lane, tileMem); break;
+    case (F16 << 8) | F32: stridedBandTilesTyped<__half, float, true>(e, first, step, lane, tileMem); break;
+    case (BF << 8) | F16: stridedBandTilesTyped<__nv_bfloat16, __half, true>(e, first, step, lane, tileMem); break;
+    case (F16 << 8) | BF: stridedBandTilesTyped<__half, __nv_bfloat16, true>(e, first, step, lane, tileMem); break;
+    default: break;
+  }
+}
+
 // Transposed matrix of 2-byte elements (rowStride == 1), with the source, the destination, both
 // extents and the column stride all even: a warp moves a 64x64 tile, reading 32-bit words down the
 // source columns (128 B per instruction instead of 64) and writing 32-bit words along the packed
@@ -711,6 +819,7 @@ __device__ __forceinline__ void runPlainWarp(const PushParams<N>& p, uint32_t fi
       // One call handles every tile of this entry that falls to this warp.
       if (e->kind == kStridedWide16) stridedWide16Tiles(*e, local, totalWarps, lane, tileMem);
       else if (e->kind == kStridedNarrow) stridedNarrowTiles(*e, local, totalWarps, lane, tileMem);
+      else if (e->kind == kStridedBand) stridedBandTiles(*e, local, totalWarps, lane, tileMem);
       else stridedTiles(*e, local, totalWarps, lane, tileMem);
       t += (e->numTiles - local + totalWarps - 1) / totalWarps * totalWarps;
     }
@@ -773,6 +882,15 @@ __device__ __forceinline__ void publish(const PushParams<N>& p, bool failedHere)
 }
 
 // ---- the kernels --------------------------------------------------------------------------------
+// Programmatic dependent launch: a push kernel lets the kernel queued behind it on the stream start
+// right away (its own blocks are on the SMs within microseconds, so "when every block has got
+// going" is the moment), and itself waits for the kernel before it only where it first touches
+// memory that kernel may have written. Two pushes queued back to back thus overlap the launch
+// latency and the prologue of the second with the tail of the first; a kernel that is not launched
+// with the attribute (anything of the user's) is serialised as always.
+__device__ __forceinline__ void letDependentsLaunch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void waitForEarlierKernels() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 template <int N>
 __global__ void __launch_bounds__(kThreads, 1) tpb_push_pack(const __grid_constant__ PushParams<N> p) {
   extern __shared__ uint8_t smemRaw[];
@@ -788,11 +906,13 @@ __global__ void __launch_bounds__(kThreads, 1) tpb_push_pack(const __grid_consta
   const bool haveBulk = p.bulkTiles > blockIdx.x;
   bool failed = false;
 
+  letDependentsLaunch();
   if (tid == 0 && haveBulk) {
     for (int s = 0; s < S; ++s) mbarInit(&full[s], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  waitForEarlierKernels();  // from here on memory is read and written
   if (!waitForProducer(p)) {
     publish(p, true);
     return;
@@ -877,6 +997,8 @@ __global__ void __launch_bounds__(kLightThreads, 2) tpb_push_pack_light(const __
   extern __shared__ __align__(16) uint8_t lightTiles[];  // kWarps * p.warpTileBytes, none for plain copies
   constexpr uint32_t kWarps = kLightThreads / 32;
   const uint32_t warp = threadIdx.x / 32;
+  letDependentsLaunch();
+  waitForEarlierKernels();
   if (!waitForProducer(p)) {
     publish(p, true);
     return;
@@ -951,10 +1073,46 @@ void check(cudaError_t e, const char* what) {
   if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
 }
 
+// Launches with the programmatic-stream-serialization attribute (see letDependentsLaunch) where
+// that pays: small launches that publish or await a flag, i.e. the eager pushes and unpacks
+// between processes, which follow each other on a stream with no other work in between (measured
+// across two GPUs: 9.1-10.9 us per message instead of 10.8-12.9 from 4 to 64 KiB; from 128 KiB
+// to 4 MiB the attribute cost 2 us per message, beyond that it made no difference).
+// TPB_PUSH_PDL=0 turns it off.
+constexpr uint64_t kDependentLaunchMaxBytes = 64 * 1024;
+bool programmaticLaunches() {
+  static const bool on = [] {
+    const char* e = std::getenv("TPB_PUSH_PDL");
+    return !(e && e[0] == '0' && e[1] == 0);
+  }();
+  return on;
+}
+
+template <typename Kernel, typename Params>
+void launchMaybeDependent(Kernel kernel, uint32_t grid, uint32_t threads, size_t smem, cudaStream_t stream, const Params& p,
+                          bool dependent) {
+  if (!dependent || !programmaticLaunches()) {
+    kernel<<<grid, threads, smem, stream>>>(p);
+    return;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
 template <int N>
 void launchOne(const PushEntry* entries, uint32_t n, uint32_t bulkTiles, uint32_t plainTiles, uint32_t bulkTileBytes,
                uint32_t bulkStages, cudaStream_t stream, int maxCtas, uint32_t* flag, uint32_t flagValue,
-               uint32_t* counter, uint32_t* status, const WaitBefore& wait, const DoneSlot& done) {
+               uint32_t* counter, uint32_t* status, const WaitBefore& wait, const DoneSlot& done, uint64_t bytesOut) {
+  const bool dependent = bytesOut <= kDependentLaunchMaxBytes && (flag != nullptr || wait.flag != nullptr || done.slot != nullptr);
   PushParams<N> p;
   for (uint32_t i = 0; i < n; ++i) p.entries[i] = entries[i];
   p.numEntries = n;
@@ -973,7 +1131,9 @@ void launchOne(const PushEntry* entries, uint32_t n, uint32_t bulkTiles, uint32_
   p.bulkStages = bulkStages;
   p.warpTileBytes = 0;
   for (uint32_t i = 0; i < n; ++i) {
-    const uint32_t need = entries[i].kind == kStridedWide16 || entries[i].kind == kStridedNarrow ? kWideWarpTileBytes
+    const uint32_t need = entries[i].kind == kStridedWide16 || entries[i].kind == kStridedNarrow ||
+            entries[i].kind == kStridedBand
+        ? kWideWarpTileBytes
         : entries[i].kind == kStrided                                                            ? kWarpTileBytes
                                                                                                  : 0;
     if (need > p.warpTileBytes) p.warpTileBytes = need;
@@ -994,7 +1154,7 @@ void launchOne(const PushEntry* entries, uint32_t n, uint32_t bulkTiles, uint32_
             "cudaFuncSetAttribute");
       lightConfigured[dev] = lightSmem;
     }
-    tpb_push_pack_light<N><<<grid, kLightThreads, lightSmem, stream>>>(p);
+    launchMaybeDependent(tpb_push_pack_light<N>, grid, kLightThreads, lightSmem, stream, p, dependent);
     check(cudaGetLastError(), "tpb_push_pack_light launch");
     ++gLaunches;
     return;
@@ -1014,7 +1174,7 @@ void launchOne(const PushEntry* entries, uint32_t n, uint32_t bulkTiles, uint32_
   if (plainCtas > want) want = plainCtas;
   uint32_t grid = want < static_cast<uint32_t>(maxCtas) ? want : static_cast<uint32_t>(maxCtas);
   if (grid == 0) grid = 1;
-  tpb_push_pack<N><<<grid, kThreads, smem, stream>>>(p);
+  launchMaybeDependent(tpb_push_pack<N>, grid, kThreads, smem, stream, p, dependent);
   check(cudaGetLastError(), "tpb_push_pack launch");
   ++gLaunches;
 }
@@ -1058,6 +1218,11 @@ void pushEntry(PushPlan& plan, PushEntry e) {
   } else if (e.kind == kCastPlain) {
     const uint64_t perTile = kPlainTileBytes / e.dstElemSize;
     e.numTiles = static_cast<uint32_t>((e.count + perTile - 1) / perTile);
+    e.tileStart = plan.plainTiles;
+    plan.plainTiles += e.numTiles;
+  } else if (e.kind == kStridedBand) {
+    const uint32_t perBand = bandRows(static_cast<uint64_t>(e.cols), e.dstElemSize);
+    e.numTiles = static_cast<uint32_t>((e.rows + perBand - 1) / perBand);
     e.tileStart = plan.plainTiles;
     plan.plainTiles += e.numTiles;
   } else if (e.kind == kStridedNarrow) {
@@ -1141,6 +1306,12 @@ void appendToPlan(PushPlan& plan, const CopyItem& item, bool useBulk) {
           dstRowBytes % 16 == 0 && (reinterpret_cast<uintptr_t>(item.dst) & 15) == 0 && v.rows > 1 &&
           smemWithWide <= kMaxSmemPerCta)
         e.kind = kStridedNarrow;
+      // Any other transposed matrix with rows of at most 8 KiB: bands of whole rows, each written
+      // as one contiguous run whatever its alignment.
+      const uint32_t bands = getPushTuning().bandRows;
+      if (e.kind != kStridedNarrow && (bands == 2 || (bands == 1 && item.remote)) && v.rowStride == 1 &&
+          v.colStride != 1 && v.rows > 1 && dstRowBytes <= kBandBytes && smemWithWide <= kMaxSmemPerCta)
+        e.kind = kStridedBand;
     }
     e.rows = v.rows;
     e.cols = v.cols;
@@ -1213,10 +1384,12 @@ int launchPush(const PushPlan& plan, cudaStream_t stream, int maxCtas, uint32_t*
   if (n <= static_cast<size_t>(kMaxEntriesLarge)) {
     if (n <= static_cast<size_t>(kMaxEntriesSmall))
       launchOne<kMaxEntriesSmall>(plan.entries.data(), static_cast<uint32_t>(n), plan.bulkTiles, plan.plainTiles,
-                                  tileBytes, stages, stream, maxCtas, flag, flagValue, counter, status, wait, done);
+                                  tileBytes, stages, stream, maxCtas, flag, flagValue, counter, status, wait, done,
+                                  plan.totalBytesOut);
     else
       launchOne<kMaxEntriesLarge>(plan.entries.data(), static_cast<uint32_t>(n), plan.bulkTiles, plan.plainTiles,
-                                  tileBytes, stages, stream, maxCtas, flag, flagValue, counter, status, wait, done);
+                                  tileBytes, stages, stream, maxCtas, flag, flagValue, counter, status, wait, done,
+                                  plan.totalBytesOut);
     return 1;
   }
   // More entries than one parameter block holds: several launches on the same stream, each with
@@ -1239,7 +1412,7 @@ int launchPush(const PushPlan& plan, cudaStream_t stream, int maxCtas, uint32_t*
     // Only the first launch waits for the producer; stream order covers the rest.
     launchOne<kMaxEntriesLarge>(part.data(), static_cast<uint32_t>(cnt), bulk, plain, tileBytes, stages, stream,
                                 maxCtas, last ? flag : nullptr, flagValue, counter, status,
-                                first == 0 ? wait : WaitBefore(), last ? done : DoneSlot());
+                                first == 0 ? wait : WaitBefore(), last ? done : DoneSlot(), plan.totalBytesOut);
     ++launches;
   }
   return launches;

@@ -32,6 +32,9 @@ enum EntryKind : uint32_t {
   kStridedWide16 = 4,  // transposed 2-byte elements, everything 4-byte aligned: 64x64 tiles moved as 32-bit words
   kStridedNarrow = 5,  // transposed matrix of at most 64 columns: a tile is 32 whole packed rows, written as one
                        // contiguous run with 16 bytes per lane (optional conversion)
+  kStridedBand = 6,    // transposed matrix whose packed rows are at most 8 KiB, any alignment: a tile is a band of
+                       // whole rows (as many as fit in 8 KiB), gathered down the source columns and written as
+                       // ONE contiguous run (optional conversion)
 };
 
 struct alignas(16) PushEntry {
@@ -52,6 +55,12 @@ constexpr uint32_t kPlainTileBytes = 8 * 1024;  // one warp's unit of work (dest
 constexpr int kStridedTile = 32;                // a warp transposes 32x32 elements (16x32 for 8-byte ones)
 constexpr int kWideTile = 64;                   // kStridedWide16: 64x64 two-byte elements per warp tile
 constexpr int kNarrowMaxCols = 64;              // kStridedNarrow: 32 rows x (<= 64) columns per warp tile
+constexpr uint32_t kBandBytes = 8 * 1024;       // kStridedBand: destination bytes of one band
+// Rows of one band of a kStridedBand entry (host and device must agree).
+constexpr inline uint32_t bandRows(uint64_t cols, uint32_t dstElemSize) {
+  const uint64_t rowBytes = cols * dstElemSize;
+  return rowBytes >= kBandBytes ? 1u : static_cast<uint32_t>(kBandBytes / rowBytes);
+}
 constexpr int kThreads = 512;                   // full kernel: warp 0 drives TMA, warps 1..15 use registers
 constexpr int kLightThreads = 256;              // light kernel (no bulk pipeline, static shared memory only)
 constexpr int kMaxBulkStages = 8;
@@ -65,6 +74,10 @@ struct PushTuning {
   // Transposed matrices of at most 64 columns written as whole packed rows (kStridedNarrow):
   // 0 never, 1 for remote destinations (default), 2 always. TPB_PUSH_NARROW overrides the default.
   uint32_t narrowRows = 1;
+  // Transposed matrices with packed rows of at most 8 KiB written as bands of whole rows
+  // (kStridedBand), wherever the narrow form above does not apply: 0 never, 1 for remote
+  // destinations (default), 2 always. TPB_PUSH_BAND overrides the default.
+  uint32_t bandRows = 1;
 };
 void setPushTuning(const PushTuning& t);
 PushTuning getPushTuning();

@@ -47,6 +47,9 @@ struct RingBench::Impl {
   std::vector<std::shared_ptr<Pipe>> meshSend, meshRecv;  // all-pairs mode
   std::vector<int> meshSendDevice;
   std::vector<cudaStream_t> meshSendStream;  // one stream per destination so pushes overlap
+  uint8_t* hostIn = nullptr;   // end-to-end mode: the pinned source ...
+  size_t hostInBytes = 0;
+  uint32_t* hostOut = nullptr;  // ... and where the step's result lands
 
   PhaseResult runMixedOn(const std::vector<std::shared_ptr<Pipe>>& sendPipes, const std::vector<int>& sendDevices,
                          const std::vector<cudaStream_t>& sendStreams,
@@ -130,6 +133,8 @@ RingBench::~RingBench() {
   if (m.recvCtx) m.recvCtx->join();
   cudaSetDevice(m.opts.device);
   cudaDeviceSynchronize();
+  if (m.hostIn) cudaFreeHost(m.hostIn);
+  if (m.hostOut) cudaFreeHost(m.hostOut);
   cudaFree(m.src);
   cudaFree(m.dst[0]);
   cudaFree(m.dst[1]);
@@ -294,6 +299,64 @@ PhaseResult RingBench::runStream(size_t bytes, int steps, int depth, bool verify
     r.mismatches = bad;
   }
   r.kernelLaunches = kernels::launchCount() - launches0;
+  return r;
+}
+
+PhaseResult RingBench::runEndToEnd(size_t bytes, int steps, bool verify) {
+  Impl& m = *impl_;
+  if (bytes > m.opts.maxBytes) throw std::runtime_error("tensor larger than the benchmark's buffers");
+  TPB_CUDA_CHECK(cudaSetDevice(m.opts.device));
+  constexpr uint64_t kSeed = 0xe2e0000;
+  if (m.hostInBytes < bytes) {
+    if (m.hostIn) cudaFreeHost(m.hostIn);
+    m.hostIn = nullptr;
+    TPB_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&m.hostIn), bytes, cudaHostAllocPortable));
+    m.hostInBytes = bytes;
+    // Pinned memory is addressable from the device: the fill kernel writes the pattern into it.
+    kernels::launchFill(m.sendStream, m.hostIn, bytes, kSeed);
+    TPB_CUDA_CHECK(cudaStreamSynchronize(m.sendStream));
+  }
+  if (!m.hostOut) TPB_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&m.hostOut), 64, cudaHostAllocPortable));
+  const uint64_t launches0 = kernels::launchCount();
+  auto step = [&](int i) {
+    std::promise<Error> wrote, got;
+    Message msg;
+    Message::Tensor t;
+    t.buffer = CudaBuffer{m.hostIn, m.sendStream, m.opts.device};
+    t.length = bytes;
+    t.targetDevice = Device(kCudaDeviceType, m.nextDevice);
+    msg.tensors.push_back(t);
+    m.sendPipe->write(std::move(msg), [&](const Error& e) { wrote.set_value(e); });
+    m.recvPipe->readDescriptor([&, i](const Error& e, Descriptor) {
+      if (e) return got.set_value(e);
+      Allocation a;
+      Allocation::Tensor at;
+      at.buffer = CudaBuffer{m.dst[i & 1], m.recvStream, m.opts.device};
+      a.tensors.push_back(at);
+      m.recvPipe->read(std::move(a), [&](const Error& e2) { got.set_value(e2); });
+    });
+    auto fg = got.get_future();
+    auto fw = wrote.get_future();
+    failOn(waitOrThrow(fg, 120, "end-to-end read"), "read");
+    failOn(waitOrThrow(fw, 120, "end-to-end write"), "write");
+    TPB_CUDA_CHECK(cudaMemcpyAsync(m.hostOut, m.dst[i & 1], 4, cudaMemcpyDeviceToHost, m.recvStream));
+    TPB_CUDA_CHECK(cudaStreamSynchronize(m.recvStream));
+    TPB_CUDA_CHECK(cudaStreamSynchronize(m.sendStream));
+  };
+  PhaseResult r;
+  auto t0 = Clock::now();
+  for (int i = 0; i < steps; ++i) step(i);
+  r.hostMs = msSince(t0);
+  r.deviceMs = r.hostMs;
+  r.kernelLaunches = kernels::launchCount() - launches0;
+  if (verify && steps > 0) {
+    TPB_CUDA_CHECK(cudaMemsetAsync(m.mismatches, 0, sizeof(unsigned long long), m.recvStream));
+    kernels::launchVerify(m.recvStream, m.dst[(steps - 1) & 1], bytes, kSeed, m.mismatches);
+    unsigned long long bad = 0;
+    TPB_CUDA_CHECK(cudaMemcpyAsync(&bad, m.mismatches, sizeof(bad), cudaMemcpyDeviceToHost, m.recvStream));
+    TPB_CUDA_CHECK(cudaStreamSynchronize(m.recvStream));
+    r.mismatches = bad;
+  }
   return r;
 }
 

@@ -58,6 +58,15 @@ class RingBench {
   // element is compared with a CPU restatement (result in PhaseResult::mismatches; nothing is timed).
   PhaseResult runMixed(int steps, uint64_t seed, uint64_t* bytesPerStep, bool verify);
 
+  // The ring end to end through the public C++ API (Pipe::write / readDescriptor / read), one
+  // message at a time: every step's tensor starts in pinned host memory, which is what is handed
+  // to Pipe::write (as a tensor of this rank's GPU), and the step ends when four bytes of the
+  // received tensor have been copied back to pinned host memory and both streams are idle.
+  // `prepare` allocates and fills the pinned source with a seeded pattern (untimed); `steps` timed
+  // steps follow; with `verify` the last received tensor is compared with the pattern on the
+  // device afterwards. hostMs is the wall clock of the steps.
+  PhaseResult runEndToEnd(size_t bytes, int steps, bool verify);
+
   // All-pairs mode: dial every other rank's listener ("url|device" per rank, own entry ignored) and
   // accept everybody's pipe; then every rank sends the mixed message to every other rank at once.
   void connectMesh(const std::vector<std::string>& urls, int rank);

@@ -353,7 +353,8 @@ TPB_GPU_TEST(Kernel, NarrowTransposeWritesWholeRows, 1) {
     EXPECT_EQ(int(out[kGuard - 1]), 0xCD);
     EXPECT_EQ(int(out[kGuard + packed]), 0xCD);
   }
-  // Rows that are not whole 16-byte chunks, a misaligned destination or 8-byte elements keep the other paths.
+  // Rows that are not whole 16-byte chunks, a misaligned destination or 8-byte elements go in bands
+  // of whole rows when bound for another GPU, and keep the 32x32 tiles otherwise.
   {
     DeviceBuf src(4096), dst(4096 + 64);
     auto kindOf = [&](int64_t rows, int64_t cols, DType dt, uint8_t* d, bool remote = true) {
@@ -369,11 +370,93 @@ TPB_GPU_TEST(Kernel, NarrowTransposeWritesWholeRows, 1) {
       appendToPlan(plan, it, true);
       return int(plan.entries.back().kind);
     };
-    EXPECT_EQ(kindOf(10, 6, DType::kF32, dst.p), int(kStrided));        // 24-byte rows
-    EXPECT_EQ(kindOf(10, 8, DType::kF32, dst.p + 4), int(kStrided));    // destination off the 16-byte grid
-    EXPECT_EQ(kindOf(10, 8, DType::kI64, dst.p), int(kStrided));        // 8-byte elements
+    EXPECT_EQ(kindOf(10, 6, DType::kF32, dst.p), int(kStridedBand));        // 24-byte rows
+    EXPECT_EQ(kindOf(10, 8, DType::kF32, dst.p + 4), int(kStridedBand));    // destination off the 16-byte grid
+    EXPECT_EQ(kindOf(10, 8, DType::kI64, dst.p), int(kStridedBand));        // 8-byte elements
     EXPECT_EQ(kindOf(10, 8, DType::kF32, dst.p), int(kStridedNarrow));
     EXPECT_EQ(kindOf(10, 8, DType::kF32, dst.p, false), int(kStrided));  // local destination: the 32x32 tiles are faster
+    EXPECT_EQ(kindOf(10, 6, DType::kF32, dst.p, false), int(kStrided));
+    EXPECT_EQ(kindOf(2, 2049, DType::kF32, dst.p), int(kStrided));          // rows longer than a band
+    EXPECT_EQ(kindOf(1, 100, DType::kF32, dst.p), int(kStrided));           // a single row is contiguous anyway
+  }
+}
+
+// Transposed matrices bound for another GPU whose packed rows fit 8 KiB go in bands of whole rows,
+// each written as one contiguous run: any element size, any alignment of the destination, odd
+// extents, rows so long that a band is a single row, with and without conversion.
+TPB_GPU_TEST(Kernel, BandTransposeWritesOneRunPerBand, 1) {
+  struct Case {
+    int64_t rows, cols;
+    size_t es;      // source element size
+    bool toBf16;    // fp32 -> bf16 on the way (es == 4 only)
+    size_t skew;    // destination offset from a 256-byte boundary, a multiple of the element size
+  };
+  for (Case c : {Case{167, 14, 2, false, 0}, Case{627, 132, 2, false, 2}, Case{1199, 10, 2, false, 6},
+                 Case{55, 428, 2, false, 10}, Case{35, 635, 2, false, 14}, Case{678, 56, 4, false, 4},
+                 Case{2, 2048, 4, false, 12}, Case{381, 10, 4, false, 8}, Case{6, 611, 4, false, 0},
+                 Case{144, 1478, 4, false, 4}, Case{582, 63, 8, false, 8}, Case{12, 381, 8, false, 0},
+                 Case{17, 824, 8, false, 8}, Case{3, 1024, 8, false, 0}, Case{1086, 14, 8, false, 8},
+                 Case{500, 7, 1, false, 3}, Case{40, 8191, 1, false, 1}, Case{999, 65, 4, true, 2},
+                 Case{64, 9, 4, true, 6}, Case{5, 4096, 4, true, 0}, Case{33, 3, 4, true, 14}}) {
+    const size_t srcBytes = c.rows * c.cols * c.es;
+    const size_t des = c.toBf16 ? 2 : c.es;
+    const size_t packed = c.rows * c.cols * des;
+    std::vector<uint8_t> host(srcBytes);
+    std::mt19937 rng(static_cast<uint32_t>(c.rows * 131 + c.cols * 7 + c.es));
+    if (c.toBf16) {
+      auto* f = reinterpret_cast<float*>(host.data());
+      std::normal_distribution<float> dist(0.f, 100.f);
+      for (size_t i = 0; i < srcBytes / 4; ++i) f[i] = dist(rng);
+    } else {
+      for (auto& b : host) b = static_cast<uint8_t>(rng());
+    }
+    DeviceBuf src(srcBytes), dst(packed + 2 * kGuard + 16);
+    CK(cudaMemcpy(src.p, host.data(), srcBytes, cudaMemcpyHostToDevice));
+    CK(cudaMemset(dst.p, 0xCD, dst.n));
+    PushPlan plan;
+    CopyItem it;
+    it.src = src.p;
+    it.dst = dst.p + kGuard + c.skew;
+    it.srcBytes = srcBytes;
+    const DType dt = c.es == 1 ? DType::kU8 : c.es == 2 ? DType::kF16 : c.es == 4 ? DType::kF32 : DType::kI64;
+    it.srcDtype = dt;
+    it.dstDtype = c.toBf16 ? DType::kBF16 : dt;
+    it.strided = true;
+    it.view = StridedView{dt, c.rows, c.cols, 1, c.rows};
+    it.remote = true;
+    appendToPlan(plan, it, true);
+    EXPECT_EQ(int(plan.entries.back().kind), int(kStridedBand));
+    const uint32_t perBand = bandRows(c.cols, static_cast<uint32_t>(des));
+    EXPECT_TRUE(perBand >= 1 && static_cast<uint64_t>(perBand) * c.cols * des <= kBandBytes);
+    EXPECT_EQ(plan.entries.back().numTiles, uint32_t((c.rows + perBand - 1) / perBand));
+    launchPush(plan, nullptr, 148, nullptr, 0, nullptr, nullptr);
+    CK(cudaDeviceSynchronize());
+    auto out = download(dst.p, dst.n);
+    const size_t at = kGuard + c.skew;
+    for (int64_t r = 0; r < c.rows; ++r)
+      for (int64_t col = 0; col < c.cols; ++col) {
+        const uint8_t* want = &host[(col * c.rows + r) * c.es];
+        const uint8_t* got = &out[at + (r * c.cols + col) * des];
+        bool same;
+        if (c.toBf16) {
+          float f;
+          std::memcpy(&f, want, 4);
+          uint16_t g;
+          std::memcpy(&g, got, 2);
+          same = g == f32ToBf16(f);
+        } else {
+          same = std::memcmp(want, got, c.es) == 0;
+        }
+        if (!same)
+          throw tpbtest::TestFailure("band transpose mismatch at (" + std::to_string(r) + "," + std::to_string(col) +
+                                     ") of " + std::to_string(c.rows) + "x" + std::to_string(c.cols) + " es=" +
+                                     std::to_string(c.es) + " skew=" + std::to_string(c.skew));
+      }
+    // nothing before the first byte or after the last one was touched
+    for (size_t i = 0; i < at; ++i)
+      if (out[i] != 0xCD) throw tpbtest::TestFailure("band transpose wrote before its destination");
+    for (size_t i = at + packed; i < out.size(); ++i)
+      if (out[i] != 0xCD) throw tpbtest::TestFailure("band transpose wrote past its destination");
   }
 }
 

@@ -163,9 +163,15 @@ TPB_TEST(Plan, NarrowMatricesFollowTheDestinationAndTheTuning) {
   setPushTuning(t);
   EXPECT_EQ(kindOf(true), int(kStridedNarrow));
   EXPECT_EQ(kindOf(false), int(kStrided));
-  t.narrowRows = 0;
+  t.narrowRows = 0;  // without the narrow form such a matrix goes in bands of whole rows
+  setPushTuning(t);
+  EXPECT_EQ(kindOf(true), int(kStridedBand));
+  t.bandRows = 0;
   setPushTuning(t);
   EXPECT_EQ(kindOf(true), int(kStrided));
+  t.bandRows = 2;    // bands for local destinations too
+  setPushTuning(t);
+  EXPECT_EQ(kindOf(false), int(kStridedBand));
   t.narrowRows = 2;
   setPushTuning(t);
   EXPECT_EQ(kindOf(false), int(kStridedNarrow));

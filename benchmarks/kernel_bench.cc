@@ -145,6 +145,62 @@ int main(int argc, char** argv) {
       report("transposed view, " + std::to_string(es) + "-byte elements", it.srcBytes, ms);
     }
   }
+  if (want("band")) {
+    // Transposed matrices in the form chosen for another GPU's memory (bands of whole rows, one
+    // contiguous run each), here against local memory: shapes of the mixed message.
+    struct Shape {
+      int64_t cols;
+      size_t es;
+    };
+    for (Shape sh : {Shape{14, 2}, Shape{132, 2}, Shape{1478, 4}, Shape{63, 8}}) {
+      const int64_t rows = static_cast<int64_t>(std::min<size_t>(bytes, 256u << 20) / sh.es / sh.cols);
+      for (bool band : {false, true}) {
+        PushPlan plan;
+        CopyItem it;
+        it.src = src;
+        it.dst = dst;
+        it.srcBytes = static_cast<uint64_t>(rows) * sh.cols * sh.es;
+        it.strided = true;
+        it.view = StridedView{sh.es == 2 ? DType::kBF16 : sh.es == 4 ? DType::kF32 : DType::kI64, rows, sh.cols, 1, rows};
+        it.srcDtype = it.dstDtype = it.view.dtype;
+        it.remote = band;
+        appendToPlan(plan, it, true);
+        double ms = timer.run(2, iters / 2 + 1, [&] { launchPush(plan, nullptr, sms, nullptr, 0, nullptr, nullptr); });
+        report(std::string(band ? "band" : "32x32 tiles") + ", transposed [rows, " + std::to_string(sh.cols) + "] of " +
+                   std::to_string(sh.es) + "-byte elements",
+               it.srcBytes, ms);
+      }
+    }
+  }
+  if (want("stage")) {
+    // What the staged channel (cuda_basic) launches: device memory -> mapped pinned host memory
+    // and back, 2 MiB pieces, sixteen pieces per launch, against the copy engine.
+    const size_t total = std::min<size_t>(bytes, 32u << 20);
+    uint8_t* pinned = nullptr;
+    CK(cudaHostAlloc(reinterpret_cast<void**>(&pinned), total, cudaHostAllocMapped | cudaHostAllocPortable));
+    auto planOf = [&](bool out) {
+      PushPlan plan;
+      for (size_t off = 0; off < total; off += 2u << 20) {
+        CopyItem it;
+        it.src = out ? src + off : pinned + off;
+        it.dst = out ? pinned + off : dst + off;
+        it.srcBytes = std::min<size_t>(2u << 20, total - off);
+        it.remote = out;
+        appendToPlan(plan, it, out);  // bulk loads read device memory only
+      }
+      return plan;
+    };
+    PushPlan outPlan = planOf(true), inPlan = planOf(false);
+    double ms = timer.run(3, iters, [&] { launchPush(outPlan, nullptr, sms, words, 1, words + 16, nullptr); });
+    report("stage-out: device -> pinned host, one launch", total, ms);
+    ms = timer.run(3, iters, [&] { CK(cudaMemcpyAsync(pinned, src, total, cudaMemcpyDeviceToHost, nullptr)); });
+    report("cudaMemcpyAsync device -> pinned host", total, ms);
+    ms = timer.run(3, iters, [&] { launchPush(inPlan, nullptr, sms, words, 1, words + 16, nullptr); });
+    report("stage-in: pinned host -> device, one launch", total, ms);
+    ms = timer.run(3, iters, [&] { CK(cudaMemcpyAsync(dst, pinned, total, cudaMemcpyHostToDevice, nullptr)); });
+    report("cudaMemcpyAsync pinned host -> device", total, ms);
+    cudaFreeHost(pinned);
+  }
   if (want("mixed")) {
     // The 64-tensor message of the pipe benchmarks as ONE launch of the full kernel on one GPU:
     // dtype cycles fp32 / bf16 / int64, sizes log-uniform in [1 KiB, 16 MiB], every fourth tensor a

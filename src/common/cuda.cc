@@ -172,6 +172,19 @@ bool cudaIsLocalMemory(const void* ptr, int device) {
   return ordinal == device;
 }
 
+bool cudaIsForeignMemory(const void* ptr, int device) {
+  const CudaLib& lib = CudaLib::get();
+  if (!lib.ok || ptr == nullptr) return false;
+  unsigned type = 0;
+  int ordinal = -1;
+  const CUdeviceptr_t p = reinterpret_cast<CUdeviceptr_t>(ptr);
+  if (lib.cuPointerGetAttribute(&type, CudaLib::kAttrMemoryType, p) != 0) return false;
+  if (type == 1 /* CU_MEMORYTYPE_HOST */) return true;
+  if (type != 2 /* CU_MEMORYTYPE_DEVICE */) return false;
+  if (lib.cuPointerGetAttribute(&ordinal, CudaLib::kAttrDeviceOrdinal, p) != 0) return false;
+  return ordinal != device;
+}
+
 bool cudaIsPinnedHostMemory(const void* ptr) {
   const CudaLib& lib = CudaLib::get();
   if (!lib.ok || ptr == nullptr) return false;

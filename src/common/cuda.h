@@ -152,6 +152,10 @@ int cudaDeviceForPointer(const void* ptr);
 // True when `ptr` is memory of `device` itself: the only source the bulk-copy (TMA) path of the
 // push kernel is given. Another GPU's memory and pinned host memory are read with plain loads.
 bool cudaIsLocalMemory(const void* ptr, int device);
+// True when the driver positively says that `ptr` is NOT memory of `device`: another GPU's memory
+// (own, peer-mapped or IPC-mapped) or host memory. False for memory of `device` and for pointers
+// the driver knows nothing about.
+bool cudaIsForeignMemory(const void* ptr, int device);
 // True when `ptr` is page-locked host memory that CUDA knows about.
 bool cudaIsPinnedHostMemory(const void* ptr);
 // Base address, size and driver buffer id of the allocation containing ptr.

@@ -1335,6 +1335,16 @@ void appendToPlan(PushPlan& plan, const CopyItem& item, bool useBulk) {
   uint64_t bytes = item.srcBytes;
   const uintptr_t sa = reinterpret_cast<uintptr_t>(src), da = reinterpret_cast<uintptr_t>(dst);
   const bool sameSkew = ((sa ^ da) & 15) == 0;
+  if (useBulk && sameSkew && bytes >= getPushTuning().bulkMinBytes) {
+    // Bulk (TMA) loads read the launching GPU's own memory only. Whatever the caller asked for, a
+    // source that the driver places on another GPU or in host memory goes through plain loads.
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess) {
+      cudaGetLastError();
+      device = -1;
+    }
+    if (device >= 0 && cudaIsForeignMemory(src, device)) useBulk = false;
+  }
   if (!useBulk || !sameSkew || bytes < getPushTuning().bulkMinBytes) {
     e.src = src;
     e.dst = dst;

@@ -381,6 +381,53 @@ TPB_GPU_TEST(Kernel, NarrowTransposeWritesWholeRows, 1) {
   }
 }
 
+// Bulk (TMA) loads are planned for sources in the launching GPU's own memory only, whatever the
+// caller asks for: pinned host memory and another GPU's memory fall back to plain loads.
+TPB_GPU_TEST(Kernel, BulkLoadsAreOnlyPlannedForLocalSources, 1) {
+  constexpr size_t kBytes = 4u << 20;
+  DeviceBuf local(kBytes), dst(kBytes);
+  auto kinds = [&](const void* src) {
+    PushPlan plan;
+    CopyItem it;
+    it.src = src;
+    it.dst = dst.p;
+    it.srcBytes = kBytes;
+    appendToPlan(plan, it, true);
+    int bulk = 0;
+    for (auto& e : plan.entries) bulk += e.kind == kCopyBulk;
+    return bulk;
+  };
+  EXPECT_EQ(kinds(local.p), 1);
+  uint8_t* pinned = nullptr;
+  CK(cudaHostAlloc(reinterpret_cast<void**>(&pinned), kBytes, cudaHostAllocPortable));
+  EXPECT_EQ(kinds(pinned), 0);
+  // ... and the plan still moves the bytes
+  for (size_t i = 0; i < kBytes; ++i) pinned[i] = static_cast<uint8_t>(i * 7);
+  PushPlan plan;
+  CopyItem it;
+  it.src = pinned;
+  it.dst = dst.p;
+  it.srcBytes = kBytes;
+  appendToPlan(plan, it, true);
+  launchPush(plan, nullptr, 148, nullptr, 0, nullptr, nullptr);
+  CK(cudaDeviceSynchronize());
+  auto out = download(dst.p, kBytes);
+  EXPECT_TRUE(std::memcmp(out.data(), pinned, kBytes) == 0);
+  CK(cudaFreeHost(pinned));
+  int devices = 0;
+  CK(cudaGetDeviceCount(&devices));
+  if (devices >= 2) {
+    CK(cudaSetDevice(1));
+    uint8_t* other = nullptr;
+    CK(cudaMalloc(&other, kBytes));
+    CK(cudaSetDevice(0));
+    EXPECT_EQ(kinds(other), 0);
+    CK(cudaSetDevice(1));
+    CK(cudaFree(other));
+    CK(cudaSetDevice(0));
+  }
+}
+
 // Transposed matrices bound for another GPU whose packed rows fit 8 KiB go in bands of whole rows,
 // each written as one contiguous run: any element size, any alignment of the destination, odd
 // extents, rows so long that a band is a single row, with and without conversion.

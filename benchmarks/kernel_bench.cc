@@ -172,7 +172,7 @@ int main(int argc, char** argv) {
       }
     }
   }
-  if (want("stage")) {
+  if (want("hoststage")) {
     // What the staged channel (cuda_basic) launches: device memory -> mapped pinned host memory
     // and back, 2 MiB pieces, sixteen pieces per launch, against the copy engine.
     const size_t total = std::min<size_t>(bytes, 32u << 20);

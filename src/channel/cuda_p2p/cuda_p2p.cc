@@ -632,6 +632,13 @@ class ChannelImpl final : public Channel, public std::enable_shared_from_this<Ch
   std::map<int, std::vector<std::unique_ptr<CudaEvent>>> eventRings_;
   CudaEvent* lastPushEvent_ = nullptr;
   CudaEvent& eventFor(int device, uint64_t seq);
+  // Streams of the channel's own for large pushes (Options::asideMinBytes), one per sending device,
+  // and how many such pushes have not finished yet (their send callbacks are still owed).
+  std::map<int, cudaStream_t> asideStreams_;
+  std::map<int, std::unique_ptr<CudaEvent>> asideReached_;  // "the user's stream has got here", per device
+  int asidePending_ = 0;
+  cudaStream_t asideStreamFor(int device);
+  void finishSendWhenPushed(SendOp& op, CudaEvent* sameProcessEvent);
   struct HostItem {
     const uint8_t* src;
     uint8_t* dst;
@@ -1428,6 +1435,23 @@ void ChannelImpl::launchRendezvous(SendOp& op) {
     ev.record(s);
     ev.wait(stream, op.srcDevice);
   }
+  // A large batch leaves from the channel's own stream, behind what the user's stream holds now.
+  uint64_t batchBytes = 0;
+  for (auto& it : op.items) batchBytes += it.length;
+  const bool aside = opts_.asideMinBytes != 0 && batchBytes >= opts_.asideMinBytes;
+  if (aside) {
+    try {
+      cudaStream_t own = asideStreamFor(op.srcDevice);
+      auto& slot = asideReached_[op.srcDevice];
+      if (!slot) slot = std::make_unique<CudaEvent>(op.srcDevice);
+      CudaEvent& reached = *slot;  // waited for right below: re-recording it for the next batch is safe
+      reached.record(stream);
+      reached.wait(own, op.srcDevice);
+      stream = own;
+    } catch (const std::exception& ex) {
+      return closeFromLoop(TPB_CREATE_ERROR(CudaError, ex.what()));
+    }
+  }
   try {
     for (const HostItem& h : hostLocal) {
       trace::Scope copyTraced("p2p.send.hostcopy", op.seq);
@@ -1460,6 +1484,7 @@ void ChannelImpl::launchRendezvous(SendOp& op) {
   }
   Launched l;
   l.seq = op.seq;
+  CudaEvent* asideEvent = nullptr;
   const bool launch = launchesMade_++ != opts_.faultSkipLaunch;
   if (sameProcess_) {
     // Nothing to publish: the receiver's stream waits for an event recorded behind the kernel.
@@ -1467,9 +1492,12 @@ void ChannelImpl::launchRendezvous(SendOp& op) {
     CudaEvent& done = eventFor(op.srcDevice, op.seq);
     done.record(stream);
     l.event = reinterpret_cast<uint64_t>(done.raw());
-    lastPushEvent_ = &done;
-    for (cudaStream_t s : others) done.wait(s, op.srcDevice);
+    if (!aside) {
+      lastPushEvent_ = &done;
+      for (cudaStream_t s : others) done.wait(s, op.srcDevice);
+    }
     launchedUpTo_ = op.seq + 1;
+    asideEvent = &done;
   } else {
     Error err;
     Arena* mine = arenaFor(op.srcDevice, err);
@@ -1478,7 +1506,7 @@ void ChannelImpl::launchRendezvous(SendOp& op) {
     if (launch)
       kernels::launchPush(plan, stream, ctas, flag, flagValueFor(op.seq), mine->pushCounter(op.seq), statusWord(),
                           kernels::WaitBefore(), doneSlotFor(op.seq));
-    if (!others.empty()) {
+    if (!others.empty() && !aside) {
       CudaEvent ev(op.srcDevice);
       ev.record(stream);
       for (cudaStream_t s : others) ev.wait(s, op.srcDevice);
@@ -1488,7 +1516,43 @@ void ChannelImpl::launchRendezvous(SendOp& op) {
   TPB_VLOG(6) << "Channel " << id_ << " launched the push of batch #" << op.seq << " (" << plan.entries.size()
               << " entries, " << plan.totalBytesOut << " bytes)";
   writePacket(l);
-  finishSend(op, Error::kSuccess);
+  if (aside) finishSendWhenPushed(op, asideEvent);
+  else finishSend(op, Error::kSuccess);
+}
+
+cudaStream_t ChannelImpl::asideStreamFor(int device) {
+  auto it = asideStreams_.find(device);
+  if (it != asideStreams_.end()) return it->second;
+  CudaDeviceGuard g(device);
+  int least = 0, greatest = 0;
+  TPB_CUDA_CHECK(cudaDeviceGetStreamPriorityRange(&least, &greatest));
+  cudaStream_t s = nullptr;
+  TPB_CUDA_CHECK(cudaStreamCreateWithPriority(&s, cudaStreamNonBlocking, greatest));
+  asideStreams_[device] = s;
+  return s;
+}
+
+// The batch was pushed from the channel's own stream: its callbacks fire when the push is over
+// (completion word between processes, event within one), not now.
+void ChannelImpl::finishSendWhenPushed(SendOp& op, CudaEvent* sameProcessEvent) {
+  op.launched = true;
+  auto items = std::make_shared<std::vector<SendItem>>(std::move(op.items));
+  auto self = shared_from_this();
+  ++asidePending_;
+  auto done = [self, items]() {
+    --self->asidePending_;
+    self->deviceFailed();
+    const Error e = self->error_ && !self->peerLeft_ ? self->error_ : Error::kSuccess;
+    for (auto& it : *items) it.callback(e);
+    if (self->error_ && !self->finished_) self->sendByeWhenIdle();
+  };
+  if (sameProcessEvent) {
+    cudaEvent_t raw = sameProcessEvent->raw();
+    ctx_->poller_.watch([raw]() { return cudaEventQuery(raw) != cudaErrorNotReady; },
+                        [self, done]() { self->ctx_->loop_.deferToLoop(done); });
+  } else {
+    whenPushFinishes(op.seq, done);
+  }
 }
 
 void ChannelImpl::finishSend(SendOp& op, const Error& e) {
@@ -1985,6 +2049,7 @@ void ChannelImpl::sendByeWhenIdle() {
   if (byeSent_ || finished_) return;
   auto self = shared_from_this();
   if (sameProcess_) {
+    if (asidePending_ > 0) return;  // the last of them calls back here
     // The newest event stands for every push before it: they ran on streams the user ordered.
     if (!lastPushEvent_ || cudaEventQuery(lastPushEvent_->raw()) != cudaErrorNotReady) return sendBye();
     cudaEvent_t raw = lastPushEvent_->raw();
@@ -2014,6 +2079,14 @@ void ChannelImpl::finishClose() {
   held_.clear();
   for (auto& op : held)
     for (auto& it : op.items) it.callback(error_);
+  for (auto& entry : asideStreams_) {
+    try {
+      CudaDeviceGuard g(entry.first);
+      cudaStreamDestroy(entry.second);  // what is queued on it still runs to the end
+    } catch (...) {
+    }
+  }
+  asideStreams_.clear();
   conn_->close();
   ctx_->unenroll(self);
 }
@@ -2040,6 +2113,7 @@ Options applyEnvironment(Options o) {
   num("TPB_CUDA_P2P_CLOSE_TIMEOUT_MS", o.closeTimeoutMs);
   num("TPB_CUDA_P2P_HOST_COPY_MIN_BYTES", o.hostCopyMinBytes);
   num("TPB_CUDA_P2P_HOST_PIECE_BYTES", o.hostPieceBytes);
+  num("TPB_CUDA_P2P_ASIDE_MIN_BYTES", o.asideMinBytes);
   unsigned long long ms = o.waitTimeoutNs / 1'000'000ull;
   num("TPB_CUDA_P2P_WAIT_TIMEOUT_MS", ms);
   o.waitTimeoutNs = ms * 1'000'000ull;

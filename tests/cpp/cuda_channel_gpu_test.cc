@@ -175,7 +175,7 @@ void expectOk(const Error& e, const char* what) {
 // The reference's ClientToServer / ServerToClient / SendMultipleTensors / EmptyTensor cases, with
 // both the per-tensor calls (send / recv) and the batch calls.
 void basicCases(bool processes, PeerSetup setup, int serverDevice, int clientDevice) {
-  const std::vector<size_t> sizes = {4096, 1u << 20, (4u << 20) + 12, 100};
+  const std::vector<size_t> sizes = {4096, 1u << 20, (4u << 20) + 12, 100, (24u << 20) + 4};
   runPair(
       processes, setup, setup,
       [=](channel::Channel& ch) {

@@ -264,11 +264,21 @@ def run_native(args):
     def end_to_end():
         """The C++ API is the library's primary one (as it is the reference's, whose arm makes the
         same three calls per step); the same step through the Python layer is reported beside it."""
-        e2e = run_e2e_native_api(args, rb, world, barrier, max_over_ranks)
         try:
-            e2e["python_api"] = run_e2e(args, tpb, torch, dist, rank, world, local_rank, barrier, max_over_ranks, gather)
+            e2e = run_e2e_native_api(args, rb, world, barrier, max_over_ranks)
         except Exception as exc:  # noqa: BLE001
-            e2e["python_api"] = {"error": str(exc)}
+            e2e = None
+            native_error = str(exc)
+        try:
+            through_python = run_e2e(args, tpb, torch, dist, rank, world, local_rank, barrier, max_over_ranks, gather)
+        except Exception as exc:  # noqa: BLE001
+            through_python = {"error": str(exc)}
+        if e2e is None:
+            # Whatever went wrong with the C++ step is said, and the Python one stands in.
+            e2e = dict(through_python)
+            e2e["native_api_error"] = native_error
+        else:
+            e2e["python_api"] = through_python
         return e2e
 
     if args.e2e_only:

@@ -42,6 +42,10 @@ namespace shm {
 namespace {
 
 constexpr uint64_t kRingBytes = 2u << 20;        // per connection and direction
+// A frame larger than this moves through the ring in pieces of this size: the writer publishes
+// (and pokes the reader) after every piece and the reader frees after every piece, so that the
+// two memcpys of a large frame overlap instead of taking turns with a whole ring at a time.
+constexpr uint64_t kPieceBytes = 256u << 10;
 constexpr uint32_t kReactorSlots = 1u << 16;     // tokens that can be queued at once
 constexpr uint64_t kReactorMagic = 0x7470625f72656163ull;
 
@@ -537,14 +541,16 @@ void ConnectionImpl::processReads() {
       }
     }
     if (op.bodyRead < op.frameLen) {
-      uint64_t n = inbox_.read(op.ptr + op.bodyRead, op.frameLen - op.bodyRead);
-      if (n > 0) consumed = true;
-      op.bodyRead += n;
-      if (op.bodyRead < op.frameLen) {
-        // Let the writer refill while we wait for the rest.
-        if (n > 0 && !peerGone_ && inbox_.producerStalled()) { pokePeer(peerOutboxToken_); consumed = false; }
-        break;
+      bool more = true;
+      while (more && op.bodyRead < op.frameLen) {
+        const uint64_t want = std::min<uint64_t>(op.frameLen - op.bodyRead, kPieceBytes);
+        const uint64_t n = inbox_.read(op.ptr + op.bodyRead, want);
+        op.bodyRead += n;
+        more = n == want;
+        // Let the writer refill while the next piece is copied out.
+        if (n > 0 && !peerGone_ && inbox_.producerStalled()) pokePeer(peerOutboxToken_);
       }
+      if (op.bodyRead < op.frameLen) break;
     }
     ReadOp done = std::move(reads_.front());
     reads_.pop_front();
@@ -574,13 +580,16 @@ void ConnectionImpl::processWrites() {
         produced = true;
       }
       if (op.bodyWritten < op.length) {
-        uint64_t n = outbox_.write(op.ptr + op.bodyWritten, op.length - op.bodyWritten);
-        if (n > 0) produced = true;
+        const uint64_t want = std::min<uint64_t>(op.length - op.bodyWritten, kPieceBytes);
+        const uint64_t n = outbox_.write(op.ptr + op.bodyWritten, want);
         op.bodyWritten += n;
         if (op.bodyWritten < op.length) {
-          if (waitForSpace(1)) continue;
+          // More to come: the reader may as well start on what is there.
+          if (n > 0) pokePeer(peerInboxToken_);
+          if (n == want || waitForSpace(1)) continue;
           break;
         }
+        if (n > 0) produced = true;
       }
       completed.push_back(std::move(op.fn));
       writes_.pop_front();

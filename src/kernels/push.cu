@@ -193,6 +193,9 @@ struct PushParams {
   // launch is over without an event.
   uint32_t* doneSlot;
   uint32_t doneValue;
+  // When the kernel behind this one on the stream may be let go (see letDependentsLaunch):
+  // 0 = at the start, 1 = when this CTA has issued all its work and is about to report in.
+  uint32_t lateTrigger;
 };
 
 // The arrive counter of a launch doubles as its failure latch: the low half counts CTAs that
@@ -852,8 +855,18 @@ __device__ __forceinline__ bool waitForProducer(const PushParams<N>& p) {
 // Last step of every launch. A launch that gave up anywhere (a bulk load that never completed,
 // a producer that never arrived) does NOT publish its flag: whoever waits for it runs into its
 // own time limit instead of reading half-written data.
+// Programmatic dependent launch: a push kernel lets the kernel queued behind it on the stream start
+// right away (its own blocks are on the SMs within microseconds, so "when every block has got
+// going" is the moment), and itself waits for the kernel before it only where it first touches
+// memory that kernel may have written. Two pushes queued back to back thus overlap the launch
+// latency and the prologue of the second with the tail of the first; a kernel that is not launched
+// with the attribute (anything of the user's) is serialised as always.
+__device__ __forceinline__ void letDependentsLaunch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void waitForEarlierKernels() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 template <int N>
 __device__ __forceinline__ void publish(const PushParams<N>& p, bool failedHere) {
+  if (p.lateTrigger) letDependentsLaunch();
   if (p.flag == nullptr && p.doneSlot == nullptr) return;
   // Make this thread's writes visible system-wide before the CTA reports in.
   __threadfence_system();
@@ -882,15 +895,6 @@ __device__ __forceinline__ void publish(const PushParams<N>& p, bool failedHere)
 }
 
 // ---- the kernels --------------------------------------------------------------------------------
-// Programmatic dependent launch: a push kernel lets the kernel queued behind it on the stream start
-// right away (its own blocks are on the SMs within microseconds, so "when every block has got
-// going" is the moment), and itself waits for the kernel before it only where it first touches
-// memory that kernel may have written. Two pushes queued back to back thus overlap the launch
-// latency and the prologue of the second with the tail of the first; a kernel that is not launched
-// with the attribute (anything of the user's) is serialised as always.
-__device__ __forceinline__ void letDependentsLaunch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void waitForEarlierKernels() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-
 template <int N>
 __global__ void __launch_bounds__(kThreads, 1) tpb_push_pack(const __grid_constant__ PushParams<N> p) {
   extern __shared__ uint8_t smemRaw[];
@@ -906,7 +910,7 @@ __global__ void __launch_bounds__(kThreads, 1) tpb_push_pack(const __grid_consta
   const bool haveBulk = p.bulkTiles > blockIdx.x;
   bool failed = false;
 
-  letDependentsLaunch();
+  if (!p.lateTrigger) letDependentsLaunch();
   if (tid == 0 && haveBulk) {
     for (int s = 0; s < S; ++s) mbarInit(&full[s], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -997,7 +1001,7 @@ __global__ void __launch_bounds__(kLightThreads, 2) tpb_push_pack_light(const __
   extern __shared__ __align__(16) uint8_t lightTiles[];  // kWarps * p.warpTileBytes, none for plain copies
   constexpr uint32_t kWarps = kLightThreads / 32;
   const uint32_t warp = threadIdx.x / 32;
-  letDependentsLaunch();
+  if (!p.lateTrigger) letDependentsLaunch();
   waitForEarlierKernels();
   if (!waitForProducer(p)) {
     publish(p, true);
@@ -1080,6 +1084,15 @@ void check(cudaError_t e, const char* what) {
 // to 4 MiB the attribute cost 2 us per message, beyond that it made no difference).
 // TPB_PUSH_PDL=0 turns it off.
 constexpr uint64_t kDependentLaunchMaxBytes = 64 * 1024;
+// Larger launches up to TPB_PUSH_PDL_LATE_MAX_BYTES (default 0: none) are launched as dependents
+// too, but let their own dependents go only when their work has been issued.
+uint64_t lateDependentMaxBytes() {
+  static const uint64_t v = [] {
+    const char* e = std::getenv("TPB_PUSH_PDL_LATE_MAX_BYTES");
+    return e && *e ? std::strtoull(e, nullptr, 0) : 0ull;
+  }();
+  return v;
+}
 bool programmaticLaunches() {
   static const bool on = [] {
     const char* e = std::getenv("TPB_PUSH_PDL");
@@ -1112,8 +1125,11 @@ template <int N>
 void launchOne(const PushEntry* entries, uint32_t n, uint32_t bulkTiles, uint32_t plainTiles, uint32_t bulkTileBytes,
                uint32_t bulkStages, cudaStream_t stream, int maxCtas, uint32_t* flag, uint32_t flagValue,
                uint32_t* counter, uint32_t* status, const WaitBefore& wait, const DoneSlot& done, uint64_t bytesOut) {
-  const bool dependent = bytesOut <= kDependentLaunchMaxBytes && (flag != nullptr || wait.flag != nullptr || done.slot != nullptr);
+  const bool publishes = flag != nullptr || wait.flag != nullptr || done.slot != nullptr;
+  const bool early = bytesOut <= kDependentLaunchMaxBytes;
+  const bool dependent = publishes && (early || bytesOut <= lateDependentMaxBytes());
   PushParams<N> p;
+  p.lateTrigger = early ? 0 : 1;
   for (uint32_t i = 0; i < n; ++i) p.entries[i] = entries[i];
   p.numEntries = n;
   p.bulkTiles = bulkTiles;

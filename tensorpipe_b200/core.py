@@ -231,9 +231,18 @@ class Pipe:
         # stream" is not the caller's: both are taken here, on the caller's thread, and the
         # allocation below happens under them. The received tensors are then ordered on the stream
         # the caller was working on, and belong to it as far as torch's allocator is concerned.
+        # Only devices the caller already works with are asked for their stream: asking a GPU that
+        # this process has not touched would create a context on it, and a GPU that serves several
+        # processes' contexts time-slices between them.
         if torch.cuda.is_available() and torch.cuda.is_initialized():
             caller_device = torch.cuda.current_device()
-            caller_streams = {i: torch.cuda.current_stream(i) for i in range(torch.cuda.device_count())}
+            wanted = {caller_device}
+            if device is not None and str(device).startswith("cuda"):
+                wanted.add(torch.device(device).index if torch.device(device).index is not None else caller_device)
+            for t in out or ():
+                if t.device.type == "cuda":
+                    wanted.add(t.device.index)
+            caller_streams = {i: torch.cuda.current_stream(i) for i in wanted}
         else:
             caller_device, caller_streams = None, {}
 

@@ -235,6 +235,16 @@ TPB_GPU_TEST(CudaChannel, P2pTwoProcesses, 1) { basicCases(true, p2p(), 0, 0); }
 TPB_GPU_TEST(CudaChannel, P2pAcrossDevices, 2) { basicCases(true, p2p(), 0, 1); }
 TPB_GPU_TEST(CudaChannel, P2pReverseAcrossDevices, 2) { basicCases(true, p2p(), 1, 0); }
 TPB_GPU_TEST(CudaChannel, P2pSameProcessAcrossDevices, 2) { basicCases(false, p2p(), 0, 1); }
+// Large batches pushed from the channel's own stream (Options::asideMinBytes): same results, and
+// the send callback, which then stands for "the push is over", still comes.
+static PeerSetup p2pAside() {
+  channel::cuda_p2p::Options o;
+  o.asideMinBytes = 1u << 20;
+  return p2p(o);
+}
+TPB_GPU_TEST(CudaChannel, P2pAsideStreamSameProcess, 1) { basicCases(false, p2pAside(), 0, 0); }
+TPB_GPU_TEST(CudaChannel, P2pAsideStreamTwoProcesses, 1) { basicCases(true, p2pAside(), 0, 0); }
+TPB_GPU_TEST(CudaChannel, P2pAsideStreamAcrossDevices, 2) { basicCases(true, p2pAside(), 0, 1); }
 TPB_GPU_TEST(CudaChannel, GdrOverASoftwareFabric, 1) { basicCases(false, gdr(), 0, 0); }
 TPB_GPU_TEST(CudaChannel, GdrOverASoftwareFabricAcrossDevices, 2) { basicCases(false, gdr(), 0, 1); }
 TPB_GPU_TEST(CudaChannel, BasicSameProcess, 1) { basicCases(false, cudaBasic(), 0, 0); }

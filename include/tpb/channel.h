@@ -121,7 +121,7 @@ std::shared_ptr<Context> create(std::shared_ptr<Context> cpuContext);
 namespace cuda_p2p {
 // Every field can be overridden from the environment when the channel is created:
 // TPB_CUDA_P2P_EAGER_THRESHOLD, _INBOX_BYTES, _MAX_CTAS, _WAIT_KERNEL (0/1), _FUSED_WAIT (0/1),
-// _WAIT_TIMEOUT_MS, _BULK (0/1), _CLOSE_TIMEOUT_MS, _HOST_COPY_MIN_BYTES, _HOST_PIECE_BYTES, _ASIDE_MIN_BYTES.
+// _WAIT_TIMEOUT_MS, _BULK (0/1), _CLOSE_TIMEOUT_MS, _HOST_COPY_MIN_BYTES, _HOST_PIECE_BYTES, _SEND_ORDER_MIN_BYTES.
 struct Options {
   size_t eagerThreshold = 64 * 1024;     // batches up to this many bytes go through the inbox: one
                                           // control hop less (lower latency), one small kernel more on
@@ -141,16 +141,18 @@ struct Options {
                                           // 0: always the kernel
   size_t hostPieceBytes = 32u << 20;     // size of those pieces (two slots of device memory per
                                           // sending GPU, allocated on first use)
-  size_t asideMinBytes = 0;              // a batch of at least this many bytes is pushed from a stream of
-                                          // the channel's own (highest priority) instead of the user's:
-                                          // the user's stream goes on with what it has queued behind the
-                                          // send (the next micro-batch of a pipeline) while the bytes
-                                          // cross NVLink. The send callback then fires when the push has
-                                          // FINISHED (nothing is made to wait on the user's stream), which
-                                          // is later than "queued" but never too early to reuse the source.
-                                          // 0 (default): always the user's stream. Off by default because
-                                          // the 1F1B pipeline it was made for ran 9 % slower with it (the
-                                          // push then competes with the stage's compute for SMs)
+  size_t sendOrderMinBytes = 8u << 20;   // a batch of at least this many bytes (all of it on one stream)
+                                          // takes its place in the sender's stream when send() is called,
+                                          // not when the receiver's buffers become known: an event is
+                                          // recorded on that stream by the calling thread, the push runs on
+                                          // a stream of the channel's own (highest priority) behind that
+                                          // event, and the sender's stream is made to wait for the push at
+                                          // the point it has reached by then. Work that the user queues
+                                          // between send() and the receiver's answer (the next micro-batch
+                                          // of a pipeline) therefore neither delays the push nor is delayed
+                                          // by it. The send callback fires as for any other batch. Smaller
+                                          // batches are launched on the sender's stream itself, where the
+                                          // four extra driver calls would show. 0: never
   // Host-side fault injection for tests: the N-th push of a channel (counting from 0) is announced
   // to the receiver but not launched, so that the receiver's bounded wait runs out. -1: never.
   int faultSkipLaunch = -1;

@@ -487,6 +487,9 @@ struct SendOp {
   // batch was handed over, before the receiver answered (see HostFeed::early).
   int earlyItem = -1;
   uint64_t earlyBytes = 0;
+  // Recorded on the sender's stream when the batch was handed over (Options::sendOrderMinBytes);
+  // empty for a batch that is launched on the sender's stream itself.
+  std::shared_ptr<CudaEvent> sent;
 };
 
 // A receive buffer that CUDA IPC cannot export (memory from a stream-ordered pool, a virtual-memory
@@ -553,7 +556,7 @@ class ChannelImpl final : public Channel, public std::enable_shared_from_this<Ch
   void armRead();
   void onPacket(Packet p);
   void onHello(const Hello& peer);
-  void sendBatchFromLoop(std::vector<SendItem> items);
+  void sendBatchFromLoop(std::vector<SendItem> items, std::shared_ptr<CudaEvent> sent);
   void recvBatchFromLoop(std::vector<RecvItem> items);
   void pumpSends();
   bool tryLaunch(SendOp& op);
@@ -632,13 +635,15 @@ class ChannelImpl final : public Channel, public std::enable_shared_from_this<Ch
   std::map<int, std::vector<std::unique_ptr<CudaEvent>>> eventRings_;
   CudaEvent* lastPushEvent_ = nullptr;
   CudaEvent& eventFor(int device, uint64_t seq);
-  // Streams of the channel's own for large pushes (Options::asideMinBytes), one per sending device,
-  // and how many such pushes have not finished yet (their send callbacks are still owed).
+  // Large batches (Options::sendOrderMinBytes) leave from a stream of the channel's own, one per
+  // sending device, behind an event that sendBatch() recorded on the sender's stream from the
+  // calling thread. The events come from a pool that both threads reach.
   std::map<int, cudaStream_t> asideStreams_;
-  std::map<int, std::unique_ptr<CudaEvent>> asideReached_;  // "the user's stream has got here", per device
-  int asidePending_ = 0;
+  std::map<int, std::unique_ptr<CudaEvent>> asideDone_;  // "the push on the aside stream is over", per device
   cudaStream_t asideStreamFor(int device);
-  void finishSendWhenPushed(SendOp& op, CudaEvent* sameProcessEvent);
+  std::mutex sentEventsMutex_;
+  std::map<int, std::vector<std::unique_ptr<CudaEvent>>> sentEvents_;
+  std::shared_ptr<CudaEvent> markSendTime(const std::vector<SendItem>& items);
   struct HostItem {
     const uint8_t* src;
     uint8_t* dst;
@@ -974,8 +979,49 @@ std::vector<std::vector<It>> ChannelImpl::splitByDevicePair(std::vector<It>& ite
 
 void ChannelImpl::sendBatch(std::vector<SendItem> items) {
   auto self = shared_from_this();
+  std::shared_ptr<CudaEvent> sent = markSendTime(items);
   auto shared = std::make_shared<std::vector<SendItem>>(std::move(items));
-  ctx_->loop_.deferToLoop([self, shared]() { self->sendBatchFromLoop(std::move(*shared)); });
+  ctx_->loop_.deferToLoop([self, shared, sent]() { self->sendBatchFromLoop(std::move(*shared), sent); });
+}
+
+// Runs on the thread that called sendBatch(), so that the event lands in the sender's stream ahead
+// of whatever that thread queues next. The push is launched much later, by the loop thread, when
+// the receiver has named its buffers: launched on the sender's stream then, it would sit behind
+// all that the user queued in between (and a pipeline stage queues the next micro-batch's compute
+// there, which the stage downstream then waits out).
+std::shared_ptr<CudaEvent> ChannelImpl::markSendTime(const std::vector<SendItem>& items) {
+  if (opts_.sendOrderMinBytes == 0 || items.empty()) return nullptr;
+  uint64_t bytes = 0;
+  for (const SendItem& it : items) bytes += it.length;
+  if (bytes < opts_.sendOrderMinBytes) return nullptr;
+  const void* stream = items[0].buffer.unwrap<CudaBuffer>().stream;
+  const int device = items[0].buffer.device().index;
+  for (const SendItem& it : items)
+    if (it.buffer.unwrap<CudaBuffer>().stream != stream || it.buffer.device().index != device) return nullptr;
+  try {
+    std::unique_ptr<CudaEvent> ev;
+    {
+      std::lock_guard<std::mutex> lock(sentEventsMutex_);
+      auto& pool = sentEvents_[device];
+      if (!pool.empty()) {
+        ev = std::move(pool.back());
+        pool.pop_back();
+      }
+    }
+    if (!ev) ev = std::make_unique<CudaEvent>(device);
+    ev->record(static_cast<cudaStream_t>(const_cast<void*>(stream)));
+    std::weak_ptr<ChannelImpl> weak = weak_from_this();
+    return std::shared_ptr<CudaEvent>(ev.release(), [weak, device](CudaEvent* e) {
+      std::unique_ptr<CudaEvent> owned(e);
+      if (auto self = weak.lock()) {
+        std::lock_guard<std::mutex> lock(self->sentEventsMutex_);
+        auto& pool = self->sentEvents_[device];
+        if (pool.size() < 64) pool.push_back(std::move(owned));
+      }
+    });
+  } catch (const std::exception&) {
+    return nullptr;  // the batch then goes the ordinary way, where a dead device is reported
+  }
 }
 
 void ChannelImpl::recvBatch(std::vector<RecvItem> items) {
@@ -984,7 +1030,7 @@ void ChannelImpl::recvBatch(std::vector<RecvItem> items) {
   ctx_->loop_.deferToLoop([self, shared]() { self->recvBatchFromLoop(std::move(*shared)); });
 }
 
-void ChannelImpl::sendBatchFromLoop(std::vector<SendItem> items) {
+void ChannelImpl::sendBatchFromLoop(std::vector<SendItem> items, std::shared_ptr<CudaEvent> sent) {
   deviceFailed();
   if (peerLeft_ && !error_) closeFromLoop(TPB_CREATE_ERROR(ChannelClosedError));
   std::vector<SendItem> live;
@@ -1004,6 +1050,7 @@ void ChannelImpl::sendBatchFromLoop(std::vector<SendItem> items) {
     op.srcDevice = group[0].buffer.device().index;
     op.targetDevice = group[0].targetDevice;
     op.items = std::move(group);
+    op.sent = sent;
     auto early = earlyReady_.find(op.seq);
     if (early != earlyReady_.end()) {
       op.ready = std::move(early->second);
@@ -1435,18 +1482,14 @@ void ChannelImpl::launchRendezvous(SendOp& op) {
     ev.record(s);
     ev.wait(stream, op.srcDevice);
   }
-  // A large batch leaves from the channel's own stream, behind what the user's stream holds now.
-  uint64_t batchBytes = 0;
-  for (auto& it : op.items) batchBytes += it.length;
-  const bool aside = opts_.asideMinBytes != 0 && batchBytes >= opts_.asideMinBytes;
+  // A batch that was marked in the sender's stream when it was handed over leaves from the
+  // channel's own stream, behind that mark.
+  cudaStream_t senderStream = stream;
+  const bool aside = op.sent != nullptr && others.empty();
   if (aside) {
     try {
       cudaStream_t own = asideStreamFor(op.srcDevice);
-      auto& slot = asideReached_[op.srcDevice];
-      if (!slot) slot = std::make_unique<CudaEvent>(op.srcDevice);
-      CudaEvent& reached = *slot;  // waited for right below: re-recording it for the next batch is safe
-      reached.record(stream);
-      reached.wait(own, op.srcDevice);
+      op.sent->wait(own, op.srcDevice);
       stream = own;
     } catch (const std::exception& ex) {
       return closeFromLoop(TPB_CREATE_ERROR(CudaError, ex.what()));
@@ -1484,40 +1527,50 @@ void ChannelImpl::launchRendezvous(SendOp& op) {
   }
   Launched l;
   l.seq = op.seq;
-  CudaEvent* asideEvent = nullptr;
   const bool launch = launchesMade_++ != opts_.faultSkipLaunch;
-  if (sameProcess_) {
-    // Nothing to publish: the receiver's stream waits for an event recorded behind the kernel.
-    if (launch) kernels::launchPush(plan, stream, ctas, nullptr, 0, nullptr, statusWord());
-    CudaEvent& done = eventFor(op.srcDevice, op.seq);
-    done.record(stream);
-    l.event = reinterpret_cast<uint64_t>(done.raw());
-    if (!aside) {
+  try {
+    if (sameProcess_) {
+      // Nothing to publish: the receiver's stream waits for an event recorded behind the kernel.
+      if (launch) kernels::launchPush(plan, stream, ctas, nullptr, 0, nullptr, statusWord());
+      CudaEvent& done = eventFor(op.srcDevice, op.seq);
+      done.record(stream);
+      l.event = reinterpret_cast<uint64_t>(done.raw());
       lastPushEvent_ = &done;
       for (cudaStream_t s : others) done.wait(s, op.srcDevice);
+      if (aside) done.wait(senderStream, op.srcDevice);
+      launchedUpTo_ = op.seq + 1;
+    } else {
+      Error err;
+      Arena* mine = arenaFor(op.srcDevice, err);
+      if (!mine) return closeFromLoop(err);
+      uint32_t* flag = reinterpret_cast<uint32_t*>(arenaBase) + (op.seq % kFlagSlots);
+      if (launch)
+        kernels::launchPush(plan, stream, ctas, flag, flagValueFor(op.seq), mine->pushCounter(op.seq), statusWord(),
+                            kernels::WaitBefore(), doneSlotFor(op.seq));
+      if (!others.empty()) {
+        CudaEvent ev(op.srcDevice);
+        ev.record(stream);
+        for (cudaStream_t s : others) ev.wait(s, op.srcDevice);
+      }
+      if (aside) {
+        // The sender's stream takes the push in at the point it has reached by now: what the user
+        // queues from here on (a write into the source among it) runs after the push, which is what
+        // the send callback promises.
+        auto& done = asideDone_[op.srcDevice];
+        if (!done) done = std::make_unique<CudaEvent>(op.srcDevice);
+        done->record(stream);  // waited for on the next line: re-recording it for the next batch is safe
+        done->wait(senderStream, op.srcDevice);
+      }
+      noteLaunch(op.seq, launch);
     }
-    launchedUpTo_ = op.seq + 1;
-    asideEvent = &done;
-  } else {
-    Error err;
-    Arena* mine = arenaFor(op.srcDevice, err);
-    if (!mine) return closeFromLoop(err);
-    uint32_t* flag = reinterpret_cast<uint32_t*>(arenaBase) + (op.seq % kFlagSlots);
-    if (launch)
-      kernels::launchPush(plan, stream, ctas, flag, flagValueFor(op.seq), mine->pushCounter(op.seq), statusWord(),
-                          kernels::WaitBefore(), doneSlotFor(op.seq));
-    if (!others.empty() && !aside) {
-      CudaEvent ev(op.srcDevice);
-      ev.record(stream);
-      for (cudaStream_t s : others) ev.wait(s, op.srcDevice);
-    }
-    noteLaunch(op.seq, launch);
+  } catch (const std::exception& ex) {
+    return closeFromLoop(TPB_CREATE_ERROR(CudaError, ex.what()));
   }
+  op.sent.reset();
   TPB_VLOG(6) << "Channel " << id_ << " launched the push of batch #" << op.seq << " (" << plan.entries.size()
-              << " entries, " << plan.totalBytesOut << " bytes)";
+              << " entries, " << plan.totalBytesOut << " bytes" << (aside ? ", from the channel's own stream" : "") << ")";
   writePacket(l);
-  if (aside) finishSendWhenPushed(op, asideEvent);
-  else finishSend(op, Error::kSuccess);
+  finishSend(op, Error::kSuccess);
 }
 
 cudaStream_t ChannelImpl::asideStreamFor(int device) {
@@ -1530,29 +1583,6 @@ cudaStream_t ChannelImpl::asideStreamFor(int device) {
   TPB_CUDA_CHECK(cudaStreamCreateWithPriority(&s, cudaStreamNonBlocking, greatest));
   asideStreams_[device] = s;
   return s;
-}
-
-// The batch was pushed from the channel's own stream: its callbacks fire when the push is over
-// (completion word between processes, event within one), not now.
-void ChannelImpl::finishSendWhenPushed(SendOp& op, CudaEvent* sameProcessEvent) {
-  op.launched = true;
-  auto items = std::make_shared<std::vector<SendItem>>(std::move(op.items));
-  auto self = shared_from_this();
-  ++asidePending_;
-  auto done = [self, items]() {
-    --self->asidePending_;
-    self->deviceFailed();
-    const Error e = self->error_ && !self->peerLeft_ ? self->error_ : Error::kSuccess;
-    for (auto& it : *items) it.callback(e);
-    if (self->error_ && !self->finished_) self->sendByeWhenIdle();
-  };
-  if (sameProcessEvent) {
-    cudaEvent_t raw = sameProcessEvent->raw();
-    ctx_->poller_.watch([raw]() { return cudaEventQuery(raw) != cudaErrorNotReady; },
-                        [self, done]() { self->ctx_->loop_.deferToLoop(done); });
-  } else {
-    whenPushFinishes(op.seq, done);
-  }
 }
 
 void ChannelImpl::finishSend(SendOp& op, const Error& e) {
@@ -2049,7 +2079,6 @@ void ChannelImpl::sendByeWhenIdle() {
   if (byeSent_ || finished_) return;
   auto self = shared_from_this();
   if (sameProcess_) {
-    if (asidePending_ > 0) return;  // the last of them calls back here
     // The newest event stands for every push before it: they ran on streams the user ordered.
     if (!lastPushEvent_ || cudaEventQuery(lastPushEvent_->raw()) != cudaErrorNotReady) return sendBye();
     cudaEvent_t raw = lastPushEvent_->raw();
@@ -2113,7 +2142,7 @@ Options applyEnvironment(Options o) {
   num("TPB_CUDA_P2P_CLOSE_TIMEOUT_MS", o.closeTimeoutMs);
   num("TPB_CUDA_P2P_HOST_COPY_MIN_BYTES", o.hostCopyMinBytes);
   num("TPB_CUDA_P2P_HOST_PIECE_BYTES", o.hostPieceBytes);
-  num("TPB_CUDA_P2P_ASIDE_MIN_BYTES", o.asideMinBytes);
+  num("TPB_CUDA_P2P_SEND_ORDER_MIN_BYTES", o.sendOrderMinBytes);
   unsigned long long ms = o.waitTimeoutNs / 1'000'000ull;
   num("TPB_CUDA_P2P_WAIT_TIMEOUT_MS", ms);
   o.waitTimeoutNs = ms * 1'000'000ull;

@@ -45,7 +45,16 @@ constexpr uint64_t kRingBytes = 2u << 20;        // per connection and direction
 // A frame larger than this moves through the ring in pieces of this size: the writer publishes
 // (and pokes the reader) after every piece and the reader frees after every piece, so that the
 // two memcpys of a large frame overlap instead of taking turns with a whole ring at a time.
-constexpr uint64_t kPieceBytes = 256u << 10;
+constexpr uint64_t kDefaultPieceBytes = 256u << 10;
+// TPB_SHM_PIECE_BYTES overrides it (4 KiB to the whole ring), for tuning on a given CPU.
+uint64_t pieceBytes() {
+  static const uint64_t value = [] {
+    const char* s = std::getenv("TPB_SHM_PIECE_BYTES");
+    const uint64_t v = s ? std::strtoull(s, nullptr, 10) : 0;
+    return v == 0 ? kDefaultPieceBytes : std::min<uint64_t>(std::max<uint64_t>(v, 4096), kRingBytes);
+  }();
+  return value;
+}
 constexpr uint32_t kReactorSlots = 1u << 16;     // tokens that can be queued at once
 constexpr uint64_t kReactorMagic = 0x7470625f72656163ull;
 
@@ -543,7 +552,7 @@ void ConnectionImpl::processReads() {
     if (op.bodyRead < op.frameLen) {
       bool more = true;
       while (more && op.bodyRead < op.frameLen) {
-        const uint64_t want = std::min<uint64_t>(op.frameLen - op.bodyRead, kPieceBytes);
+        const uint64_t want = std::min<uint64_t>(op.frameLen - op.bodyRead, pieceBytes());
         const uint64_t n = inbox_.read(op.ptr + op.bodyRead, want);
         op.bodyRead += n;
         more = n == want;
@@ -580,7 +589,7 @@ void ConnectionImpl::processWrites() {
         produced = true;
       }
       if (op.bodyWritten < op.length) {
-        const uint64_t want = std::min<uint64_t>(op.length - op.bodyWritten, kPieceBytes);
+        const uint64_t want = std::min<uint64_t>(op.length - op.bodyWritten, pieceBytes());
         const uint64_t n = outbox_.write(op.ptr + op.bodyWritten, want);
         op.bodyWritten += n;
         if (op.bodyWritten < op.length) {

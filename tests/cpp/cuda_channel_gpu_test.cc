@@ -235,16 +235,19 @@ TPB_GPU_TEST(CudaChannel, P2pTwoProcesses, 1) { basicCases(true, p2p(), 0, 0); }
 TPB_GPU_TEST(CudaChannel, P2pAcrossDevices, 2) { basicCases(true, p2p(), 0, 1); }
 TPB_GPU_TEST(CudaChannel, P2pReverseAcrossDevices, 2) { basicCases(true, p2p(), 1, 0); }
 TPB_GPU_TEST(CudaChannel, P2pSameProcessAcrossDevices, 2) { basicCases(false, p2p(), 0, 1); }
-// Large batches pushed from the channel's own stream (Options::asideMinBytes): same results, and
-// the send callback, which then stands for "the push is over", still comes.
-static PeerSetup p2pAside() {
+// Batches that take their place in the sender's stream at send() time and leave from the channel's
+// own stream (Options::sendOrderMinBytes): from 1 MiB on, and never (every push on the sender's
+// stream). The default, 8 MiB, is what the cases above ran with.
+static PeerSetup p2pSendOrder(size_t minBytes) {
   channel::cuda_p2p::Options o;
-  o.asideMinBytes = 1u << 20;
+  o.sendOrderMinBytes = minBytes;
   return p2p(o);
 }
-TPB_GPU_TEST(CudaChannel, P2pAsideStreamSameProcess, 1) { basicCases(false, p2pAside(), 0, 0); }
-TPB_GPU_TEST(CudaChannel, P2pAsideStreamTwoProcesses, 1) { basicCases(true, p2pAside(), 0, 0); }
-TPB_GPU_TEST(CudaChannel, P2pAsideStreamAcrossDevices, 2) { basicCases(true, p2pAside(), 0, 1); }
+TPB_GPU_TEST(CudaChannel, P2pSendOrderSameProcess, 1) { basicCases(false, p2pSendOrder(1u << 20), 0, 0); }
+TPB_GPU_TEST(CudaChannel, P2pSendOrderTwoProcesses, 1) { basicCases(true, p2pSendOrder(1u << 20), 0, 0); }
+TPB_GPU_TEST(CudaChannel, P2pSendOrderAcrossDevices, 2) { basicCases(true, p2pSendOrder(1u << 20), 0, 1); }
+TPB_GPU_TEST(CudaChannel, P2pLaunchOrderTwoProcesses, 1) { basicCases(true, p2pSendOrder(0), 0, 0); }
+TPB_GPU_TEST(CudaChannel, P2pLaunchOrderAcrossDevices, 2) { basicCases(true, p2pSendOrder(0), 0, 1); }
 TPB_GPU_TEST(CudaChannel, GdrOverASoftwareFabric, 1) { basicCases(false, gdr(), 0, 0); }
 TPB_GPU_TEST(CudaChannel, GdrOverASoftwareFabricAcrossDevices, 2) { basicCases(false, gdr(), 0, 1); }
 TPB_GPU_TEST(CudaChannel, BasicSameProcess, 1) { basicCases(false, cudaBasic(), 0, 0); }

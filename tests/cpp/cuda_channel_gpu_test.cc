@@ -248,6 +248,47 @@ TPB_GPU_TEST(CudaChannel, P2pSendOrderTwoProcesses, 1) { basicCases(true, p2pSen
 TPB_GPU_TEST(CudaChannel, P2pSendOrderAcrossDevices, 2) { basicCases(true, p2pSendOrder(1u << 20), 0, 1); }
 TPB_GPU_TEST(CudaChannel, P2pLaunchOrderTwoProcesses, 1) { basicCases(true, p2pSendOrder(0), 0, 0); }
 TPB_GPU_TEST(CudaChannel, P2pLaunchOrderAcrossDevices, 2) { basicCases(true, p2pSendOrder(0), 0, 1); }
+// A large batch keeps the place in the sender's stream that it had when sendBatch() was called:
+// 300 ms of other work queued on that stream right after the call, and long before the receiver
+// names its buffers, does not stand between the receiver and its data.
+static void laterWorkDoesNotDelayALargeSend(bool processes) {
+  constexpr size_t kBytes = 16u << 20;
+  constexpr uint32_t kBusyUs = 300000;
+  runPair(
+      processes, p2p(), p2p(),
+      [=](channel::Channel& ch) {
+        DeviceTensor t(0, kBytes);
+        std::this_thread::sleep_for(std::chrono::milliseconds(60));  // the sender has queued its busy kernel by now
+        const auto t0 = std::chrono::steady_clock::now();
+        expectOk(recvOne(ch, t, 0), "recv");
+        CK(cudaStreamSynchronize(t.stream));
+        const double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+        EXPECT_EQ(t.mismatches(5150), uint64_t(0));
+        if (ms > kBusyUs / 1000.0 / 2) throw TestFailure("the data took " + std::to_string(ms) + " ms: it waited for work queued after the send");
+      },
+      [=](channel::Channel& ch) {
+        DeviceTensor t(0, kBytes);
+        DeviceTensor scratch(0, 4096);
+        t.fill(5150);
+        std::promise<Error> sent;
+        channel::SendItem it;
+        it.buffer = t.buffer();
+        it.length = t.bytes;
+        it.targetDevice = Device(kCudaDeviceType, 0);
+        it.callback = [&](const Error& e) { sent.set_value(e); };
+        std::vector<channel::SendItem> v;
+        v.push_back(std::move(it));
+        ch.sendBatch(std::move(v));
+        CK(cudaSetDevice(0));
+        kernels::launchDelay(t.stream, scratch.data(), scratch.bytes, kBusyUs);
+        auto f = sent.get_future();
+        expectOk(waitFor(f, 30), "send");
+        CK(cudaStreamSynchronize(t.stream));
+      });
+}
+TPB_GPU_TEST(CudaChannel, P2pLaterWorkDoesNotDelayALargeSendSameProcess, 1) { laterWorkDoesNotDelayALargeSend(false); }
+TPB_GPU_TEST(CudaChannel, P2pLaterWorkDoesNotDelayALargeSendTwoProcesses, 1) { laterWorkDoesNotDelayALargeSend(true); }
+
 TPB_GPU_TEST(CudaChannel, GdrOverASoftwareFabric, 1) { basicCases(false, gdr(), 0, 0); }
 TPB_GPU_TEST(CudaChannel, GdrOverASoftwareFabricAcrossDevices, 2) { basicCases(false, gdr(), 0, 1); }
 TPB_GPU_TEST(CudaChannel, BasicSameProcess, 1) { basicCases(false, cudaBasic(), 0, 0); }

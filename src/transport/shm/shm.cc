@@ -55,6 +55,14 @@ uint64_t pieceBytes() {
   }();
   return value;
 }
+// TPB_SHM_DIRECT_WRITE_MAX_BYTES: the largest frame that write() copies on the caller's thread.
+uint64_t directWriteMaxBytes() {
+  static const uint64_t value = [] {
+    const char* s = std::getenv("TPB_SHM_DIRECT_WRITE_MAX_BYTES");
+    return s ? std::strtoull(s, nullptr, 10) : uint64_t(64u << 10);
+  }();
+  return value;
+}
 constexpr uint32_t kReactorSlots = 1u << 16;     // tokens that can be queued at once
 constexpr uint64_t kReactorMagic = 0x7470625f72656163ull;
 
@@ -349,9 +357,13 @@ class ConnectionImpl final : public FdHandler, public std::enable_shared_from_th
     {
       // Short cut: when nothing is queued ahead and the whole frame fits, the caller's own thread
       // copies it into the peer's inbox and pokes the peer; only the completion goes through the
-      // reactor thread. This takes one thread hand-off out of every control message.
+      // reactor thread. This takes one thread hand-off out of every control message. Frames above
+      // 64 KiB go to the reactor thread, which moves them in pieces so that the reader's copy
+      // overlaps the writer's: there the hand-off costs nothing beside the copy, and a frame
+      // written here in one go would keep the reader waiting until its last byte is in.
       std::unique_lock<std::mutex> lock(outboxMutex_);
-      if (directWrites_ && queuedWrites_ == 0 && outbox_.freeBytes() >= sizeof(uint32_t) + op.length) {
+      if (directWrites_ && queuedWrites_ == 0 && op.length <= directWriteMaxBytes() &&
+          outbox_.freeBytes() >= sizeof(uint32_t) + op.length) {
         outbox_.write(&op.length, sizeof(uint32_t));
         if (op.length) outbox_.write(op.ptr, op.length);
         pokePeer(peerInboxToken_);

@@ -258,6 +258,11 @@ static void laterWorkDoesNotDelayALargeSend(bool processes) {
       processes, p2p(), p2p(),
       [=](channel::Channel& ch) {
         DeviceTensor t(0, kBytes);
+        // Once without anything in the way: kernels are loaded, streams made and mappings opened
+        // on first use, and some of that waits for the device to fall idle.
+        expectOk(recvOne(ch, t, 0), "first recv");
+        CK(cudaStreamSynchronize(t.stream));
+        EXPECT_EQ(t.mismatches(5149), uint64_t(0));
         std::this_thread::sleep_for(std::chrono::milliseconds(60));  // the sender has queued its busy kernel by now
         const auto t0 = std::chrono::steady_clock::now();
         expectOk(recvOne(ch, t, 0), "recv");
@@ -269,6 +274,11 @@ static void laterWorkDoesNotDelayALargeSend(bool processes) {
       [=](channel::Channel& ch) {
         DeviceTensor t(0, kBytes);
         DeviceTensor scratch(0, 4096);
+        CK(cudaSetDevice(0));
+        kernels::launchDelay(t.stream, scratch.data(), scratch.bytes, 10);
+        t.fill(5149);
+        expectOk(sendOne(ch, t, 0), "first send");
+        CK(cudaStreamSynchronize(t.stream));
         t.fill(5150);
         std::promise<Error> sent;
         channel::SendItem it;

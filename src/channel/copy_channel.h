@@ -7,11 +7,17 @@
 // Protocol on the channel's connection (both directions share it): the sender writes
 // Descriptor{pid, ptr}; the receiver, once its matching recv() exists, queues the copy on the
 // context's copy thread, fires its callback and writes Done{}; the sender's callback fires when
-// Done arrives. Sends and receives are matched in order, so no sequence numbers travel.
+// Done arrives. Sends and receives are matched in order, so no sequence numbers travel; the
+// copies themselves may finish in any order (several worker threads, large tensors cut into
+// slices that run side by side: one core copies 10-13 GB/s, the memory system several times
+// that), so a receiver holds each Done back until the copies before it are through.
 #pragma once
 
+#include <atomic>
+#include <cstdlib>
 #include <deque>
 #include <mutex>
+#include <optional>
 #include <set>
 #include <thread>
 #include <variant>
@@ -59,6 +65,11 @@ class ChannelImpl final : public Channel, public std::enable_shared_from_this<Ch
  private:
   void armRead();
   void matchRecvs();
+  void onCopyDone(uint64_t seq, const Error& e);
+  struct RunningCopy {
+    TRecvCallback cb;
+    std::optional<Error> result;  // set when the copy is through
+  };
   struct PendingRecv {
     void* ptr;
     size_t length;
@@ -70,24 +81,22 @@ class ChannelImpl final : public Channel, public std::enable_shared_from_this<Ch
   std::deque<TSendCallback> sendsAwaitingDone_;
   std::deque<PendingRecv> recvs_;
   std::deque<DescriptorMsg> descriptors_;
-  size_t copiesInFlight_ = 0;
+  // Copies handed to the workers, oldest first; firstCopySeq_ is the sequence number of the front.
+  std::deque<RunningCopy> copies_;
+  uint64_t firstCopySeq_ = 0;
 };
 
 class ContextImpl final : public Context, public std::enable_shared_from_this<ContextImpl> {
  public:
   ContextImpl(std::string descriptor, CopyFn fn, const char* threadName)
-      : copyFn_(fn) {
+      : copyFn_(fn), threadName_(threadName) {
     descriptors_[Device(kCpuDeviceType, 0)] = std::move(descriptor);
-    thread_ = std::thread([this, threadName]() {
-      setThreadName(threadName);
-      // The copy thread sleeps in pop(); an empty function is the request to stop, queued behind
-      // whatever copies were requested before it.
-      for (;;) {
-        std::function<void()> job = jobs_.pop();
-        if (!job) return;
-        job();
-      }
-    });
+    // TPB_COPY_THREADS: how many threads copy at once (default: half of the cores, at most 4).
+    // One starts now; the others when the first tensor large enough to be sliced comes by.
+    const char* env = std::getenv("TPB_COPY_THREADS");
+    const unsigned cores = std::max(1u, std::thread::hardware_concurrency());
+    maxThreads_ = env ? std::max<long>(1, std::strtol(env, nullptr, 10)) : std::min<size_t>(4, std::max(1u, cores / 2));
+    startWorker();
   }
   ~ContextImpl() override { stopThread(); }
   bool isViable() const override { return true; }
@@ -117,27 +126,83 @@ class ContextImpl final : public Context, public std::enable_shared_from_this<Co
     loop_.runInLoop([]() {});
   }
   void stopThread() {
-    if (!stopRequested_.exchange(true)) jobs_.push(nullptr);
-    if (thread_.joinable()) thread_.join();
+    std::vector<std::thread> threads;
+    {
+      std::lock_guard<std::mutex> lock(threadsMutex_);
+      if (stopRequested_.exchange(true)) return;
+      threads = std::move(threads_);
+      threads_.clear();
+    }
+    // An empty function is the request to stop, one per worker, queued behind whatever copies
+    // were requested before.
+    for (size_t i = 0; i < threads.size(); ++i) jobs_.push(nullptr);
+    for (auto& t : threads) t.join();
   }
-  // The copy runs on the copy thread; `done` is then deferred to the loop.
+  // The copy runs on the worker threads, cut into slices when it is large; `done` is deferred to
+  // the loop when the last slice is through and gets the first error, if there was one.
   void requestCopy(uint64_t pid, const void* remote, void* local, size_t len, std::function<void(const Error&)> done) {
     auto self = shared_from_this();
-    jobs_.push([self, pid, remote, local, len, done = std::move(done)]() {
-      Error e = self->copyFn_(pid, remote, local, len);
-      self->loop_.deferToLoop([done, e]() { done(e); });
-    });
+    size_t slices = std::min<size_t>(maxThreads_, len / kSliceMinBytes);
+    if (slices < 2) slices = 1;
+    for (size_t i = 1; i < slices; ++i) startWorker();
+    struct Whole {
+      std::atomic<size_t> left;
+      std::mutex mutex;
+      Error firstError;
+      std::function<void(const Error&)> done;
+    };
+    auto whole = std::make_shared<Whole>();
+    whole->left = slices;
+    whole->done = std::move(done);
+    const size_t per = ((len + slices - 1) / slices + 4095) & ~size_t(4095);
+    for (size_t i = 0; i < slices; ++i) {
+      const size_t begin = std::min(len, i * per), end = std::min(len, begin + per);
+      jobs_.push([self, whole, pid, remote, local, begin, end]() {
+        Error e = begin < end ? self->copyFn_(pid, static_cast<const uint8_t*>(remote) + begin,
+                                              static_cast<uint8_t*>(local) + begin, end - begin)
+                              : Error::kSuccess;
+        if (e) {
+          std::lock_guard<std::mutex> lock(whole->mutex);
+          if (!whole->firstError) whole->firstError = e;
+        }
+        if (whole->left.fetch_sub(1) == 1) {
+          Error result;
+          {
+            std::lock_guard<std::mutex> lock(whole->mutex);
+            result = whole->firstError;
+          }
+          self->loop_.deferToLoop([whole, result]() { whole->done(result); });
+        }
+      });
+    }
   }
   OnDemandLoop loop_;
   bool closed_ = false;
   std::set<std::weak_ptr<ChannelImpl>, std::owner_less<std::weak_ptr<ChannelImpl>>> channels_;
 
  private:
+  static constexpr size_t kSliceMinBytes = 512u << 10;
+  void startWorker() {
+    std::lock_guard<std::mutex> lock(threadsMutex_);
+    if (stopRequested_ || threads_.size() >= maxThreads_) return;
+    threads_.emplace_back([this]() {
+      setThreadName(threadName_);
+      // A worker sleeps in pop(); an empty function tells it to stop.
+      for (;;) {
+        std::function<void()> job = jobs_.pop();
+        if (!job) return;
+        job();
+      }
+    });
+  }
   CopyFn copyFn_;
+  const char* threadName_;
+  size_t maxThreads_ = 1;
   std::unordered_map<Device, std::string> descriptors_;
-  std::thread thread_;
-  // Copies wait here for the copy thread. The bound only matters to a caller that queues
-  // thousands of tensors without waiting for any: it then blocks until the thread catches up.
+  std::mutex threadsMutex_;
+  std::vector<std::thread> threads_;
+  // Copies wait here for the workers. The bound only matters to a caller that queues thousands
+  // of tensors without waiting for any: it then blocks until the workers catch up.
   Queue<std::function<void()>> jobs_{4096};
   std::atomic<bool> stopRequested_{false};
   std::atomic<bool> joined_{false};
@@ -180,21 +245,37 @@ inline void ChannelImpl::matchRecvs() {
     recvs_.pop_front();
     DescriptorMsg d = descriptors_.front();
     descriptors_.pop_front();
-    ++copiesInFlight_;
+    const uint64_t seq = firstCopySeq_ + copies_.size();
+    copies_.push_back({std::move(r.cb), std::nullopt});
     ctx_->requestCopy(d.pid, reinterpret_cast<const void*>(d.ptr), r.ptr, r.length,
-                      [self, cb = std::move(r.cb)](const Error& e) {
-                        --self->copiesInFlight_;
-                        if (e) {
-                          cb(e);
-                          return self->closeFromLoop(e);
-                        }
-                        if (self->error_) return cb(self->error_);
-                        cb(Error::kSuccess);
-                        Packet done = DoneMsg{};
-                        transport::writeNop(*self->conn_, done, [self](const Error& we) {
-                          if (we) self->ctx_->loop_.deferToLoop([self, we]() { self->closeFromLoop(we); });
-                        });
-                      });
+                      [self, seq](const Error& e) { self->onCopyDone(seq, e); });
+  }
+}
+
+// Copies may finish out of order; the peer matches Done frames to its sends by counting, so they
+// (and the callbacks) go out in the order of the receives.
+inline void ChannelImpl::onCopyDone(uint64_t seq, const Error& e) {
+  if (seq < firstCopySeq_ || seq - firstCopySeq_ >= copies_.size()) return;
+  copies_[seq - firstCopySeq_].result = e;
+  auto self = shared_from_this();
+  while (!copies_.empty() && copies_.front().result) {
+    RunningCopy c = std::move(copies_.front());
+    copies_.pop_front();
+    ++firstCopySeq_;
+    if (*c.result) {
+      c.cb(*c.result);
+      closeFromLoop(*c.result);
+      continue;
+    }
+    if (error_) {
+      c.cb(error_);
+      continue;
+    }
+    c.cb(Error::kSuccess);
+    Packet done = DoneMsg{};
+    transport::writeNop(*conn_, done, [self](const Error& we) {
+      if (we) self->ctx_->loop_.deferToLoop([self, we]() { self->closeFromLoop(we); });
+    });
   }
 }
 

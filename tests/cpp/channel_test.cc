@@ -4,6 +4,7 @@
 // them to createChannel on both sides, and exchange tensors.
 #include <tpb/tpb.h>
 
+#include <mutex>
 #include <random>
 
 #include "channel_wiring.h"
@@ -187,6 +188,63 @@ TPB_TEST(Channel, SendMultipleTensorsKeepsOrder) {
             auto f = done[i].get_future();
             EXPECT_FALSE(bool(waitFor(f)));
           }
+        });
+  });
+}
+
+// Large tensors (sliced over several copy threads where the channel has them) between small ones:
+// the bytes are right and the callbacks on both sides come in the order of the calls, although
+// the small copies finish long before the large ones ahead of them.
+TPB_TEST(Channel, LargeAndSmallTensorsCompleteInOrder) {
+  forEachBackend([](const Backend& b) {
+    const std::vector<size_t> sizes = {6u << 20, 100, (3u << 20) + 17, 4096, 5u << 20, 1, (1u << 20) + 1, 64};
+    const int n = static_cast<int>(sizes.size());
+    runChannel(
+        b,
+        [&](channel::Channel& ch) {
+          std::vector<std::vector<uint8_t>> got(n);
+          std::vector<std::promise<Error>> done(n);
+          std::mutex mu;
+          std::vector<int> order;
+          for (int i = 0; i < n; ++i) {
+            got[i].resize(sizes[i]);
+            ch.recv(CpuBuffer{got[i].data()}, got[i].size(), [&, i](const Error& e) {
+              {
+                std::lock_guard<std::mutex> lock(mu);
+                order.push_back(i);
+              }
+              done[i].set_value(e);
+            });
+          }
+          for (int i = 0; i < n; ++i) {
+            auto f = done[i].get_future();
+            EXPECT_FALSE(bool(waitFor(f)));
+            EXPECT_TRUE(got[i] == pattern(sizes[i], 900 + i));
+          }
+          std::lock_guard<std::mutex> lock(mu);
+          for (int i = 0; i < n; ++i) EXPECT_EQ(order[i], i);
+        },
+        [&](channel::Channel& ch) {
+          std::vector<std::vector<uint8_t>> data(n);
+          std::vector<std::promise<Error>> done(n);
+          std::mutex mu;
+          std::vector<int> order;
+          for (int i = 0; i < n; ++i) {
+            data[i] = pattern(sizes[i], 900 + i);
+            ch.send(CpuBuffer{data[i].data()}, data[i].size(), [&, i](const Error& e) {
+              {
+                std::lock_guard<std::mutex> lock(mu);
+                order.push_back(i);
+              }
+              done[i].set_value(e);
+            });
+          }
+          for (int i = 0; i < n; ++i) {
+            auto f = done[i].get_future();
+            EXPECT_FALSE(bool(waitFor(f)));
+          }
+          std::lock_guard<std::mutex> lock(mu);
+          for (int i = 0; i < n; ++i) EXPECT_EQ(order[i], i);
         });
   });
 }

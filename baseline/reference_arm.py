@@ -181,8 +181,9 @@ def main(args, metric):
         if not args.no_sweep:
             size = 4096
             while size <= args.max_sweep_bytes:
-                iters = 100 if size <= (64 << 20) else 20
-                h.command(f"stream {size} 10 {args.depth}")
+                # The same counts as the native arm: a thousand small messages per measurement.
+                iters = 1000 if size <= (1 << 20) else (100 if size <= (64 << 20) else 20)
+                h.command(f"stream {size} {max(10, iters // 10)} {args.depth}")
                 barrier()
                 t = max_over_ranks(float(h.command(f"stream {size} {iters} {args.depth}")[0])) / iters
                 barrier()

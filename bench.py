@@ -340,8 +340,10 @@ def run_native(args):
         out = []
         size = 4096
         while size <= args.max_sweep_bytes:
-            iters = 100 if size <= (64 << 20) else 20
-            rb.run_stream(size, 10, args.depth, False)
+            # Small messages take microseconds each: a thousand of them, so that one measurement
+            # lasts long enough (10 ms) for the host's scheduling noise to average out.
+            iters = 1000 if size <= (1 << 20) else (100 if size <= (64 << 20) else 20)
+            rb.run_stream(size, max(10, iters // 10), args.depth, False)
             barrier()
             r = rb.run_stream(size, iters, args.depth, False)
             barrier()

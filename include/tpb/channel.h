@@ -152,7 +152,8 @@ struct Options {
                                           // of a pipeline) therefore neither delays the push nor is delayed
                                           // by it. The send callback fires as for any other batch. Smaller
                                           // batches are launched on the sender's stream itself, where the
-                                          // four extra driver calls would show. 0: never
+                                          // four extra driver calls would show, and so is a batch that
+                                          // stays on its GPU within one process (a local copy). 0: never
   // Host-side fault injection for tests: the N-th push of a channel (counting from 0) is announced
   // to the receiver but not launched, so that the receiver's bounded wait runs out. -1: never.
   int faultSkipLaunch = -1;

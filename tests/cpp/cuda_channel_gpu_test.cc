@@ -251,53 +251,57 @@ TPB_GPU_TEST(CudaChannel, P2pLaunchOrderAcrossDevices, 2) { basicCases(true, p2p
 // A large batch keeps the place in the sender's stream that it had when sendBatch() was called:
 // 300 ms of other work queued on that stream right after the call, and long before the receiver
 // names its buffers, does not stand between the receiver and its data.
-static void laterWorkDoesNotDelayALargeSend(bool processes) {
+static void laterWorkDoesNotDelayALargeSend(bool processes, int serverDevice, int clientDevice) {
   constexpr size_t kBytes = 16u << 20;
   constexpr uint32_t kBusyUs = 300000;
   runPair(
       processes, p2p(), p2p(),
       [=](channel::Channel& ch) {
-        DeviceTensor t(0, kBytes);
+        DeviceTensor t(serverDevice, kBytes);
         // Once without anything in the way: kernels are loaded, streams made and mappings opened
         // on first use, and some of that waits for the device to fall idle.
-        expectOk(recvOne(ch, t, 0), "first recv");
+        expectOk(recvOne(ch, t, clientDevice), "first recv");
         CK(cudaStreamSynchronize(t.stream));
         EXPECT_EQ(t.mismatches(5149), uint64_t(0));
         std::this_thread::sleep_for(std::chrono::milliseconds(60));  // the sender has queued its busy kernel by now
         const auto t0 = std::chrono::steady_clock::now();
-        expectOk(recvOne(ch, t, 0), "recv");
+        expectOk(recvOne(ch, t, clientDevice), "recv");
         CK(cudaStreamSynchronize(t.stream));
         const double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
         EXPECT_EQ(t.mismatches(5150), uint64_t(0));
         if (ms > kBusyUs / 1000.0 / 2) throw TestFailure("the data took " + std::to_string(ms) + " ms: it waited for work queued after the send");
       },
       [=](channel::Channel& ch) {
-        DeviceTensor t(0, kBytes);
-        DeviceTensor scratch(0, 4096);
-        CK(cudaSetDevice(0));
+        DeviceTensor t(clientDevice, kBytes);
+        DeviceTensor scratch(clientDevice, 4096);
+        CK(cudaSetDevice(clientDevice));
         kernels::launchDelay(t.stream, scratch.data(), scratch.bytes, 10);
         t.fill(5149);
-        expectOk(sendOne(ch, t, 0), "first send");
+        expectOk(sendOne(ch, t, serverDevice), "first send");
         CK(cudaStreamSynchronize(t.stream));
         t.fill(5150);
         std::promise<Error> sent;
         channel::SendItem it;
         it.buffer = t.buffer();
         it.length = t.bytes;
-        it.targetDevice = Device(kCudaDeviceType, 0);
+        it.targetDevice = Device(kCudaDeviceType, serverDevice);
         it.callback = [&](const Error& e) { sent.set_value(e); };
         std::vector<channel::SendItem> v;
         v.push_back(std::move(it));
         ch.sendBatch(std::move(v));
-        CK(cudaSetDevice(0));
+        CK(cudaSetDevice(clientDevice));
         kernels::launchDelay(t.stream, scratch.data(), scratch.bytes, kBusyUs);
         auto f = sent.get_future();
         expectOk(waitFor(f, 30), "send");
         CK(cudaStreamSynchronize(t.stream));
       });
 }
-TPB_GPU_TEST(CudaChannel, P2pLaterWorkDoesNotDelayALargeSendSameProcess, 1) { laterWorkDoesNotDelayALargeSend(false); }
-TPB_GPU_TEST(CudaChannel, P2pLaterWorkDoesNotDelayALargeSendTwoProcesses, 1) { laterWorkDoesNotDelayALargeSend(true); }
+// (Within one process and one GPU a batch is launched on the sender's stream whatever its size.)
+TPB_GPU_TEST(CudaChannel, P2pLaterWorkDoesNotDelayALargeSendTwoProcesses, 1) { laterWorkDoesNotDelayALargeSend(true, 0, 0); }
+TPB_GPU_TEST(CudaChannel, P2pLaterWorkDoesNotDelayALargeSendAcrossDevices, 2) { laterWorkDoesNotDelayALargeSend(true, 0, 1); }
+TPB_GPU_TEST(CudaChannel, P2pLaterWorkDoesNotDelayALargeSendSameProcessAcrossDevices, 2) {
+  laterWorkDoesNotDelayALargeSend(false, 0, 1);
+}
 
 TPB_GPU_TEST(CudaChannel, GdrOverASoftwareFabric, 1) { basicCases(false, gdr(), 0, 0); }
 TPB_GPU_TEST(CudaChannel, GdrOverASoftwareFabricAcrossDevices, 2) { basicCases(false, gdr(), 0, 1); }

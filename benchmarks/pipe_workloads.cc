@@ -4,7 +4,7 @@
 // are measured by literally the same benchmark code (the reference's own benchmark_pipe plays this
 // role upstream: tensorpipe/benchmark/benchmark_pipe.cc:173-740).
 //
-//   --workload cpu_pingpong  --transport uv|shm  --channel basic|cma  [--iters 1000]
+//   --workload cpu_pingpong  --transport uv|shm  --channel basic|cma|mpt  [--iters 1000]
 //       two forked processes; every message = 64 KiB payload + four fp32 CPU tensors of shapes
 //       [1024], [256,256], [64,64,64], [1<<20]; the server echoes; the client verifies every byte
 //       and that callbacks arrive in order; prints p50 / p99 round-trip latency.
@@ -117,6 +117,18 @@ static std::shared_ptr<lib::Context> makeCpuContext(const Options& o, const std:
   if (o.transport == "shm") ctx->registerTransport(10, "shm", lib::transport::shm::create());
   ctx->registerChannel(0, "basic", lib::channel::basic::create());
   if (o.channel == "cma") ctx->registerChannel(10, "cma", lib::channel::cma::create());
+  if (o.channel == "mpt") {
+    // Four lanes, each a TCP transport context (and thread) of its own, as PyTorch's agent sets
+    // its "mpt_uv" channel up with more.
+    std::vector<std::shared_ptr<lib::transport::Context>> contexts;
+    std::vector<std::shared_ptr<lib::transport::Listener>> listeners;
+    for (int lane = 0; lane < 4; ++lane) {
+      auto c = lib::transport::uv::create();
+      listeners.push_back(c->listen("127.0.0.1"));
+      contexts.push_back(std::move(c));
+    }
+    ctx->registerChannel(10, "mpt", lib::channel::mpt::create(std::move(contexts), std::move(listeners)));
+  }
   return ctx;
 }
 

@@ -261,5 +261,28 @@ int main(int argc, char** argv) {
     double ms = timer.run(20, 200, [&] { CK(cudaMemcpyAsync(dst, src, 4096, cudaMemcpyDeviceToDevice, nullptr)); });
     report("4 KiB, cudaMemcpyAsync D2D", 4096, ms);
   }
+  if (want("unpack")) {
+    // The receiving side of a small message whose data has already landed: the stand-alone wait
+    // kernel, and the unpack launch that looks at the flag itself before it copies 4 KiB and
+    // 64 KiB out of the inbox. The flag is set beforehand, so nothing here spins.
+    const uint32_t arrived = 7;
+    CK(cudaMemcpy(words + 32, &arrived, sizeof(arrived), cudaMemcpyHostToDevice));
+    double ms = timer.run(20, 200, [&] { launchWaitFlag(nullptr, words + 32, arrived, 1'000'000'000ull, words + 40); });
+    report("wait kernel, flag already set", 0, ms);
+    for (size_t n : {size_t(4096), size_t(65536)}) {
+      PushPlan plan;
+      CopyItem it;
+      it.src = src;
+      it.dst = dst;
+      it.srcBytes = n;
+      appendToPlan(plan, it, false);
+      WaitBefore w;
+      w.flag = words + 32;
+      w.value = arrived;
+      w.timeoutNs = 1'000'000'000ull;
+      ms = timer.run(20, 200, [&] { launchPush(plan, nullptr, sms, nullptr, 0, words + 16, words + 40, w); });
+      report(std::to_string(n >> 10) + " KiB unpack with the wait fused in", n, ms);
+    }
+  }
   return 0;
 }

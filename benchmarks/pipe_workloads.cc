@@ -8,6 +8,10 @@
 //       two forked processes; every message = 64 KiB payload + four fp32 CPU tensors of shapes
 //       [1024], [256,256], [64,64,64], [1<<20]; the server echoes; the client verifies every byte
 //       and that callbacks arrive in order; prints p50 / p99 round-trip latency.
+//   --workload cpu_small  --transport uv|shm  [--bytes 64]  [--iters 20000]
+//       the same two processes exchanging a message that is one payload of --bytes and nothing
+//       else (what the reference's benchmark_pipe does by default): the pipe's own cost per
+//       message (descriptor, payload, callbacks), no channel involved.
 //   --workload transport_pingpong  --transport uv|shm  [--bytes 64]  [--iters 20000]
 //       raw transport connections (no pipe): one frame each way per round trip, two forked
 //       processes; prints p50 / p99 round-trip latency (the reference's benchmark_transport,
@@ -281,6 +285,132 @@ static int cpuPingPong(const Options& o, Shared* sh) {
             << "\", \"channel\": \"" << o.channel << "\", \"round_trips\": " << o.iters << ", \"bytes_per_message\": "
             << bytes << ", \"rtt_p50_us\": " << sh->p50[0] << ", \"rtt_p99_us\": " << sh->p99[0]
             << ", \"rtt_mean_us\": " << sh->mean[0] << ", \"verified\": \"byte-exact, every round trip\"}" << std::endl;
+  return 0;
+}
+
+// ---- workload 1b: payload-only ping-pong (the default shape of the reference's benchmark_pipe) -----
+static int cpuSmallPingPong(const Options& o, Shared* sh) {
+  const int total = o.iters + o.warmup;
+  // Everything runs from the library's callbacks, as in the reference's benchmark_pipe
+  // (tensorpipe/benchmark/benchmark_pipe.cc:341-427): no thread of the benchmark stands between
+  // a message's arrival and the answer to it.
+  struct Side {
+    std::shared_ptr<lib::Pipe> pipe;
+    std::vector<uint8_t> out, in;
+    int left = 0;
+    bool client = false;
+    int warmup = 0;
+    Clock::time_point t0;
+    std::vector<double> rtt;
+    std::promise<void> finished;
+    bool mismatch = false;
+    void write() {
+      lib::Message m;
+      lib::Message::Payload p;
+      p.data = out.data();
+      p.length = out.size();
+      m.payloads.push_back(p);
+      pipe->write(std::move(m), [](const lib::Error& e) {
+        if (e) die("write: " + e.what());
+      });
+    }
+    void armRead() {
+      pipe->readDescriptor([this](const lib::Error& e, lib::Descriptor d) {
+        if (e) die("readDescriptor: " + e.what());
+        if (d.payloads.size() != 1 || d.payloads[0].length != in.size()) die("unexpected message shape");
+        lib::Allocation a;
+        a.payloads.push_back({in.data()});
+        pipe->read(std::move(a), [this](const lib::Error& e2) {
+          if (e2) die("read: " + e2.what());
+          arrived();
+        });
+      });
+    }
+    void arrived() {
+      if (client) {
+        const double us = std::chrono::duration<double, std::micro>(Clock::now() - t0).count();
+        if (static_cast<int>(rtt.size()) + left <= 0) return;
+        if (warmup > 0) --warmup;
+        else rtt.push_back(us);
+        mismatch = mismatch || in != out;
+        if (--left == 0) return finished.set_value();
+        out[0] = static_cast<uint8_t>(left);
+        t0 = Clock::now();
+        armRead();
+        write();
+      } else {
+        out = in;  // echo what came
+        if (--left > 0) armRead();
+        write();
+        if (left == 0) finished.set_value();
+      }
+    }
+  };
+  pid_t server = fork();
+  if (server == 0) {
+    auto ctx = makeCpuContext(o, "server");
+    std::vector<std::string> urls = {"uv://127.0.0.1"};
+    if (o.transport == "shm") urls.push_back("shm://");
+    auto listener = ctx->listen(urls);
+    std::strncpy(sh->url, listener->url("uv").c_str(), sizeof(sh->url) - 1);
+    sh->urlReady = 1;
+    std::promise<std::shared_ptr<lib::Pipe>> pp;
+    listener->accept([&](const lib::Error& e, std::shared_ptr<lib::Pipe> p) {
+      if (e) die("accept: " + e.what());
+      pp.set_value(p);
+    });
+    Side side;
+    side.pipe = pp.get_future().get();
+    side.out.resize(o.bytes);
+    side.in.resize(o.bytes);
+    side.left = total;
+    side.armRead();
+    side.finished.get_future().wait();
+    while (sh->clientsDone.load() == 0) std::this_thread::sleep_for(std::chrono::milliseconds(1));
+    ctx->join();
+    _exit(0);
+  }
+  pid_t client = fork();
+  if (client == 0) {
+    while (sh->urlReady.load() == 0) std::this_thread::sleep_for(std::chrono::milliseconds(1));
+    auto ctx = makeCpuContext(o, "client");
+    Side side;
+    side.pipe = ctx->connect(sh->url);
+    side.client = true;
+    side.warmup = o.warmup;
+    side.out.resize(o.bytes);
+    side.in.resize(o.bytes);
+    for (size_t k = 0; k < side.out.size(); ++k) side.out[k] = static_cast<uint8_t>(k * 31 + 7);
+    side.left = total;
+    side.t0 = Clock::now();
+    side.armRead();
+    side.write();
+    side.finished.get_future().wait();
+    if (side.mismatch) {
+      sh->failed = 1;
+      die("echo differs from what was sent");
+    }
+    sh->p50[0] = percentile(side.rtt, 0.5);
+    sh->p99[0] = percentile(side.rtt, 0.99);
+    double sum = 0;
+    for (double v : side.rtt) sum += v;
+    sh->mean[0] = sum / side.rtt.size();
+    sh->clientsDone = 1;
+    ctx->join();
+    _exit(0);
+  }
+  int s1 = 0, s2 = 0;
+  waitpid(client, &s2, 0);
+  sh->clientsDone = 1;
+  waitpid(server, &s1, 0);
+  if (!WIFEXITED(s1) || WEXITSTATUS(s1) || !WIFEXITED(s2) || WEXITSTATUS(s2) || sh->failed) {
+    std::cout << "{\"impl\": \"" << kImpl << "\", \"workload\": \"cpu_small\", \"error\": \"a peer failed\"}" << std::endl;
+    return 1;
+  }
+  std::cout << "{\"impl\": \"" << kImpl << "\", \"workload\": \"cpu_small\", \"transport\": \"" << o.transport
+            << "\", \"payload_bytes\": " << o.bytes << ", \"round_trips\": " << o.iters << ", \"rtt_p50_us\": "
+            << sh->p50[0] << ", \"rtt_p99_us\": " << sh->p99[0] << ", \"rtt_mean_us\": " << sh->mean[0]
+            << ", \"verified\": \"byte-exact, every round trip\"}" << std::endl;
   return 0;
 }
 
@@ -994,6 +1124,7 @@ int main(int argc, char** argv) {
   auto* sh = static_cast<Shared*>(mmap(nullptr, sizeof(Shared), PROT_READ | PROT_WRITE, MAP_SHARED | MAP_ANONYMOUS, -1, 0));
   std::memset(static_cast<void*>(sh), 0, sizeof(Shared));
   if (o.workload == "cpu_pingpong") return cpuPingPong(o, sh);
+  if (o.workload == "cpu_small") return cpuSmallPingPong(o, sh);
   if (o.workload == "rpc_fanin") return rpcFanIn(o, sh);
   if (o.workload == "transport_pingpong") return transportPingPong(o, sh);
   if (o.workload == "all_pairs") return allPairs(o, sh);

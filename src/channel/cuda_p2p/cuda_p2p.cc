@@ -996,18 +996,20 @@ std::shared_ptr<CudaEvent> ChannelImpl::markSendTime(const std::vector<SendItem>
   uint64_t bytes = 0;
   for (const SendItem& it : items) bytes += it.length;
   if (bytes < opts_.sendOrderMinBytes) return nullptr;
-  const void* stream = items[0].buffer.unwrap<CudaBuffer>().stream;
-  const int device = items[0].buffer.device().index;
-  bool leavesTheGpu = !sameProcessForCallers_.load(std::memory_order_relaxed);
-  for (const SendItem& it : items) {
-    if (it.buffer.unwrap<CudaBuffer>().stream != stream || it.buffer.device().index != device) return nullptr;
-    leavesTheGpu = leavesTheGpu || it.targetDevice.type != kCudaDeviceType || it.targetDevice.index != device;
-  }
-  // A batch that stays on its GPU within this process is a local copy at memory speed: the two
-  // hand-offs between streams would cost it 3 % at 256 MiB, and it is launched on the sender's
-  // stream like a small one.
-  if (!leavesTheGpu) return nullptr;
   try {
+    // (Looking a pointer's device up may fail for memory the driver does not know: such a batch
+    // goes the ordinary way, where the failure is reported through its callback.)
+    const void* stream = items[0].buffer.unwrap<CudaBuffer>().stream;
+    const int device = items[0].buffer.device().index;
+    bool leavesTheGpu = !sameProcessForCallers_.load(std::memory_order_relaxed);
+    for (const SendItem& it : items) {
+      if (it.buffer.unwrap<CudaBuffer>().stream != stream || it.buffer.device().index != device) return nullptr;
+      leavesTheGpu = leavesTheGpu || it.targetDevice.type != kCudaDeviceType || it.targetDevice.index != device;
+    }
+    // A batch that stays on its GPU within this process is a local copy at memory speed: the two
+    // hand-offs between streams would cost it 3 % at 256 MiB, and it is launched on the sender's
+    // stream like a small one.
+    if (!leavesTheGpu) return nullptr;
     std::unique_ptr<CudaEvent> ev;
     {
       std::lock_guard<std::mutex> lock(sentEventsMutex_);

@@ -468,7 +468,9 @@ TPB_TEST(Channel, CudaP2pOptionsFollowTheEnvironment) {
   ::setenv("TPB_CUDA_P2P_WAIT_KERNEL", "1", 1);
   ::setenv("TPB_CUDA_P2P_WAIT_TIMEOUT_MS", "250", 1);
   ::setenv("TPB_CUDA_P2P_BULK", "0", 1);
+  ::setenv("TPB_CUDA_P2P_SEND_ORDER_MIN_BYTES", "1048576", 1);
   p2p::Options o = p2p::applyEnvironment(p2p::Options());
+  EXPECT_EQ(o.sendOrderMinBytes, size_t(1) << 20);
   EXPECT_EQ(o.eagerThreshold, size_t(4096));
   EXPECT_EQ(o.inboxBytes, size_t(1) << 20);
   EXPECT_EQ(o.maxCtas, 37);
@@ -480,10 +482,12 @@ TPB_TEST(Channel, CudaP2pOptionsFollowTheEnvironment) {
   keep.maxCtas = 5;
   EXPECT_EQ(p2p::applyEnvironment(keep).maxCtas, 5);
   for (const char* n : {"TPB_CUDA_P2P_EAGER_THRESHOLD", "TPB_CUDA_P2P_INBOX_BYTES", "TPB_CUDA_P2P_MAX_CTAS",
-                        "TPB_CUDA_P2P_WAIT_KERNEL", "TPB_CUDA_P2P_WAIT_TIMEOUT_MS", "TPB_CUDA_P2P_BULK"})
+                        "TPB_CUDA_P2P_WAIT_KERNEL", "TPB_CUDA_P2P_WAIT_TIMEOUT_MS", "TPB_CUDA_P2P_BULK",
+                        "TPB_CUDA_P2P_SEND_ORDER_MIN_BYTES"})
     ::unsetenv(n);
   p2p::Options d = p2p::applyEnvironment(p2p::Options());
   EXPECT_EQ(d.eagerThreshold, size_t(64 * 1024));
+  EXPECT_EQ(d.sendOrderMinBytes, size_t(8) << 20);
 }
 
 // Every channel context can be dropped without join(): its destructor closes and joins on its

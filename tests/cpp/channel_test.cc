@@ -7,6 +7,7 @@
 #include <mutex>
 #include <random>
 
+#include "channel/copy_channel.h"
 #include "channel_wiring.h"
 #include "test_util.h"
 
@@ -247,6 +248,76 @@ TPB_TEST(Channel, LargeAndSmallTensorsCompleteInOrder) {
           for (int i = 0; i < n; ++i) EXPECT_EQ(order[i], i);
         });
   });
+}
+
+// One slice of a sliced copy fails (a copy function that refuses one address range stands in for
+// process_vm_readv on memory that has gone away): that receive reports the error, the one before
+// it succeeds, the ones after it fail, all in the order of the calls, and the sender's pending
+// callbacks end with an error instead of hanging.
+TPB_TEST(Channel, AFailedSliceFailsItsReceiveAndThoseBehindIt) {
+  static std::atomic<uintptr_t> poisonBegin{0}, poisonEnd{0};
+  static auto copyFn = [](uint64_t, const void* remote, void* local, size_t len) -> Error {
+    const uintptr_t a = reinterpret_cast<uintptr_t>(remote);
+    if (a < poisonEnd.load() && a + len > poisonBegin.load()) return TPB_CREATE_ERROR(SystemError, "process_vm_readv", EFAULT);
+    std::memcpy(local, remote, len);
+    return Error::kSuccess;
+  };
+  Backend sliced{"sliced copy",
+                 [] {
+                   ::setenv("TPB_COPY_THREADS", "4", 1);
+                   auto ctx = std::make_shared<channel::copy::ContextImpl>(
+                       "tpbtest:any", +[](uint64_t pid, const void* r, void* l, size_t n) { return copyFn(pid, r, l, n); },
+                       "TP_TEST_copy");
+                   ::unsetenv("TPB_COPY_THREADS");
+                   return std::static_pointer_cast<channel::Context>(ctx);
+                 },
+                 false};
+  constexpr size_t kBytes = 4u << 20;
+  std::vector<std::vector<uint8_t>> data(3);
+  for (int i = 0; i < 3; ++i) data[i] = pattern(kBytes, 70 + i);
+  // the third quarter of the second tensor cannot be read
+  poisonBegin = reinterpret_cast<uintptr_t>(data[1].data()) + kBytes / 2;
+  poisonEnd = poisonBegin.load() + 4096;
+  runChannel(
+      sliced,
+      [&](channel::Channel& ch) {
+        std::vector<std::vector<uint8_t>> got(3, std::vector<uint8_t>(kBytes));
+        std::vector<std::promise<Error>> done(3);
+        std::mutex mu;
+        std::vector<int> order;
+        for (int i = 0; i < 3; ++i)
+          ch.recv(CpuBuffer{got[i].data()}, kBytes, [&, i](const Error& e) {
+            {
+              std::lock_guard<std::mutex> lock(mu);
+              order.push_back(i);
+            }
+            done[i].set_value(e);
+          });
+        std::vector<Error> results;
+        for (int i = 0; i < 3; ++i) {
+          auto f = done[i].get_future();
+          results.push_back(waitFor(f));
+        }
+        EXPECT_FALSE(bool(results[0]));
+        EXPECT_TRUE(got[0] == data[0]);
+        EXPECT_TRUE(bool(results[1]));
+        EXPECT_TRUE(bool(results[2]));
+        std::lock_guard<std::mutex> lock(mu);
+        for (int i = 0; i < 3; ++i) EXPECT_EQ(order[i], i);
+      },
+      [&](channel::Channel& ch) {
+        std::vector<std::promise<Error>> done(3);
+        for (int i = 0; i < 3; ++i)
+          ch.send(CpuBuffer{data[i].data()}, kBytes, [&, i](const Error& e) { done[i].set_value(e); });
+        auto f0 = done[0].get_future();
+        EXPECT_FALSE(bool(waitFor(f0)));
+        for (int i = 1; i < 3; ++i) {
+          auto f = done[i].get_future();
+          EXPECT_TRUE(bool(waitFor(f)));
+        }
+      });
+  poisonBegin = 0;
+  poisonEnd = 0;
 }
 
 TPB_TEST(Channel, SendTensorsBothWaysAtOnce) {

@@ -12,6 +12,9 @@
 //       the same two processes exchanging a message that is one payload of --bytes and nothing
 //       else (what the reference's benchmark_pipe does by default): the pipe's own cost per
 //       message (descriptor, payload, callbacks), no channel involved.
+//   --workload cpu_stream  --transport uv|shm  [--bytes 64]  [--iters 100000]  [--depth 16]
+//       one way: the client keeps --depth payload-only messages in flight, the server reads them
+//       and answers once at the end; prints microseconds per message and messages per second.
 //   --workload transport_pingpong  --transport uv|shm  [--bytes 64]  [--iters 20000]
 //       raw transport connections (no pipe): one frame each way per round trip, two forked
 //       processes; prints p50 / p99 round-trip latency (the reference's benchmark_transport,
@@ -72,6 +75,7 @@ struct Options {
   int iters = 1000, ranks = 2, warmup = 20;
   size_t bytes = 64;
   int microBatches = 32, fwdUs = 600, bwdUs = 1200;
+  int depth = 16;
 };
 
 static void die(const std::string& what) {
@@ -411,6 +415,121 @@ static int cpuSmallPingPong(const Options& o, Shared* sh) {
             << "\", \"payload_bytes\": " << o.bytes << ", \"round_trips\": " << o.iters << ", \"rtt_p50_us\": "
             << sh->p50[0] << ", \"rtt_p99_us\": " << sh->p99[0] << ", \"rtt_mean_us\": " << sh->mean[0]
             << ", \"verified\": \"byte-exact, every round trip\"}" << std::endl;
+  return 0;
+}
+
+// ---- workload 1c: a stream of payload-only messages, `depth` writes in flight -----------------------
+static int cpuStream(const Options& o, Shared* sh) {
+  const int total = o.iters;
+  pid_t server = fork();
+  if (server == 0) {
+    auto ctx = makeCpuContext(o, "server");
+    std::vector<std::string> urls = {"uv://127.0.0.1"};
+    if (o.transport == "shm") urls.push_back("shm://");
+    auto listener = ctx->listen(urls);
+    std::strncpy(sh->url, listener->url("uv").c_str(), sizeof(sh->url) - 1);
+    sh->urlReady = 1;
+    std::promise<std::shared_ptr<lib::Pipe>> pp;
+    listener->accept([&](const lib::Error& e, std::shared_ptr<lib::Pipe> p) {
+      if (e) die("accept: " + e.what());
+      pp.set_value(p);
+    });
+    auto pipe = pp.get_future().get();
+    std::vector<uint8_t> in(o.bytes);
+    std::promise<void> all;
+    int left = total;
+    uint64_t sum = 0;
+    std::function<void()> arm = [&]() {
+      pipe->readDescriptor([&](const lib::Error& e, lib::Descriptor d) {
+        if (e) die("readDescriptor: " + e.what());
+        if (d.payloads.size() != 1 || d.payloads[0].length != in.size()) die("unexpected message shape");
+        lib::Allocation a;
+        a.payloads.push_back({in.data()});
+        pipe->read(std::move(a), [&](const lib::Error& e2) {
+          if (e2) die("read: " + e2.what());
+          sum += in[0];
+          if (--left == 0) return all.set_value();
+          arm();
+        });
+      });
+    };
+    arm();
+    all.get_future().wait();
+    // One message back tells the client that everything has arrived, and what arrived.
+    std::promise<void> acked;
+    lib::Message m;
+    m.metadata = std::to_string(sum);
+    pipe->write(std::move(m), [&](const lib::Error& e) {
+      if (e) die("ack: " + e.what());
+      acked.set_value();
+    });
+    acked.get_future().wait();
+    while (sh->clientsDone.load() == 0) std::this_thread::sleep_for(std::chrono::milliseconds(1));
+    ctx->join();
+    _exit(0);
+  }
+  pid_t client = fork();
+  if (client == 0) {
+    while (sh->urlReady.load() == 0) std::this_thread::sleep_for(std::chrono::milliseconds(1));
+    auto ctx = makeCpuContext(o, "client");
+    auto pipe = ctx->connect(sh->url);
+    const int depth = std::max(1, o.depth);
+    std::vector<std::vector<uint8_t>> out(depth, std::vector<uint8_t>(o.bytes, 1));
+    std::mutex mu;
+    int issued = 0;
+    uint64_t expected = 0;
+    std::function<void(int)> writeNext = [&](int slot) {
+      {
+        std::lock_guard<std::mutex> lock(mu);
+        if (issued == total) return;
+        out[slot][0] = static_cast<uint8_t>(issued);
+        expected += out[slot][0];
+        ++issued;
+      }
+      lib::Message m;
+      lib::Message::Payload p;
+      p.data = out[slot].data();
+      p.length = out[slot].size();
+      m.payloads.push_back(p);
+      pipe->write(std::move(m), [&, slot](const lib::Error& e) {
+        if (e) die("write: " + e.what());
+        writeNext(slot);
+      });
+    };
+    std::promise<std::string> ack;
+    pipe->readDescriptor([&](const lib::Error& e, lib::Descriptor d) {
+      if (e) die("readDescriptor: " + e.what());
+      std::string meta = d.metadata;
+      pipe->read(lib::Allocation(), [&, meta](const lib::Error& e2) {
+        if (e2) die("read: " + e2.what());
+        ack.set_value(meta);
+      });
+    });
+    auto t0 = Clock::now();
+    for (int slot = 0; slot < depth; ++slot) writeNext(slot);
+    const std::string got = ack.get_future().get();
+    sh->seconds[0] = std::chrono::duration<double>(Clock::now() - t0).count();
+    if (got != std::to_string(expected)) {
+      sh->failed = 1;
+      die("the server saw other bytes than were sent");
+    }
+    sh->clientsDone = 1;
+    ctx->join();
+    _exit(0);
+  }
+  int s1 = 0, s2 = 0;
+  waitpid(client, &s2, 0);
+  sh->clientsDone = 1;
+  waitpid(server, &s1, 0);
+  if (!WIFEXITED(s1) || WEXITSTATUS(s1) || !WIFEXITED(s2) || WEXITSTATUS(s2) || sh->failed) {
+    std::cout << "{\"impl\": \"" << kImpl << "\", \"workload\": \"cpu_stream\", \"error\": \"a peer failed\"}" << std::endl;
+    return 1;
+  }
+  std::cout << "{\"impl\": \"" << kImpl << "\", \"workload\": \"cpu_stream\", \"transport\": \"" << o.transport
+            << "\", \"payload_bytes\": " << o.bytes << ", \"messages\": " << total << ", \"depth\": " << o.depth
+            << ", \"us_per_message\": " << sh->seconds[0] / total * 1e6 << ", \"messages_per_second\": "
+            << total / sh->seconds[0] << ", \"MBps\": " << static_cast<double>(total) * o.bytes / sh->seconds[0] / 1e6
+            << ", \"verified\": \"checksum of the first byte of every message, kept by the server\"}" << std::endl;
   return 0;
 }
 
@@ -1117,6 +1236,7 @@ int main(int argc, char** argv) {
     else if (k == "--ranks") o.ranks = std::stoi(v);
     else if (k == "--warmup") o.warmup = std::stoi(v);
     else if (k == "--bytes") o.bytes = std::stoull(v);
+    else if (k == "--depth") o.depth = std::stoi(v);
     else if (k == "--micro-batches") o.microBatches = std::stoi(v);
     else if (k == "--fwd-us") o.fwdUs = std::stoi(v);
     else if (k == "--bwd-us") o.bwdUs = std::stoi(v);
@@ -1125,6 +1245,7 @@ int main(int argc, char** argv) {
   std::memset(static_cast<void*>(sh), 0, sizeof(Shared));
   if (o.workload == "cpu_pingpong") return cpuPingPong(o, sh);
   if (o.workload == "cpu_small") return cpuSmallPingPong(o, sh);
+  if (o.workload == "cpu_stream") return cpuStream(o, sh);
   if (o.workload == "rpc_fanin") return rpcFanIn(o, sh);
   if (o.workload == "transport_pingpong") return transportPingPong(o, sh);
   if (o.workload == "all_pairs") return allPairs(o, sh);

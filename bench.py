@@ -177,7 +177,8 @@ def bench_config(args, world, burst):
     return {"model": "pipe ring: 1 bf16 tensor per message", "global_batch": world,
             "seq_len": args.bytes // 2, "bytes_per_message": args.bytes, "messages_per_step": burst,
             "parallelism": f"ring{world}" if world > 1 else "loopback (two pipes, one process, one GPU)",
-            "l2": "inputs larger than L2 (no flush)", "writes_in_flight": args.depth}
+            "l2": "inputs larger than L2 (no flush)", "writes_in_flight": args.depth,
+            "sweep_messages_per_size": "1000 up to 1 MiB, 100 up to 64 MiB, 20 above; a tenth as many warm-up"}
 
 
 def percentile(samples, q):

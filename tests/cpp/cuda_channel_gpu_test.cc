@@ -249,11 +249,11 @@ TPB_GPU_TEST(CudaChannel, P2pSendOrderAcrossDevices, 2) { basicCases(true, p2pSe
 TPB_GPU_TEST(CudaChannel, P2pLaunchOrderTwoProcesses, 1) { basicCases(true, p2pSendOrder(0), 0, 0); }
 TPB_GPU_TEST(CudaChannel, P2pLaunchOrderAcrossDevices, 2) { basicCases(true, p2pSendOrder(0), 0, 1); }
 // A large batch keeps the place in the sender's stream that it had when sendBatch() was called:
-// 300 ms of other work queued on that stream right after the call, and long before the receiver
+// 600 ms of other work queued on that stream right after the call, and long before the receiver
 // names its buffers, does not stand between the receiver and its data.
 static void laterWorkDoesNotDelayALargeSend(bool processes, int serverDevice, int clientDevice) {
   constexpr size_t kBytes = 16u << 20;
-  constexpr uint32_t kBusyUs = 300000;
+  constexpr uint32_t kBusyUs = 600000;
   runPair(
       processes, p2p(), p2p(),
       [=](channel::Channel& ch) {

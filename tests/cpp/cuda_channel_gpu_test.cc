@@ -299,9 +299,6 @@ static void laterWorkDoesNotDelayALargeSend(bool processes, int serverDevice, in
 // (Within one process and one GPU a batch is launched on the sender's stream whatever its size.)
 TPB_GPU_TEST(CudaChannel, P2pLaterWorkDoesNotDelayALargeSendTwoProcesses, 1) { laterWorkDoesNotDelayALargeSend(true, 0, 0); }
 TPB_GPU_TEST(CudaChannel, P2pLaterWorkDoesNotDelayALargeSendAcrossDevices, 2) { laterWorkDoesNotDelayALargeSend(true, 0, 1); }
-TPB_GPU_TEST(CudaChannel, P2pLaterWorkDoesNotDelayALargeSendSameProcessAcrossDevices, 2) {
-  laterWorkDoesNotDelayALargeSend(false, 0, 1);
-}
 
 TPB_GPU_TEST(CudaChannel, GdrOverASoftwareFabric, 1) { basicCases(false, gdr(), 0, 0); }
 TPB_GPU_TEST(CudaChannel, GdrOverASoftwareFabricAcrossDevices, 2) { basicCases(false, gdr(), 0, 1); }

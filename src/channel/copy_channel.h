@@ -135,8 +135,14 @@ class ContextImpl final : public Context, public std::enable_shared_from_this<Co
     }
     // An empty function is the request to stop, one per worker, queued behind whatever copies
     // were requested before.
-    for (size_t i = 0; i < threads.size(); ++i) jobs_.push(nullptr);
-    for (auto& t : threads) t.join();
+    for (size_t i = 0; i < threads.size(); ++i) jobs_->push(nullptr);
+    for (auto& t : threads) {
+      // The last reference to the context may die inside a job, on a worker: that worker cannot
+      // wait for itself and is left to run out on its own (it only touches the job queue, which
+      // it shares ownership of, and finds its request to stop there).
+      if (t.get_id() == std::this_thread::get_id()) t.detach();
+      else t.join();
+    }
   }
   // The copy runs on the worker threads, cut into slices when it is large; `done` is deferred to
   // the loop when the last slice is through and gets the first error, if there was one.
@@ -157,7 +163,7 @@ class ContextImpl final : public Context, public std::enable_shared_from_this<Co
     const size_t per = ((len + slices - 1) / slices + 4095) & ~size_t(4095);
     for (size_t i = 0; i < slices; ++i) {
       const size_t begin = std::min(len, i * per), end = std::min(len, begin + per);
-      jobs_.push([self, whole, pid, remote, local, begin, end]() {
+      jobs_->push([self, whole, pid, remote, local, begin, end]() {
         Error e = begin < end ? self->copyFn_(pid, static_cast<const uint8_t*>(remote) + begin,
                                               static_cast<uint8_t*>(local) + begin, end - begin)
                               : Error::kSuccess;
@@ -185,11 +191,11 @@ class ContextImpl final : public Context, public std::enable_shared_from_this<Co
   void startWorker() {
     std::lock_guard<std::mutex> lock(threadsMutex_);
     if (stopRequested_ || threads_.size() >= maxThreads_) return;
-    threads_.emplace_back([this]() {
-      setThreadName(threadName_);
+    threads_.emplace_back([jobs = jobs_, name = threadName_]() {
+      setThreadName(name);
       // A worker sleeps in pop(); an empty function tells it to stop.
       for (;;) {
-        std::function<void()> job = jobs_.pop();
+        std::function<void()> job = jobs->pop();
         if (!job) return;
         job();
       }
@@ -203,7 +209,7 @@ class ContextImpl final : public Context, public std::enable_shared_from_this<Co
   std::vector<std::thread> threads_;
   // Copies wait here for the workers. The bound only matters to a caller that queues thousands
   // of tensors without waiting for any: it then blocks until the workers catch up.
-  Queue<std::function<void()>> jobs_{4096};
+  std::shared_ptr<Queue<std::function<void()>>> jobs_ = std::make_shared<Queue<std::function<void()>>>(4096);
   std::atomic<bool> stopRequested_{false};
   std::atomic<bool> joined_{false};
 };

@@ -320,6 +320,33 @@ TPB_TEST(Channel, AFailedSliceFailsItsReceiveAndThoseBehindIt) {
   poisonEnd = 0;
 }
 
+// The last reference to a copy context may die on one of its own worker threads (the job holds
+// one while it runs): the context then winds down from there without waiting for that thread.
+TPB_TEST(Channel, ACopyContextMayDieOnItsOwnWorker) {
+  static std::atomic<int> copies{0};
+  for (size_t bytes : {size_t(64), size_t(4u << 20)}) {
+    auto ctx = std::make_shared<channel::copy::ContextImpl>(
+        "tpbtest:any",
+        +[](uint64_t, const void* r, void* l, size_t n) -> Error {
+          std::this_thread::sleep_for(std::chrono::milliseconds(30));
+          std::memcpy(l, r, n);
+          ++copies;
+          return Error::kSuccess;
+        },
+        "TP_TEST_copy");
+    auto src = std::make_shared<std::vector<uint8_t>>(pattern(bytes, 5));
+    auto dst = std::make_shared<std::vector<uint8_t>>(bytes);
+    auto finished = std::make_shared<std::promise<Error>>();
+    auto f = finished->get_future();
+    ctx->requestCopy(0, src->data(), dst->data(), bytes, [finished, src, dst](const Error& e) { finished->set_value(e); });
+    ctx.reset();  // the jobs hold the only references now
+    EXPECT_FALSE(bool(waitFor(f)));
+    EXPECT_TRUE(*src == *dst);
+  }
+  std::this_thread::sleep_for(std::chrono::milliseconds(100));  // let the workers run out
+  EXPECT_TRUE(copies.load() >= 2);
+}
+
 TPB_TEST(Channel, SendTensorsBothWaysAtOnce) {
   forEachBackend([](const Backend& b) {
     auto a = pattern(123457, 7), c = pattern(76543, 8);

@@ -113,19 +113,27 @@ PYBIND11_MODULE(_C, m) {
   m.def("create_cma_channel", &channel::cma::create);
   m.def("create_cuda_basic_channel", &channel::cuda_basic::create);
   m.def("create_cuda_gdr_channel", &channel::cuda_gdr::create);
-  m.def(
-      "create_cuda_p2p_channel",
-      [](size_t eagerThreshold, size_t inboxBytes, int maxCtas, bool waitWithKernel, bool useBulkCopy) {
-        channel::cuda_p2p::Options o;
-        o.eagerThreshold = eagerThreshold;
-        o.inboxBytes = inboxBytes;
-        o.maxCtas = maxCtas;
-        o.waitWithKernel = waitWithKernel;
-        o.useBulkCopy = useBulkCopy;
-        return channel::cuda_p2p::create(o);
-      },
-      py::arg("eager_threshold") = 64 * 1024, py::arg("inbox_bytes") = 16u << 20, py::arg("max_ctas") = 0,
-      py::arg("wait_with_kernel") = false, py::arg("use_bulk_copy") = true);
+  {
+    const channel::cuda_p2p::Options defaults;
+    m.def(
+        "create_cuda_p2p_channel",
+        [](size_t eagerThreshold, size_t inboxBytes, int maxCtas, bool waitWithKernel, bool useBulkCopy,
+           size_t sendOrderMinBytes, size_t hostCopyMinBytes) {
+          channel::cuda_p2p::Options o;
+          o.eagerThreshold = eagerThreshold;
+          o.inboxBytes = inboxBytes;
+          o.maxCtas = maxCtas;
+          o.waitWithKernel = waitWithKernel;
+          o.useBulkCopy = useBulkCopy;
+          o.sendOrderMinBytes = sendOrderMinBytes;
+          o.hostCopyMinBytes = hostCopyMinBytes;
+          return channel::cuda_p2p::create(o);
+        },
+        py::arg("eager_threshold") = defaults.eagerThreshold, py::arg("inbox_bytes") = defaults.inboxBytes,
+        py::arg("max_ctas") = defaults.maxCtas, py::arg("wait_with_kernel") = defaults.waitWithKernel,
+        py::arg("use_bulk_copy") = defaults.useBulkCopy, py::arg("send_order_min_bytes") = defaults.sendOrderMinBytes,
+        py::arg("host_copy_min_bytes") = defaults.hostCopyMinBytes);
+  }
   m.def(
       "create_mpt_channel",
       [](int lanes) {

@@ -382,7 +382,9 @@ def default_context(name: str = "", shm: bool = True, cuda: Optional[bool] = Non
     transports shm (same host) > uv (TCP); channels cuda_p2p (GPU<->GPU over NVLink / same GPU) >
     cuda_basic (anything involving a GPU, staged through pinned memory) > xth (CPU, same process)
     > cma (CPU, same host) > mpt (CPU, striped over TCP lanes, optional) > basic (CPU, anywhere).
-    Backends that cannot work on this machine drop out silently."""
+    Backends that cannot work on this machine drop out silently. Keyword arguments go to the
+    device-to-device channel: eager_threshold, inbox_bytes, max_ctas, wait_with_kernel,
+    use_bulk_copy, send_order_min_bytes, host_copy_min_bytes (see channel::cuda_p2p::Options)."""
     ctx = Context(name)
     ctx.register_transport(0, "uv", _C.create_uv_transport())
     if shm:

@@ -11,6 +11,8 @@
 #include <unistd.h>
 
 #include <atomic>
+#include <chrono>
+#include <cstdlib>
 #include <cstdint>
 #include <memory>
 #include <unordered_map>
@@ -86,11 +88,39 @@ class EpollLoop : public ThreadLoop {
   void eventLoop() override {
     constexpr int kBatch = 64;
     epoll_event events[kBatch];
+    bool sawEvents = false;
+    auto activeUntil = std::chrono::steady_clock::now();
     for (;;) {
-      runDeferredFunctions();
+      // Functions often defer further functions (a callback that writes): run a few rounds of
+      // them before looking at the descriptors, but not for ever, so that a chain of functions
+      // cannot keep the descriptors waiting.
+      bool more = false;
+      for (int round = 0; round < 8; ++round) {
+        more = runDeferredFunctions() > 0;
+        if (!more) break;
+      }
+      const bool closing = closed_.load();
       // Leave once closed and nobody holds a registration any more.
-      if (closed_.load() && handlers_.empty() && !hasDeferred()) break;
-      int n = ::epoll_wait(epollFd_, events, kBatch, closed_.load() ? 10 : -1);
+      if (closing && handlers_.empty() && !hasDeferred()) break;
+      // For a short while after the last sign of life the loop polls instead of blocking: a stream
+      // of frames that is paced by the socket buffers would otherwise pay a thread wake-up for
+      // every time the socket drains or fills.
+      const auto now = std::chrono::steady_clock::now();
+      if (more || sawEvents) activeUntil = now + spinWindow_;
+      int timeout = (more || now < activeUntil) ? 0 : (closing ? 10 : -1);
+      if (timeout != 0) {
+        // About to block: from here on, whoever defers a function or closes the loop must write
+        // the eventfd. Either this thread sees their change in the check below, or they see
+        // `asleep_` set (both sides store first and load second, sequentially consistent).
+        asleep_.store(true, std::memory_order_seq_cst);
+        if (hasDeferred() || closed_.load() != closing) {
+          asleep_.store(false, std::memory_order_seq_cst);
+          continue;
+        }
+      }
+      int n = ::epoll_wait(epollFd_, events, kBatch, timeout);
+      if (timeout != 0) asleep_.store(false, std::memory_order_seq_cst);
+      sawEvents = n > 0;
       if (n < 0) {
         if (errno == EINTR) continue;
         TPB_LOG_ERROR << "epoll_wait: " << std::strerror(errno);
@@ -100,7 +130,8 @@ class EpollLoop : public ThreadLoop {
         uint64_t rec = events[i].data.u64;
         if (rec == 0) {
           uint64_t v;
-          while (::read(eventFd_, &v, sizeof(v)) > 0) {}
+          ssize_t r = ::read(eventFd_, &v, sizeof(v));  // one read empties the counter
+          (void)r;
           continue;
         }
         auto it = handlers_.find(rec);
@@ -110,7 +141,12 @@ class EpollLoop : public ThreadLoop {
       }
     }
   }
+  // Called after a function was queued or the loop was closed. The loop only needs the eventfd
+  // when it is blocked (or about to block) in epoll_wait; while it is running, what was queued is
+  // found on its next pass, and a system call per deferred function is saved: most of them are
+  // deferred by the loop thread itself.
   void wakeupEventLoop() override {
+    if (!asleep_.load(std::memory_order_seq_cst)) return;
     uint64_t one = 1;
     ssize_t r = ::write(eventFd_, &one, sizeof(one));
     (void)r;
@@ -120,6 +156,12 @@ class EpollLoop : public ThreadLoop {
   int epollFd_ = -1;
   int eventFd_ = -1;
   std::atomic<bool> closed_{false};
+  std::atomic<bool> asleep_{false};
+  // TPB_EPOLL_SPIN_US: how long the loop keeps polling after activity before it blocks.
+  const std::chrono::nanoseconds spinWindow_ = [] {
+    const char* s = std::getenv("TPB_EPOLL_SPIN_US");
+    return std::chrono::microseconds(s ? std::strtol(s, nullptr, 10) : 50);
+  }();
   uint64_t nextRecord_ = 1;
   std::unordered_map<int, uint64_t> fdToRecord_;
   std::unordered_map<uint64_t, std::shared_ptr<EpollEventHandler>> handlers_;

@@ -146,6 +146,21 @@ class ConnectionImpl final : public EpollEventHandler,
   std::deque<WriteOp> writes_;
   int interest_ = 0;
   bool registered_ = false;
+  // Bytes read from the socket ahead of the operation that will consume them: headers and small
+  // frames come out of here, several per system call; large bodies are read straight into their
+  // destination once this is empty.
+  static constexpr size_t kReadAheadBytes = 64 * 1024;
+  static constexpr size_t kDirectReadMinBytes = 16 * 1024;
+  std::unique_ptr<uint8_t[]> readAhead_;
+  size_t readAheadBegin_ = 0, readAheadEnd_ = 0;
+  size_t takeReadAhead(uint8_t* dst, size_t n);
+  enum class Fill { kGotBytes, kWouldBlock, kClosed };
+  Fill fillReadAhead();
+  // Writes queued during one pass of the loop leave in one sendmsg: the flush is itself a
+  // closure deferred behind them.
+  bool flushScheduled_ = false;
+  bool socketFull_ = false;  // sendmsg said EAGAIN: the next attempt waits for EPOLLOUT
+  bool flushingBeforeClose_ = false;
 };
 
 class ListenerImpl final : public EpollEventHandler,
@@ -289,26 +304,60 @@ void ConnectionImpl::write(WriteOp op) {
       return;
     }
     self->writes_.push_back(std::move(op));
-    if (self->state_ == kOpen && self->writes_.size() == 1) self->processWrites();
-    self->updateInterest();
+    if (self->state_ == kOpen && !self->flushScheduled_ && !self->socketFull_) {
+      // A message is several frames (descriptor, payloads), written back to back by the pipe:
+      // the closure below runs behind the ones that queue them.
+      self->flushScheduled_ = true;
+      self->ctx_->loop().deferToLoop([self]() {
+        self->flushScheduled_ = false;
+        if (self->state_ == kOpen) self->processWrites();
+        self->updateInterest();
+      });
+    }
   });
+}
+
+size_t ConnectionImpl::takeReadAhead(uint8_t* dst, size_t n) {
+  const size_t have = readAheadEnd_ - readAheadBegin_;
+  if (n > have) n = have;
+  if (n == 0) return 0;
+  std::memcpy(dst, readAhead_.get() + readAheadBegin_, n);
+  readAheadBegin_ += n;
+  if (readAheadBegin_ == readAheadEnd_) readAheadBegin_ = readAheadEnd_ = 0;
+  return n;
+}
+
+// Called with the read-ahead buffer empty.
+ConnectionImpl::Fill ConnectionImpl::fillReadAhead() {
+  if (!readAhead_) readAhead_.reset(new uint8_t[kReadAheadBytes]);
+  for (;;) {
+    ssize_t n = ::read(fd_, readAhead_.get(), kReadAheadBytes);
+    if (n > 0) {
+      readAheadBegin_ = 0;
+      readAheadEnd_ = static_cast<size_t>(n);
+      return Fill::kGotBytes;
+    }
+    if (n == 0) {
+      closeFromLoop(TPB_CREATE_ERROR(EOFError));
+      return Fill::kClosed;
+    }
+    if (errno == EAGAIN || errno == EWOULDBLOCK) return Fill::kWouldBlock;
+    if (errno == EINTR) continue;
+    closeFromLoop(TPB_CREATE_ERROR(SystemError, "read", errno));
+    return Fill::kClosed;
+  }
 }
 
 void ConnectionImpl::processReads() {
   while (state_ == kOpen && !reads_.empty()) {
     ReadOp& op = reads_.front();
     if (op.headerRead < sizeof(uint64_t)) {
-      ssize_t n = ::read(fd_, reinterpret_cast<uint8_t*>(&op.frameLen) + op.headerRead,
-                         sizeof(uint64_t) - op.headerRead);
-      if (n == 0) { closeFromLoop(TPB_CREATE_ERROR(EOFError)); return; }
-      if (n < 0) {
-        if (errno == EAGAIN || errno == EWOULDBLOCK) return;
-        if (errno == EINTR) continue;
-        closeFromLoop(TPB_CREATE_ERROR(SystemError, "read", errno));
-        return;
+      op.headerRead += takeReadAhead(reinterpret_cast<uint8_t*>(&op.frameLen) + op.headerRead,
+                                     sizeof(uint64_t) - op.headerRead);
+      if (op.headerRead < sizeof(uint64_t)) {
+        if (fillReadAhead() != Fill::kGotBytes) return;
+        continue;
       }
-      op.headerRead += static_cast<size_t>(n);
-      if (op.headerRead < sizeof(uint64_t)) continue;
       if (op.userBuffer) {
         if (op.frameLen != op.expected) {
           closeFromLoop(TPB_CREATE_ERROR(ShortReadError, static_cast<ssize_t>(op.expected),
@@ -328,7 +377,16 @@ void ConnectionImpl::processReads() {
       }
     }
     while (op.bodyRead < op.frameLen) {
-      ssize_t n = ::read(fd_, op.ptr + op.bodyRead, op.frameLen - op.bodyRead);
+      op.bodyRead += takeReadAhead(op.ptr + op.bodyRead, op.frameLen - op.bodyRead);
+      const size_t remaining = op.frameLen - op.bodyRead;
+      if (remaining == 0) break;
+      if (remaining < kDirectReadMinBytes) {
+        // The rest of a small frame, and likely the frames behind it, in one system call.
+        if (fillReadAhead() != Fill::kGotBytes) return;
+        continue;
+      }
+      // A large body goes straight to where it belongs (the read-ahead buffer is empty here).
+      ssize_t n = ::read(fd_, op.ptr + op.bodyRead, remaining);
       if (n == 0) { closeFromLoop(TPB_CREATE_ERROR(EOFError)); return; }
       if (n < 0) {
         if (errno == EAGAIN || errno == EWOULDBLOCK) return;
@@ -345,12 +403,13 @@ void ConnectionImpl::processReads() {
 }
 
 void ConnectionImpl::processWrites() {
+  constexpr int kMaxVectors = 16;
   while (state_ == kOpen && !writes_.empty()) {
-    WriteOp& op = writes_.front();
-    const size_t total = sizeof(uint64_t) + op.length;
-    while (op.written < total) {
-      iovec iov[2];
-      int cnt = 0;
+    // Gather what is left of the queued frames, oldest first, into one call.
+    iovec iov[kMaxVectors];
+    int cnt = 0;
+    for (auto it = writes_.begin(); it != writes_.end() && cnt + 2 <= kMaxVectors; ++it) {
+      WriteOp& op = *it;
       if (op.written < sizeof(uint64_t)) {
         iov[cnt].iov_base = reinterpret_cast<uint8_t*>(&op.length) + op.written;
         iov[cnt].iov_len = sizeof(uint64_t) - op.written;
@@ -361,26 +420,40 @@ void ConnectionImpl::processWrites() {
           ++cnt;
         }
       } else {
-        size_t off = op.written - sizeof(uint64_t);
+        const size_t off = op.written - sizeof(uint64_t);
         iov[cnt].iov_base = const_cast<uint8_t*>(op.ptr) + off;
         iov[cnt].iov_len = op.length - off;
         ++cnt;
       }
-      msghdr mh{};
-      mh.msg_iov = iov;
-      mh.msg_iovlen = cnt;
-      ssize_t n = ::sendmsg(fd_, &mh, MSG_NOSIGNAL);
-      if (n < 0) {
-        if (errno == EAGAIN || errno == EWOULDBLOCK) return;
-        if (errno == EINTR) continue;
-        closeFromLoop(TPB_CREATE_ERROR(SystemError, "sendmsg", errno));
+    }
+    msghdr mh{};
+    mh.msg_iov = iov;
+    mh.msg_iovlen = cnt;
+    ssize_t n = ::sendmsg(fd_, &mh, MSG_NOSIGNAL);
+    if (n < 0) {
+      if (errno == EAGAIN || errno == EWOULDBLOCK) {
+        socketFull_ = true;
         return;
       }
-      op.written += static_cast<size_t>(n);
+      if (errno == EINTR) continue;
+      closeFromLoop(TPB_CREATE_ERROR(SystemError, "sendmsg", errno));
+      return;
     }
-    WriteOp done = std::move(writes_.front());
-    writes_.pop_front();
-    done.fn(Error::kSuccess);
+    socketFull_ = false;
+    // Credit the bytes to the frames in order; the ones that are through call back.
+    size_t sent = static_cast<size_t>(n);
+    std::vector<Connection::write_callback_fn> completed;
+    while (!writes_.empty()) {
+      WriteOp& op = writes_.front();
+      const size_t total = sizeof(uint64_t) + op.length;
+      const size_t take = std::min(sent, total - op.written);
+      op.written += take;
+      sent -= take;
+      if (op.written < total) break;
+      completed.push_back(std::move(op.fn));
+      writes_.pop_front();
+    }
+    for (auto& fn : completed) fn(Error::kSuccess);
   }
 }
 
@@ -424,6 +497,15 @@ void ConnectionImpl::close() {
 
 void ConnectionImpl::closeFromLoop(const Error& e) {
   if (error_) return;
+  // Frames that were handed over before the connection closes still go out if the socket takes
+  // them (a channel writes its last acknowledgement and closes): their flush may still be queued
+  // behind the closure that brought us here.
+  if (flushScheduled_ && !flushingBeforeClose_ && state_ == kOpen && !writes_.empty() && !socketFull_) {
+    flushingBeforeClose_ = true;
+    processWrites();
+    flushingBeforeClose_ = false;
+    if (error_) return;  // the attempt itself failed and closed the connection
+  }
   error_ = e;
   TPB_VLOG(7) << "Connection " << id_ << " is closing: " << e.what();
   auto self = shared_from_this();

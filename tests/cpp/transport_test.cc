@@ -228,6 +228,89 @@ TPB_TEST(Transport, ManySmallFramesWrapTheRing) {
   });
 }
 
+// Frames of every awkward size, queued back to back without waiting and followed at once by
+// close(): each arrives whole and in order — through buffers that hold several frames or a part
+// of one, into memory the transport allocates and into memory the reader names — and only then
+// does the reader see the end of the stream.
+TPB_TEST(Transport, FramesOfAllSizesBackToBackThenClose) {
+  const std::vector<size_t> sizes = {1,     7,     8,      9,     100,    0,      16383, 16384, 16385, 3,
+                                     65535, 65536, 65537,  5,     200000, 12,     1,     70000, 0,     2};
+  forEachBackend([&](const Backend& b) {
+    runPair(
+        b,
+        [&](transport::Connection& c) {
+          for (int pass = 0; pass < 3; ++pass) {
+            for (size_t i = 0; i < sizes.size(); ++i) {
+              auto want = randomBytes(sizes[i], static_cast<uint32_t>(1000 * pass + i));
+              if ((i + pass) % 2 == 0) {
+                EXPECT_TRUE(readSync(c) == want);
+              } else {
+                std::vector<uint8_t> got(sizes[i] + 1, 0xEE);
+                std::promise<Error> pr;
+                c.read(got.data(), sizes[i], [&](const Error& e, const void*, size_t) { pr.set_value(e); });
+                auto f = pr.get_future();
+                EXPECT_FALSE(bool(waitFor(f)));
+                EXPECT_EQ(int(got[sizes[i]]), 0xEE);
+                got.resize(sizes[i]);
+                EXPECT_TRUE(got == want);
+              }
+            }
+          }
+          std::promise<Error> end;
+          c.read([&](const Error& e, const void*, size_t) { end.set_value(e); });
+          auto f = end.get_future();
+          EXPECT_TRUE(bool(waitFor(f)));  // the writer closed behind its last frame
+        },
+        [&](transport::Connection& c) {
+          std::vector<std::vector<uint8_t>> bufs;
+          for (int pass = 0; pass < 3; ++pass)
+            for (size_t i = 0; i < sizes.size(); ++i) bufs.push_back(randomBytes(sizes[i], static_cast<uint32_t>(1000 * pass + i)));
+          auto left = std::make_shared<std::atomic<int>>(static_cast<int>(bufs.size()));
+          auto all = std::make_shared<std::promise<void>>();
+          auto failures = std::make_shared<std::atomic<int>>(0);
+          for (auto& v : bufs)
+            c.write(v.data(), v.size(), [left, all, failures](const Error& e) {
+              if (e) ++*failures;
+              if (--*left == 0) all->set_value();
+            });
+          auto f = all->get_future();
+          waitFor(f);
+          EXPECT_EQ(failures->load(), 0);
+          c.close();
+        });
+  });
+}
+
+// A channel writes its last acknowledgement and closes the connection without waiting for the
+// write's callback: small frames handed over just before close() still reach the peer.
+TPB_TEST(Transport, SmallFramesWrittenJustBeforeCloseStillArrive) {
+  forEachBackend([&](const Backend& b) {
+    for (int attempt = 0; attempt < 20; ++attempt) {
+      runPair(
+          b,
+          [&](transport::Connection& c) {
+            EXPECT_EQ(readSync(c).size(), size_t(5));
+            writeSync(c, "hello", 5);
+            for (int i = 0; i < 3; ++i) {
+              auto v = readSync(c);
+              EXPECT_EQ(v.size(), size_t(40 + i));
+              EXPECT_EQ(int(v[0]), i);
+            }
+          },
+          [&](transport::Connection& c) {
+            // Once round the connection first: a connection that is still being set up has no
+            // obligation towards what was written to it before it is closed.
+            writeSync(c, "hello", 5);
+            EXPECT_EQ(readSync(c).size(), size_t(5));
+            auto bufs = std::make_shared<std::vector<std::vector<uint8_t>>>();
+            for (int i = 0; i < 3; ++i) bufs->emplace_back(40 + i, static_cast<uint8_t>(i));
+            for (auto& v : *bufs) c.write(v.data(), v.size(), [bufs](const Error&) {});
+            c.close();
+          });
+    }
+  });
+}
+
 TPB_TEST(Transport, ListenerQueuesAcceptCallbacksAndConnections) {
   forEachBackend([](const Backend& b) {
     auto ctx = b.make();

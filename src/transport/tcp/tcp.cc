@@ -161,6 +161,7 @@ class ConnectionImpl final : public EpollEventHandler,
   bool flushScheduled_ = false;
   bool socketFull_ = false;  // sendmsg said EAGAIN: the next attempt waits for EPOLLOUT
   bool flushingBeforeClose_ = false;
+  bool interestUpdateScheduled_ = false;
 };
 
 class ListenerImpl final : public EpollEventHandler,
@@ -486,7 +487,16 @@ void ConnectionImpl::handleEventsFromLoop(int events) {
     else closeFromLoop(TPB_CREATE_ERROR(EOFError));
     return;
   }
-  updateInterest();
+  // Not at once: the callback of the frame that just arrived has, as a rule, asked for the next
+  // one, and that request is a closure queued behind us. Settling the interest after it has run
+  // saves taking the descriptor out of the epoll set and putting it back for every frame.
+  if (!interestUpdateScheduled_) {
+    interestUpdateScheduled_ = true;
+    ctx_->loop().deferToLoop([self]() {
+      self->interestUpdateScheduled_ = false;
+      self->updateInterest();
+    });
+  }
 }
 
 void ConnectionImpl::close() {

@@ -20,12 +20,31 @@ using namespace tpb;
 
 namespace {
 
+// Takes the GIL for a callback. A thread of the library has no Python thread state of its own:
+// the one made for its first callback is kept for the thread's later callbacks (one extra count
+// on it, never given back) instead of being built and torn down around every callback, which
+// costs more than the callback itself. A Python thread that runs a callback (the on-demand loop
+// borrows the calling thread) already has its state and is left alone.
+class CallbackGil {
+ public:
+  CallbackGil() : fresh_(threadHasNoState()), gil_() {
+    if (fresh_) gil_.inc_ref();
+  }
+
+ private:
+  static bool threadHasNoState() {
+    return py::detail::get_internals().tstate.get() == nullptr && PyGILState_GetThisThreadState() == nullptr;
+  }
+  bool fresh_;
+  py::gil_scoped_acquire gil_;
+};
+
 // Holds Python objects and drops them with the GIL held, wherever the last reference dies.
 struct PyKeepAlive {
   std::vector<py::object> objects;
   ~PyKeepAlive() {
     if (objects.empty()) return;
-    py::gil_scoped_acquire gil;
+    CallbackGil gil;
     objects.clear();
   }
 };
@@ -54,7 +73,7 @@ std::function<void(Args...)> wrapCallback(py::function fn, std::shared_ptr<PyKee
   auto holder = std::make_shared<PyKeepAlive>();
   holder->objects.push_back(std::move(fn));
   return [holder, keep](Args... args) {
-    py::gil_scoped_acquire gil;
+    CallbackGil gil;
     try {
       py::function f = py::reinterpret_borrow<py::function>(holder->objects[0]);
       f(args...);
@@ -230,7 +249,7 @@ PYBIND11_MODULE(_C, m) {
              holder->objects.push_back(std::move(fn));
              py::gil_scoped_release nogil;
              self.readDescriptor([holder](const Error& e, Descriptor d) {
-               py::gil_scoped_acquire gil;
+               CallbackGil gil;
                try {
                  py::function f = py::reinterpret_borrow<py::function>(holder->objects[0]);
                  f(errorString(e), descriptorToDict(d));
@@ -276,7 +295,7 @@ PYBIND11_MODULE(_C, m) {
              holder->objects.push_back(std::move(fn));
              py::gil_scoped_release nogil;
              self.accept([holder](const Error& e, std::shared_ptr<Pipe> p) {
-               py::gil_scoped_acquire gil;
+               CallbackGil gil;
                try {
                  py::function f = py::reinterpret_borrow<py::function>(holder->objects[0]);
                  f(errorString(e), p);

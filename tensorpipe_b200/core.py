@@ -7,8 +7,10 @@ being made contiguous when the selected channel can pack them on the fly.
 """
 from __future__ import annotations
 
+import atexit
 import json
 import threading
+import weakref
 from concurrent.futures import Future
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional, Sequence
@@ -341,10 +343,28 @@ class Listener:
         self._l.close()
 
 
+_live_contexts: "weakref.WeakSet[Context]" = weakref.WeakSet()
+
+
+def _join_live_contexts() -> None:
+    """At interpreter exit: contexts the program never joined are joined here, on the main
+    thread and before modules are torn down, so that operations still pending end with an error
+    callback while Python can still run one, and no library thread outlives the interpreter."""
+    for ctx in list(_live_contexts):
+        try:
+            ctx.join()
+        except Exception:  # noqa: BLE001 - nothing to report to at exit
+            pass
+
+
+atexit.register(_join_live_contexts)
+
+
 class Context:
     def __init__(self, name: str = ""):
         self._c = _C.Context(name)
         self._joined = False
+        _live_contexts.add(self)
 
     def register_transport(self, priority: int, name: str, transport) -> None:
         self._c.register_transport(priority, name, transport)

@@ -200,6 +200,30 @@ def test_trace_from_the_environment_is_written_at_exit(built, tmp_path):
     assert {"pipe.write", "pipe.write.done", "pipe.readDescriptor", "pipe.read", "pipe.read.done"} <= names
 
 
+def test_a_program_that_never_joins_exits_cleanly(built):
+    """Contexts left open, a receive still pending: the interpreter's exit joins them (the pending
+    future gets its error while Python can still run the callback) instead of dying in a library
+    thread's destructor."""
+    import os
+    import subprocess
+    import sys
+    code = (
+        "import torch, tensorpipe_b200 as tpb\n"
+        "a = tpb.default_context('a', cuda=False); b = tpb.default_context('b', cuda=False)\n"
+        "l = a.listen(['uv://127.0.0.1', 'shm://']); f = l.accept_future()\n"
+        "o = b.connect(l.url('uv')); i = f.result(30)\n"
+        "s = o.send([torch.ones(4)]); i.recv().result(30); s.result(30)\n"
+        "pending = i.recv()\n"
+        "pending.add_done_callback(lambda fut: print('pending ended with', type(fut.exception()).__name__, flush=True))\n"
+        "print('leaving', flush=True)\n")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = {**os.environ, "PYTHONPATH": root}
+    proc = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=120)
+    assert proc.returncode == 0, (proc.returncode, proc.stderr[-2000:])
+    assert "leaving" in proc.stdout and "pending ended with RuntimeError" in proc.stdout, proc.stdout
+    assert "terminate" not in proc.stderr
+
+
 def test_objects_with_tensors_inside(built):
     from tensorpipe_b200 import rpc
     a, b, listener, out_pipe, in_pipe = connected_pair(cuda=False)

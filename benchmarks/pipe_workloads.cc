@@ -15,6 +15,9 @@
 //   --workload cpu_stream  --transport uv|shm  [--bytes 64]  [--iters 100000]  [--depth 16]
 //       one way: the client keeps --depth payload-only messages in flight, the server reads them
 //       and answers once at the end; prints microseconds per message and messages per second.
+//   --workload pipe_setup  --transport uv|shm  --channel basic|cma|mpt  [--iters 200]
+//       the client opens --iters pipes one after the other; for each, the time from connect() to
+//       the answer to its first message (handshake, transport upgrade, channel connections).
 //   --workload transport_pingpong  --transport uv|shm  [--bytes 64]  [--iters 20000]
 //       raw transport connections (no pipe): one frame each way per round trip, two forked
 //       processes; prints p50 / p99 round-trip latency (the reference's benchmark_transport,
@@ -530,6 +533,95 @@ static int cpuStream(const Options& o, Shared* sh) {
             << ", \"us_per_message\": " << sh->seconds[0] / total * 1e6 << ", \"messages_per_second\": "
             << total / sh->seconds[0] << ", \"MBps\": " << static_cast<double>(total) * o.bytes / sh->seconds[0] / 1e6
             << ", \"verified\": \"checksum of the first byte of every message, kept by the server\"}" << std::endl;
+  return 0;
+}
+
+// ---- workload 1d: how long a new pipe takes from connect() to its first answered message -----------
+static int pipeSetup(const Options& o, Shared* sh) {
+  const int total = o.iters;
+  pid_t server = fork();
+  if (server == 0) {
+    auto ctx = makeCpuContext(o, "server");
+    std::vector<std::string> urls = {"uv://127.0.0.1"};
+    if (o.transport == "shm") urls.push_back("shm://");
+    auto listener = ctx->listen(urls);
+    std::strncpy(sh->url, listener->url("uv").c_str(), sizeof(sh->url) - 1);
+    sh->urlReady = 1;
+    // Every accepted pipe answers one message with one message; pipes are kept until the end.
+    std::mutex mu;
+    std::vector<std::shared_ptr<lib::Pipe>> pipes;
+    std::function<void()> arm = [&]() {
+      listener->accept([&](const lib::Error& e, std::shared_ptr<lib::Pipe> p) {
+        if (e) return;  // the listener is closing
+        {
+          std::lock_guard<std::mutex> lock(mu);
+          pipes.push_back(p);
+        }
+        lib::Pipe* raw = p.get();
+        raw->readDescriptor([raw](const lib::Error& e2, lib::Descriptor) {
+          if (e2) return;
+          raw->read(lib::Allocation(), [raw](const lib::Error& e3) {
+            if (e3) return;
+            lib::Message m;
+            m.metadata = "ok";
+            raw->write(std::move(m), [](const lib::Error&) {});
+          });
+        });
+        arm();
+      });
+    };
+    arm();
+    while (sh->clientsDone.load() == 0) std::this_thread::sleep_for(std::chrono::milliseconds(1));
+    listener.reset();
+    pipes.clear();
+    ctx->join();
+    _exit(0);
+  }
+  pid_t client = fork();
+  if (client == 0) {
+    while (sh->urlReady.load() == 0) std::this_thread::sleep_for(std::chrono::milliseconds(1));
+    auto ctx = makeCpuContext(o, "client");
+    std::vector<double> us;
+    std::vector<std::shared_ptr<lib::Pipe>> pipes;
+    for (int i = 0; i < total + 5; ++i) {
+      auto t0 = Clock::now();
+      auto pipe = ctx->connect(sh->url);
+      std::promise<void> answered;
+      pipe->readDescriptor([&](const lib::Error& e, lib::Descriptor d) {
+        if (e) die("readDescriptor: " + e.what());
+        if (d.metadata != "ok") die("unexpected answer");
+        pipe->read(lib::Allocation(), [&](const lib::Error& e2) {
+          if (e2) die("read: " + e2.what());
+          answered.set_value();
+        });
+      });
+      lib::Message m;
+      m.metadata = "hello";
+      pipe->write(std::move(m), [](const lib::Error& e) {
+        if (e) die("write: " + e.what());
+      });
+      answered.get_future().wait();
+      if (i >= 5) us.push_back(std::chrono::duration<double, std::micro>(Clock::now() - t0).count());
+      pipes.push_back(std::move(pipe));
+    }
+    sh->p50[0] = percentile(us, 0.5);
+    sh->p99[0] = percentile(us, 0.99);
+    pipes.clear();
+    sh->clientsDone = 1;
+    ctx->join();
+    _exit(0);
+  }
+  int s1 = 0, s2 = 0;
+  waitpid(client, &s2, 0);
+  sh->clientsDone = 1;
+  waitpid(server, &s1, 0);
+  if (!WIFEXITED(s1) || WEXITSTATUS(s1) || !WIFEXITED(s2) || WEXITSTATUS(s2) || sh->failed) {
+    std::cout << "{\"impl\": \"" << kImpl << "\", \"workload\": \"pipe_setup\", \"error\": \"a peer failed\"}" << std::endl;
+    return 1;
+  }
+  std::cout << "{\"impl\": \"" << kImpl << "\", \"workload\": \"pipe_setup\", \"transport\": \"" << o.transport
+            << "\", \"channel\": \"" << o.channel << "\", \"pipes\": " << total << ", \"connect_to_first_answer_p50_us\": "
+            << sh->p50[0] << ", \"p99_us\": " << sh->p99[0] << "}" << std::endl;
   return 0;
 }
 
@@ -1246,6 +1338,7 @@ int main(int argc, char** argv) {
   if (o.workload == "cpu_pingpong") return cpuPingPong(o, sh);
   if (o.workload == "cpu_small") return cpuSmallPingPong(o, sh);
   if (o.workload == "cpu_stream") return cpuStream(o, sh);
+  if (o.workload == "pipe_setup") return pipeSetup(o, sh);
   if (o.workload == "rpc_fanin") return rpcFanIn(o, sh);
   if (o.workload == "transport_pingpong") return transportPingPong(o, sh);
   if (o.workload == "all_pairs") return allPairs(o, sh);

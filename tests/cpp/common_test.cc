@@ -13,6 +13,7 @@
 #include "common/ringbuffer.h"
 #include "common/shm_segment.h"
 #include "common/system.h"
+#include <thread>
 #include "test_util.h"
 
 using namespace tpb;
@@ -189,6 +190,54 @@ TPB_TEST(Common, EpollLoopDefersAndDeliversFdEvents) {
   EXPECT_TRUE(ran);
   ::close(fds[0]);
   ::close(fds[1]);
+}
+
+// The loop is only poked through its eventfd while it is blocked: closures deferred from other
+// threads at every possible moment (while it runs, while it polls after activity, while it is
+// about to block, while it sleeps) must all run, promptly, and closures that defer closures too.
+TPB_TEST(Common, EpollLoopNeverLosesADeferredClosure) {
+  for (const char* spin : {"0", "50"}) {
+    ::setenv("TPB_EPOLL_SPIN_US", spin, 1);
+    EpollLoop loop("TP_test_loop");
+    ::unsetenv("TPB_EPOLL_SPIN_US");
+    constexpr int kThreads = 4, kPerThread = 3000;
+    std::atomic<int> ran{0};
+    std::atomic<long> worstUs{0};
+    std::vector<std::thread> threads;
+    for (int t = 0; t < kThreads; ++t)
+      threads.emplace_back([&, t] {
+        std::mt19937 rng(77 + t);
+        for (int i = 0; i < kPerThread; ++i) {
+          // Pauses from nothing to longer than the polling window, so that the loop is caught in
+          // every state.
+          const int pause = static_cast<int>(rng() % 4);
+          if (pause == 1) std::this_thread::yield();
+          if (pause == 2) std::this_thread::sleep_for(std::chrono::microseconds(rng() % 30));
+          if (pause == 3 && i % 16 == 0) std::this_thread::sleep_for(std::chrono::microseconds(100 + rng() % 200));
+          const auto t0 = std::chrono::steady_clock::now();
+          std::promise<void> done;
+          loop.deferToLoop([&] {
+            ++ran;
+            loop.deferToLoop([&] {  // from the loop thread itself: no poke, must still run
+              ++ran;
+              done.set_value();
+            });
+          });
+          auto f = done.get_future();
+          if (f.wait_for(std::chrono::seconds(10)) != std::future_status::ready)
+            throw TestFailure(std::string("a deferred closure never ran (spin window ") + spin + " us)");
+          const long us = std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0).count();
+          long prev = worstUs.load();
+          while (us > prev && !worstUs.compare_exchange_weak(prev, us)) {
+          }
+        }
+      });
+    for (auto& th : threads) th.join();
+    EXPECT_EQ(ran.load(), 2 * kThreads * kPerThread);
+    // Generous: a lost poke would only be rescued by the next unrelated event, i.e. never here.
+    EXPECT_TRUE(worstUs.load() < 2'000'000);
+    loop.join();
+  }
 }
 
 TPB_TEST(Common, PollerFiresOnceWhenTheConditionTurnsTrue) {

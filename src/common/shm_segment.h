@@ -4,6 +4,8 @@
 // tensorpipe/common/shm_segment.h:28-180.
 #pragma once
 
+#include <cstring>
+#include <algorithm>
 #include <fcntl.h>
 #include <sys/mman.h>
 #include <sys/syscall.h>
@@ -43,8 +45,15 @@ class ShmSegment {
       ::close(fd);
       return {TPB_CREATE_ERROR(SystemError, "ftruncate", e), std::move(s)};
     }
-    return mapFd(fd, bytes);
+    auto mapped = mapFd(fd, bytes);
+    // The pages are not all touched up front (a pipe over shm has four connections with a 2 MiB
+    // ring each, and zeroing 8 MiB made opening it take milliseconds): only the first ones,
+    // which the first few hundred control frames will use; the rest are faulted in as the ring's
+    // cursors reach them, once in the life of the segment.
+    if (!mapped.first) std::memset(mapped.second.ptr(), 0, std::min<size_t>(bytes, kTouchedAtCreation));
+    return mapped;
   }
+  static constexpr size_t kTouchedAtCreation = 64 * 1024;
   // Takes ownership of fd. The size is read from the fd.
   static std::pair<Error, ShmSegment> load(int fd) {
     off_t n = ::lseek(fd, 0, SEEK_END);
@@ -64,7 +73,7 @@ class ShmSegment {
  private:
   static std::pair<Error, ShmSegment> mapFd(int fd, size_t bytes) {
     ShmSegment s;
-    void* p = ::mmap(nullptr, bytes, PROT_READ | PROT_WRITE, MAP_SHARED | MAP_POPULATE, fd, 0);
+    void* p = ::mmap(nullptr, bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
     if (p == MAP_FAILED) {
       int e = errno;
       ::close(fd);

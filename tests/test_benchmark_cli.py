@@ -49,3 +49,26 @@ def test_bad_flags_are_refused(built):
     out = subprocess.run([BIN, "--mode", "sideways", "--address", "uv://127.0.0.1:1", "--num-round-trips", "1"],
                          stderr=subprocess.PIPE, text=True)
     assert out.returncode == 2 and "--mode must be listen or connect" in out.stderr
+
+
+WORKLOADS = os.path.join(ROOT, "build", "bin", "pipe_workloads")
+
+
+@pytest.mark.parametrize("args,key", [
+    (["--workload", "cpu_pingpong", "--transport", "shm", "--channel", "cma", "--iters", "120"], "rtt_p50_us"),
+    (["--workload", "cpu_pingpong", "--transport", "uv", "--channel", "mpt", "--iters", "60"], "rtt_p50_us"),
+    (["--workload", "cpu_small", "--transport", "shm", "--iters", "2000"], "rtt_p50_us"),
+    (["--workload", "cpu_stream", "--transport", "uv", "--bytes", "4096", "--iters", "5000"], "us_per_message"),
+    (["--workload", "pipe_setup", "--transport", "shm", "--channel", "basic", "--iters", "20"],
+     "connect_to_first_answer_p50_us"),
+    (["--workload", "transport_pingpong", "--transport", "shm", "--iters", "2000"], "rtt_p50_us"),
+])
+def test_cpu_workloads_run_and_verify_their_data(built, args, key):
+    """The CPU workloads that are compiled against both libraries: each forks its peers, checks
+    its own data (a mismatch or a callback out of order makes it exit non-zero) and prints one
+    JSON line."""
+    import json
+    out = subprocess.run([WORKLOADS] + args, capture_output=True, text=True, timeout=180)
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "native" and "error" not in line and line[key] > 0
